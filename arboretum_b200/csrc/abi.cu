@@ -1,0 +1,470 @@
+// extern "C" boundary of libarboretum.so: the reference's fourteen entry points
+// (python-wrapper/arboretum_wrapper.cu:16-205) plus the additive ones declared in
+// include/arboretum_b200.h.  Every exception becomes the returned message.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <climits>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/arboretum_b200.h"
+#include "garden.h"
+
+using namespace arb;
+
+namespace {
+
+thread_local std::string g_error;
+
+const char *fail(const std::exception &e) {
+  g_error = e.what();
+  return g_error.c_str();
+}
+const char *fail(const char *msg) {
+  g_error = msg;
+  return g_error.c_str();
+}
+
+#define ARB_TRY try {
+#define ARB_CATCH                                 \
+  return nullptr;                                 \
+  }                                               \
+  catch (const std::exception &e) { return fail(e); } \
+  catch (const char *e) { return fail(e); }       \
+  catch (...) { return fail("unknown error"); }
+
+// ---- NCCL through dlopen: the library has no link-time dependency on it -------
+struct NcclApi {
+  void *handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+  void load() {
+    if (handle) return;
+    // a copy that the process already loaded (torch ships one) is found first
+    handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!handle) handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!handle) throw std::runtime_error(std::string("cannot load libnccl.so.2: ") + dlerror());
+    GetUniqueId = reinterpret_cast<decltype(GetUniqueId)>(dlsym(handle, "ncclGetUniqueId"));
+    CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(handle, "ncclCommInitRank"));
+    AllReduce = reinterpret_cast<decltype(AllReduce)>(dlsym(handle, "ncclAllReduce"));
+    CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(handle, "ncclCommDestroy"));
+    GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(handle, "ncclGetErrorString"));
+    if (!GetUniqueId || !CommInitRank || !AllReduce || !CommDestroy || !GetErrorString)
+      throw std::runtime_error("libnccl.so.2 lacks a required symbol");
+  }
+};
+NcclApi g_nccl;
+
+struct NcclCtx {
+  ncclComm_t comm = nullptr;
+};
+
+int nccl_allreduce(void *ctx, long long *buf, size_t count, cudaStream_t s) {
+  NcclCtx *c = static_cast<NcclCtx *>(ctx);
+  const ncclResult_t r = g_nccl.AllReduce(buf, buf, count, ncclInt64, ncclSum, c->comm, s);
+  return r == ncclSuccess ? 0 : 1;
+}
+
+void host_scales(float max_g, float max_h, int qb, bool pair, QuantScale *q) {
+  int eg = 0, eh = 0;
+  if (max_g > 0.0f && std::isfinite(max_g)) std::frexp(max_g, &eg);
+  if (max_h > 0.0f && std::isfinite(max_h)) std::frexp(max_h, &eh);
+  q->sg = std::ldexp(1.0f, qb - eg);
+  q->inv_sg = std::ldexp(1.0, eg - qb);
+  q->sh = pair ? std::ldexp(1.0f, qb - eh) : 1.0f;
+  q->inv_sh = pair ? std::ldexp(1.0, eh - qb) : 1.0;
+  q->max_g_bits = q->max_h_bits = 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *ACreateFromDenseMatrix(const float *data, const unsigned int *categories, int nrow,
+                                   int ncol, int ccol, float missing, VoidPointer *out) {
+  ARB_TRY
+  (void)missing;     // never read by the reference either (arboretum_wrapper.cu:16-39)
+  (void)categories;  // categorical training is a stub in the reference (hist_tree_grower.h:55-63)
+  ARB_CHECK(out != nullptr, "out is NULL");
+  ARB_CHECK(nrow > 0 && ncol > 0 && ccol >= 0, "bad matrix shape");
+  ARB_CHECK(data != nullptr, "data is NULL");
+  ARB_CHECK(ccol == 0, "categorical columns are not supported by this build");
+  std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, ccol));
+  m->x.assign(data, data + size_t(nrow) * ncol);
+  *out = m.release();
+  ARB_CATCH
+}
+
+const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol, int hist_size,
+                                    VoidPointer *out) {
+  ARB_TRY
+  ARB_CHECK(out != nullptr && bins != nullptr, "NULL argument");
+  ARB_CHECK(nrow > 0 && ncol > 0, "bad matrix shape");
+  ARB_CHECK(hist_size > 0 && hist_size < 256, "pre-binned input needs 0 < hist_size < 256");
+  std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, 0));
+  m->prebinned = true;
+  m->hist_size = hist_size;
+  m->host_bins.assign(bins, bins + size_t(nrow) * ncol);
+  *out = m.release();
+  ARB_CATCH
+}
+
+const char *ASetY(VoidPointer data, const float *y) {
+  ARB_TRY
+  ARB_CHECK(data && y, "NULL argument");
+  DataMatrix *d = static_cast<DataMatrix *>(data);
+  d->y.assign(y, y + d->rows);
+  ARB_CATCH
+}
+
+const char *ASetLabel(VoidPointer data, const unsigned char *labels) {
+  ARB_TRY
+  ARB_CHECK(data && labels, "NULL argument");
+  DataMatrix *d = static_cast<DataMatrix *>(data);
+  d->labels.assign(labels, labels + d->rows);
+  ARB_CATCH
+}
+
+const char *ASetWeights(VoidPointer data, const float *weights) {
+  ARB_TRY
+  ARB_CHECK(data && weights, "NULL argument");
+  DataMatrix *d = static_cast<DataMatrix *>(data);
+  d->weights.assign(weights, weights + d->rows);  // stored, unused: as in the reference
+  ARB_CATCH
+}
+
+const char *ASetThresholds(VoidPointer data, const float *thr, const int *size, int hist_size) {
+  ARB_TRY
+  ARB_CHECK(data && thr && size, "NULL argument");
+  DataMatrix *d = static_cast<DataMatrix *>(data);
+  ARB_CHECK(!d->binned, "the matrix is already quantised");
+  d->thr.assign(thr, thr + size_t(d->cols_dense) * hist_size);
+  d->fsize.assign(size, size + d->cols_dense);
+  d->thresholds_given = true;
+  d->hist_size = hist_size;
+  ARB_CATCH
+}
+
+const char *AQuantize(VoidPointer data, int hist_size, int missing_bin, float *thr, int *size,
+                      uint16_t *bins) {
+  ARB_TRY
+  ARB_CHECK(data, "NULL argument");
+  DataMatrix *d = static_cast<DataMatrix *>(data);
+  ARB_CHECK(!d->thresholds_given || d->hist_size == hist_size, "hist_size differs from ASetThresholds");
+  d->InitHist(hist_size, missing_bin != 0, false, nullptr);
+  ARB_CHECK(d->hist_size == hist_size, "the matrix was quantised with another hist_size");
+  const int F = d->cols_dense;
+  if (thr) std::copy(d->thr.begin(), d->thr.end(), thr);
+  if (size) std::copy(d->fsize.begin(), d->fsize.end(), size);
+  if (bins) {
+    std::vector<unsigned char> raw(size_t(d->rows) * d->pitch);
+    ARB_CUDA(cudaMemcpy(raw.data(), d->d_bins.p, raw.size(), cudaMemcpyDeviceToHost));
+    for (int64_t r = 0; r < d->rows; ++r)
+      for (int f = 0; f < F; ++f)
+        bins[r * F + f] = d->bin_bytes == 1
+                            ? raw[r * d->pitch + f]
+                            : reinterpret_cast<const uint16_t *>(raw.data() + r * d->pitch)[f];
+  }
+  ARB_CATCH
+}
+
+const char *AInitGarden(const char *configuration, VoidPointer *out) {
+  ARB_TRY
+  ARB_CHECK(configuration && out, "NULL argument");
+  const Configuration cfg = Configuration::Parse(configuration);
+  *out = new Garden(cfg);
+  ARB_CATCH
+}
+
+const char *AGrowTree(VoidPointer garden, VoidPointer data, const float *grad) {
+  ARB_TRY
+  ARB_CHECK(garden && data, "NULL argument");
+  static_cast<Garden *>(garden)->GrowTree(static_cast<DataMatrix *>(data), grad);
+  ARB_CATCH
+}
+
+static const char *to_new_array(const std::vector<float> &v, const float **out) {
+  float *p = new (std::nothrow) float[v.size() ? v.size() : 1];
+  if (!p) return fail("unable to allocate the result array");
+  std::copy(v.begin(), v.end(), p);
+  *out = p;
+  return nullptr;
+}
+
+const char *APredict(VoidPointer garden, VoidPointer data, const float **out, const int n_rounds) {
+  ARB_TRY
+  ARB_CHECK(garden && data && out, "NULL argument");
+  std::vector<float> result;
+  static_cast<Garden *>(garden)->Predict(static_cast<DataMatrix *>(data), result,
+                                         n_rounds == -1 ? INT_MAX : n_rounds);
+  if (const char *e = to_new_array(result, out)) return e;
+  ARB_CATCH
+}
+
+const char *AGetY(VoidPointer garden, VoidPointer data, const float **out) {
+  ARB_TRY
+  ARB_CHECK(garden && data && out, "NULL argument");
+  std::vector<float> result;
+  static_cast<Garden *>(garden)->GetY(static_cast<DataMatrix *>(data), result);
+  if (const char *e = to_new_array(result, out)) return e;
+  ARB_CATCH
+}
+
+const char *AAppendLastTree(VoidPointer garden, VoidPointer data) {
+  ARB_TRY
+  ARB_CHECK(garden && data, "NULL argument");
+  static_cast<Garden *>(garden)->UpdateByLastTree(static_cast<DataMatrix *>(data));
+  ARB_CATCH
+}
+
+const char *ADumpModel(const char **model, VoidPointer garden) {
+  ARB_TRY
+  ARB_CHECK(garden && model, "NULL argument");
+  const std::string s = static_cast<Garden *>(garden)->GetModel();
+  char *c = new char[s.size() + 1];  // owned by the caller side, as in model_helper.cpp:19-22
+  std::memcpy(c, s.c_str(), s.size() + 1);
+  *model = c;
+  ARB_CATCH
+}
+
+const char *ALoadModel(const char *model, VoidPointer garden) {
+  ARB_TRY
+  ARB_CHECK(garden && model, "NULL argument");
+  static_cast<Garden *>(garden)->Restore(model);
+  ARB_CATCH
+}
+
+const char *AFreeDMatrix(VoidPointer ptr) {
+  ARB_TRY
+  delete static_cast<DataMatrix *>(ptr);
+  ARB_CATCH
+}
+
+const char *AFreeGarden(VoidPointer ptr) {
+  ARB_TRY
+  Garden *g = static_cast<Garden *>(ptr);
+  if (g && g->allreduce_ctx) {
+    NcclCtx *c = static_cast<NcclCtx *>(g->allreduce_ctx);
+    if (c->comm) g_nccl.CommDestroy(c->comm);
+    delete c;
+    g->allreduce_ctx = nullptr;
+  }
+  delete g;
+  ARB_CATCH
+}
+
+const char *ADeleteArray(float *in) {
+  delete[] in;
+  return nullptr;
+}
+
+const char *AGetTrainY(VoidPointer garden, float *out) {
+  ARB_TRY
+  ARB_CHECK(garden && out, "NULL argument");
+  BuilderView::train_yhat(static_cast<Garden *>(garden), out);
+  ARB_CATCH
+}
+
+const char *AGetLevelStats(VoidPointer garden, int level, unsigned *node_begin, float *gain, int *fid,
+                           int *bin, double *left_g, double *left_h, double *tot_g, double *tot_h,
+                           unsigned *left_count) {
+  ARB_TRY
+  ARB_CHECK(garden, "NULL argument");
+  Garden *g = static_cast<Garden *>(garden);
+  int max_nodes = 0, levels = 0, stride = 0;
+  const NodeRec *rec = BuilderView::host_rec(g, &max_nodes, &levels);
+  const unsigned *nb = BuilderView::host_node_begin(g, &stride);
+  ARB_CHECK(level >= 0 && level < levels, "level out of range");
+  QuantScale q;
+  BuilderView::scales(g, &q);
+  const int L = 1 << level;
+  for (int i = 0; i <= L && node_begin; ++i) node_begin[i] = nb[size_t(level) * stride + i];
+  for (int i = 0; i < L; ++i) {
+    const NodeRec &r = rec[size_t(level) * max_nodes + i];
+    if (gain) gain[i] = r.gain;
+    if (fid) fid[i] = r.fid;
+    if (bin) bin[i] = r.bin;
+    if (left_g) left_g[i] = double(r.lg) * q.inv_sg;
+    if (left_h) left_h[i] = double(r.lh) * q.inv_sh;
+    if (tot_g) tot_g[i] = double(r.tg) * q.inv_sg;
+    if (tot_h) tot_h[i] = double(r.th) * q.inv_sh;
+    if (left_count) left_count[i] = r.left_count;
+  }
+  ARB_CATCH
+}
+
+const char *ASetProfile(VoidPointer garden, int on) {
+  ARB_TRY
+  ARB_CHECK(garden, "NULL argument");
+  Garden *g = static_cast<Garden *>(garden);
+  g->profile = on != 0;
+  g->times = PhaseTimes();
+  ARB_CATCH
+}
+
+const char *AGetTimings(VoidPointer garden, const char **json) {
+  ARB_TRY
+  ARB_CHECK(garden && json, "NULL argument");
+  Garden *g = static_cast<Garden *>(garden);
+  const PhaseTimes &t = g->times;
+  Json j = Json::object();
+  j["trees"] = Json::integer(t.trees);
+  j["grad_ms"] = Json::number(t.grad);
+  j["hist_ms"] = Json::number(t.hist);
+  j["plan_ms"] = Json::number(t.plan);
+  j["subtract_ms"] = Json::number(t.subtract);
+  j["split_ms"] = Json::number(t.split);
+  j["partition_ms"] = Json::number(t.partition);
+  j["update_ms"] = Json::number(t.update);
+  j["allreduce_ms"] = Json::number(t.allreduce);
+  j["hist_launches"] = Json::integer(t.hist_launches);
+  j["hist_rows"] = Json::number(t.hist_rows);
+  j["hist_row_features"] = Json::number(t.hist_features);
+  j["hist_bytes"] = Json::number(t.hist_bytes);
+  j["kernel_launches"] = Json::integer(g_kernel_launches);
+  static thread_local std::string text;
+  text.clear();
+  json_write(j, text);
+  *json = text.c_str();
+  ARB_CATCH
+}
+
+const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                            const float *grad, int pair, const unsigned *rowid,
+                            const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
+                            double *out_h, int reps, float *ms) {
+  ARB_TRY
+  ARB_CHECK(bins && grad && node_begin && out_g && out_h, "NULL argument");
+  ARB_CHECK(bin_bytes == 1 || bin_bytes == 2, "bin_bytes must be 1 or 2");
+  ARB_CHECK(nrow > 0 && ncol > 0 && n_nodes > 0, "bad shape");
+  ARB_CHECK(hist_size > 0 && hist_size < 2048 && (bin_bytes == 2 || hist_size < 256), "bad hist_size");
+  ARB_CHECK(quant_bits >= 10 && quant_bits <= 21, "quant_bits must be in [10, 21]");
+  const size_t n = size_t(nrow);
+  Geometry geo;
+  geo.pitch = DataMatrix::PitchFor(ncol, bin_bytes);
+  geo.bin_bytes = bin_bytes;
+  geo.F = ncol;
+  geo.hist_size = hist_size;
+  int bins_pad = 256;
+  while (bins_pad < hist_size + 1) bins_pad <<= 1;
+  geo.BINS = bins_pad;
+  geo.TW = kHistWords / bins_pad;
+  geo.NT = (ncol + geo.TW - 1) / geo.TW;
+  cudaStream_t s;
+  ARB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  DevBuf d_bins, d_grad, d_rowid, d_items, d_nitems, d_hist, d_qs;
+  d_bins.alloc(n * geo.pitch);
+  ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, d_bins.bytes, s));
+  ARB_CUDA(cudaMemcpy2DAsync(d_bins.p, geo.pitch, bins, size_t(ncol) * bin_bytes,
+                             size_t(ncol) * bin_bytes, n, cudaMemcpyHostToDevice, s));
+  geo.bins = d_bins.as<unsigned char>();
+  const size_t gsz = pair ? 2 : 1;
+  d_grad.alloc(n * gsz * sizeof(float));
+  ARB_CUDA(cudaMemcpyAsync(d_grad.p, grad, d_grad.bytes, cudaMemcpyHostToDevice, s));
+  if (rowid) {
+    d_rowid.alloc(n * sizeof(unsigned));
+    ARB_CUDA(cudaMemcpyAsync(d_rowid.p, rowid, d_rowid.bytes, cudaMemcpyHostToDevice, s));
+  }
+  float max_g = 0.f, max_h = 0.f;
+  for (size_t i = 0; i < n; ++i) {
+    max_g = std::max(max_g, std::fabs(grad[i * gsz]));
+    if (pair) max_h = std::max(max_h, grad[i * gsz + 1]);
+  }
+  QuantScale q;
+  host_scales(max_g, max_h, quant_bits, pair != 0, &q);
+  d_qs.alloc(sizeof q);
+  ARB_CUDA(cudaMemcpyAsync(d_qs.p, &q, sizeof q, cudaMemcpyHostToDevice, s));
+  const unsigned cap = 1u << (31 - quant_bits);
+  std::vector<WorkItem> items;
+  for (int node = 0; node < n_nodes; ++node)
+    for (unsigned b = node_begin[node]; b < node_begin[node + 1]; b += cap)
+      items.push_back(WorkItem{b, std::min(cap, node_begin[node + 1] - b), node, 0});
+  ARB_CHECK(!items.empty(), "no rows");
+  const int n_items = int(items.size());
+  d_items.alloc(items.size() * sizeof(WorkItem));
+  d_nitems.alloc(sizeof(int));
+  ARB_CUDA(cudaMemcpyAsync(d_items.p, items.data(), d_items.bytes, cudaMemcpyHostToDevice, s));
+  ARB_CUDA(cudaMemcpyAsync(d_nitems.p, &n_items, sizeof(int), cudaMemcpyHostToDevice, s));
+  const size_t words = size_t(n_nodes) * geo.NT * kHistWords * 2;
+  d_hist.alloc(words * sizeof(long long));
+  HistLaunch h;
+  h.geo = geo;
+  h.rowid = rowid ? d_rowid.as<unsigned>() : nullptr;
+  h.grad = d_grad.p;
+  h.pair = pair != 0;
+  h.items = d_items.as<WorkItem>();
+  h.n_items = d_nitems.as<int>();
+  h.max_items = n_items;
+  h.hist = d_hist.as<long long>();
+  h.qs = d_qs.as<QuantScale>();
+  if (reps > 0) {
+    cudaEvent_t e0, e1;
+    ARB_CUDA(cudaEventCreate(&e0));
+    ARB_CUDA(cudaEventCreate(&e1));
+    ARB_CUDA(cudaMemsetAsync(d_hist.p, 0, d_hist.bytes, s));
+    for (int i = 0; i < 3; ++i) launch_hist(h, s);
+    ARB_CUDA(cudaEventRecord(e0, s));
+    for (int i = 0; i < reps; ++i) launch_hist(h, s);
+    ARB_CUDA(cudaEventRecord(e1, s));
+    ARB_CUDA(cudaEventSynchronize(e1));
+    float t = 0;
+    ARB_CUDA(cudaEventElapsedTime(&t, e0, e1));
+    if (ms) *ms = t / reps;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
+  ARB_CUDA(cudaMemsetAsync(d_hist.p, 0, d_hist.bytes, s));
+  launch_hist(h, s);
+  std::vector<long long> host(words);
+  ARB_CUDA(cudaMemcpyAsync(host.data(), d_hist.p, d_hist.bytes, cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaStreamSynchronize(s));
+  cudaStreamDestroy(s);
+  const int HW = hist_size + 1;
+  for (int node = 0; node < n_nodes; ++node)
+    for (int f = 0; f < ncol; ++f) {
+      const int tile = f / geo.TW, lane = f % geo.TW;
+      for (int b = 0; b < HW; ++b) {
+        const size_t src = (((size_t(node) * geo.NT + tile) * geo.BINS + b) * geo.TW + lane) * 2;
+        const size_t dst = (size_t(node) * ncol + f) * HW + b;
+        out_g[dst] = double(host[src]) * q.inv_sg;
+        out_h[dst] = double(host[src + 1]) * q.inv_sh;
+      }
+    }
+  ARB_CATCH
+}
+
+const char *ANcclUniqueId(char *id128) {
+  ARB_TRY
+  ARB_CHECK(id128, "NULL argument");
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  g_nccl.load();
+  ncclUniqueId id;
+  const ncclResult_t r = g_nccl.GetUniqueId(&id);
+  if (r != ncclSuccess) throw std::runtime_error(std::string("ncclGetUniqueId: ") + g_nccl.GetErrorString(r));
+  std::memcpy(id128, &id, 128);
+  ARB_CATCH
+}
+
+const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128) {
+  ARB_TRY
+  ARB_CHECK(garden && id128, "NULL argument");
+  ARB_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank / world size");
+  Garden *g = static_cast<Garden *>(garden);
+  ARB_CHECK(g->builder == nullptr, "AInitNccl must precede the first AGrowTree");
+  g_nccl.load();
+  ncclUniqueId id;
+  std::memcpy(&id, id128, 128);
+  std::unique_ptr<NcclCtx> c(new NcclCtx());
+  const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
+  if (r != ncclSuccess) throw std::runtime_error(std::string("ncclCommInitRank: ") + g_nccl.GetErrorString(r));
+  g->allreduce = nccl_allreduce;
+  g->allreduce_ctx = c.release();
+  ARB_CATCH
+}
+
+}  // extern "C"

@@ -1,0 +1,121 @@
+// Shared host/device utilities of the B200 training core.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace arb {
+
+// Every CUDA failure becomes a C++ exception; the C-ABI layer turns it into the
+// error string the caller receives.  (The reference prints and calls exit():
+// src/core/cuda_helpers.h:12-20.)
+#define ARB_CUDA(cmd)                                                          \
+  do {                                                                         \
+    cudaError_t e__ = (cmd);                                                   \
+    if (e__ != cudaSuccess) {                                                  \
+      throw std::runtime_error(std::string("CUDA error ") +                   \
+                               cudaGetErrorString(e__) + " at " + __FILE__ +   \
+                               ":" + std::to_string(__LINE__));                \
+    }                                                                          \
+  } while (0)
+
+#define ARB_CHECK(cond, msg)                                                   \
+  do {                                                                         \
+    if (!(cond)) throw std::runtime_error(std::string(msg));                   \
+  } while (0)
+
+// Owning device allocation.
+struct DevBuf {
+  void *p = nullptr;
+  size_t bytes = 0;
+  DevBuf() {}
+  DevBuf(const DevBuf &) = delete;
+  DevBuf &operator=(const DevBuf &) = delete;
+  ~DevBuf() { release(); }
+  void alloc(size_t n) {
+    release();
+    if (n == 0) return;
+    ARB_CUDA(cudaMalloc(&p, n));
+    bytes = n;
+  }
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    bytes = 0;
+  }
+  template <typename T>
+  T *as() const {
+    return static_cast<T *>(p);
+  }
+};
+
+// Owning pinned host allocation.
+struct PinnedBuf {
+  void *p = nullptr;
+  size_t bytes = 0;
+  PinnedBuf() {}
+  PinnedBuf(const PinnedBuf &) = delete;
+  PinnedBuf &operator=(const PinnedBuf &) = delete;
+  ~PinnedBuf() { release(); }
+  void alloc(size_t n) {
+    release();
+    if (n == 0) return;
+    ARB_CUDA(cudaMallocHost(&p, n));
+    bytes = n;
+  }
+  void release() {
+    if (p) cudaFreeHost(p);
+    p = nullptr;
+    bytes = 0;
+  }
+  template <typename T>
+  T *as() const {
+    return static_cast<T *>(p);
+  }
+};
+
+static inline int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
+
+// Kernels of this library launched so far in this process (reported by AGetTimings).
+extern long long g_kernel_launches;
+static inline void count_launch(int n = 1) { g_kernel_launches += n; }
+
+// ---------------------------------------------------------------------------
+// Device-side records of the level loop.
+// ---------------------------------------------------------------------------
+
+// Best split of one node at one level.  Sums are the fixed-point integers the
+// histograms are built from (see hist.cu); `fid < 0` means "no split: all rows
+// go left" (hist_tree_grower.cu:84-93 of the reference).
+struct NodeRec {
+  float gain;
+  int fid;
+  int bin;
+  unsigned left_count;  // rows that went left (filled by the partition pass)
+  long long lg, lh;     // left child sums
+  long long tg, th;     // node totals
+};
+
+// A contiguous piece of one node's row list, the unit of work of the histogram
+// and partition kernels.
+struct WorkItem {
+  unsigned begin;  // first position in the row-id list
+  unsigned len;
+  int node;        // node index inside its level
+  int pad;
+};
+
+// Scales of the per-round fixed-point gradient representation:
+// g_q = rint(g * sg), h_q = max(1, rint(h * sh)); sums convert back with
+// inv_sg / inv_sh (both scales are powers of two, so this is exact).
+struct QuantScale {
+  float sg, sh;
+  double inv_sg, inv_sh;
+  unsigned max_g_bits, max_h_bits;  // float bit patterns, written by atomicMax
+};
+
+}  // namespace arb

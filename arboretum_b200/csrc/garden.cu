@@ -1,0 +1,712 @@
+// Orchestration of one boosting round (rows F, N, T of the hot path; reference:
+// Garden::GrowTree src/core/garden.cu:585-625 and ContinuousGardenBuilder
+// :78-504).  A whole tree is enqueued on one stream without host
+// synchronisation: node sizes, work lists and split records stay in device
+// memory, and the host reads the finished tree back once per tree.
+#include "garden.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+namespace arb {
+
+long long g_kernel_launches = 0;
+
+// ---------------------------------------------------------------------------
+// DataMatrix
+// ---------------------------------------------------------------------------
+void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s) {
+  if (binned) return;
+  const int F = cols_dense;
+  ARB_CHECK(hs > 0 && hs < 2048, "hist_size must be in [1, 2047]");
+  ARB_CHECK(F > 0 && rows > 0, "empty data matrix");
+  hist_size = hs;
+  // io.cu:342-347: hist_size < 256 -> uint8 bins, else uint16
+  bin_bytes = hs < 256 ? 1 : 2;
+  pitch = PitchFor(F, bin_bytes);
+  const size_t n = size_t(rows);
+  if (!prebinned) {
+    DevBuf d_x, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
+    d_x.alloc(n * F * sizeof(float));
+    ARB_CUDA(cudaMemcpyAsync(d_x.p, x.data(), n * F * sizeof(float), cudaMemcpyHostToDevice, s));
+    if (!thresholds_given) {
+      d_col.alloc(n * sizeof(float));
+      d_sorted.alloc(n * sizeof(float));
+      d_scratch.alloc(thresholds_scratch_words(n) * sizeof(unsigned));
+      d_thr_f.alloc(size_t(F) * hs * sizeof(float));
+      for (int f = 0; f < F; ++f) {
+        launch_extract_column(d_x.as<float>(), n, F, f, d_col.as<float>(), s);
+        sort_floats(d_col.as<float>(), d_sorted.as<float>(), n, d_tmp, s);
+        launch_thresholds(d_sorted.as<float>(), n, hs, d_thr_f.as<float>() + size_t(f) * hs,
+                          d_scratch.as<unsigned>(), s);
+      }
+      thr.resize(size_t(F) * hs);
+      ARB_CUDA(cudaMemcpyAsync(thr.data(), d_thr_f.p, thr.size() * sizeof(float),
+                               cudaMemcpyDeviceToHost, s));
+      ARB_CUDA(cudaStreamSynchronize(s));
+      fsize.resize(F);
+      for (int f = 0; f < F; ++f) {  // io.cu:403-410
+        int unique = 0;
+        while (unique < hs && !std::isinf(thr[size_t(f) * hs + unique])) ++unique;
+        ++unique;
+        fsize[f] = std::min(unique, hs);
+      }
+    }
+    ARB_CHECK(int(thr.size()) == F * hs && int(fsize.size()) == F, "threshold table has the wrong shape");
+    DevBuf d_thr, d_fsize;
+    d_thr.alloc(thr.size() * sizeof(float));
+    d_fsize.alloc(F * sizeof(int));
+    ARB_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), thr.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+    ARB_CUDA(cudaMemcpyAsync(d_fsize.p, fsize.data(), F * sizeof(int), cudaMemcpyHostToDevice, s));
+    d_bins.alloc(n * pitch);
+    ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
+    launch_binning(d_x.as<float>(), n, F, d_thr.as<float>(), d_fsize.as<int>(), hs, missing_bin,
+                   d_bins.as<unsigned char>(), pitch, bin_bytes, s);
+    ARB_CUDA(cudaStreamSynchronize(s));
+  } else {
+    // rows arrive already binned: copy them into the padded row-major layout
+    ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
+    d_bins.alloc(n * pitch);
+    ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
+    ARB_CUDA(cudaMemcpy2DAsync(d_bins.p, pitch, host_bins.data(), size_t(F), size_t(F), n,
+                               cudaMemcpyHostToDevice, s));
+    if (thr.empty()) {  // threshold of bin q is q + 0.5: "bin <= q" <=> "value < q + 0.5"
+      thr.resize(size_t(F) * hs);
+      fsize.assign(F, hs);
+      for (int f = 0; f < F; ++f)
+        for (int q = 0; q < hs; ++q) thr[size_t(f) * hs + q] = q + 0.5f;
+    }
+    ARB_CUDA(cudaStreamSynchronize(s));
+  }
+  max_reduced_bits = 0;
+  for (int f = 0; f < F; ++f) {
+    int bits = 0;
+    for (int v = fsize[f]; v > 0; v >>= 1) ++bits;  // io.cu:411  32 - clz(size)
+    max_reduced_bits = std::max(max_reduced_bits, bits);
+    if (verbose) printf("feature %d has been reduced to %d bits \n", f, bits);
+  }
+  if (verbose) printf("max feature size %d \n", max_reduced_bits);
+  binned = true;
+}
+
+// ---------------------------------------------------------------------------
+// Builder: device state of one (Garden, DataMatrix) pair
+// ---------------------------------------------------------------------------
+class Builder {
+ public:
+  Builder(Garden *g, DataMatrix *d);
+  void UpdateGrad();
+  void GrowTree(int label, Tree *tree);
+  DataMatrix *data;
+
+ private:
+  Garden *g_;
+  size_t n_;
+  int F_, K_, levels_, max_nodes_, nb_stride_;
+  bool pair_;
+  Geometry geo_;
+  int item_cap_;       // rows an int32 sub-histogram may take (2^(31 - quant_bits))
+  int max_hist_items_, max_part_items_;
+  std::default_random_engine rnd_;  // garden.cu:87
+  std::vector<unsigned> active_fids_;
+  std::vector<unsigned char> active_host_;
+  GainParams gp_;
+
+  DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_flags_, d_node_begin_, d_rec_, d_hist_[2],
+    d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_item_left_;
+  DevBuf d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
+  PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
+  PlanBuffers pb_;
+  cudaEvent_t ev_[2 * 8 * kMaxLevels];
+  friend class Garden;
+  friend struct BuilderView;
+
+  unsigned *node_begin(int level) { return d_node_begin_.as<unsigned>() + size_t(level) * nb_stride_; }
+  NodeRec *rec(int level) { return d_rec_.as<NodeRec>() + size_t(level) * max_nodes_; }
+};
+
+Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.internal.seed) {
+  const Configuration &cfg = g->cfg;
+  const TreeParam &tp = cfg.tree;
+  cudaStream_t s = g->stream;
+  n_ = size_t(d->rows);
+  F_ = d->cols_dense;
+  K_ = int(tp.labels_count);
+  ARB_CHECK(tp.depth >= 2 && tp.depth <= kMaxLevels, "max_depth must be in [1, 15]");
+  ARB_CHECK(n_ < (size_t(1) << 31), "row count must be below 2^31");
+  levels_ = int(tp.depth) - 1;
+  max_nodes_ = 1 << (levels_ - 1);
+  nb_stride_ = 2 * max_nodes_ + 1;
+  pair_ = cfg.objective != kLinearRegression;
+  ARB_CHECK(!(pair_ && tp.min_leaf_size > 1),
+            "min_leaf_size > 1 with a (gradient, hessian) objective is not supported by this build");
+  if (cfg.objective == kSoftMaxOneVsAll)
+    ARB_CHECK(d->labels.size() == n_, "multi:softmax needs labels (ASetLabel)");
+  else
+    ARB_CHECK(d->y.size() == n_, "labels are not set (ASetY)");
+
+  geo_.bins = d->d_bins.as<unsigned char>();
+  geo_.pitch = d->pitch;
+  geo_.bin_bytes = d->bin_bytes;
+  geo_.F = F_;
+  geo_.hist_size = d->hist_size;
+  int bins_pad = 256;
+  while (bins_pad < d->hist_size + 1) bins_pad <<= 1;
+  geo_.BINS = bins_pad;
+  geo_.TW = kHistWords / bins_pad;
+  geo_.NT = (F_ + geo_.TW - 1) / geo_.TW;
+
+  const int qb = cfg.internal.quant_bits;
+  ARB_CHECK(qb >= 10 && qb <= 21, "internals.quant_bits must be in [10, 21]");
+  item_cap_ = 1 << (31 - qb);
+  max_hist_items_ = int(n_ / 1024) + max_nodes_ + 1;
+  max_part_items_ = int(n_ / kPartRows) + max_nodes_ + 1;
+
+  gp_ = GainParams{tp.min_leaf_size, tp.min_child_weight, tp.gamma_absolute, tp.gamma_relative,
+                   tp.lambda,        tp.alpha,            tp.max_leaf_weight};
+
+  // per-row state
+  if (cfg.objective == kSoftMaxOneVsAll) {
+    d_label_.alloc(n_);
+    ARB_CUDA(cudaMemcpyAsync(d_label_.p, d->labels.data(), n_, cudaMemcpyHostToDevice, s));
+  } else {
+    d_y_.alloc(n_ * sizeof(float));
+    ARB_CUDA(cudaMemcpyAsync(d_y_.p, d->y.data(), n_ * sizeof(float), cudaMemcpyHostToDevice, s));
+  }
+  d_yhat_.alloc(n_ * K_ * sizeof(float));
+  {  // garden.cu:105: y_hat starts at IntoInternal(initial_y)
+    std::vector<float> init(n_ * K_, g->InternalInitialY());
+    ARB_CUDA(cudaMemcpyAsync(d_yhat_.p, init.data(), init.size() * sizeof(float),
+                             cudaMemcpyHostToDevice, s));
+    ARB_CUDA(cudaStreamSynchronize(s));
+  }
+  d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
+  d_rowid_[0].alloc(n_ * sizeof(unsigned));
+  d_rowid_[1].alloc(n_ * sizeof(unsigned));
+  d_flags_.alloc(n_);
+  // level state
+  d_node_begin_.alloc(size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
+  ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
+  const unsigned root[2] = {0u, unsigned(n_)};
+  ARB_CUDA(cudaMemcpyAsync(d_node_begin_.p, root, sizeof root, cudaMemcpyHostToDevice, s));
+  d_rec_.alloc(size_t(levels_) * max_nodes_ * sizeof(NodeRec));
+  ARB_CUDA(cudaMemsetAsync(d_rec_.p, 0, d_rec_.bytes, s));
+  const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
+  d_hist_[0].alloc(level_hist_bytes);
+  d_hist_[1].alloc(level_hist_bytes);
+  d_keys_.alloc(max_nodes_ * sizeof(unsigned long long));
+  d_qs_.alloc(sizeof(QuantScale));
+  ARB_CUDA(cudaMemsetAsync(d_qs_.p, 0, sizeof(QuantScale), s));
+  d_leaf_w_.alloc(2 * max_nodes_ * sizeof(float));
+  d_active_.alloc(size_t(levels_) * F_);
+  d_fsize_.alloc(F_ * sizeof(int));
+  ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
+  d_item_left_.alloc(max_part_items_ * sizeof(unsigned));
+  d_part_items_.alloc(max_part_items_ * sizeof(WorkItem));
+  d_hist_items_.alloc(max_hist_items_ * sizeof(WorkItem));
+  d_counters_.alloc(2 * sizeof(int));
+  d_first_[0].alloc((max_nodes_ + 1) * sizeof(int));
+  d_first_[1].alloc((max_nodes_ + 1) * sizeof(int));
+  d_built_.alloc(max_nodes_ * sizeof(int));
+  d_scratch_.alloc(3 * size_t(max_nodes_) * sizeof(unsigned));
+  pb_.part_items = d_part_items_.as<WorkItem>();
+  pb_.n_part_items = d_counters_.as<int>();
+  pb_.part_item_first = d_first_[0].as<int>();
+  pb_.hist_items = d_hist_items_.as<WorkItem>();
+  pb_.n_hist_items = d_counters_.as<int>() + 1;
+  pb_.hist_item_first = d_first_[1].as<int>();
+  pb_.built_child = d_built_.as<int>();
+  pb_.scratch_begin = d_scratch_.as<unsigned>();
+  pb_.scratch_len = d_scratch_.as<unsigned>() + max_nodes_;
+  pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * max_nodes_);
+  h_rec_.alloc(d_rec_.bytes);
+  h_leaf_w_.alloc(d_leaf_w_.bytes);
+  h_node_begin_.alloc(d_node_begin_.bytes);
+  active_fids_.resize(F_);
+  active_host_.resize(size_t(levels_) * F_);
+  for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
+  ARB_CUDA(cudaStreamSynchronize(s));
+}
+
+void Builder::UpdateGrad() {  // objective.cu:28-56
+  cudaStream_t s = g_->stream;
+  if (g_->profile) ARB_CUDA(cudaEventRecord(ev_[0], s));
+  launch_gradients(g_->cfg.objective, K_, n_, d_y_.as<float>(), d_label_.as<unsigned char>(),
+                   d_yhat_.as<float>(), d_grad_.p, d_qs_.as<QuantScale>(), s);
+  launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
+  if (g_->profile) {
+    ARB_CUDA(cudaEventRecord(ev_[1], s));
+    ARB_CUDA(cudaEventSynchronize(ev_[1]));
+    float ms;
+    ARB_CUDA(cudaEventElapsedTime(&ms, ev_[0], ev_[1]));
+    g_->times.grad += ms;
+  }
+}
+
+void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
+  const Configuration &cfg = g_->cfg;
+  const TreeParam &tp = cfg.tree;
+  cudaStream_t s = g_->stream;
+  const bool prof = g_->profile;
+  QuantScale *qs = d_qs_.as<QuantScale>();
+  const void *grad = static_cast<const char *>(d_grad_.p) +
+                     size_t(label) * n_ * (pair_ ? sizeof(float2) : sizeof(float));
+
+  // ---- feature sampling: garden.cu:126-165,252-253 ---------------------------
+  int take = int(tp.colsample_bytree * F_);
+  if (take == 0) throw std::runtime_error("colsample_bytree is too small");
+  take = int(tp.colsample_bytree * tp.colsample_bylevel * F_);
+  if (take == 0) throw std::runtime_error("colsample_bytree and colsample_bylevel are too small");
+  for (int i = 0; i < F_; ++i) active_fids_[i] = i;
+  std::shuffle(active_fids_.begin(), active_fids_.end(), rnd_);
+  std::fill(active_host_.begin(), active_host_.end(), 0);
+  for (int l = 0; l < levels_; ++l) {
+    std::shuffle(active_fids_.begin(), active_fids_.begin() + int(tp.colsample_bytree * F_), rnd_);
+    const unsigned take_l = unsigned(tp.colsample_bylevel * tp.colsample_bytree * F_);
+    for (unsigned j = 0; j < take_l && j < unsigned(F_); ++j)
+      active_host_[size_t(l) * F_ + active_fids_[j]] = 1;
+  }
+  ARB_CUDA(cudaMemcpyAsync(d_active_.p, active_host_.data(), active_host_.size(),
+                           cudaMemcpyHostToDevice, s));
+
+  const bool use_trick = cfg.internal.use_hist_subtraction_trick;
+  const bool by_hessian = g_->allreduce != nullptr;
+  int ev = 0;
+  auto mark = [&]() {
+    if (prof) ARB_CUDA(cudaEventRecord(ev_[ev], s));
+    ++ev;
+  };
+  // events per level: 0 begin, 1 partition done, 2 plan + clear done, 3 histogram done,
+  // 4 allreduce done, 5 subtraction done, 6 split search done
+  for (int l = 0; l < levels_; ++l) {
+    const int L = 1 << l;
+    mark();
+    if (l > 0) {
+      PartitionLaunch p;
+      p.geo = geo_;
+      p.rowid_src = (l - 1 == 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>();
+      p.rowid_dst = d_rowid_[l & 1].as<unsigned>();
+      p.flags = d_flags_.as<unsigned char>();
+      p.item_left = d_item_left_.as<unsigned>();
+      p.node_begin = node_begin(l - 1);
+      p.node_begin_next = node_begin(l);
+      p.rec = rec(l - 1);
+      p.pb = pb_;
+      p.L = L / 2;
+      p.max_items = max_part_items_;
+      p.n_rows = unsigned(n_);
+      launch_partition(p, s);
+    }
+    mark();
+    // rows scanned this level: all at the root, at most half with the trick
+    // (the hessian rule of multi-GPU runs has no such bound)
+    const bool half = l > 0 && use_trick && !by_hessian;
+    const size_t level_rows = half ? n_ / 2 + 1 : n_;
+    int item_rows = 1024;
+    while (item_rows < item_cap_ && size_t(item_rows) * 888 < level_rows) item_rows <<= 1;
+    launch_plan_hist(node_begin(l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
+                     pb_, max_hist_items_, s);
+    long long *hist = d_hist_[l & 1].as<long long>();
+    ARB_CUDA(cudaMemsetAsync(hist, 0, size_t(L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+    mark();
+    HistLaunch h;
+    h.geo = geo_;
+    h.rowid = l == 0 ? nullptr : d_rowid_[l & 1].as<unsigned>();
+    h.grad = grad;
+    h.pair = pair_;
+    h.items = pb_.hist_items;
+    h.n_items = pb_.n_hist_items;
+    h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + L + 1));
+    h.hist = hist;
+    h.qs = qs;
+    launch_hist(h, s);
+    mark();
+    if (g_->allreduce) {
+      const size_t count = size_t(L) * geo_.NT * kHistWords * 2;
+      if (g_->allreduce(g_->allreduce_ctx, hist, count, s) != 0)
+        throw std::runtime_error("histogram allreduce failed");
+    }
+    mark();
+    if (use_trick && l > 0)
+      launch_subtract(hist, d_hist_[(l - 1) & 1].as<long long>(), pb_.built_child, L / 2, geo_.NT, s);
+    mark();
+    SplitLaunch sp;
+    sp.geo = geo_;
+    sp.hist = hist;
+    sp.node_begin = node_begin(l);
+    sp.feature_active = d_active_.as<unsigned char>() + size_t(l) * F_;
+    sp.feature_size = d_fsize_.as<int>();
+    sp.keys = d_keys_.as<unsigned long long>();
+    sp.rec = rec(l);
+    sp.parent_rec = l > 0 ? rec(l - 1) : nullptr;
+    sp.qs = qs;
+    sp.gp = gp_;
+    sp.pair = pair_;
+    sp.L = L;
+    launch_split(sp, s);
+    mark();
+  }
+  // ---- leaves and prediction update (garden.cu:487-503, :45-76) -----------------
+  LeafLaunch lf;
+  lf.last_rec = rec(levels_ - 1);
+  lf.L = max_nodes_;
+  lf.leaf_w = d_leaf_w_.as<float>();
+  lf.qs = qs;
+  lf.mcw = tp.min_child_weight;
+  lf.mls = tp.min_leaf_size;
+  lf.lambda = tp.lambda;
+  lf.alpha = tp.alpha;
+  lf.mlw = tp.max_leaf_weight;
+  lf.eta = tp.eta;
+  lf.pair = pair_;
+  launch_leaf_weights(lf, s);
+  launch_update_yhat(geo_, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(),
+                     d_yhat_.as<float>() + size_t(label) * n_, n_, s);
+  mark();
+  ARB_CUDA(cudaMemcpyAsync(h_rec_.p, d_rec_.p, d_rec_.bytes, cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaMemcpyAsync(h_leaf_w_.p, d_leaf_w_.p, d_leaf_w_.bytes, cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
+                           cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaStreamSynchronize(s));
+
+  // ---- UpdateTree garden.cu:447-485 -----------------------------------------------
+  const int depth = int(tp.depth);
+  tree->depth = depth;
+  tree->label = label;
+  tree->nodes.assign((size_t(1) << depth) - 1, TreeNode());
+  tree->weights.assign(size_t(1) << (depth - 1), 0.0f);
+  const NodeRec *hrec = h_rec_.as<NodeRec>();
+  const int H = data->hist_size;
+  for (int l = 0; l < levels_; ++l) {
+    const int L = 1 << l, offset = L - 1;
+    for (int i = 0; i < L; ++i) {
+      const NodeRec &r = hrec[size_t(l) * max_nodes_ + i];
+      TreeNode &nd = tree->nodes[i + offset];
+      if (r.fid >= 0) {
+        nd.fid = r.fid;
+        nd.quantized = unsigned(r.bin);
+        // a split on the last bin in use separates present from missing values
+        const bool last_real = r.bin >= data->fsize[r.fid] - 1;
+        nd.threshold = (r.bin >= H || last_real) ? std::numeric_limits<float>::infinity()
+                                                 : data->thr[size_t(r.fid) * H + r.bin];
+      } else {
+        nd.fid = 0;
+        nd.quantized = unsigned(-1);
+        nd.threshold = std::numeric_limits<float>::infinity();
+      }
+    }
+  }
+  const float *hw = h_leaf_w_.as<float>();
+  for (int i = 0; i < 2 * max_nodes_; ++i) tree->weights[i] = hw[i];
+
+  if (prof) {
+    PhaseTimes &t = g_->times;
+    const unsigned *hnb = h_node_begin_.as<unsigned>();
+    int e = 0;
+    auto span = [&](int a, int b) {
+      float ms;
+      ARB_CUDA(cudaEventElapsedTime(&ms, ev_[a], ev_[b]));
+      return double(ms);
+    };
+    for (int l = 0; l < levels_; ++l) {
+      t.partition += span(e, e + 1);
+      t.plan += span(e + 1, e + 2);
+      t.hist += span(e + 2, e + 3);
+      t.allreduce += span(e + 3, e + 4);
+      t.subtract += span(e + 4, e + 5);
+      t.split += span(e + 5, e + 6);
+      e += 7;
+      // rows scanned by this level's histogram launch
+      double rows = 0;
+      const int L = 1 << l;
+      const unsigned *nb = hnb + size_t(l) * nb_stride_;
+      if (l == 0 || !use_trick) {
+        rows = double(n_);
+      } else {
+        for (int p = 0; p < L / 2; ++p) {
+          const unsigned ls = nb[2 * p + 1] - nb[2 * p], rs = nb[2 * p + 2] - nb[2 * p + 1];
+          if (by_hessian) {
+            const NodeRec &pr = hrec[size_t(l - 1) * max_nodes_ + p];
+            rows += (pr.lh <= pr.th - pr.lh) ? ls : rs;
+          } else {
+            rows += std::min(ls, rs);
+          }
+        }
+      }
+      t.hist_rows += rows;
+      t.hist_features += double(F_);
+      t.hist_bytes += rows * (double(F_) * geo_.bin_bytes + (pair_ ? 8.0 : 4.0));
+      t.hist_launches += 1;
+    }
+    t.update += span(e - 1, e);
+    t.trees += 1;
+  }
+}
+
+const NodeRec *BuilderView::host_rec(const Garden *g, int *max_nodes, int *levels) {
+  ARB_CHECK(g->builder && !g->trees.empty(), "no tree has been grown yet");
+  *max_nodes = g->builder->max_nodes_;
+  *levels = g->builder->levels_;
+  return g->builder->h_rec_.as<NodeRec>();
+}
+const unsigned *BuilderView::host_node_begin(const Garden *g, int *stride) {
+  ARB_CHECK(g->builder && !g->trees.empty(), "no tree has been grown yet");
+  *stride = g->builder->nb_stride_;
+  return g->builder->h_node_begin_.as<unsigned>();
+}
+void BuilderView::scales(Garden *g, QuantScale *out) {
+  ARB_CHECK(g->builder, "no tree has been grown yet");
+  ARB_CUDA(cudaMemcpy(out, g->builder->d_qs_.p, sizeof(QuantScale), cudaMemcpyDeviceToHost));
+}
+void BuilderView::train_yhat(Garden *g, float *out) {
+  ARB_CHECK(g->builder, "no tree has been grown yet");
+  ARB_CUDA(cudaStreamSynchronize(g->stream));
+  ARB_CUDA(cudaMemcpy(out, g->builder->d_yhat_.p, g->builder->d_yhat_.bytes, cudaMemcpyDeviceToHost));
+}
+
+// ---------------------------------------------------------------------------
+// Garden
+// ---------------------------------------------------------------------------
+Garden::Garden(const Configuration &c) : cfg(c) {
+  // garden.cu:571-583: only these objectives exist (multi:softmax is this
+  // build's completion of the reference's stub)
+  if (cfg.objective != kLinearRegression && cfg.objective != kLogisticRegression &&
+      cfg.objective != kSoftMaxOneVsAll)
+    throw std::runtime_error("Unknown objective function " + std::to_string(cfg.objective));
+  if (cfg.method != kHist)
+    throw std::runtime_error("method 0 (exact) is not part of this build; use method 1 (hist)");
+  if (cfg.objective == kSoftMaxOneVsAll && cfg.tree.labels_count < 2)
+    throw std::runtime_error("multi:softmax needs tree.labels_count >= 2");
+  if (cfg.internal.device >= 0) ARB_CUDA(cudaSetDevice(cfg.internal.device));
+  ARB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+}
+
+Garden::~Garden() {
+  delete builder;
+  if (stream) cudaStreamDestroy(stream);
+}
+
+float Garden::InternalInitialY() const {  // objective.h:19,55-57
+  const float v = cfg.tree.initial_y;
+  if (cfg.objective == kLogisticRegression) return std::log(v / (1 - v));
+  return v;
+}
+
+void Garden::GrowTree(DataMatrix *data, const float *grad) {
+  (void)grad;  // custom gradients are ignored by the reference as well (garden.cu:609-614)
+  data->InitHist(cfg.internal.hist_size, cfg.internal.missing_bin, cfg.verbose.data, stream);
+  if (!builder) {
+    builder = new Builder(this, data);
+  } else if (builder->data != data) {
+    throw std::runtime_error("this Garden is already bound to another DMatrix");
+  }
+  builder->UpdateGrad();
+  for (unsigned k = 0; k < cfg.tree.labels_count; ++k) {
+    Tree t;
+    builder->GrowTree(int(k), &t);
+    trees.push_back(std::move(t));
+  }
+}
+
+void Garden::SyncForest() {
+  if (forest_trees_on_device == trees.size()) return;
+  const int depth = int(cfg.tree.depth);
+  const size_t nodes = (size_t(1) << depth) - 1, leaves = size_t(1) << (depth - 1);
+  std::vector<int> fid(trees.size() * nodes), label(trees.size());
+  std::vector<float> thr(trees.size() * nodes), w(trees.size() * leaves);
+  for (size_t t = 0; t < trees.size(); ++t) {
+    ARB_CHECK(trees[t].depth == depth, "tree depth differs from the configuration");
+    for (size_t i = 0; i < nodes; ++i) {
+      fid[t * nodes + i] = trees[t].nodes[i].fid;
+      thr[t * nodes + i] = trees[t].nodes[i].threshold;
+    }
+    std::copy(trees[t].weights.begin(), trees[t].weights.end(), w.begin() + t * leaves);
+    label[t] = trees[t].label;
+  }
+  d_fid.alloc(fid.size() * sizeof(int));
+  d_thr.alloc(thr.size() * sizeof(float));
+  d_w.alloc(w.size() * sizeof(float));
+  d_label.alloc(label.size() * sizeof(int));
+  ARB_CUDA(cudaMemcpyAsync(d_fid.p, fid.data(), d_fid.bytes, cudaMemcpyHostToDevice, stream));
+  ARB_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), d_thr.bytes, cudaMemcpyHostToDevice, stream));
+  ARB_CUDA(cudaMemcpyAsync(d_w.p, w.data(), d_w.bytes, cudaMemcpyHostToDevice, stream));
+  ARB_CUDA(cudaMemcpyAsync(d_label.p, label.data(), d_label.bytes, cudaMemcpyHostToDevice, stream));
+  ARB_CUDA(cudaStreamSynchronize(stream));
+  forest_trees_on_device = trees.size();
+}
+
+namespace {
+// rows of `data` as fp32 on the device, `chunk` rows at a time
+struct RowFeeder {
+  DataMatrix *d;
+  DevBuf buf;
+  std::vector<float> staged;
+  size_t chunk;
+  explicit RowFeeder(DataMatrix *dm) : d(dm) {
+    const size_t row_bytes = size_t(d->cols_dense) * sizeof(float);
+    chunk = std::max<size_t>(1, std::min<size_t>(size_t(d->rows), (size_t(1) << 30) / row_bytes));
+    buf.alloc(chunk * row_bytes);
+  }
+  const float *load(size_t first, size_t count, cudaStream_t s) {
+    const int F = d->cols_dense;
+    if (d->prebinned) {  // pre-binned rows predict on their bin ids as values
+      staged.resize(count * F);
+      for (size_t i = 0; i < count * F; ++i) staged[i] = float(d->host_bins[first * F + i]);
+      ARB_CUDA(cudaMemcpyAsync(buf.p, staged.data(), count * F * sizeof(float), cudaMemcpyHostToDevice, s));
+    } else {
+      ARB_CUDA(cudaMemcpyAsync(buf.p, d->x.data() + first * F, count * F * sizeof(float),
+                               cudaMemcpyHostToDevice, s));
+    }
+    return buf.as<float>();
+  }
+};
+}  // namespace
+
+// Garden::Predict garden.cu:643-657; n_rounds counts trees, like the reference
+void Garden::Predict(DataMatrix *data, std::vector<float> &out, int n_rounds) {
+  const int K = int(cfg.tree.labels_count);
+  const size_t n = size_t(data->rows);
+  out.resize(n * K);
+  SyncForest();
+  const int use = int(std::min<long long>(n_rounds, (long long)trees.size()));
+  RowFeeder feed(data);
+  DevBuf d_int, d_out;
+  d_int.alloc(feed.chunk * K * sizeof(float));
+  d_out.alloc(feed.chunk * K * sizeof(float));
+  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>()};
+  std::vector<float> init;
+  for (size_t first = 0; first < n; first += feed.chunk) {
+    const size_t count = std::min(feed.chunk, n - first);
+    const float *X = feed.load(first, count, stream);
+    init.assign(count * K, InternalInitialY());
+    ARB_CUDA(cudaMemcpyAsync(d_int.p, init.data(), count * K * sizeof(float), cudaMemcpyHostToDevice, stream));
+    launch_predict(X, count, data->cols_dense, pt, 0, use, int(cfg.tree.depth), d_int.as<float>(), stream);
+    launch_link(cfg.objective, K, count, d_int.as<float>(), d_out.as<float>(), stream);
+    ARB_CUDA(cudaMemcpyAsync(out.data() + first * K, d_out.p, count * K * sizeof(float),
+                             cudaMemcpyDeviceToHost, stream));
+    ARB_CUDA(cudaStreamSynchronize(stream));
+  }
+}
+
+// Garden::UpdateByLastTree garden.cu:627-635: add the last round's trees to the
+// matrix's accumulated prediction (kept on the device here)
+void Garden::UpdateByLastTree(DataMatrix *data) {
+  const int K = int(cfg.tree.labels_count);
+  const size_t n = size_t(data->rows);
+  ARB_CHECK(trees.size() >= size_t(K), "no tree has been grown yet");
+  if (!data->d_yhat.p || data->yhat_planes != K) {
+    data->d_yhat.alloc(n * K * sizeof(float));
+    data->yhat_planes = K;
+    std::vector<float> init(n * K, InternalInitialY());
+    ARB_CUDA(cudaMemcpyAsync(data->d_yhat.p, init.data(), init.size() * sizeof(float),
+                             cudaMemcpyHostToDevice, stream));
+    ARB_CUDA(cudaStreamSynchronize(stream));
+  }
+  SyncForest();
+  RowFeeder feed(data);
+  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>()};
+  DevBuf d_tmp;
+  d_tmp.alloc(feed.chunk * K * sizeof(float));
+  for (size_t first = 0; first < n; first += feed.chunk) {
+    const size_t count = std::min(feed.chunk, n - first);
+    const float *X = feed.load(first, count, stream);
+    // gather the chunk's planes, add the trees, scatter back
+    for (int k = 0; k < K; ++k)
+      ARB_CUDA(cudaMemcpyAsync(d_tmp.as<float>() + size_t(k) * count,
+                               data->d_yhat.as<float>() + size_t(k) * n + first, count * sizeof(float),
+                               cudaMemcpyDeviceToDevice, stream));
+    launch_predict(X, count, data->cols_dense, pt, int(trees.size()) - K, K, int(cfg.tree.depth),
+                   d_tmp.as<float>(), stream);
+    for (int k = 0; k < K; ++k)
+      ARB_CUDA(cudaMemcpyAsync(data->d_yhat.as<float>() + size_t(k) * n + first,
+                               d_tmp.as<float>() + size_t(k) * count, count * sizeof(float),
+                               cudaMemcpyDeviceToDevice, stream));
+    ARB_CUDA(cudaStreamSynchronize(stream));
+  }
+}
+
+// Garden::GetY garden.cu:637-641: link-transformed accumulated prediction
+void Garden::GetY(DataMatrix *data, std::vector<float> &out) {
+  const int K = int(cfg.tree.labels_count);
+  const size_t n = size_t(data->rows);
+  if (!data->d_yhat.p) {  // nothing appended yet: the reference returns an empty vector
+    out.clear();
+    return;
+  }
+  out.resize(n * K);
+  DevBuf d_out;
+  d_out.alloc(n * K * sizeof(float));
+  launch_link(cfg.objective, K, n, data->d_yhat.as<float>(), d_out.as<float>(), stream);
+  ARB_CUDA(cudaMemcpyAsync(out.data(), d_out.p, n * K * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  ARB_CUDA(cudaStreamSynchronize(stream));
+}
+
+// model_helper.cpp:16-23, json_conversion.h:13-49
+std::string Garden::GetModel() const {
+  Json root = Json::object();
+  root["configuration"] = cfg.ToJson();
+  Json model = Json::array();
+  for (const Tree &t : trees) {
+    Json jt = Json::object();
+    jt["depth"] = Json::integer(t.depth);
+    Json nodes = Json::array();
+    const unsigned first_leaf = (1u << (t.depth - 1)) - 1;
+    for (unsigned i = 0; i < t.nodes.size(); ++i) {
+      Json jn = Json::object();
+      jn["id"] = Json::integer(i);
+      const bool leaf = i >= first_leaf;
+      jn["leaf"] = Json::boolean(leaf);
+      if (!leaf) {
+        jn["left"] = Json::integer(2 * i + 1);
+        jn["right"] = Json::integer(2 * i + 2);
+        jn["threshold"] = Json::number(double(t.nodes[i].threshold));  // +inf -> null
+        jn["fid"] = Json::integer(t.nodes[i].fid);
+      } else {
+        jn["idx"] = Json::integer(i - first_leaf);
+      }
+      nodes.arr.push_back(jn);
+    }
+    jt["nodes"] = nodes;
+    Json w = Json::array();
+    for (float v : t.weights) w.arr.push_back(Json::number(double(v)));
+    jt["weights"] = w;
+    model.arr.push_back(jt);
+  }
+  root["model"] = model;
+  std::string out;
+  json_write(root, out);
+  return out;
+}
+
+// Garden::Restore garden.cu:659-677 (every restored tree gets label 0, as there)
+void Garden::Restore(const char *json_model) {
+  const Json j = JsonParser(json_model).parse();
+  const Json &model = j.at("model");
+  ARB_CHECK(model.type == Json::Arr, "model must be an array of trees");
+  for (const Json &jt : model.arr) {
+    Tree t;
+    t.depth = int(jt.at("depth").as_num());
+    t.label = 0;
+    const Json &nodes = jt.at("nodes");
+    t.nodes.assign(nodes.arr.size(), TreeNode());
+    for (const Json &jn : nodes.arr) {
+      const size_t id = size_t(jn.at("id").as_num());
+      ARB_CHECK(id < t.nodes.size(), "node id out of range");
+      if (jn.has("threshold")) {
+        const Json &th = jn.at("threshold");
+        t.nodes[id].threshold = th.type == Json::Null ? std::numeric_limits<float>::infinity()
+                                                      : float(th.as_num());
+      }
+      if (jn.has("fid")) t.nodes[id].fid = int(jn.at("fid").as_num());
+    }
+    for (const Json &w : jt.at("weights").arr) t.weights.push_back(float(w.as_num()));
+    ARB_CHECK(t.depth >= 1 && t.nodes.size() == (size_t(1) << t.depth) - 1 &&
+                t.weights.size() == (size_t(1) << (t.depth - 1)),
+              "tree shape does not match its depth");
+    trees.push_back(std::move(t));
+  }
+}
+
+}  // namespace arb

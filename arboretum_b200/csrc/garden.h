@@ -1,0 +1,117 @@
+// Host-side objects behind the C ABI: DataMatrix (src/io/io.h:15-83 of the
+// reference) and Garden (src/core/garden.h:141-160), rebuilt around a device
+// resident, row-major bin matrix and a level loop that never returns to the host
+// inside a tree.
+#pragma once
+#include <cstdint>
+#include <memory>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "config.h"
+#include "kernels.cuh"
+
+namespace arb {
+
+class DataMatrix {
+ public:
+  DataMatrix(int64_t rows, int cols_dense, int cols_cat)
+      : rows(rows), cols_dense(cols_dense), cols_cat(cols_cat) {}
+
+  int64_t rows;
+  int cols_dense;
+  int cols_cat;
+  std::vector<float> x;  // dense features, row-major copy of the caller's matrix
+  std::vector<float> y;
+  std::vector<unsigned char> labels;
+  std::vector<float> weights;
+
+  // quantised form (built by the first AGrowTree, like DataMatrix::InitHist)
+  bool binned = false;
+  bool prebinned = false;
+  bool thresholds_given = false;
+  int hist_size = 0;
+  int bin_bytes = 1;
+  size_t pitch = 0;
+  DevBuf d_bins;
+  std::vector<float> thr;  // [F][hist_size] data_reduced_mapping
+  std::vector<int> fsize;  // bins in use per feature
+  int max_reduced_bits = 0;
+  std::vector<unsigned char> host_bins;  // caller's pre-binned rows (row-major), if any
+
+  // predictions accumulated by AAppendLastTree, internal scale, [K][rows]
+  DevBuf d_yhat;
+  int yhat_planes = 0;
+
+  void InitHist(int hist_size, bool missing_bin, bool verbose, cudaStream_t s);
+  static size_t PitchFor(int F, int bin_bytes) {
+    return (size_t(F) * bin_bytes + 31) / 32 * 32;
+  }
+};
+
+struct TreeNode {  // reg_tree.h:16-38
+  int fid = 0;
+  float threshold = 0.0f;
+  unsigned quantized = 0;
+};
+struct Tree {  // reg_tree.h:40-45 + RegTree::label
+  int depth = 0;
+  int label = 0;
+  std::vector<TreeNode> nodes;  // heap order, (1 << depth) - 1
+  std::vector<float> weights;   // 1 << (depth - 1), already multiplied by eta
+};
+
+// Optional exchange step of multi-GPU training: sums `count` int64 values in
+// place across all ranks, ordered on `stream`.  Returns 0 on success.
+typedef int (*AllreduceFn)(void *ctx, long long *device_buf, size_t count, cudaStream_t stream);
+
+struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
+  double grad = 0, hist = 0, subtract = 0, split = 0, partition = 0, plan = 0, update = 0, allreduce = 0;
+  long long hist_launches = 0;
+  double hist_rows = 0;      // rows scanned by histogram launches
+  double hist_features = 0;  // features per scanned row (summed per launch)
+  double hist_bytes = 0;     // algorithmic bytes of those launches
+  long long trees = 0;
+};
+
+class Builder;
+class Garden;
+
+// Read-only window on the builder's state of the last grown tree, for the
+// read-back entry points of the C ABI.
+struct BuilderView {
+  static const NodeRec *host_rec(const Garden *g, int *max_nodes, int *levels);
+  static const unsigned *host_node_begin(const Garden *g, int *stride);
+  static void scales(Garden *g, QuantScale *out);
+  static void train_yhat(Garden *g, float *out);
+};
+
+class Garden {
+ public:
+  explicit Garden(const Configuration &cfg);
+  ~Garden();
+  Configuration cfg;
+  void GrowTree(DataMatrix *data, const float *grad);
+  void Predict(DataMatrix *data, std::vector<float> &out, int n_rounds);
+  void UpdateByLastTree(DataMatrix *data);
+  void GetY(DataMatrix *data, std::vector<float> &out);
+  std::string GetModel() const;
+  void Restore(const char *json_model);
+  float InternalInitialY() const;
+
+  std::vector<Tree> trees;
+  AllreduceFn allreduce = nullptr;
+  void *allreduce_ctx = nullptr;
+  bool profile = false;
+  PhaseTimes times;
+  // device copies of the forest for inference
+  void SyncForest();
+  DevBuf d_fid, d_thr, d_w, d_label;
+  size_t forest_trees_on_device = 0;
+  cudaStream_t stream = nullptr;
+  Builder *builder = nullptr;
+};
+
+}  // namespace arb

@@ -1,0 +1,149 @@
+// Launchers of the level-loop kernels.  All of them enqueue on the given stream
+// and never synchronise; sizes that depend on the data (node sizes, work-item
+// counts) live in device memory and are read by the kernels themselves.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "gain.cuh"
+
+namespace arb {
+
+constexpr int kHistWords = 8192;      // words of one shared-memory histogram plane
+constexpr int kHistThreads = 256;     // threads of a histogram CTA
+constexpr int kPartRows = 2048;       // rows of one partition work item
+constexpr int kPartThreads = 256;
+constexpr int kMaxLevels = 16;
+
+// Geometry of the binned matrix and of the histograms built from it.
+//   bins : row-major, `pitch` bytes per row, feature f of row r at
+//          bins[r * pitch + f * bin_bytes]; pitch is a multiple of 32.
+//   tiles: TW consecutive features; TW * BINS == kHistWords, so one tile of one
+//          node is kHistWords (g, h) pairs: hist[((node * NT + tile) * BINS + bin) * TW + lane]
+struct Geometry {
+  const unsigned char *bins;
+  size_t pitch;
+  int bin_bytes;
+  int F;
+  int TW, NT, BINS;
+  int hist_size;  // bins a split may use (config value); id hist_size = missing
+};
+
+struct HistLaunch {
+  Geometry geo;
+  const unsigned *rowid;  // nullptr: positions are row ids (root level)
+  const void *grad;       // float2[N] (pair) or float[N]
+  bool pair;
+  const WorkItem *items;
+  const int *n_items;
+  int max_items;
+  long long *hist;  // level buffer
+  const QuantScale *qs;
+};
+void launch_hist(const HistLaunch &a, cudaStream_t s);
+
+// sibling = parent - built child, for every parent of the level above
+void launch_subtract(long long *level_hist, const long long *parent_hist, const int *built_child,
+                     int n_parents, int NT, cudaStream_t s);
+
+struct SplitLaunch {
+  Geometry geo;
+  const long long *hist;       // level buffer
+  const unsigned *node_begin;  // L+1 prefix counts of this level
+  const unsigned char *feature_active;  // F flags: evaluated at this level
+  const int *feature_size;     // bins in use per feature
+  unsigned long long *keys;    // L packed (gain, feature, bin) maxima, zeroed here
+  NodeRec *rec;                // L records out
+  const NodeRec *parent_rec;   // level above (nullptr at the root)
+  const QuantScale *qs;
+  GainParams gp;
+  bool pair;
+  int L;
+};
+void launch_split(const SplitLaunch &a, cudaStream_t s);
+
+// --- row partition ----------------------------------------------------------
+struct PlanBuffers {
+  WorkItem *part_items;
+  int *n_part_items;
+  int *part_item_first;  // per node of the level: first item, L+1 entries
+  WorkItem *hist_items;
+  int *n_hist_items;
+  int *hist_item_first;  // scratch, max_nodes + 1
+  int *built_child;  // per parent: 0 = left child built, 1 = right child
+  unsigned *scratch_begin, *scratch_len;  // scratch, max_nodes each
+  int *scratch_node;
+};
+// items of the partition pass over the nodes of `level`
+void launch_plan_partition(const unsigned *node_begin, int L, PlanBuffers pb, int max_items,
+                           cudaStream_t s);
+// choose which child of every parent to build and cut those children into items
+void launch_plan_hist(const unsigned *node_begin, const NodeRec *parent_rec, int L, int item_rows,
+                      bool use_trick, bool by_hessian, PlanBuffers pb, int max_items,
+                      cudaStream_t s);
+
+struct PartitionLaunch {
+  Geometry geo;
+  const unsigned *rowid_src;  // nullptr: identity (root)
+  unsigned *rowid_dst;
+  unsigned char *flags;       // N scratch bytes
+  unsigned *item_left;        // per item: lefts, then exclusive prefix inside node
+  const unsigned *node_begin; // level L prefix counts
+  unsigned *node_begin_next;  // 2L+1 prefix counts out
+  NodeRec *rec;               // split records of the level (left_count filled)
+  PlanBuffers pb;
+  int L;
+  int max_items;
+  unsigned n_rows;
+};
+void launch_partition(const PartitionLaunch &a, cudaStream_t s);
+
+// --- objective, leaves, prediction ----------------------------------------------
+// grad from (y, yhat); also tracks max|g|, max h in qs
+void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
+                      const float *yhat, void *grad, QuantScale *qs, cudaStream_t s);
+void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s);
+
+struct LeafLaunch {
+  const NodeRec *last_rec;
+  int L;  // nodes of the last level
+  float *leaf_w;  // 2L
+  const QuantScale *qs;
+  float mcw;
+  unsigned mls;
+  float lambda, alpha, mlw, eta;
+  bool pair;
+};
+void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s);
+
+// yhat[row] += leaf weight of the tree just grown, walking the tree over bins
+void launch_update_yhat(const Geometry &geo, const NodeRec *rec /*[levels][max_nodes]*/,
+                        int levels, int max_nodes, const float *leaf_w, float *yhat, size_t n,
+                        cudaStream_t s);
+
+// inference over raw fp32 rows (RegTree::Predict of the reference, on the device)
+struct PackedTree {  // device arrays of one forest
+  const int *fid;        // [trees][nodes]
+  const float *thr;      // [trees][nodes]
+  const float *weights;  // [trees][leaves]
+  const int *label;      // [trees]
+};
+void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tree, int n_trees,
+                    int depth, float *out /*[K][n]*/, cudaStream_t s);
+void launch_link(int objective, int K, size_t n, const float *internal /*[K][n]*/,
+                 float *out /*[n][K]*/, cudaStream_t s);
+
+// --- quantizer ---------------------------------------------------------------------
+// thresholds of one sorted column (device) -> thr[hist_size]
+void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
+                       cudaStream_t s);
+size_t thresholds_scratch_words(size_t n);
+// bin every (row, feature) of a row-major fp32 matrix
+void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist_size]*/,
+                    const int *fsize, int hist_size, bool missing_bin, unsigned char *bins,
+                    size_t pitch, int bin_bytes, cudaStream_t s);
+void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s);
+// sorts n fp32 keys (radix order); tmp sizes itself on first use
+void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s);
+
+}  // namespace arb

@@ -1,0 +1,243 @@
+// Objective gradients, leaf weights, prediction update and inference (rows G, W, U
+// and Pred of the hot path; reference: src/core/objective.cu:15-56,
+// src/core/objective.h:19-113, src/core/garden.cu:45-76,487-503,
+// src/core/garden.h:70-90).
+#include <cfloat>
+
+#include "kernels.cuh"
+
+namespace arb {
+
+namespace {
+
+// objective.h:66-68: the exponential is evaluated in float, the rest in double.
+__device__ __forceinline__ float sigmoid(float x) { return float(1.0 / (1.0 + expf(-x))); }
+
+__device__ __forceinline__ void block_max_to(unsigned *dst, float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0 && v > 0.0f) atomicMax(dst, __float_as_uint(v));
+}
+
+// Sign convention of the reference: grad = negative gradient (objective.cu:31,45).
+__global__ void grad_linear_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
+                                   float *__restrict__ grad, QuantScale *qs, size_t n) {
+  float m = 0.0f;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const float g = y[i] - yhat[i];
+    grad[i] = g;
+    m = fmaxf(m, fabsf(g));
+  }
+  block_max_to(&qs->max_g_bits, m);
+}
+
+__global__ void grad_logistic_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
+                                     float2 *__restrict__ grad, QuantScale *qs, size_t n) {
+  float mg = 0.0f, mh = 0.0f;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const float s = sigmoid(yhat[i]);
+    const float2 g = make_float2(y[i] - s, s * (1.0f - s));
+    grad[i] = g;
+    mg = fmaxf(mg, fabsf(g.x));
+    mh = fmaxf(mh, g.y);
+  }
+  block_max_to(&qs->max_g_bits, mg);
+  block_max_to(&qs->max_h_bits, mh);
+}
+
+// multi:softmax as the reference intends it (objective.cu:60-89, objective.h:100-112):
+// probabilities in double, g_k = 1[k == label] - p_k, h_k = 2 p_k (1 - p_k).
+__global__ void grad_softmax_kernel(const unsigned char *__restrict__ label,
+                                    const float *__restrict__ yhat, float2 *__restrict__ grad,
+                                    QuantScale *qs, size_t n, int K) {
+  float mg = 0.0f, mh = 0.0f;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    double sum = 0.0;
+    for (int k = 0; k < K; ++k) sum += exp(double(yhat[size_t(k) * n + i]));
+    const int lab = label[i];
+    for (int k = 0; k < K; ++k) {
+      const double p = exp(double(yhat[size_t(k) * n + i])) / sum;
+      const float2 g = make_float2(float((k == lab ? 1.0 : 0.0) - p), float(2.0 * p * (1.0 - p)));
+      grad[size_t(k) * n + i] = g;
+      mg = fmaxf(mg, fabsf(g.x));
+      mh = fmaxf(mh, g.y);
+    }
+  }
+  block_max_to(&qs->max_g_bits, mg);
+  block_max_to(&qs->max_h_bits, mh);
+}
+
+__global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) {
+  // largest |g| < 2^e  =>  |g * 2^(quant_bits - e)| < 2^quant_bits
+  int eg = 0, eh = 0;
+  const float mg = __uint_as_float(qs->max_g_bits), mh = __uint_as_float(qs->max_h_bits);
+  if (mg > 0.0f && mg <= FLT_MAX) frexpf(mg, &eg);
+  if (mh > 0.0f && mh <= FLT_MAX) frexpf(mh, &eh);
+  qs->sg = ldexpf(1.0f, quant_bits - eg);
+  qs->inv_sg = ldexp(1.0, eg - quant_bits);
+  if (pair) {
+    qs->sh = ldexpf(1.0f, quant_bits - eh);
+    qs->inv_sh = ldexp(1.0, eh - quant_bits);
+  } else {
+    qs->sh = 1.0f;
+    qs->inv_sh = 1.0;
+  }
+}
+
+template <bool PAIR>
+__global__ void leaf_weights_kernel(LeafLaunch a) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= a.L) return;
+  const NodeRec r = a.last_rec[n];
+  const double isg = a.qs->inv_sg, ish = a.qs->inv_sh;
+  const long long rg = r.tg - r.lg, rh = r.th - r.lh;
+  // counts only gate `c >= min_leaf_size`; see split.cu for the PAIR stand-in
+  const unsigned lc = PAIR ? unsigned(r.lh > 0) : unsigned(r.lh);
+  const unsigned rc = PAIR ? unsigned(rh > 0) : unsigned(rh);
+  // garden.cu:487-503, split.cu:25-35: eta is applied to the float weight
+  a.leaf_w[2 * n] = leaf_weight<PAIR>(double(r.lg) * isg, double(r.lh) * ish, lc, a.mcw, a.mls,
+                                      a.lambda, a.alpha, a.mlw) * a.eta;
+  a.leaf_w[2 * n + 1] = leaf_weight<PAIR>(double(rg) * isg, double(rh) * ish, rc, a.mcw, a.mls,
+                                          a.lambda, a.alpha, a.mlw) * a.eta;
+}
+
+// garden.cu:45-76 restated over the immutable bin matrix: every row walks the
+// tree that was just grown (left <=> bin <= split bin, builder.h:113-120).
+template <typename BIN_T>
+__global__ void update_yhat_kernel(const unsigned char *__restrict__ bins, size_t pitch,
+                                   const NodeRec *__restrict__ rec, int levels, int max_nodes,
+                                   const float *__restrict__ leaf_w, float *__restrict__ yhat,
+                                   size_t n) {
+  extern __shared__ int2 snode[];  // (fid, bin) per (level, node) when it fits
+  const int total = levels * max_nodes;
+  const bool cached = total * sizeof(int2) <= 40 * 1024;
+  if (cached) {
+    for (int i = threadIdx.x; i < total; i += blockDim.x)
+      snode[i] = make_int2(rec[i].fid, rec[i].bin);
+    __syncthreads();
+  }
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const BIN_T *row = reinterpret_cast<const BIN_T *>(bins + i * pitch);
+    int node = 0;
+    for (int l = 0; l < levels; ++l) {
+      const int2 fb = cached ? snode[l * max_nodes + node]
+                             : make_int2(rec[l * max_nodes + node].fid, rec[l * max_nodes + node].bin);
+      const int right = fb.x >= 0 && int(row[fb.x]) > fb.y;
+      node = 2 * node + right;
+    }
+    yhat[i] += leaf_w[node];
+  }
+}
+
+// RegTree::Predict garden.h:70-90 (dense features): x < threshold goes left, so
+// NaN goes right; trees are added in order, in float, like the reference's loop
+// in Garden::Predict garden.cu:643-657.
+__global__ void predict_kernel(const float *__restrict__ X, size_t n, int F, PackedTree t,
+                               int first_tree, int n_trees, int depth, float *__restrict__ out) {
+  const int nodes = (1 << depth) - 1;
+  const int leaves = 1 << (depth - 1);
+  const int offset = leaves - 1;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const float *row = X + i * F;
+    for (int k = first_tree; k < first_tree + n_trees; ++k) {
+      const int *fid = t.fid + size_t(k) * nodes;
+      const float *thr = t.thr + size_t(k) * nodes;
+      int node = 0;
+      for (int j = 1; j < depth; ++j) node = row[fid[node]] < thr[node] ? 2 * node + 1 : 2 * node + 2;
+      out[size_t(t.label[k]) * n + i] += t.weights[size_t(k) * leaves + node - offset];
+    }
+  }
+}
+
+__global__ void link_kernel(int objective, int K, size_t n, const float *__restrict__ in,
+                            float *__restrict__ out) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    if (objective == 1) {  // objective.h:58-64
+      out[i] = sigmoid(in[i]);
+    } else if (objective == 3) {  // objective.h:80-113
+      double sum = 0.0;
+      for (int k = 0; k < K; ++k) sum += exp(double(in[size_t(k) * n + i]));
+      for (int k = 0; k < K; ++k) out[i * K + k] = float(exp(double(in[size_t(k) * n + i])) / sum);
+    } else {
+      out[i] = in[i];
+    }
+  }
+}
+
+inline int grid_for(size_t n, int threads) {
+  return int(std::min<size_t>((n + threads - 1) / threads, size_t(148) * 16));
+}
+
+}  // namespace
+
+void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
+                      const float *yhat, void *grad, QuantScale *qs, cudaStream_t s) {
+  ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
+  const int threads = 256;
+  const int grid = grid_for(n, threads);
+  if (objective == 0)
+    grad_linear_kernel<<<grid, threads, 0, s>>>(y, yhat, static_cast<float *>(grad), qs, n);
+  else if (objective == 1)
+    grad_logistic_kernel<<<grid, threads, 0, s>>>(y, yhat, static_cast<float2 *>(grad), qs, n);
+  else
+    grad_softmax_kernel<<<grid, threads, 0, s>>>(label, yhat, static_cast<float2 *>(grad), qs, n, K);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s) {
+  (void)K;
+  finish_scales_kernel<<<1, 1, 0, s>>>(qs, quant_bits, pair);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s) {
+  const int threads = 128;
+  if (a.pair)
+    leaf_weights_kernel<true><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
+  else
+    leaf_weights_kernel<false><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_update_yhat(const Geometry &geo, const NodeRec *rec, int levels, int max_nodes,
+                        const float *leaf_w, float *yhat, size_t n, cudaStream_t s) {
+  const int threads = 256;
+  const int grid = grid_for(n, threads);
+  size_t smem = size_t(levels) * max_nodes * sizeof(int2);
+  if (smem > 40 * 1024) smem = 0;
+  if (geo.bin_bytes == 1)
+    update_yhat_kernel<unsigned char><<<grid, threads, smem, s>>>(geo.bins, geo.pitch, rec, levels,
+                                                                  max_nodes, leaf_w, yhat, n);
+  else
+    update_yhat_kernel<unsigned short><<<grid, threads, smem, s>>>(geo.bins, geo.pitch, rec, levels,
+                                                                   max_nodes, leaf_w, yhat, n);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tree, int n_trees,
+                    int depth, float *out, cudaStream_t s) {
+  if (n_trees <= 0 || n == 0) return;
+  const int threads = 256;
+  predict_kernel<<<grid_for(n, threads), threads, 0, s>>>(X, n, F, t, first_tree, n_trees, depth, out);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_link(int objective, int K, size_t n, const float *internal, float *out, cudaStream_t s) {
+  if (n == 0) return;
+  const int threads = 256;
+  link_kernel<<<grid_for(n, threads), threads, 0, s>>>(objective, K, n, internal, out);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+}  // namespace arb

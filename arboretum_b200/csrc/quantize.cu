@@ -1,0 +1,211 @@
+// Feature quantizer (row Q of the hot path; reference: DataMatrix::InitHistInternal,
+// src/io/io.cu:349-435, with ValueSegmentIterator :27-142, SegmentLength :144-153,
+// ThresholdOutputIterator :255-271 and build_histogram :293-312).
+//
+// Thresholds must be bit-identical to the reference's, so the column is sorted in
+// fp32 radix order (the toolkit's cub::DeviceRadixSort, the same primitive the
+// reference calls) and the border scan is restated as three small kernels:
+//   count borders per block -> scan the block counts -> for every border i with
+//   inclusive border count c, slot k = min(c + 1, i / seg + 1) - 2 receives
+//   min(thr[k], float((s[i] + s[i-1]) * 0.5)).
+// Binning then maps all features of all rows in one pass over the row-major fp32
+// matrix and writes the row-major bin matrix the histogram kernels read.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "kernels.cuh"
+
+namespace arb {
+
+namespace {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+__device__ __forceinline__ bool is_border(const float *s, size_t i) { return i > 0 && s[i] != s[i - 1]; }
+
+__global__ void border_count_kernel(const float *__restrict__ s, size_t n, unsigned *block_count) {
+  __shared__ unsigned warp_sums[kScanThreads / 32];
+  const size_t base = size_t(blockIdx.x) * kScanTile + size_t(threadIdx.x) * kScanItems;
+  unsigned c = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k)
+    if (base + k < n) c += is_border(s, base + k);
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned t = 0;
+    for (int w = 0; w < kScanThreads / 32; ++w) t += warp_sums[w];
+    block_count[blockIdx.x] = t;
+  }
+}
+
+// exclusive scan of the block counts, one CTA (the array has n / 2048 entries)
+__global__ void border_scan_kernel(unsigned *block_count, int nblocks) {
+  __shared__ unsigned warp_sums[32];
+  __shared__ unsigned carry_s;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < nblocks; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const unsigned v = i < nblocks ? block_count[i] : 0u;
+    unsigned incl = v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    unsigned off = 0;
+    for (int w = 0; w < warp; ++w) off += warp_sums[w];
+    const unsigned carry = carry_s;
+    if (i < nblocks) block_count[i] = carry + off + incl - v;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry_s = carry + off + incl;
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void atomic_min_float(float *addr, float v) {  // io.cu:258-269
+  int *a = reinterpret_cast<int *>(addr);
+  int old = *a;
+  while (v < __int_as_float(old)) {
+    const int seen = atomicCAS(a, old, __float_as_int(v));
+    if (seen == old) break;
+    old = seen;
+  }
+}
+
+__global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_t seg, int hist_size,
+                                    const unsigned *__restrict__ block_off, float *thr) {
+  __shared__ unsigned warp_sums[kScanThreads / 32];
+  const size_t base = size_t(blockIdx.x) * kScanTile + size_t(threadIdx.x) * kScanItems;
+  bool flag[kScanItems];
+  unsigned c = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    flag[k] = base + k < n && is_border(s, base + k);
+    c += flag[k];
+  }
+  unsigned incl = c;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  unsigned run = block_off[blockIdx.x] + incl - c;
+  for (int w = 0; w < warp; ++w) run += warp_sums[w];
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    if (!flag[k]) continue;
+    ++run;  // inclusive border count of position i (io.cu:144-153)
+    const size_t i = base + k;
+    const float mid = float((s[i] + s[i - 1]) * 0.5);  // io.cu:72-79
+    const long long a = (long long)run + 1, b = (long long)(i / seg) + 1;
+    const long long slot = (a < b ? a : b) - 2;  // io.cu:257
+    // slots past the table are a defect of the reference (out-of-range write); skipped
+    if (slot >= 0 && slot < hist_size) atomic_min_float(thr + slot, mid);
+  }
+}
+
+__global__ void fill_inf_kernel(float *thr, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) thr[i] = INFINITY;
+}
+
+__global__ void extract_column_kernel(const float *__restrict__ X, size_t n, int F, int f,
+                                      float *__restrict__ col) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    float v = X[i * F + f];
+    // every NaN sorts last, as the positive quiet NaN does in the reference's sort
+    if (v != v) v = __int_as_float(0x7fc00000);
+    col[i] = v;
+  }
+}
+
+// cuda_helpers.h:207-222 over v[0..size-2] = thr, v[size-1] = +INF (io.cu:297-310)
+__device__ __forceinline__ unsigned lower_bound_thr(const float *thr, int size, float x) {
+  unsigned l = 0, h = unsigned(size);
+  while (l < h) {
+    const unsigned mid = (l + h) / 2;
+    const float v = int(mid) < size - 1 ? __ldg(thr + mid) : INFINITY;
+    if (x <= v) h = mid; else l = mid + 1;
+  }
+  return l;
+}
+
+template <typename BIN_T>
+__global__ void binning_kernel(const float *__restrict__ X, size_t n, int F,
+                               const float *__restrict__ thr, const int *__restrict__ fsize,
+                               int hist_size, bool missing_bin, unsigned char *__restrict__ bins,
+                               size_t pitch) {
+  const size_t total = n * size_t(F);
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = e / F;
+    const int f = int(e - r * F);
+    const float x = X[e];
+    unsigned b;
+    if (missing_bin && x != x)
+      b = unsigned(hist_size);
+    else
+      b = lower_bound_thr(thr + size_t(f) * hist_size, fsize[f], x);
+    reinterpret_cast<BIN_T *>(bins + r * pitch)[f] = BIN_T(b);
+  }
+}
+
+}  // namespace
+
+size_t thresholds_scratch_words(size_t n) { return (n + kScanTile - 1) / kScanTile + 1; }
+
+void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
+                       cudaStream_t s) {
+  fill_inf_kernel<<<ceil_div(hist_size, 256), 256, 0, s>>>(thr, hist_size);  // io.cu:387
+  if (n < 2) return;
+  const int nblocks = int((n + kScanTile - 1) / kScanTile);
+  const size_t seg = std::max<size_t>(1, n / size_t(hist_size));  // io.cu:376-377
+  border_count_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, scratch);
+  border_scan_kernel<<<1, 1024, 0, s>>>(scratch, nblocks);
+  border_apply_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, seg, hist_size, scratch, thr);
+  ARB_CUDA(cudaGetLastError());
+  count_launch(4);
+}
+
+void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s) {
+  const int threads = 256;
+  const int grid = int(std::min<size_t>((n + threads - 1) / threads, size_t(148) * 16));
+  extract_column_kernel<<<grid, threads, 0, s>>>(X, n, F, f, col);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s) {
+  size_t bytes = 0;
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes, in, out, n, 0, 32, s));
+  if (tmp.bytes < bytes) tmp.alloc(bytes);
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(tmp.p, bytes, in, out, n, 0, 32, s));
+}
+
+void launch_binning(const float *X, size_t n, int F, const float *thr, const int *fsize,
+                    int hist_size, bool missing_bin, unsigned char *bins, size_t pitch, int bin_bytes,
+                    cudaStream_t s) {
+  if (n == 0) return;
+  const int threads = 256;
+  const size_t total = n * size_t(F);
+  const int grid = int(std::min<size_t>((total + threads - 1) / threads, size_t(148) * 32));
+  if (bin_bytes == 1)
+    binning_kernel<unsigned char><<<grid, threads, 0, s>>>(X, n, F, thr, fsize, hist_size, missing_bin,
+                                                           bins, pitch);
+  else
+    binning_kernel<unsigned short><<<grid, threads, 0, s>>>(X, n, F, thr, fsize, hist_size,
+                                                            missing_bin, bins, pitch);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+}  // namespace arb

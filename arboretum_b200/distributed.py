@@ -1,0 +1,72 @@
+"""Host-side plumbing of row-sharded multi-GPU training (one process per GPU).
+
+The data path needs exactly one exchange: the per-level histogram sum, done by the
+library with ncclAllReduce on its own stream.  What this module does on the host,
+through ``torch.distributed`` (NCCL or gloo), is the set-up around it:
+
+* ``shard_rows``      -- the contiguous row range of a rank;
+* ``share_thresholds``-- one rank quantises, everybody bins with the same thresholds
+                         (bins must not depend on the number of GPUs);
+* ``init_nccl``       -- rank 0 creates the ncclUniqueId, the others receive it, and
+                         every rank joins the communicator of its Garden.
+"""
+import ctypes
+
+import numpy as np
+
+
+def shard_rows(n_rows, rank, world):
+    """[begin, end) of the rows rank `rank` owns out of `n_rows`."""
+    if not (0 <= rank < world):
+        raise ValueError("rank %d outside world of %d" % (rank, world))
+    return (n_rows * rank) // world, (n_rows * (rank + 1)) // world
+
+
+def _broadcast_bytes(buf, src=0):
+    """Broadcast a numpy uint8 array in place from rank `src`."""
+    import torch
+    import torch.distributed as dist
+    t = torch.from_numpy(buf)
+    if dist.get_backend() == "nccl":
+        d = t.cuda()
+        dist.broadcast(d, src)
+        buf[:] = d.cpu().numpy()
+    else:
+        dist.broadcast(t, src)
+    return buf
+
+
+def share_thresholds(data, hist_size, rank, world, thresholds=None, sizes=None, src=0):
+    """Give every rank's DMatrix the same thresholds.
+
+    With `thresholds` / `sizes` given on rank `src` (computed from the whole data
+    set before sharding) they are used as they are; otherwise rank `src` quantises
+    its own shard and shares the result (an approximation: 1/world of the rows).
+    """
+    F = data.columns
+    quantized_here = False
+    if rank == src and thresholds is None:
+        thresholds, sizes, _ = data.quantize(hist_size, True, want_bins=False)
+        quantized_here = True  # this DMatrix is binned with these thresholds already
+    thr = np.zeros((F, hist_size), dtype=np.float32)
+    size = np.zeros(F, dtype=np.int32)
+    if rank == src:
+        thr[:] = thresholds
+        size[:] = sizes
+    _broadcast_bytes(thr.view(np.uint8).reshape(-1), src)
+    _broadcast_bytes(size.view(np.uint8).reshape(-1), src)
+    if not quantized_here:
+        data.set_thresholds(thr, size)
+    return thr, size
+
+
+def init_nccl(garden, rank, world, src=0):
+    """Create the Garden's communicator; must precede its first grow_tree."""
+    from . import core
+    garden._ensure_init()
+    uid = np.zeros(128, dtype=np.uint8)
+    if rank == src:
+        core._call_and_throw_if_error(core.lib().ANcclUniqueId(uid.ctypes.data_as(ctypes.c_void_p)))
+    _broadcast_bytes(uid, src)
+    core._call_and_throw_if_error(core.lib().AInitNccl(garden.handle, rank, world,
+                                                      uid.ctypes.data_as(ctypes.c_void_p)))

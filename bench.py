@@ -1,0 +1,304 @@
+#!/usr/bin/env python
+"""Benchmark of the boosting hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rows R]
+
+Workload (N = 1): the binary-classification configuration the headline metric is
+quoted on -- 10 M rows x 28 fp32 features (21 ~ N(0,1) plus 7 derived ones), label
+~ Bernoulli(sigmoid(w.x + 0.3 * sum of pair products)), hist_size 255, reg:logistic,
+max_depth 8, eta 0.1, min_child_weight 1.  The data are seeded synthetic stand-ins
+(there is no public data set behind the metric).  One step = one boosting round
+(AGrowTree).  For N > 1 the same rows are sharded over one process per GPU (strong
+scaling) and every level's histogram is summed with ncclAllReduce.
+
+`value` is rounds/s with the binned matrix resident in HBM; `e2e` is rounds/s of the
+whole job through the C ABI from host buffers: DMatrix construction (host->device
+copy, quantisation), K rounds, read-back of the training predictions.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FULL_ROWS = 10_000_000
+FEATURES = 28
+CONFIG = {"objective": 1, "method": 1,
+          "internals": {"double_precision": False, "compute_overlap": 2, "seed": 0,
+                        "use_hist_subtraction_trick": True, "upload_features": True,
+                        "hist_size": 255},
+          "verbose": {"gpu": False, "booster": False, "data": False},
+          "tree": {"eta": 0.1, "max_depth": 8, "min_child_weight": 1.0, "min_leaf_size": 1,
+                   "lambda": 1.0, "alpha": 0.0, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}}
+# DRAM bytes per algorithmic byte of the histogram kernel, from the ncu capture
+# summarised in profiles/ (None until a capture exists for this kernel version).
+HIST_TRAFFIC_RATIO = None
+
+
+def make_rows(n, seed):
+    """Rows of the 10M x 28 logistic configuration; weights are fixed by seed 2."""
+    wrng = np.random.default_rng(2)
+    w = wrng.normal(size=FEATURES).astype(np.float32)
+    rng = np.random.default_rng([2, seed])
+    X = np.empty((n, FEATURES), dtype=np.float32)
+    X[:, :21] = rng.standard_normal((n, 21), dtype=np.float32)
+    X[:, 21] = X[:, 0] * X[:, 1]
+    X[:, 22] = X[:, 2] * X[:, 3]
+    X[:, 23] = X[:, 4] * X[:, 5]
+    X[:, 24] = X[:, 6] * X[:, 7]
+    X[:, 25] = np.abs(X[:, 8] - X[:, 9])
+    X[:, 26] = np.abs(X[:, 10] + X[:, 11])
+    X[:, 27] = np.abs(X[:, 12] * X[:, 13])
+    logit = X @ w
+    for j in range(7):
+        logit += 0.3 * X[:, 2 * j] * X[:, 2 * j + 1]
+    y = (rng.random(n, dtype=np.float32) < 1.0 / (1.0 + np.exp(-logit))).astype(np.float32)
+    return X, y
+
+
+class ClockSampler(object):
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(smax)) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def oracle_rounds_per_s(rows, rounds, warmup):
+    """The CPU port of the path on a bounded sample: rounds/s at `rows` rows."""
+    from oracle import oracle as orc
+    X, y = make_rows(rows, seed=1000)
+    o = orc.Oracle(CONFIG, missing_bin=True).set_dense(X).set_y(y)
+    o.grow(warmup)
+    t0 = time.perf_counter()
+    o.grow(rounds)
+    return rounds / (time.perf_counter() - t0)
+
+
+def run_reference(args, rank, world):
+    """Reference arm: arboretum has no CPU training path, so this times the CPU port
+    of its algorithm (oracle/) with all host threads on a bounded row sample."""
+    if rank != 0:
+        return
+    sample = min(args.rows, 1_000_000)
+    cores = os.cpu_count() or 1
+    rps_sample = oracle_rounds_per_s(sample, max(1, args.steps), max(0, args.warmup))
+    value = rps_sample * sample / args.rows  # cost is linear in rows
+    line = {"impl": "reference", "metric": "boosting_rounds_per_sec", "value": value,
+            "unit": "rounds/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": workload_config(args, world),
+            "cpu_baseline": {"value": value, "unit": "rounds/s", "cores": cores, "kind": "port",
+                             "sample": "%d of %d rows, %d rounds timed, rounds/s scaled by rows"
+                                       % (sample, args.rows, args.steps)},
+            "e2e": {"value": value, "unit": "rounds/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": "binary classification %d x %d fp32, hist_size 255, reg:logistic, "
+                        "max_depth 8, eta 0.1 (configs[1])" % (args.rows, FEATURES),
+            "rows": args.rows, "features": FEATURES, "max_depth": 8,
+            "rows_per_gpu": args.rows // world, "parallelism": "rows sharded x%d" % world,
+            "l2": "inputs (bins %.0f MB + gradients %.0f MB per GPU) exceed the 126 MB L2"
+                  % (args.rows // world * 32 / 1e6, args.rows // world * 8 / 1e6)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--rows", type=int, default=FULL_ROWS)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import arboretum_b200 as arboretum
+    from arboretum_b200 import distributed as adist
+
+    args.warmup = max(args.warmup, 3)
+    n_local = args.rows // world
+    X, y = make_rows(n_local, seed=rank)
+    xp = torch.from_numpy(X).pin_memory()  # the job's host buffers are pinned
+    yp = torch.from_numpy(y).pin_memory()
+    Xh, yh = xp.numpy(), yp.numpy()
+    cfg = json.loads(json.dumps(CONFIG))
+    cfg["internals"]["device"] = local_rank
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def new_model():
+        data = arboretum.DMatrix(Xh, y=yh)
+        model = arboretum.Garden(cfg)
+        model.data = data
+        if world > 1:
+            adist.share_thresholds(data, cfg["internals"]["hist_size"], rank, world)
+            adist.init_nccl(model, rank, world)
+        return model, data
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- end to end: host buffers -> model -> predictions on the host --------------
+    barrier()
+    t0 = time.perf_counter()
+    model, data = new_model()
+    for _ in range(args.steps):
+        model.grow_tree()
+    yhat = model.train_yhat()
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e = {"value": args.steps / e2e_s, "unit": "rounds/s",
+           "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) * world / args.steps),
+           "d2h_bytes_per_step": int(yhat.nbytes * world / args.steps),
+           "what": "DMatrix from pinned host fp32 + quantise + %d rounds + predictions to host"
+                   % args.steps}
+
+    # ---- device-resident rounds (the model above is already bound and warm) ---------
+    for _ in range(args.warmup):
+        model.grow_tree()
+    sampler = ClockSampler(local_rank)
+    launches0 = model.timings()["kernel_launches"]
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.grow_tree()
+    ev1.record()
+    barrier()
+    wall_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    step_s = max_over_ranks(ev0.elapsed_time(ev1) / 1000.0)
+    launches = model.timings()["kernel_launches"] - launches0
+
+    # ---- roofline of the dominant kernel: CUDA events on the library's own stream ----
+    model.set_profile(True)
+    prof_rounds = 3
+    for _ in range(prof_rounds):
+        model.grow_tree()
+    t = model.timings()
+    model.set_profile(False)
+    peak, peak_src = measured_peak()
+    hist_gbs = t["hist_bytes"] / (t["hist_ms"] * 1e-3) / 1e9
+    per_launch_bytes = t["hist_bytes"] / max(1, t["hist_launches"])
+    roofline = {"bound": "hbm", "kernel": "hist_u8_kernel", "achieved": hist_gbs, "peak": peak,
+                "unit": "GB/s", "frac": hist_gbs / peak, "peak_source": peak_src,
+                "frac_of_nominal_8TBs": hist_gbs / 8000.0,
+                "traffic": None if HIST_TRAFFIC_RATIO is None else per_launch_bytes * HIST_TRAFFIC_RATIO,
+                "algorithmic_bytes_per_launch": per_launch_bytes,
+                "avg_launch_ms": t["hist_ms"] / max(1, t["hist_launches"]),
+                "rows_x_features_per_s_per_gpu": t["hist_rows"] * FEATURES / (t["hist_ms"] * 1e-3),
+                "smem_atomic_updates_per_s": 2.0 * t["hist_rows"] * FEATURES / (t["hist_ms"] * 1e-3),
+                "phase_ms_per_round": {k: t[k] / prof_rounds for k in
+                                       ("grad_ms", "partition_ms", "plan_ms", "hist_ms", "allreduce_ms",
+                                        "subtract_ms", "split_ms", "update_ms")}}
+
+    if rank == 0:
+        line = {"metric": "boosting_rounds_per_sec", "value": args.steps / step_s, "unit": "rounds/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": 1000.0 * step_s / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "int64 fixed-point sums of f32 gradients",
+                "data": "synthetic", "config": workload_config(args, world), "clocks": clocks,
+                "e2e": e2e, "gpu_launches": int(launches), "wall_ms_per_step": 1000.0 * wall_s / args.steps,
+                "roofline": roofline}
+        if world == 1 and not args.no_cpu_baseline:
+            sample = min(args.rows, 500_000)
+            cores = os.cpu_count() or 1
+            rps = oracle_rounds_per_s(sample, 2, 1) * sample / args.rows
+            line["cpu_baseline"] = {"value": rps, "unit": "rounds/s", "cores": cores, "kind": "port",
+                                    "sample": "%d of %d rows, 2 rounds timed after 1, rounds/s scaled "
+                                              "by rows" % (sample, args.rows)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

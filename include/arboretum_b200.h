@@ -1,0 +1,98 @@
+/* C ABI of libarboretum.so (B200 build).
+ *
+ * The first fourteen functions are the reference's python-wrapper ABI
+ * (python-wrapper/arboretum_wrapper.h:4-39), re-exported one to one so that the
+ * reference's python-package/arboretum/core.py loads this library unchanged.
+ * Every function returns NULL on success, else a NUL-terminated message owned by
+ * the library (valid until the next failing call on the same thread).  Handles
+ * are opaque; a NULL handle passed to a free function is ignored.  Unlike the
+ * reference no call ever exits the process or lets a C++ exception escape.
+ *
+ * The functions below the "additive" line do not exist in the reference.
+ */
+#ifndef ARBORETUM_B200_H
+#define ARBORETUM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *VoidPointer;
+
+/* arboretum_wrapper.h:6-9 / arboretum_wrapper.cu:16-39.  `data` is row-major
+ * [nrow][ncol] fp32, `categories` row-major [nrow][ccol] or NULL; both are
+ * copied.  `missing` is accepted and ignored, like in the reference. */
+const char *ACreateFromDenseMatrix(const float *data, const unsigned int *categories, int nrow,
+                                   int ncol, int ccol, float missing, VoidPointer *out);
+/* arboretum_wrapper.h:11 / .cu:41-55 */
+const char *ASetY(VoidPointer data, const float *y);
+/* arboretum_wrapper.h:13 / .cu:57-71 */
+const char *ASetLabel(VoidPointer data, const unsigned char *labels);
+/* arboretum_wrapper.h:15 / .cu:73-86 */
+const char *ASetWeights(VoidPointer data, const float *weights);
+/* arboretum_wrapper.h:17-18 / .cu:88-99: nested JSON configuration */
+const char *AInitGarden(const char *configuration, VoidPointer *garden);
+/* arboretum_wrapper.h:20-21 / .cu:101-111: one boosting round (labels_count trees).
+ * The first call quantises `data` and binds the garden to it. */
+const char *AGrowTree(VoidPointer garden, VoidPointer data, const float *grad);
+/* arboretum_wrapper.h:23 / .cu:180-191 */
+const char *AAppendLastTree(VoidPointer garden, VoidPointer data);
+/* arboretum_wrapper.h:25-26 / .cu:153-178: *out = new float[rows * labels] */
+const char *AGetY(VoidPointer garden, VoidPointer data, const float **out);
+/* arboretum_wrapper.h:28-29 / .cu:113-139: n_rounds == -1 means all trees */
+const char *APredict(VoidPointer garden, VoidPointer data, const float **out, const int n_rounds);
+/* arboretum_wrapper.h:31 / .cu:141-145: *model = heap C string (argument order as there) */
+const char *ADumpModel(const char **model, VoidPointer garden);
+/* arboretum_wrapper.h:33 / .cu:147-151 */
+const char *ALoadModel(const char *model, VoidPointer garden);
+/* arboretum_wrapper.h:35-39 / .cu:193-205 */
+const char *AFreeDMatrix(VoidPointer ptr);
+const char *AFreeGarden(VoidPointer ptr);
+const char *ADeleteArray(float *in);
+
+/* ------------------------------- additive ---------------------------------- */
+
+/* Rows that are already binned (uint8 ids < hist_size, row-major [nrow][ncol]);
+ * the reference ingests fp32 only (arboretum_wrapper.h:6-9). */
+const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol, int hist_size,
+                                    VoidPointer *out);
+/* Thresholds computed elsewhere (e.g. on the whole data set before sharding rows
+ * over GPUs): thr is [ncol][hist_size], size[f] = bins in use.  Must precede the
+ * first AGrowTree. */
+const char *ASetThresholds(VoidPointer data, const float *thr, const int *size, int hist_size);
+/* Quantise now (what the first AGrowTree would do) and read the result back:
+ * thr [ncol][hist_size], size [ncol], bins [nrow][ncol] uint16; any may be NULL. */
+const char *AQuantize(VoidPointer data, int hist_size, int missing_bin, float *thr, int *size,
+                      uint16_t *bins);
+/* Training-time predictions of the bound DMatrix, internal scale, [labels][rows]. */
+const char *AGetTrainY(VoidPointer garden, float *out);
+/* Split records of level `level` of the last grown tree: arrays of 1 << level
+ * entries (node_begin: one more).  Sums are in gradient units. */
+const char *AGetLevelStats(VoidPointer garden, int level, unsigned *node_begin, float *gain,
+                           int *fid, int *bin, double *left_g, double *left_h, double *tot_g,
+                           double *tot_h, unsigned *left_count);
+/* CUDA-event timing of the kernel classes: switch on, then read a JSON summary. */
+const char *ASetProfile(VoidPointer garden, int on);
+const char *AGetTimings(VoidPointer garden, const char **json);
+/* One histogram launch over host buffers (kernel-level parity and measurement):
+ * bins row-major [nrow][ncol] of `bin_bytes`-byte ids, grad [nrow] (pair == 0) or
+ * [nrow][2]; rowid (NULL = identity) grouped by node with node_begin[n_nodes + 1];
+ * out_g / out_h [n_nodes][ncol][hist_size + 1] doubles.  When `reps` > 0 the
+ * launch is repeated and its mean device time is stored in *ms. */
+const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                            const float *grad, int pair, const unsigned *rowid,
+                            const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
+                            double *out_h, int reps, float *ms);
+/* Multi-GPU: rows are sharded over one process per GPU; every level's histogram
+ * is summed over the ranks with ncclAllReduce.  `id` is the 128-byte
+ * ncclUniqueId made by rank 0 (ANcclUniqueId) and sent to the others by the host. */
+const char *ANcclUniqueId(char *id128);
+const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARBORETUM_B200_H */

@@ -519,6 +519,7 @@ class Trainer : public TrainerBase {
         if (!y.empty()) scatter(y, 0, idx);
         if (!label.empty()) scatter(label, 0, idx);
         scatter(orig, 0, idx);
+#pragma omp parallel for
         for (int f = 0; f < F; ++f) scatter(bins[f], 0, idx);  // hist_tree_grower.cu:346-348
         std::fill(go_right.begin(), go_right.end(), 0);
       }
@@ -526,11 +527,22 @@ class Trainer : public TrainerBase {
       st.node_begin.assign(pcount.begin(), pcount.begin() + L + 1);
       std::vector<float> top1(L, 0.f), top2(L, 0.f);
 
-      std::vector<S> sum(size_t(L) * HW), prefix(size_t(L) * HW);
-      std::vector<uint32_t> cnt(size_t(L) * HW), cprefix(size_t(L) * HW);
+      // Per-feature work (histogram, scans, gain search) is independent until the
+      // candidates are folded into the per-node best, so it runs on all host
+      // threads; the fold below stays in the reference's feature order.
+      struct Cand {
+        std::vector<float> cgain, t1, t2;
+        std::vector<unsigned> cidx;
+        std::vector<S> sum_at;
+        std::vector<uint32_t> cnt_at;
+      };
+      std::vector<Cand> cands(F);
+#pragma omp parallel for schedule(dynamic)
       for (int j = 0; j < F; ++j) {
         const int fid = int(active[j]);
         if (unsigned(j) >= takel) continue;  // partition_only features
+        std::vector<S> sum(size_t(L) * HW), prefix(size_t(L) * HW);
+        std::vector<uint32_t> cnt(size_t(L) * HW), cprefix(size_t(L) * HW);
         // ---- histogram (hist_tree_grower.cu:365-390) -----------------------
         for (auto &v : sum) zero(v);
         std::fill(cnt.begin(), cnt.end(), 0);
@@ -589,8 +601,13 @@ class Trainer : public TrainerBase {
           }
         }
         // ---- hist_gain_kernel hist_tree_grower.cu:9-35 ----------------------
-        std::vector<float> cgain(L, 0.f);
-        std::vector<unsigned> cidx(L, 0);
+        Cand &cd = cands[j];
+        cd.cgain.assign(L, 0.f);
+        cd.cidx.assign(L, 0);
+        cd.t1.assign(L, 0.f);
+        cd.t2.assign(L, 0.f);
+        std::vector<float> &cgain = cd.cgain, &top1l = cd.t1, &top2l = cd.t2;
+        std::vector<unsigned> &cidx = cd.cidx;
         for (size_t i = 0; i < size_t(L) * HW; ++i) {
           const unsigned seg = unsigned(i / HW);
           const S lsum = prefix[i] - psum[seg];
@@ -599,15 +616,43 @@ class Trainer : public TrainerBase {
           const uint32_t tcnt = pcount[seg + 1] - pcount[seg];
           const float gn = gain_func(lsum, tsum, lcnt, tcnt, gp);
           if (gn > 0.0) {  // updateAtomicMax builder.h:39-49: ties -> higher index
-            if (gn > top1[seg]) {  // bookkeeping for the tests only
-              top2[seg] = top1[seg];
-              top1[seg] = gn;
-            } else if (gn < top1[seg] && gn > top2[seg]) {
-              top2[seg] = gn;
+            if (gn > top1l[seg]) {  // bookkeeping for the tests only
+              top2l[seg] = top1l[seg];
+              top1l[seg] = gn;
+            } else if (gn < top1l[seg] && gn > top2l[seg]) {
+              top2l[seg] = gn;
             }
             if (cgain[seg] < gn || (cgain[seg] == gn && cidx[seg] < unsigned(i))) {
               cgain[seg] = gn;
               cidx[seg] = unsigned(i);
+            }
+          }
+        }
+        cd.sum_at.resize(L);
+        cd.cnt_at.resize(L);
+        for (int node = 0; node < L; ++node) {
+          cd.sum_at[node] = prefix[cidx[node]];
+          cd.cnt_at[node] = cprefix[cidx[node]];
+        }
+        if (cfg.use_trick) {  // Histogram::Update histogram.cu:30-44
+          saved_sum[fid] = sum;
+          saved_count[fid] = cnt;
+          at_level[fid] = level;
+        }
+      }
+      for (int j = 0; j < F; ++j) {
+        const int fid = int(active[j]);
+        if (unsigned(j) >= takel) continue;
+        const Cand &cd = cands[j];
+        const std::vector<float> &cgain = cd.cgain;
+        const std::vector<unsigned> &cidx = cd.cidx;
+        for (int node = 0; node < L; ++node) {  // merge the test bookkeeping
+          for (float gn : {cd.t1[node], cd.t2[node]}) {
+            if (gn > top1[node]) {
+              top2[node] = top1[node];
+              top1[node] = gn;
+            } else if (gn < top1[node] && gn > top2[node]) {
+              top2[node] = gn;
             }
           }
         }
@@ -622,16 +667,16 @@ class Trainer : public TrainerBase {
                 (best_gain[node] == gn && fid < best_fid[node])) {
               best_gain[node] = gn;
               best_fid[node] = fid;
-              best_sum[node] = prefix[idx] - psum[node];
-              best_count[node] = cprefix[idx] - nstart;
+              best_sum[node] = cd.sum_at[node] - psum[node];
+              best_count[node] = cd.cnt_at[node] - nstart;
               const unsigned thr = idx % HW;
               best_split[node] = thr;
               // apply_split builder.h:107-123: right <=> bin >= thr + 1
               for (uint32_t i = nstart; i < nend; ++i)
                 go_right[i] = bins[fid][i] >= thr + 1;
-              pcount_next[2 * node + 1] = cprefix[idx];
+              pcount_next[2 * node + 1] = cd.cnt_at[node];
               pcount_next[2 * node + 2] = nend;
-              psum_next[2 * node + 1] = prefix[idx];
+              psum_next[2 * node + 1] = cd.sum_at[node];
               psum_next[2 * node + 2] = psum[node + 1];
             } else if (best_gain[node] == 0 && best_fid[node] == -1) {
               best_sum[node] = psum[node + 1] - psum[node];
@@ -644,11 +689,6 @@ class Trainer : public TrainerBase {
             pcount_next[2 * node + 1] = pcount_next[2 * node + 2] = nend;
             psum_next[2 * node + 1] = psum_next[2 * node + 2] = psum[node + 1];
           }
-        }
-        if (cfg.use_trick) {  // Histogram::Update histogram.cu:30-44
-          saved_sum[fid] = sum;
-          saved_count[fid] = cnt;
-          at_level[fid] = level;
         }
       }
       // ---- UpdateTree garden.cu:447-485 --------------------------------------

@@ -1,0 +1,366 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and with the
+reference's golden vectors.  Integer results (bins, node row counts, split
+feature / bin) must match exactly; histogram sums within 1e-5 relative; tree
+structures must be identical wherever the oracle's best and runner-up gains of a
+node differ by more than 1e-6 relative; predictions within 1e-4."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "iris_hist_golden.json")
+HIST_RTOL = 1e-5
+GAIN_GAP = 1e-6
+PRED_ATOL = 1e-4
+
+
+def arb():
+    import arboretum_b200
+    return arboretum_b200
+
+
+# ---------------------------------------------------------------------------------
+# quantizer
+# ---------------------------------------------------------------------------------
+def _quantize_gpu(X, hist_size, missing_bin=False):
+    d = arb().DMatrix(np.ascontiguousarray(X, dtype=np.float32))
+    return d.quantize(hist_size, missing_bin)
+
+
+KAT_COLUMNS = [  # tests/cpp/test_datamatrix.cu
+    (np.array([128 - i for i in range(128)], dtype=np.float32), 8,
+     [8 - (i // 16) - 1 for i in range(128)]),
+    (np.arange(1024, dtype=np.float32), 255,
+     [i // 4 if i < 1020 else 254 for i in range(1024)]),
+    (np.array([10, 0, 11, 1, 0, 2, 3, 0, 0, 0, 0, 0], dtype=np.float32), 4,
+     [3, 0, 3, 1, 0, 2, 3, 0, 0, 0, 0, 0]),
+    (np.array([0, 0, 0, 1, 0, 2, 0, 0, 0, 0, 0, 0], dtype=np.float32), 4,
+     [0, 0, 0, 1, 0, 2, 0, 0, 0, 0, 0, 0]),
+    (np.array([10, 10, 10, 1, 10, 2, 10, 10, 10, 10, 10, 10], dtype=np.float32), 4, [0] * 12),
+]
+
+
+@pytest.mark.parametrize("case", range(len(KAT_COLUMNS)))
+def test_quantizer_reference_kats(case):
+    col, hist_size, expected = KAT_COLUMNS[case]
+    thr, size, bins = _quantize_gpu(col.reshape(-1, 1), hist_size)
+    assert bins[:, 0].tolist() == expected
+
+
+@pytest.mark.parametrize("n,F,hist_size,kind", [
+    (5000, 7, 255, "normal"), (20000, 28, 255, "normal"), (3000, 5, 16, "dups"),
+    (4096, 3, 512, "normal"), (1500, 4, 1023, "normal"), (2000, 6, 255, "nan"),
+    (700, 2, 255, "const"), (100003, 3, 255, "lognormal")])
+def test_quantizer_matches_oracle_bit_exactly(n, F, hist_size, kind):
+    rng = np.random.default_rng(n + F)
+    X = rng.normal(size=(n, F)).astype(np.float32)
+    missing = False
+    if kind == "dups":
+        X = np.round(X * 3).astype(np.float32)
+    elif kind == "nan":
+        X[rng.random(X.shape) < 0.2] = np.nan
+        missing = True
+    elif kind == "const":
+        X[:, 0] = 3.5
+    elif kind == "lognormal":
+        X = np.exp(X).astype(np.float32)
+    thr, size, bins = _quantize_gpu(X, hist_size, missing)
+    for f in range(F):
+        othr, osize, obins = orc.quantize_column(X[:, f], hist_size, missing)
+        assert size[f] == osize
+        assert thr[f].tobytes() == othr.tobytes()
+        assert (bins[:, f] == obins).all()
+
+
+# ---------------------------------------------------------------------------------
+# histogram kernel
+# ---------------------------------------------------------------------------------
+def _oracle_hist(bins, g, h, rowid, node_begin, hw):
+    n, F = bins.shape
+    pos_bins = bins if rowid is None else bins[rowid]
+    pg = g if rowid is None else g[rowid]
+    ph = None if h is None else (h if rowid is None else h[rowid])
+    nn = len(node_begin) - 1
+    og = np.zeros((nn, F, hw))
+    oh = np.zeros((nn, F, hw))
+    for f in range(F):
+        a, b, c = orc.hist(pos_bins[:, f], pg, ph, node_begin, hw)
+        og[:, f, :] = a.reshape(nn, hw)
+        oh[:, f, :] = (b if ph is not None else c.astype(np.float64)).reshape(nn, hw)
+    return og, oh
+
+
+@pytest.mark.parametrize("hist_size,n", [(4, 32), (255, 1 << 12), (256, 1 << 12), (1023, 1 << 13)])
+@pytest.mark.parametrize("pair", [False, True])
+def test_histogram_reference_pattern(hist_size, n, pair):
+    # tests/cpp/test_hist_sum.cu: grad[i] = i, bin = i % hist_size, one segment
+    dtype = np.uint8 if hist_size < 256 else np.uint16
+    bins = (np.arange(n) % hist_size).astype(dtype).reshape(-1, 1)
+    g = np.arange(n, dtype=np.float32)
+    grad = np.stack([g, np.ones(n, dtype=np.float32)], axis=1) if pair else g
+    og, oh = arb().build_histogram(bins, grad, hist_size, quant_bits=17)
+    for b in range(hist_size):
+        assert og[0, 0, b] == pytest.approx(float(sum(range(b, n, hist_size))), rel=HIST_RTOL)
+        assert oh[0, 0, b] == n // hist_size
+
+
+@pytest.mark.parametrize("n,F,hist_size,nodes,pair", [
+    (50000, 28, 255, 1, True), (50000, 28, 255, 8, True), (30000, 28, 255, 4, False),
+    (20000, 70, 255, 3, True), (9000, 5, 600, 2, True), (7000, 33, 64, 5, False)])
+def test_histogram_matches_oracle(n, F, hist_size, nodes, pair):
+    rng = np.random.default_rng(n + F + nodes)
+    dtype = np.uint8 if hist_size < 256 else np.uint16
+    bins = rng.integers(0, hist_size + 1, size=(n, F)).astype(dtype)  # id hist_size = missing
+    g = rng.normal(size=n).astype(np.float32)
+    h = rng.uniform(0.01, 0.25, size=n).astype(np.float32)
+    rowid = rng.permutation(n).astype(np.uint32)
+    cuts = np.sort(rng.integers(0, n, size=nodes - 1)) if nodes > 1 else np.array([], dtype=np.int64)
+    node_begin = np.concatenate([[0], cuts, [n]]).astype(np.uint32)
+    grad = np.stack([g, h], axis=1) if pair else g
+    og, oh = arb().build_histogram(bins, grad, hist_size, rowid=rowid, node_begin=node_begin)
+    eg, eh = _oracle_hist(bins.astype(np.uint16), g, h if pair else None, rowid, node_begin, hist_size + 1)
+    scale_g = np.abs(g).sum() / (hist_size + 1)
+    assert np.allclose(og, eg, rtol=HIST_RTOL, atol=HIST_RTOL * scale_g)
+    if pair:
+        assert np.allclose(oh, eh, rtol=HIST_RTOL, atol=HIST_RTOL)
+    else:
+        assert (oh == eh).all()  # counts are exact
+
+
+# ---------------------------------------------------------------------------------
+# end to end
+# ---------------------------------------------------------------------------------
+def _iris():
+    from sklearn.datasets import load_iris
+    iris = load_iris()
+    return iris.data.astype(np.float32), (iris.target != 2).astype(np.float32)
+
+
+def _assert_model(true_model, created, rtol=1e-4, atol=1e-6):  # tests/py/utils.py:4-12
+    assert len(true_model["model"]) == len(created["model"])
+    for t, c in zip(true_model["model"], created["model"]):
+        assert np.allclose(t["weights"], c["weights"], rtol=rtol, atol=atol)
+        assert t["nodes"] == c["nodes"]
+
+
+@pytest.mark.parametrize("case", ["test_single_tree_depth_2", "test_2trees_depth_1"])
+@pytest.mark.parametrize("double_precision", [True, False])
+@pytest.mark.parametrize("use_trick", [True, False])
+def test_iris_golden_through_the_abi(case, double_precision, use_trick):
+    # tests/py/test_hist_logregression.py:10-66
+    arboretum = arb()
+    gold = json.load(open(GOLDEN))
+    c = gold["hist_logregression"][case]
+    cfg = json.loads(json.dumps(gold["config"]))
+    cfg["tree"]["max_depth"] = c["max_depth"]
+    cfg["internals"]["double_precision"] = double_precision
+    cfg["internals"]["use_hist_subtraction_trick"] = use_trick
+    X, y = _iris()
+    data = arboretum.DMatrix(X, y=y)
+    model = arboretum.train(cfg, data, c["trees"])
+    for i in range(c["trees"]):
+        assert np.allclose(model.predict(data, i + 1), c["predictions"][i])
+    dumped = model.dump()
+    _assert_model(c["model"], json.loads(dumped))
+    restored = arboretum.load(dumped)
+    for i in range(c["trees"]):
+        assert np.allclose(restored.predict(data, i + 1), c["predictions"][i])
+
+
+@pytest.mark.parametrize("hist_size", [255, 256, 511, 512, 1023])
+def test_iris_sklearn_golden(hist_size):  # tests/py/test_sklearn_classification.py:9-61
+    arboretum = arb()
+    gold = json.load(open(GOLDEN))
+    X, y = _iris()
+    data = arboretum.DMatrix(X, y=y)
+    model = arboretum.ArboretumClassifier(
+        max_depth=2, learning_rate=0.2, n_estimators=1, verbosity=0, gamma_absolute=0.0,
+        gamma_relative=0.0, min_child_weight=2.0, min_leaf_size=0, max_leaf_weight=0,
+        colsample_bytree=1.0, colsample_bylevel=1.0, l1=0, l2=0, scale_pos_weight=1.0,
+        initial_y=0.5, seed=0, double_precision=True, method='hist', hist_size=hist_size)
+    model.fit(data, y)
+    assert np.allclose(model.predict(data), gold["sklearn_classification"]["predictions"][0])
+
+
+def make_config(objective, max_depth, eta=0.1, hist_size=255, **tree):
+    t = {"eta": eta, "max_depth": max_depth, "lambda": 1.0, "alpha": 0.0, "min_child_weight": 1.0,
+         "min_leaf_size": 1, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}
+    t.update(tree)
+    return {"objective": objective, "method": 1,
+            "internals": {"double_precision": True, "compute_overlap": 2, "seed": 0,
+                          "use_hist_subtraction_trick": True, "upload_features": True,
+                          "hist_size": hist_size},
+            "verbose": {"gpu": False, "booster": False, "data": False}, "tree": t}
+
+
+def synth(kind, n, F, seed):
+    rng = np.random.default_rng(seed)
+    X = rng.normal(size=(n, F)).astype(np.float32)
+    w = rng.normal(size=F)
+    if kind == "linear":  # the small regression config: y = w.x + 0.5 x0 x1 + noise
+        y = X @ w + 0.5 * X[:, 0] * X[:, 1] + rng.normal(0, 0.1, n)
+    else:
+        logit = X @ w * 0.5 + 0.3 * X[:, 0] * X[:, 1]
+        y = (rng.random(n) < 1 / (1 + np.exp(-logit))).astype(np.float64)
+    return X, y.astype(np.float32)
+
+
+def compare_with_oracle(cfg, X, y, rounds, labels=None):
+    """Grow `rounds` rounds on both sides, comparing level by level."""
+    arboretum = arb()
+    if labels is None:
+        data = arboretum.DMatrix(X, y=y)
+        o = orc.Oracle(cfg, missing_bin=True).set_dense(X).set_y(y)
+    else:
+        data = arboretum.DMatrix(X, labels=labels)
+        o = orc.Oracle(cfg, missing_bin=True).set_dense(X).set_label(labels)
+    model = arboretum.Garden(cfg)
+    model.data = data
+    model.labels_count = data.labels_count
+    K = cfg["tree"].get("labels_count", 1)
+    depth = cfg["tree"]["max_depth"]
+    ambiguous = 0
+    for r in range(rounds):
+        model.grow_tree()
+        o.grow(1)
+        if K > 1:
+            continue  # per-level records exist for the last tree of a round only
+        diverged = False
+        for l in range(depth):
+            g = model.level_stats(l)
+            e = o.level(o.num_trees() - 1, l)
+            if l > 0 and not diverged:
+                assert (g["node_begin"] == e["node_begin"]).all(), (r, l)
+            for i in range(1 << l):
+                if diverged:
+                    break
+                same = (g["fid"][i] == e["fid"][i]) and (g["bin"][i] == e["bin"][i] or e["fid"][i] < 0)
+                if not same:
+                    gap = abs(e["gain"][i] - max(e["gain2"][i], g["gain"][i])) / max(abs(e["gain"][i]), 1e-30)
+                    assert gap <= 10 * GAIN_GAP, (r, l, i, g["fid"][i], g["bin"][i], e["fid"][i], e["bin"][i], gap)
+                    ambiguous += 1
+                    diverged = True
+                else:
+                    scale = max(abs(e["tot_g"][i]), 1e-3)
+                    assert g["tot_g"][i] == pytest.approx(e["tot_g"][i], rel=HIST_RTOL, abs=HIST_RTOL * scale)
+                    assert g["gain"][i] == pytest.approx(e["gain"][i], rel=1e-4, abs=1e-6)
+        if diverged:
+            break
+    return model, data, o, ambiguous
+
+
+@pytest.mark.parametrize("kind,objective,n,depth,rounds", [
+    ("linear", 0, 20000, 6, 5), ("logistic", 1, 30000, 8, 5), ("logistic", 1, 5000, 4, 10),
+    ("linear", 0, 3000, 3, 8)])
+def test_training_matches_oracle(kind, objective, n, depth, rounds):
+    X, y = synth(kind, n, 28, seed=depth)
+    cfg = make_config(objective, depth)
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, rounds)
+    if ambiguous == 0:
+        pred = model.predict(data)
+        assert np.allclose(pred, o.predict(X), atol=PRED_ATOL, rtol=0)
+        assert np.allclose(model.train_yhat()[0], o.yhat()[0], atol=PRED_ATOL, rtol=0)
+        md, od = json.loads(model.dump())["model"], o.model_dict()
+        for a, b in zip(md, od):
+            assert a["nodes"] == b["nodes"]
+            assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
+
+
+def test_training_is_deterministic():
+    arboretum = arb()
+    X, y = synth("logistic", 40000, 28, seed=11)
+    cfg = make_config(1, 6)
+    dumps = []
+    for _ in range(2):
+        data = arboretum.DMatrix(X, y=y)
+        dumps.append(arboretum.train(cfg, data, 4).dump())
+    assert dumps[0] == dumps[1]
+
+
+def test_trick_and_no_trick_give_identical_trees():
+    arboretum = arb()
+    X, y = synth("logistic", 25000, 28, seed=5)
+    out = []
+    for trick in (True, False):
+        cfg = make_config(1, 6)
+        cfg["internals"]["use_hist_subtraction_trick"] = trick
+        out.append(json.loads(arboretum.train(cfg, arboretum.DMatrix(X, y=y), 3).dump())["model"])
+    assert out[0] == out[1]
+
+
+def test_colsample_follows_the_reference_rng():
+    X, y = synth("linear", 8000, 28, seed=3)
+    cfg = make_config(0, 4, colsample_bytree=0.5, colsample_bylevel=0.7)
+    cfg["internals"]["seed"] = 7
+    compare_with_oracle(cfg, X, y, 4)
+
+
+def test_missing_values_go_right():
+    arboretum = arb()
+    X, y = synth("linear", 6000, 8, seed=9)
+    X[np.random.default_rng(1).random(X.shape) < 0.2] = np.nan
+    cfg = make_config(0, 4)
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 3)
+    if ambiguous == 0:
+        assert np.allclose(model.predict(data), o.predict(X), atol=PRED_ATOL, rtol=0)
+
+
+def test_uint16_bins_training():
+    X, y = synth("logistic", 6000, 10, seed=21)
+    cfg = make_config(1, 4, hist_size=600)
+    compare_with_oracle(cfg, X, y, 3)
+
+
+def test_append_last_tree_and_get_y():
+    arboretum = arb()
+    X, y = synth("logistic", 4000, 12, seed=2)
+    cfg = make_config(1, 3)
+    data = arboretum.DMatrix(X, y=y)
+    ev = arboretum.DMatrix(X[:500])
+    model = arboretum.Garden(cfg)
+    model.data = data
+    for _ in range(3):
+        model.grow_tree()
+        model.append_last_tree(ev)
+    assert np.allclose(model.get_y(ev), model.predict(ev), atol=1e-6)
+
+
+def test_softmax_rounds_match_oracle():
+    rng = np.random.default_rng(4)
+    n, F, K = 6000, 10, 4
+    X = rng.normal(size=(n, F)).astype(np.float32)
+    labels = np.argmax(X @ rng.normal(size=(F, K)) + rng.gumbel(size=(n, K)), axis=1).astype(np.uint8)
+    cfg = make_config(3, 3, eta=0.2, labels_count=K)
+    model, data, o, _ = compare_with_oracle(cfg, X, None, 2, labels=labels)
+    pred = model.predict(data)
+    assert pred.shape == (n, K)
+    assert np.allclose(pred.sum(axis=1), 1.0, atol=1e-5)
+    assert np.allclose(pred, o.predict(X), atol=1e-3)
+
+
+def test_prebinned_input_equals_dense_input():
+    arboretum = arb()
+    X, y = synth("logistic", 8000, 12, seed=8)
+    cfg = make_config(1, 4)
+    dense = arboretum.DMatrix(X, y=y)
+    thr, size, bins = dense.quantize(255, True)
+    m1 = json.loads(arboretum.train(cfg, dense, 3).dump())["model"]
+    pre = arboretum.DMatrix(bins.astype(np.uint8), y=y, binned_hist_size=255)
+    m2 = json.loads(arboretum.train(cfg, pre, 3).dump())["model"]
+    for a, b in zip(m1, m2):
+        assert [n.get("fid") for n in a["nodes"]] == [n.get("fid") for n in b["nodes"]]
+        assert a["weights"] == b["weights"]
+
+
+def test_bad_calls_return_errors():
+    arboretum = arb()
+    X, y = synth("linear", 100, 4, seed=1)
+    with pytest.raises(arboretum.ArboretumError):
+        arboretum.train(make_config(0, 3, colsample_bytree=0.01), arboretum.DMatrix(X, y=y), 1)
+    with pytest.raises(arboretum.ArboretumError):
+        arboretum.train(make_config(0, 3), arboretum.DMatrix(X), 1)  # no labels
