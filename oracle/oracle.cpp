@@ -298,6 +298,7 @@ struct LevelStat {  // what the parity tests compare level by level
   std::vector<int> fid;
   std::vector<int> bin;
   std::vector<double> left_g, left_h, tot_g, tot_h;
+  std::vector<double> abs_g;  // sum |g| over the node's rows: scale of the tolerance
   std::vector<uint32_t> left_count;
 };
 
@@ -728,6 +729,9 @@ class Trainer : public TrainerBase {
         const S tot = psum[i + 1] - psum[i];
         st.tot_g[i] = gx(tot);
         st.tot_h[i] = gy(tot);
+        double ag = 0;
+        for (uint32_t p = pcount[i]; p < pcount[i + 1]; ++p) ag += std::fabs(gx(g[p]));
+        st.abs_g.push_back(ag);
         st.left_count[i] = best_count[i];
       }
       tstats.push_back(st);
@@ -972,7 +976,7 @@ void orc_get_tree(void *p, int t, int *fid, int *quantized, float *threshold,
 // per-level stats of tree t, level l (L = 1<<l entries; node_begin L+1)
 void orc_get_level(void *p, int t, int l, uint32_t *node_begin, float *gain, float *gain2,
                    int *fid, int *bin, double *left_g, double *left_h, double *tot_g,
-                   double *tot_h, uint32_t *left_count) {
+                   double *tot_h, uint32_t *left_count, double *abs_g) {
   Handle *h = static_cast<Handle *>(p);
   const LevelStat &s = h->trainer->stats[t][l];
   const int L = 1 << l;
@@ -987,6 +991,7 @@ void orc_get_level(void *p, int t, int l, uint32_t *node_begin, float *gain, flo
     tot_g[i] = s.tot_g[i];
     tot_h[i] = s.tot_h[i];
     left_count[i] = s.left_count[i];
+    abs_g[i] = s.abs_g[i];
   }
 }
 // histogram of (level, feature) of the last grown tree (needs orc_keep_hist)

@@ -94,7 +94,7 @@ def lib():
         L.orc_get_tree.restype = None
         L.orc_get_tree.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 4
         L.orc_get_level.restype = None
-        L.orc_get_level.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 10
+        L.orc_get_level.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 11
         L.orc_get_hist.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 3
         L.orc_get_yhat.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         L.orc_predict.restype = None
@@ -247,10 +247,11 @@ class Oracle(object):
                "gain": np.empty(L, dtype=np.float32), "gain2": np.empty(L, dtype=np.float32),
                "fid": np.empty(L, dtype=np.int32), "bin": np.empty(L, dtype=np.int32),
                "left_g": np.empty(L), "left_h": np.empty(L), "tot_g": np.empty(L),
-               "tot_h": np.empty(L), "left_count": np.empty(L, dtype=np.uint32)}
+               "tot_h": np.empty(L), "left_count": np.empty(L, dtype=np.uint32),
+               "abs_g": np.empty(L)}
         lib().orc_get_level(self.h, t, l, *[_p(out[k]) for k in
                                             ("node_begin", "gain", "gain2", "fid", "bin", "left_g",
-                                             "left_h", "tot_g", "tot_h", "left_count")])
+                                             "left_h", "tot_g", "tot_h", "left_count", "abs_g")])
         return out
 
     def hist(self, level, fid):
