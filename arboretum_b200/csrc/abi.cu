@@ -343,7 +343,7 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   ARB_CHECK(bin_bytes == 1 || bin_bytes == 2, "bin_bytes must be 1 or 2");
   ARB_CHECK(nrow > 0 && ncol > 0 && n_nodes > 0, "bad shape");
   ARB_CHECK(hist_size > 0 && hist_size < 2048 && (bin_bytes == 2 || hist_size < 256), "bad hist_size");
-  ARB_CHECK(quant_bits >= 10 && quant_bits <= 21, "quant_bits must be in [10, 21]");
+  ARB_CHECK(quant_bits >= 10 && quant_bits <= 20, "quant_bits must be in [10, 20]");
   const size_t n = size_t(nrow);
   Geometry geo;
   geo.pitch = DataMatrix::PitchFor(ncol, bin_bytes);
@@ -379,17 +379,29 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   host_scales(max_g, max_h, quant_bits, pair != 0, &q);
   d_qs.alloc(sizeof q);
   ARB_CUDA(cudaMemcpyAsync(d_qs.p, &q, sizeof q, cudaMemcpyHostToDevice, s));
+  launch_quantize_grads(d_grad.p, n, pair != 0, d_qs.as<QuantScale>(), s);
   const unsigned cap = 1u << (31 - quant_bits);
   std::vector<WorkItem> items;
-  for (int node = 0; node < n_nodes; ++node)
+  std::vector<int> first(n_nodes + 1, 0), ids(n_nodes);
+  for (int node = 0; node < n_nodes; ++node) {
+    first[node] = int(items.size());
+    ids[node] = node;
     for (unsigned b = node_begin[node]; b < node_begin[node + 1]; b += cap)
       items.push_back(WorkItem{b, std::min(cap, node_begin[node + 1] - b), node, 0});
+  }
+  first[n_nodes] = int(items.size());
   ARB_CHECK(!items.empty(), "no rows");
   const int n_items = int(items.size());
+  DevBuf d_first, d_ids, d_partials;
   d_items.alloc(items.size() * sizeof(WorkItem));
   d_nitems.alloc(sizeof(int));
+  d_first.alloc(first.size() * sizeof(int));
+  d_ids.alloc(ids.size() * sizeof(int));
+  d_partials.alloc(size_t(n_items) * geo.NT * 2 * kHistWords * sizeof(int));
   ARB_CUDA(cudaMemcpyAsync(d_items.p, items.data(), d_items.bytes, cudaMemcpyHostToDevice, s));
   ARB_CUDA(cudaMemcpyAsync(d_nitems.p, &n_items, sizeof(int), cudaMemcpyHostToDevice, s));
+  ARB_CUDA(cudaMemcpyAsync(d_first.p, first.data(), d_first.bytes, cudaMemcpyHostToDevice, s));
+  ARB_CUDA(cudaMemcpyAsync(d_ids.p, ids.data(), d_ids.bytes, cudaMemcpyHostToDevice, s));
   const size_t words = size_t(n_nodes) * geo.NT * kHistWords * 2;
   d_hist.alloc(words * sizeof(long long));
   HistLaunch h;
@@ -400,13 +412,21 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   h.items = d_items.as<WorkItem>();
   h.n_items = d_nitems.as<int>();
   h.max_items = n_items;
-  h.hist = d_hist.as<long long>();
-  h.qs = d_qs.as<QuantScale>();
+  h.partials = d_partials.as<int>();
+  ReduceLaunch rd;
+  rd.partials = d_partials.as<int>();
+  rd.item_first = d_first.as<int>();
+  rd.build_node = d_ids.as<int>();
+  rd.n_build = n_nodes;
+  rd.NT = geo.NT;
+  rd.level_hist = d_hist.as<long long>();
+  rd.parent_hist = nullptr;
+  rd.subtract = false;
+  rd.zero_sibling = false;
   if (reps > 0) {
     cudaEvent_t e0, e1;
     ARB_CUDA(cudaEventCreate(&e0));
     ARB_CUDA(cudaEventCreate(&e1));
-    ARB_CUDA(cudaMemsetAsync(d_hist.p, 0, d_hist.bytes, s));
     for (int i = 0; i < 3; ++i) launch_hist(h, s);
     ARB_CUDA(cudaEventRecord(e0, s));
     for (int i = 0; i < reps; ++i) launch_hist(h, s);
@@ -418,8 +438,8 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
   }
-  ARB_CUDA(cudaMemsetAsync(d_hist.p, 0, d_hist.bytes, s));
   launch_hist(h, s);
+  launch_reduce(rd, s);
   std::vector<long long> host(words);
   ARB_CUDA(cudaMemcpyAsync(host.data(), d_hist.p, d_hist.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaStreamSynchronize(s));

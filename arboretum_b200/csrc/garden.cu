@@ -116,7 +116,7 @@ class Builder {
 
   DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_flags_, d_node_begin_, d_rec_, d_hist_[2],
     d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_item_left_;
-  DevBuf d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
+  DevBuf d_partials_, d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
   PlanBuffers pb_;
   cudaEvent_t ev_[2 * 8 * kMaxLevels];
@@ -159,9 +159,9 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   geo_.NT = (F_ + geo_.TW - 1) / geo_.TW;
 
   const int qb = cfg.internal.quant_bits;
-  ARB_CHECK(qb >= 10 && qb <= 21, "internals.quant_bits must be in [10, 21]");
+  ARB_CHECK(qb >= 10 && qb <= 20, "internals.quant_bits must be in [10, 20]");
   item_cap_ = 1 << (31 - qb);
-  max_hist_items_ = int(n_ / 1024) + max_nodes_ + 1;
+  max_hist_items_ = int(n_ / kMinItemRows) + max_nodes_ + 1;
   max_part_items_ = int(n_ / kPartRows) + max_nodes_ + 1;
 
   gp_ = GainParams{tp.min_leaf_size, tp.min_child_weight, tp.gamma_absolute, tp.gamma_relative,
@@ -196,6 +196,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
   d_hist_[0].alloc(level_hist_bytes);
   d_hist_[1].alloc(level_hist_bytes);
+  d_partials_.alloc(size_t(max_hist_items_) * geo_.NT * 2 * kHistWords * sizeof(int));
   d_keys_.alloc(max_nodes_ * sizeof(unsigned long long));
   d_qs_.alloc(sizeof(QuantScale));
   ARB_CUDA(cudaMemsetAsync(d_qs_.p, 0, sizeof(QuantScale), s));
@@ -236,6 +237,7 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   launch_gradients(g_->cfg.objective, K_, n_, d_y_.as<float>(), d_label_.as<unsigned char>(),
                    d_yhat_.as<float>(), d_grad_.p, d_qs_.as<QuantScale>(), s);
   launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
+  launch_quantize_grads(d_grad_.p, n_ * K_, pair_, d_qs_.as<QuantScale>(), s);
   if (g_->profile) {
     ARB_CUDA(cudaEventRecord(ev_[1], s));
     ARB_CUDA(cudaEventSynchronize(ev_[1]));
@@ -302,14 +304,16 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     mark();
     // rows scanned this level: all at the root, at most half with the trick
     // (the hessian rule of multi-GPU runs has no such bound)
-    const bool half = l > 0 && use_trick && !by_hessian;
+    const bool trick_level = use_trick && l > 0;
+    const bool half = trick_level && !by_hessian;
     const size_t level_rows = half ? n_ / 2 + 1 : n_;
-    int item_rows = 1024;
-    while (item_rows < item_cap_ && size_t(item_rows) * 888 < level_rows) item_rows <<= 1;
+    const int n_build = trick_level ? L / 2 : L;
+    // items: about three per persistent CTA, at least 2048 rows, at most the int32 cap
+    const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo_.NT));
+    int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
     launch_plan_hist(node_begin(l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
                      pb_, max_hist_items_, s);
     long long *hist = d_hist_[l & 1].as<long long>();
-    ARB_CUDA(cudaMemsetAsync(hist, 0, size_t(L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
     mark();
     HistLaunch h;
     h.geo = geo_;
@@ -318,10 +322,20 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     h.pair = pair_;
     h.items = pb_.hist_items;
     h.n_items = pb_.n_hist_items;
-    h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + L + 1));
-    h.hist = hist;
-    h.qs = qs;
+    h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
+    h.partials = d_partials_.as<int>();
     launch_hist(h, s);
+    ReduceLaunch rd;
+    rd.partials = d_partials_.as<int>();
+    rd.item_first = pb_.hist_item_first;
+    rd.build_node = pb_.scratch_node;
+    rd.n_build = n_build;
+    rd.NT = geo_.NT;
+    rd.level_hist = hist;
+    rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
+    rd.subtract = trick_level && !g_->allreduce;
+    rd.zero_sibling = trick_level && g_->allreduce;
+    launch_reduce(rd, s);
     mark();
     if (g_->allreduce) {
       const size_t count = size_t(L) * geo_.NT * kHistWords * 2;
@@ -329,7 +343,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         throw std::runtime_error("histogram allreduce failed");
     }
     mark();
-    if (use_trick && l > 0)
+    if (trick_level && g_->allreduce)
       launch_subtract(hist, d_hist_[(l - 1) & 1].as<long long>(), pb_.built_child, L / 2, geo_.NT, s);
     mark();
     SplitLaunch sp;

@@ -3,147 +3,239 @@
 // and update_multi_node, :6-33).
 //
 // Design for sm_100a:
-//  * Gradients are turned into fixed-point integers per round (g_q, h_q), so a
-//    histogram is an exact integer sum: any CTA order, any number of GPUs and
-//    the sibling subtraction all give bit-identical results.
-//  * One CTA owns (work item = piece of one node's row list) x (tile of TW
-//    features).  Its private sub-histogram lives in shared memory as two int32
-//    planes G[bin][lane], H[bin][lane] with lane = feature inside the tile: a
-//    warp updates one row at a time, every lane a different feature, so the 32
-//    shared-memory atomics of a warp instruction always hit 32 different banks
-//    whatever the bin values are (no bank conflicts, no same-address conflicts,
-//    also for skewed or sorted columns).
-//  * Rows are fetched by row id, one 32-byte sector per row and tile (uint8 bins,
-//    TW = 32), staged per warp in shared memory and read back transposed.
-//  * A work item has at most 2^(31 - quant_bits) rows, so an int32 plane cannot
-//    overflow; the CTA then adds its plane to the level's int64 histogram in
-//    global memory with one red.global.add.u64 per non-zero word.
+//  * Gradients are fixed-point integers (g_q, h_q) for the whole round, so a
+//    histogram is an exact integer sum: any CTA order, any number of GPUs and the
+//    sibling subtraction all give bit-identical results.
+//  * A CTA owns (work item = piece of one node's row list) x (tile of TW features)
+//    and keeps a private sub-histogram in shared memory as two int32 planes
+//    G[bin][feature], H[bin][feature] (64 KB).  A work item has at most
+//    2^(31 - quant_bits) rows, so a plane cannot overflow.
+//  * uint8 fast path (TW = 32): rows are fetched by row id, one 32-byte sector per
+//    row, with cp.async straight into a per-warp ring of shared-memory stages
+//    (the next batches are in flight while the current one is consumed).  A warp
+//    consumes 4 rows per step: lane (q, m) reads one 32-bit word = features
+//    4m..4m+3 of row 4s+q, and in pass k updates feature 4m + ((k + q) & 3).  The
+//    32 lanes of every red.shared instruction therefore hit 32 different banks
+//    whatever the bin values are -- no bank conflicts, also for skewed or sorted
+//    columns -- at 2.5 shared-memory wavefronts per row.
+//  * The CTA stores its planes with plain coalesced stores; reduce_kernel then
+//    sums the planes of every built node into the level's int64 histogram and, in
+//    the same pass, derives the sibling as parent - built (the subtraction trick).
 #include "kernels.cuh"
 
 namespace arb {
 
 namespace {
 
-__device__ __forceinline__ void quantize(float g, float h, const float sg, const float sh, bool pair,
-                                         int &gq, int &hq) {
-  gq = __float2int_rn(g * sg);
-  hq = pair ? max(1, __float2int_rn(h * sh)) : 1;
+constexpr int kStages = 2;
+constexpr int kStageBytes = 1024 + 256;  // 32 rows x 32 B of bins, 32 x (g_q, h_q)
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+  const unsigned d = unsigned(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+// copies `bytes` (0 or SIZE) and zero-fills the rest of the SIZE-byte destination
+template <int SIZE>
+__device__ __forceinline__ void cp_async_zfill(void *dst, const void *src, int bytes) {
+  const unsigned d = unsigned(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(d), "l"(src), "n"(SIZE), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void red_shared(int *p, int v) {
+  const unsigned a = unsigned(__cvta_generic_to_shared(p));
+  asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ void flush_planes(const int *G, const int *H, long long *dst) {
-  for (int w = threadIdx.x; w < kHistWords; w += blockDim.x) {
-    const int g = G[w];
-    const int h = H[w];
-    if (g != 0) atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * w), (unsigned long long)(long long)g);
-    if (h != 0) atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * w + 1), (unsigned long long)(long long)h);
-  }
+// the CTA's two int32 planes -> partials[(item * NT + tile)][2][kHistWords]
+__device__ __forceinline__ void store_planes(const int *smem, int *dst) {
+  const int4 *src4 = reinterpret_cast<const int4 *>(smem);
+  int4 *dst4 = reinterpret_cast<int4 *>(dst);
+  for (int w = threadIdx.x; w < 2 * kHistWords / 4; w += blockDim.x) dst4[w] = src4[w];
 }
 
 // uint8 bins, 32 features per tile, 256 bins.
 template <bool PAIR, bool IDENT>
-__global__ void __launch_bounds__(kHistThreads, 3)
+__global__ void __launch_bounds__(kHistThreads, 2)
 hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
-               long long *__restrict__ hist, const QuantScale *__restrict__ qs) {
+               int *__restrict__ partials) {
   extern __shared__ __align__(16) int smem[];
   int *G = smem;
-  int *H = smem + kHistWords;
   constexpr int kWarps = kHistThreads / 32;
-  // per warp: 32 rows x 32 bytes of bins, then 32 x (g_q, h_q)
-  unsigned char *stage_bins = reinterpret_cast<unsigned char *>(smem + 2 * kHistWords);
-  int2 *stage_gh = reinterpret_cast<int2 *>(stage_bins + kWarps * 1024);
-
-  if (int(blockIdx.x) >= *n_items) return;
-  const WorkItem item = items[blockIdx.x];
+  unsigned char *stage0 = reinterpret_cast<unsigned char *>(smem + 2 * kHistWords);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char *my = stage0 + warp * kStages * kStageBytes;
   const int tile = blockIdx.y;
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-
-  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
-  __syncthreads();
-
-  const float sg = qs->sg, sh = qs->sh;
-  unsigned char *my_bins = stage_bins + warp * 1024;
-  int2 *my_gh = stage_gh + warp * 32;
   const unsigned char *tile_base = bins + size_t(tile) * 32;
-
-  for (unsigned base = warp * 32; base < item.len; base += kWarps * 32) {
-    const unsigned pos = base + lane;
-    const bool valid = pos < item.len;
-    uint4 a = make_uint4(0, 0, 0, 0), b = a;
-    int gq = 0, hq = 0;
-    if (valid) {
-      const unsigned rid = IDENT ? item.begin + pos : rowid[item.begin + pos];
-      const uint4 *src = reinterpret_cast<const uint4 *>(tile_base + size_t(rid) * pitch);
-      a = __ldg(src);
-      b = __ldg(src + 1);
-      if (PAIR) {
-        const float2 g = __ldg(reinterpret_cast<const float2 *>(grad) + rid);
-        quantize(g.x, g.y, sg, sh, true, gq, hq);
-      } else {
-        const float g = __ldg(reinterpret_cast<const float *>(grad) + rid);
-        quantize(g, 1.0f, sg, sh, false, gq, hq);
-      }
-    }
-    uint4 *dst = reinterpret_cast<uint4 *>(my_bins + lane * 32);
-    dst[0] = a;
-    dst[1] = b;
-    my_gh[lane] = make_int2(gq, hq);
-    __syncwarp();
-    const int nvalid = min(32u, item.len - base);
-#pragma unroll 4
-    for (int j = 0; j < nvalid; ++j) {
-      const int bin = my_bins[j * 32 + lane];
-      const int2 gh = my_gh[j];
-      atomicAdd(&G[bin * 32 + lane], gh.x);
-      atomicAdd(&H[bin * 32 + lane], gh.y);
-    }
-    __syncwarp();
+  const int q = lane >> 3, m = lane & 7;
+  int foff[4], sh[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = (k + q) & 3;
+    foff[k] = 4 * m + r;
+    sh[k] = 8 * r;
   }
-  __syncthreads();
-  flush_planes(G, H, hist + (size_t(item.node) * NT + tile) * kHistWords * 2);
+  constexpr int GSZ = PAIR ? 8 : 4;  // bytes of one quantised gradient record
+  const int total_items = *n_items;
+
+  for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
+    const WorkItem item = items[it];
+    for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+    __syncthreads();
+    const unsigned len = item.len;
+    const int nb = int((len + 31) / 32);  // batches of 32 rows, dealt round-robin to warps
+
+    auto rid_of = [&](int b) -> unsigned {
+      const unsigned pos = min(unsigned(b * 32 + lane), len - 1);
+      return IDENT ? item.begin + pos : __ldg(rowid + item.begin + pos);
+    };
+    auto issue = [&](int b, int stage, unsigned rid_lane) {
+      unsigned char *sb = my + stage * kStageBytes;
+      // bins: lane handles half (lane & 1) of rows (lane >> 1) and 16 + (lane >> 1)
+      const unsigned r0 = __shfl_sync(0xffffffffu, rid_lane, lane >> 1);
+      const unsigned r1 = __shfl_sync(0xffffffffu, rid_lane, 16 + (lane >> 1));
+      cp_async16(sb + (lane >> 1) * 32 + (lane & 1) * 16,
+                 tile_base + size_t(r0) * pitch + (lane & 1) * 16);
+      cp_async16(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
+                 tile_base + size_t(r1) * pitch + (lane & 1) * 16);
+      // rows past the end of the item get a zero gradient record: they add nothing
+      const bool valid = unsigned(b * 32 + lane) < len;
+      cp_async_zfill<GSZ>(sb + 1024 + lane * GSZ, static_cast<const char *>(grad) + size_t(rid_lane) * GSZ,
+                          valid ? GSZ : 0);
+      cp_async_commit();
+    };
+
+    int b_issue = warp;
+    unsigned rid_next = 0;
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      if (b_issue < nb) issue(b_issue, s, rid_of(b_issue)); else cp_async_commit();
+      b_issue += kWarps;
+    }
+    if (b_issue < nb) rid_next = rid_of(b_issue);
+    int stage = 0;
+    for (int b = warp; b < nb; b += kWarps) {
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      const unsigned char *sb = my + stage * kStageBytes;
+      const int nvalid = int(min(32u, len - unsigned(b) * 32));
+#pragma unroll 2
+      for (int s = 0; s < 8; ++s) {
+        const int row = 4 * s + q;
+        const unsigned wv = *reinterpret_cast<const unsigned *>(sb + row * 32 + 4 * m);
+        int gq, hq;
+        if (PAIR) {
+          const int2 gh = *reinterpret_cast<const int2 *>(sb + 1024 + row * 8);
+          gq = gh.x;
+          hq = gh.y;
+        } else {
+          gq = *reinterpret_cast<const int *>(sb + 1024 + row * 4);
+          hq = row < nvalid;  // hessian == 1: the plane counts rows
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int bin = (wv >> sh[k]) & 255;
+          int *p = G + bin * 32 + foff[k];
+          red_shared(p, gq);
+          red_shared(p + kHistWords, hq);
+        }
+      }
+      __syncwarp();
+      if (b_issue < nb) {
+        const unsigned rid_c = rid_next;
+        const int bn = b_issue + kWarps;
+        if (bn < nb) rid_next = rid_of(bn);
+        issue(b_issue, stage, rid_c);
+      } else {
+        cp_async_commit();
+      }
+      b_issue += kWarps;
+      stage = (stage + 1 == kStages) ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    store_planes(smem, partials + (size_t(it) * NT + tile) * 2 * kHistWords);
+    __syncthreads();
+  }
 }
 
-// Any bin width / tile width: lane = (row in group, feature in tile).
+// Any bin width / tile width: thread = (row in group, feature in tile).
 template <bool PAIR, bool IDENT, typename BIN_T>
-__global__ void __launch_bounds__(kHistThreads, 3)
+__global__ void __launch_bounds__(kHistThreads, 2)
 hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                     const int TW, const int F, const unsigned *__restrict__ rowid,
                     const void *__restrict__ grad, const WorkItem *__restrict__ items,
-                    const int *__restrict__ n_items, long long *__restrict__ hist,
-                    const QuantScale *__restrict__ qs) {
+                    const int *__restrict__ n_items, int *__restrict__ partials) {
   extern __shared__ __align__(16) int smem[];
   int *G = smem;
   int *H = smem + kHistWords;
-  if (int(blockIdx.x) >= *n_items) return;
-  const WorkItem item = items[blockIdx.x];
   const int tile = blockIdx.y;
-  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
-  __syncthreads();
-  const float sg = qs->sg, sh = qs->sh;
   const int rows_per_pass = kHistThreads / TW;
   const int f_in_tile = threadIdx.x % TW;
   const int rsub = threadIdx.x / TW;
   const int f = tile * TW + f_in_tile;
-  if (f < F) {
-    for (unsigned pos = rsub; pos < item.len; pos += rows_per_pass) {
-      const unsigned rid = IDENT ? item.begin + pos : rowid[item.begin + pos];
-      const BIN_T bin = reinterpret_cast<const BIN_T *>(bins + size_t(rid) * pitch)[f];
-      int gq, hq;
-      if (PAIR) {
-        const float2 g = __ldg(reinterpret_cast<const float2 *>(grad) + rid);
-        quantize(g.x, g.y, sg, sh, true, gq, hq);
-      } else {
-        const float g = __ldg(reinterpret_cast<const float *>(grad) + rid);
-        quantize(g, 1.0f, sg, sh, false, gq, hq);
+  const int total_items = *n_items;
+  for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
+    const WorkItem item = items[it];
+    for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+    __syncthreads();
+    if (f < F) {
+      for (unsigned pos = rsub; pos < item.len; pos += rows_per_pass) {
+        const unsigned rid = IDENT ? item.begin + pos : rowid[item.begin + pos];
+        const BIN_T bin = reinterpret_cast<const BIN_T *>(bins + size_t(rid) * pitch)[f];
+        int gq, hq;
+        if (PAIR) {
+          const int2 g = __ldg(reinterpret_cast<const int2 *>(grad) + rid);
+          gq = g.x;
+          hq = g.y;
+        } else {
+          gq = __ldg(reinterpret_cast<const int *>(grad) + rid);
+          hq = 1;
+        }
+        red_shared(&G[int(bin) * TW + f_in_tile], gq);
+        red_shared(&H[int(bin) * TW + f_in_tile], hq);
       }
-      atomicAdd(&G[int(bin) * TW + f_in_tile], gq);
-      atomicAdd(&H[int(bin) * TW + f_in_tile], hq);
     }
+    __syncthreads();
+    store_planes(smem, partials + (size_t(it) * NT + tile) * 2 * kHistWords);
+    __syncthreads();
   }
-  __syncthreads();
-  flush_planes(G, H, hist + (size_t(item.node) * NT + tile) * kHistWords * 2);
+}
+
+// One thread per (built node, tile, word): sums the planes of the node's items
+// into the level's int64 histogram; with SUBTRACT the other child of the same
+// parent is written as parent - built (update_multi_node of the reference).
+template <bool SUBTRACT>
+__global__ void reduce_kernel(const int *__restrict__ partials, const int *__restrict__ item_first,
+                              const int *__restrict__ build_node, long long *__restrict__ level_hist,
+                              const long long *__restrict__ parent_hist, const int NT,
+                              const bool zero_sibling) {
+  const int b = blockIdx.z, tile = blockIdx.y;
+  const int w = blockIdx.x * blockDim.x + threadIdx.x;
+  const int first = item_first[b], last = item_first[b + 1];
+  long long g = 0, h = 0;
+  for (int it = first; it < last; ++it) {
+    const int *p = partials + (size_t(it) * NT + tile) * 2 * kHistWords;
+    g += p[w];
+    h += p[kHistWords + w];
+  }
+  const int node = build_node[b];
+  const size_t off = (size_t(node) * NT + tile) * kHistWords + w;
+  reinterpret_cast<longlong2 *>(level_hist)[off] = make_longlong2(g, h);
+  if (SUBTRACT) {
+    const size_t poff = (size_t(node >> 1) * NT + tile) * kHistWords + w;
+    const longlong2 pv = reinterpret_cast<const longlong2 *>(parent_hist)[poff];
+    const size_t soff = (size_t(node ^ 1) * NT + tile) * kHistWords + w;
+    reinterpret_cast<longlong2 *>(level_hist)[soff] = make_longlong2(pv.x - g, pv.y - h);
+  } else if (zero_sibling) {
+    const size_t soff = (size_t(node ^ 1) * NT + tile) * kHistWords + w;
+    reinterpret_cast<longlong2 *>(level_hist)[soff] = make_longlong2(0, 0);
+  }
 }
 
 __global__ void subtract_kernel(long long *__restrict__ level_hist,
@@ -174,18 +266,24 @@ __global__ void subtract_kernel(long long *__restrict__ level_hist,
 
 }  // namespace
 
+int hist_grid_x(int max_items, int NT) {
+  // persistent CTAs: two per SM over all tiles
+  const int per_tile = std::max(8, (2 * 148 + NT - 1) / NT);
+  return std::max(1, std::min(max_items, per_tile));
+}
+
 void launch_hist(const HistLaunch &a, cudaStream_t s) {
   const Geometry &g = a.geo;
-  const dim3 grid(a.max_items, g.NT);
+  const dim3 grid(hist_grid_x(a.max_items, g.NT), g.NT);
   const bool ident = a.rowid == nullptr;
   if (g.bin_bytes == 1 && g.TW == 32) {
-    const size_t smem = 2 * kHistWords * 4 + (kHistThreads / 32) * (1024 + 256);
-#define ARB_LAUNCH(P, I)                                                                       \
-  do {                                                                                         \
-    ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                                    \
-    hist_u8_kernel<P, I><<<grid, kHistThreads, smem, s>>>(g.bins, g.pitch, g.NT, a.rowid,      \
-                                                          a.grad, a.items, a.n_items, a.hist,  \
-                                                          a.qs);                               \
+    const size_t smem = 2 * kHistWords * 4 + (kHistThreads / 32) * kStages * kStageBytes;
+#define ARB_LAUNCH(P, I)                                                                      \
+  do {                                                                                        \
+    ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                               \
+    hist_u8_kernel<P, I><<<grid, kHistThreads, smem, s>>>(g.bins, g.pitch, g.NT, a.rowid,     \
+                                                          a.grad, a.items, a.n_items,         \
+                                                          a.partials);                        \
   } while (0)
     if (a.pair) {
       if (ident) ARB_LAUNCH(true, true); else ARB_LAUNCH(true, false);
@@ -195,24 +293,37 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
 #undef ARB_LAUNCH
   } else {
     const size_t smem = 2 * kHistWords * 4;
-#define ARB_LAUNCH(P, I, T)                                                                    \
-  do {                                                                                         \
-    ARB_SET_SMEM((hist_generic_kernel<P, I, T>), smem);                                            \
-    hist_generic_kernel<P, I, T><<<grid, kHistThreads, smem, s>>>(                             \
-      g.bins, g.pitch, g.NT, g.TW, g.F, a.rowid, a.grad, a.items, a.n_items, a.hist, a.qs);    \
+#define ARB_LAUNCH(P, I, T)                                                                   \
+  do {                                                                                        \
+    ARB_SET_SMEM((hist_generic_kernel<P, I, T>), smem);                                       \
+    hist_generic_kernel<P, I, T><<<grid, kHistThreads, smem, s>>>(                            \
+      g.bins, g.pitch, g.NT, g.TW, g.F, a.rowid, a.grad, a.items, a.n_items, a.partials);     \
   } while (0)
-#define ARB_LAUNCH_T(T)                                                    \
-  do {                                                                     \
-    if (a.pair) {                                                          \
+#define ARB_LAUNCH_T(T)                                                        \
+  do {                                                                         \
+    if (a.pair) {                                                              \
       if (ident) ARB_LAUNCH(true, true, T); else ARB_LAUNCH(true, false, T);   \
-    } else {                                                               \
+    } else {                                                                   \
       if (ident) ARB_LAUNCH(false, true, T); else ARB_LAUNCH(false, false, T); \
-    }                                                                      \
+    }                                                                          \
   } while (0)
     if (g.bin_bytes == 1) ARB_LAUNCH_T(unsigned char); else ARB_LAUNCH_T(unsigned short);
 #undef ARB_LAUNCH_T
 #undef ARB_LAUNCH
   }
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
+  const int threads = 256;
+  const dim3 grid(kHistWords / threads, a.NT, a.n_build);
+  if (a.subtract)
+    reduce_kernel<true><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node, a.level_hist,
+                                                 a.parent_hist, a.NT, false);
+  else
+    reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
+                                                  a.level_hist, nullptr, a.NT, a.zero_sibling);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

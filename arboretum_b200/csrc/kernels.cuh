@@ -14,6 +14,7 @@ constexpr int kHistThreads = 256;     // threads of a histogram CTA
 constexpr int kPartRows = 2048;       // rows of one partition work item
 constexpr int kPartThreads = 256;
 constexpr int kMaxLevels = 16;
+constexpr int kMinItemRows = 2048;    // smallest piece a node's row list is cut into
 
 // Geometry of the binned matrix and of the histograms built from it.
 //   bins : row-major, `pitch` bytes per row, feature f of row r at
@@ -32,15 +33,29 @@ struct Geometry {
 struct HistLaunch {
   Geometry geo;
   const unsigned *rowid;  // nullptr: positions are row ids (root level)
-  const void *grad;       // float2[N] (pair) or float[N]
+  const void *grad;       // quantised gradients: int2[N] (pair) or int[N]
   bool pair;
-  const WorkItem *items;
+  const WorkItem *items;  // every item has at most 2^(31 - quant_bits) rows
   const int *n_items;
   int max_items;
-  long long *hist;  // level buffer
-  const QuantScale *qs;
+  int *partials;  // [item][tile][2][kHistWords] int32 planes, written here
 };
 void launch_hist(const HistLaunch &a, cudaStream_t s);
+int hist_grid_x(int max_items, int NT);
+
+// planes of the items of every built node -> the level's int64 histogram
+struct ReduceLaunch {
+  const int *partials;
+  const int *item_first;  // n_build + 1: items of built node b are [first[b], first[b+1])
+  const int *build_node;  // node index (inside the level) of built node b
+  int n_build;
+  int NT;
+  long long *level_hist;
+  const long long *parent_hist;  // level above, for the subtraction
+  bool subtract;      // also write sibling = parent - built
+  bool zero_sibling;  // (no subtract) clear the sibling so the buffer can be all-reduced
+};
+void launch_reduce(const ReduceLaunch &a, cudaStream_t s);
 
 // sibling = parent - built child, for every parent of the level above
 void launch_subtract(long long *level_hist, const long long *parent_hist, const int *built_child,
@@ -103,6 +118,8 @@ void launch_partition(const PartitionLaunch &a, cudaStream_t s);
 void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
                       const float *yhat, void *grad, QuantScale *qs, cudaStream_t s);
 void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s);
+// float gradients -> fixed-point integers, in place (g_q = rint(g * sg), h_q = max(1, rint(h * sh)))
+void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, cudaStream_t s);
 
 struct LeafLaunch {
   const NodeRec *last_rec;

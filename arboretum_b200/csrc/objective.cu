@@ -86,6 +86,23 @@ __global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) 
   }
 }
 
+__global__ void quantize_pair_kernel(float2 *grad, size_t n, const QuantScale *__restrict__ qs) {
+  const float sg = qs->sg, sh = qs->sh;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const float2 g = grad[i];
+    // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
+    reinterpret_cast<int2 *>(grad)[i] = make_int2(__float2int_rn(g.x * sg), max(1, __float2int_rn(g.y * sh)));
+  }
+}
+
+__global__ void quantize_single_kernel(float *grad, size_t n, const QuantScale *__restrict__ qs) {
+  const float sg = qs->sg;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    reinterpret_cast<int *>(grad)[i] = __float2int_rn(grad[i] * sg);
+}
+
 template <bool PAIR>
 __global__ void leaf_weights_kernel(LeafLaunch a) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
@@ -193,6 +210,16 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
 void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s) {
   (void)K;
   finish_scales_kernel<<<1, 1, 0, s>>>(qs, quant_bits, pair);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, cudaStream_t s) {
+  const int threads = 256;
+  if (pair)
+    quantize_pair_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n, qs);
+  else
+    quantize_single_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float *>(grad), n, qs);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
