@@ -423,6 +423,8 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   rd.parent_hist = nullptr;
   rd.subtract = false;
   rd.zero_sibling = false;
+  rd.level_nodes = n_nodes;
+  rd.built_child = nullptr;
   if (reps > 0) {
     cudaEvent_t e0, e1;
     ARB_CUDA(cudaEventCreate(&e0));

@@ -114,8 +114,8 @@ class Builder {
   std::vector<unsigned char> active_host_;
   GainParams gp_;
 
-  DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_flags_, d_node_begin_, d_rec_, d_hist_[2],
-    d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_item_left_;
+  DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_node_begin_, d_rec_, d_hist_[2],
+    d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_cursors_;
   DevBuf d_partials_, d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
   PlanBuffers pb_;
@@ -185,7 +185,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
   d_rowid_[0].alloc(n_ * sizeof(unsigned));
   d_rowid_[1].alloc(n_ * sizeof(unsigned));
-  d_flags_.alloc(n_);
   // level state
   d_node_begin_.alloc(size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
   ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
@@ -197,14 +196,14 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_hist_[0].alloc(level_hist_bytes);
   d_hist_[1].alloc(level_hist_bytes);
   d_partials_.alloc(size_t(max_hist_items_) * geo_.NT * 2 * kHistWords * sizeof(int));
-  d_keys_.alloc(max_nodes_ * sizeof(unsigned long long));
+  d_keys_.alloc(max_nodes_ * (sizeof(unsigned long long) + sizeof(unsigned)));
   d_qs_.alloc(sizeof(QuantScale));
   ARB_CUDA(cudaMemsetAsync(d_qs_.p, 0, sizeof(QuantScale), s));
   d_leaf_w_.alloc(2 * max_nodes_ * sizeof(float));
   d_active_.alloc(size_t(levels_) * F_);
   d_fsize_.alloc(F_ * sizeof(int));
   ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
-  d_item_left_.alloc(max_part_items_ * sizeof(unsigned));
+  d_cursors_.alloc(2 * size_t(max_nodes_) * sizeof(unsigned));
   d_part_items_.alloc(max_part_items_ * sizeof(WorkItem));
   d_hist_items_.alloc(max_hist_items_ * sizeof(WorkItem));
   d_counters_.alloc(2 * sizeof(int));
@@ -290,8 +289,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       p.geo = geo_;
       p.rowid_src = (l - 1 == 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>();
       p.rowid_dst = d_rowid_[l & 1].as<unsigned>();
-      p.flags = d_flags_.as<unsigned char>();
-      p.item_left = d_item_left_.as<unsigned>();
+      p.cursors = d_cursors_.as<unsigned>();
       p.node_begin = node_begin(l - 1);
       p.node_begin_next = node_begin(l);
       p.rec = rec(l - 1);
@@ -335,6 +333,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
     rd.subtract = trick_level && !g_->allreduce;
     rd.zero_sibling = trick_level && g_->allreduce;
+    rd.level_nodes = L;
+    rd.built_child = pb_.built_child;
     launch_reduce(rd, s);
     mark();
     if (g_->allreduce) {
@@ -353,6 +353,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     sp.feature_active = d_active_.as<unsigned char>() + size_t(l) * F_;
     sp.feature_size = d_fsize_.as<int>();
     sp.keys = d_keys_.as<unsigned long long>();
+    sp.max_nodes = max_nodes_;
     sp.rec = rec(l);
     sp.parent_rec = l > 0 ? rec(l - 1) : nullptr;
     sp.qs = qs;

@@ -207,25 +207,34 @@ hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, 
   }
 }
 
-// One thread per (built node, tile, word): sums the planes of the node's items
-// into the level's int64 histogram; with SUBTRACT the other child of the same
-// parent is written as parent - built (update_multi_node of the reference).
+// One thread per (built node, slice, tile, word): sums the planes of its share of
+// the node's items.  With one slice per node the sum goes straight into the
+// level's int64 histogram and, with SUBTRACT, the other child of the same parent
+// is written as parent - built (update_multi_node of the reference); with more
+// slices (few, large nodes) the sums meet in red.global.add.u64 on a cleared
+// buffer and the subtraction runs as its own pass.
 template <bool SUBTRACT>
 __global__ void reduce_kernel(const int *__restrict__ partials, const int *__restrict__ item_first,
                               const int *__restrict__ build_node, long long *__restrict__ level_hist,
                               const long long *__restrict__ parent_hist, const int NT,
-                              const bool zero_sibling) {
-  const int b = blockIdx.z, tile = blockIdx.y;
+                              const int slices, const bool zero_sibling) {
+  const int b = blockIdx.z / slices, slice = blockIdx.z - b * slices, tile = blockIdx.y;
   const int w = blockIdx.x * blockDim.x + threadIdx.x;
   const int first = item_first[b], last = item_first[b + 1];
   long long g = 0, h = 0;
-  for (int it = first; it < last; ++it) {
+#pragma unroll 4
+  for (int it = first + slice; it < last; it += slices) {
     const int *p = partials + (size_t(it) * NT + tile) * 2 * kHistWords;
     g += p[w];
     h += p[kHistWords + w];
   }
   const int node = build_node[b];
   const size_t off = (size_t(node) * NT + tile) * kHistWords + w;
+  if (slices > 1) {
+    if (g) atomicAdd(reinterpret_cast<unsigned long long *>(level_hist) + 2 * off, (unsigned long long)g);
+    if (h) atomicAdd(reinterpret_cast<unsigned long long *>(level_hist) + 2 * off + 1, (unsigned long long)h);
+    return;
+  }
   reinterpret_cast<longlong2 *>(level_hist)[off] = make_longlong2(g, h);
   if (SUBTRACT) {
     const size_t poff = (size_t(node >> 1) * NT + tile) * kHistWords + w;
@@ -265,6 +274,9 @@ __global__ void subtract_kernel(long long *__restrict__ level_hist,
   } while (0)
 
 }  // namespace
+
+void launch_subtract(long long *level_hist, const long long *parent_hist, const int *built_child,
+                     int n_parents, int NT, cudaStream_t s);
 
 int hist_grid_x(int max_items, int NT) {
   // persistent CTAs: two per SM over all tiles
@@ -317,13 +329,26 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
 
 void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   const int threads = 256;
-  const dim3 grid(kHistWords / threads, a.NT, a.n_build);
+  // few built nodes: cut every node's item list into slices so the GPU is filled
+  int slices = 1;
+  while (slices < 64 && a.n_build * a.NT * slices < 64) slices <<= 1;
+  const dim3 grid(kHistWords / threads, a.NT, a.n_build * slices);
+  if (slices > 1) {
+    const size_t bytes = size_t(a.level_nodes) * a.NT * kHistWords * 2 * sizeof(long long);
+    ARB_CUDA(cudaMemsetAsync(a.level_hist, 0, bytes, s));
+    reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
+                                                  a.level_hist, nullptr, a.NT, slices, false);
+    ARB_CUDA(cudaGetLastError());
+    count_launch();
+    if (a.subtract) launch_subtract(a.level_hist, a.parent_hist, a.built_child, a.level_nodes / 2, a.NT, s);
+    return;
+  }
   if (a.subtract)
     reduce_kernel<true><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node, a.level_hist,
-                                                 a.parent_hist, a.NT, false);
+                                                 a.parent_hist, a.NT, 1, false);
   else
     reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, a.zero_sibling);
+                                                  a.level_hist, nullptr, a.NT, 1, a.zero_sibling);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

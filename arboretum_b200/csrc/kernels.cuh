@@ -54,6 +54,8 @@ struct ReduceLaunch {
   const long long *parent_hist;  // level above, for the subtraction
   bool subtract;      // also write sibling = parent - built
   bool zero_sibling;  // (no subtract) clear the sibling so the buffer can be all-reduced
+  int level_nodes;    // nodes of the level (size of level_hist)
+  const int *built_child;  // per parent: which child was built (for the subtraction)
 };
 void launch_reduce(const ReduceLaunch &a, cudaStream_t s);
 
@@ -67,7 +69,9 @@ struct SplitLaunch {
   const unsigned *node_begin;  // L+1 prefix counts of this level
   const unsigned char *feature_active;  // F flags: evaluated at this level
   const int *feature_size;     // bins in use per feature
-  unsigned long long *keys;    // L packed (gain, feature, bin) maxima, zeroed here
+  unsigned long long *keys;    // max_nodes packed (gain, feature, bin) maxima followed by
+                               // max_nodes u32 arrival counters; zeroed here
+  int max_nodes;
   NodeRec *rec;                // L records out
   const NodeRec *parent_rec;   // level above (nullptr at the root)
   const QuantScale *qs;
@@ -101,8 +105,7 @@ struct PartitionLaunch {
   Geometry geo;
   const unsigned *rowid_src;  // nullptr: identity (root)
   unsigned *rowid_dst;
-  unsigned char *flags;       // N scratch bytes
-  unsigned *item_left;        // per item: lefts, then exclusive prefix inside node
+  unsigned *cursors;          // 2 per node: rows placed so far in the left / right child
   const unsigned *node_begin; // level L prefix counts
   unsigned *node_begin_next;  // 2L+1 prefix counts out
   NodeRec *rec;               // split records of the level (left_count filled)

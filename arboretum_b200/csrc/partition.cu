@@ -6,9 +6,9 @@
 // The binned matrix never moves.  Each level keeps a list of row ids grouped by
 // node (`node_begin` are the prefix counts, like parent_node_count in the
 // reference) and a level step splits every node's piece of the list into its two
-// children with a stable partition: rows whose bin of the split feature is
-// <= the split bin go left (builder.h:113-120), both sides keep their order, so
-// row ids stay ascending inside every node and gathers stay local.  The
+// children: rows whose bin of the split feature is <= the split bin go left
+// (builder.h:113-120); inside every 2048-row piece both sides keep their order,
+// so row ids stay ascending in long runs and gathers stay local.  The
 // observable contract of the reference -- per-level node row counts and the leaf
 // every row ends in -- is the same; its physical order (rights reversed) is not
 // observable and is not reproduced.
@@ -99,138 +99,102 @@ __global__ void plan_hist_kernel(const unsigned *__restrict__ node_begin,
   make_items(sb, sl, sn, n_build, item_rows, first, pb.hist_items, pb.n_hist_items, max_items);
 }
 
-__device__ __forceinline__ int block_exclusive_scan(int v, int *warp_sums, int &total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int incl = v;
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) warp_sums[warp] = incl;
-  __syncthreads();
-  int off = 0, tot = 0;
-  for (int w = 0; w < kPartThreads / 32; ++w) {
-    const int s = warp_sums[w];
-    if (w < warp) off += s;
-    tot += s;
-  }
-  total = tot;
-  __syncthreads();
-  return off + incl - v;
-}
-
-// pass 1: decision flag of every row and the number of lefts of every item
+// One pass per level: every CTA takes one item (a piece of one node's row list),
+// decides left / right for its rows (left <=> bin of the split feature <= split
+// bin, builder.h:113-120), orders them in shared memory (lefts first, both sides
+// in list order) and reserves room in the two children with one atomicAdd per
+// side: lefts grow upwards from the node's begin, rights downwards from its end,
+// so both children are contiguous without knowing their sizes in advance.  The
+// order of the items inside a child depends on scheduling; nothing observable
+// does, because every sum over rows is an exact integer sum.
 template <typename BIN_T>
 __global__ void __launch_bounds__(kPartThreads)
-partition_count_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
-                       const unsigned *__restrict__ rowid, unsigned char *__restrict__ flags,
-                       unsigned *__restrict__ item_left, const NodeRec *__restrict__ rec,
-                       const WorkItem *__restrict__ items, const int *__restrict__ n_items) {
-  __shared__ int warp_sums[kPartThreads / 32];
+partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
+                 const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
+                 const NodeRec *__restrict__ rec, const unsigned *__restrict__ node_begin,
+                 unsigned *__restrict__ cursors, const WorkItem *__restrict__ items,
+                 const int *__restrict__ n_items) {
+  constexpr int kWarps = kPartThreads / 32;
+  __shared__ unsigned buf[kPartRows];
+  __shared__ int cnt[kRowsPerThread * kWarps];
+  __shared__ int pre[kRowsPerThread * kWarps + 1];
+  __shared__ unsigned base_l, base_r;
   if (int(blockIdx.x) >= *n_items) return;
   const WorkItem item = items[blockIdx.x];
   const int fid = rec[item.node].fid;
   const int split_bin = rec[item.node].bin;
-  int lefts = 0;
-  const unsigned t0 = threadIdx.x * kRowsPerThread;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned rid[kRowsPerThread];
+  int before[kRowsPerThread];  // lefts before this element inside its warp round
+  unsigned left_bits = 0;
 #pragma unroll
   for (int k = 0; k < kRowsPerThread; ++k) {
-    const unsigned off = t0 + k;
-    if (off < item.len) {
-      const unsigned pos = item.begin + off;
-      unsigned char right = 0;
-      if (fid >= 0) {
-        const unsigned rid = rowid ? rowid[pos] : pos;
-        const int b = reinterpret_cast<const BIN_T *>(bins + size_t(rid) * pitch)[fid];
-        right = b > split_bin;
-      }
-      flags[pos] = right;
-      lefts += !right;
+    const unsigned off = k * kPartThreads + threadIdx.x;
+    const bool valid = off < item.len;
+    rid[k] = 0;
+    bool left = false;
+    if (valid) {
+      rid[k] = rowid_src ? rowid_src[item.begin + off] : item.begin + off;
+      left = true;
+      if (fid >= 0) left = int(reinterpret_cast<const BIN_T *>(bins + size_t(rid[k]) * pitch)[fid]) <= split_bin;
     }
+    const unsigned bal = __ballot_sync(0xffffffffu, left);
+    before[k] = __popc(bal & ((1u << lane) - 1));
+    if (lane == 0) cnt[k * kWarps + warp] = __popc(bal);
+    left_bits |= unsigned(left) << k;
   }
-  for (int o = 16; o > 0; o >>= 1) lefts += __shfl_down_sync(0xffffffffu, lefts, o);
-  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = lefts;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int s = 0;
-    for (int w = 0; w < kPartThreads / 32; ++w) s += warp_sums[w];
-    item_left[blockIdx.x] = s;
-  }
-}
-
-// pass 2: one warp per node turns item counts into offsets and writes the next
-// level's prefix counts (count_next[2n+1] = left end, [2n+2] = node end:
-// hist_tree_grower.cu:80-83)
-__global__ void partition_scan_kernel(unsigned *__restrict__ item_left,
-                                      const int *__restrict__ item_first,
-                                      const unsigned *__restrict__ node_begin,
-                                      unsigned *__restrict__ node_begin_next,
-                                      NodeRec *__restrict__ rec, int L) {
-  const int node = blockIdx.x;
-  const int lane = threadIdx.x;
-  unsigned carry = 0;
-  const int first = item_first[node], last = item_first[node + 1];
-  for (int base = first; base < last; base += 32) {
-    const int i = base + lane;
-    const unsigned v = i < last ? item_left[i] : 0u;
-    unsigned incl = v;
+  if (warp == 0) {  // exclusive scan of the 64 (round, warp) counts
+    constexpr int kN = kRowsPerThread * kWarps;
+    const int a = cnt[2 * lane], b = cnt[2 * lane + 1];
+    int incl = a + b;
     for (int o = 1; o < 32; o <<= 1) {
-      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += t;
     }
-    if (i < last) item_left[i] = carry + incl - v;
-    carry += __shfl_sync(0xffffffffu, incl, 31);
+    static_assert(kN == 64, "two counts per lane");
+    pre[2 * lane] = incl - a - b;
+    pre[2 * lane + 1] = incl - b;
+    if (lane == 31) pre[kN] = incl;
   }
-  if (lane == 0) {
-    node_begin_next[2 * node] = node_begin[node];
-    node_begin_next[2 * node + 1] = node_begin[node] + carry;
-    if (node == L - 1) node_begin_next[2 * L] = node_begin[L];
-    rec[node].left_count = carry;
+  __syncthreads();
+  const int nl = pre[kRowsPerThread * kWarps];
+  const int nr = int(item.len) - nl;
+#pragma unroll
+  for (int k = 0; k < kRowsPerThread; ++k) {
+    const unsigned off = k * kPartThreads + threadIdx.x;
+    if (off < item.len) {
+      const int lefts_before = pre[k * kWarps + warp] + before[k];
+      if ((left_bits >> k) & 1u)
+        buf[lefts_before] = rid[k];
+      else
+        buf[nl + int(off) - lefts_before] = rid[k];
+    }
   }
+  if (threadIdx.x == 0) {
+    base_l = atomicAdd(&cursors[2 * item.node], unsigned(nl));
+    base_r = atomicAdd(&cursors[2 * item.node + 1], unsigned(nr));
+  }
+  __syncthreads();
+  const unsigned ldst = node_begin[item.node] + base_l;
+  const unsigned rdst = node_begin[item.node + 1] - base_r - unsigned(nr);
+  for (unsigned i = threadIdx.x; i < item.len; i += kPartThreads)
+    rowid_dst[int(i) < nl ? ldst + i : rdst + (i - unsigned(nl))] = buf[i];
 }
 
-// pass 3: stable scatter of the row ids into the two children
-__global__ void __launch_bounds__(kPartThreads)
-partition_scatter_kernel(const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
-                         const unsigned char *__restrict__ flags,
-                         const unsigned *__restrict__ item_left_excl,
-                         const unsigned *__restrict__ node_begin,
-                         const unsigned *__restrict__ node_begin_next,
-                         const WorkItem *__restrict__ items, const int *__restrict__ n_items) {
-  __shared__ int warp_sums[kPartThreads / 32];
-  if (int(blockIdx.x) >= *n_items) return;
-  const WorkItem item = items[blockIdx.x];
-  const unsigned t0 = threadIdx.x * kRowsPerThread;
-  unsigned rid[kRowsPerThread];
-  unsigned char fl[kRowsPerThread];
-  int lefts = 0, valid = 0;
-#pragma unroll
-  for (int k = 0; k < kRowsPerThread; ++k) {
-    const unsigned off = t0 + k;
-    fl[k] = 0;
-    rid[k] = 0;
-    if (off < item.len) {
-      const unsigned pos = item.begin + off;
-      rid[k] = rowid_src ? rowid_src[pos] : pos;
-      fl[k] = flags[pos];
-      lefts += !fl[k];
-      ++valid;
-    }
-  }
-  int total;
-  const int lo = block_exclusive_scan(lefts, warp_sums, total);
-  const int ro = int(min(t0, item.len)) - lo;
-  const unsigned nb = node_begin[item.node];
-  const unsigned left_excl = item_left_excl[blockIdx.x];
-  const unsigned right_begin = node_begin_next[2 * item.node + 1];
-  unsigned ldst = nb + left_excl + lo;
-  unsigned rdst = right_begin + (item.begin - nb - left_excl) + ro;
-#pragma unroll
-  for (int k = 0; k < kRowsPerThread; ++k) {
-    if (k < valid) {
-      if (fl[k]) rowid_dst[rdst++] = rid[k]; else rowid_dst[ldst++] = rid[k];
-    }
-  }
+// next level's prefix counts (count_next[2n+1] = left end, [2n+2] = node end:
+// hist_tree_grower.cu:80-83) and the left row count of every split record
+__global__ void partition_finish_kernel(const unsigned *__restrict__ cursors,
+                                        const unsigned *__restrict__ node_begin,
+                                        unsigned *__restrict__ node_begin_next,
+                                        NodeRec *__restrict__ rec, int L) {
+  const int node = blockIdx.x * blockDim.x + threadIdx.x;
+  if (node >= L) return;
+  const unsigned nl = cursors[2 * node];
+  node_begin_next[2 * node] = node_begin[node];
+  node_begin_next[2 * node + 1] = node_begin[node] + nl;
+  if (node == L - 1) node_begin_next[2 * L] = node_begin[L];
+  rec[node].left_count = nl;
 }
 
 }  // namespace
@@ -255,23 +219,19 @@ void launch_plan_hist(const unsigned *node_begin, const NodeRec *parent_rec, int
 
 void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
   launch_plan_partition(a.node_begin, a.L, a.pb, a.max_items, s);
+  ARB_CUDA(cudaMemsetAsync(a.cursors, 0, 2 * sizeof(unsigned) * a.L, s));
   if (a.geo.bin_bytes == 1)
-    partition_count_kernel<unsigned char><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.rowid_src, a.flags, a.item_left, a.rec, a.pb.part_items,
-      a.pb.n_part_items);
+    partition_kernel<unsigned char><<<a.max_items, kPartThreads, 0, s>>>(
+      a.geo.bins, a.geo.pitch, a.rowid_src, a.rowid_dst, a.rec, a.node_begin, a.cursors,
+      a.pb.part_items, a.pb.n_part_items);
   else
-    partition_count_kernel<unsigned short><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.rowid_src, a.flags, a.item_left, a.rec, a.pb.part_items,
-      a.pb.n_part_items);
+    partition_kernel<unsigned short><<<a.max_items, kPartThreads, 0, s>>>(
+      a.geo.bins, a.geo.pitch, a.rowid_src, a.rowid_dst, a.rec, a.node_begin, a.cursors,
+      a.pb.part_items, a.pb.n_part_items);
   ARB_CUDA(cudaGetLastError());
   count_launch();
-  partition_scan_kernel<<<a.L, 32, 0, s>>>(a.item_left, a.pb.part_item_first, a.node_begin,
-                                           a.node_begin_next, a.rec, a.L);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-  partition_scatter_kernel<<<a.max_items, kPartThreads, 0, s>>>(
-    a.rowid_src, a.rowid_dst, a.flags, a.item_left, a.node_begin, a.node_begin_next,
-    a.pb.part_items, a.pb.n_part_items);
+  partition_finish_kernel<<<ceil_div(a.L, 128), 128, 0, s>>>(a.cursors, a.node_begin,
+                                                            a.node_begin_next, a.rec, a.L);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

@@ -3,7 +3,7 @@
 // reference, src/core/hist_tree_grower.cu:9-102,393-450).
 //
 // One CTA per (node, feature tile).  A thread owns one feature of the tile and
-// 32 consecutive bins: it sums them, the CTA turns the partial sums into the
+// 8 consecutive bins: it sums them, the CTA turns the partial sums into the
 // prefix offsets of the segmented scan, and the thread then walks its bins
 // again evaluating the reference's gain for "rows with bin <= b go left".  The
 // candidates of a node meet in one 64-bit atomicMax whose integer order is the
@@ -15,107 +15,17 @@ namespace arb {
 
 namespace {
 
-constexpr int kSplitThreads = 256;
-constexpr int kBinsPerThread = 32;  // kHistWords / kSplitThreads
+constexpr int kSplitThreads = 1024;
+constexpr int kBinsPerThread = kHistWords / kSplitThreads;  // 8
 
 __device__ __forceinline__ unsigned long long pack_key(float gain, int fid, int bin) {
   return (static_cast<unsigned long long>(__float_as_uint(gain)) << 32) |
          (static_cast<unsigned long long>(0xFFFFFu - unsigned(fid)) << 12) | unsigned(bin);
 }
 
-template <bool PAIR>
-__global__ void __launch_bounds__(kSplitThreads)
-split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict__ feature_active,
-             unsigned long long *__restrict__ keys, NodeRec *__restrict__ rec,
-             const QuantScale *__restrict__ qs, const GainParams gp, const int TW, const int NT,
-             const int F, const int hist_size) {
-  __shared__ long long part_g[kSplitThreads], part_h[kSplitThreads];
-  __shared__ float best_gain[kSplitThreads];
-  __shared__ int best_bin[kSplitThreads];
-  const int node = blockIdx.x, tile = blockIdx.y;
-  const int lane = threadIdx.x % TW;
-  const int chunk = threadIdx.x / TW;
-  const int nchunks = kSplitThreads / TW;
-  const int f = tile * TW + lane;
-  const long long *base = hist + (size_t(node) * NT + tile) * kHistWords * 2;
-  const int bin0 = chunk * kBinsPerThread;
-
-  long long sg = 0, sh = 0;
-#pragma unroll 4
-  for (int k = 0; k < kBinsPerThread; ++k) {
-    const longlong2 v = *reinterpret_cast<const longlong2 *>(base + (size_t(bin0 + k) * TW + lane) * 2);
-    sg += v.x;
-    sh += v.y;
-  }
-  part_g[threadIdx.x] = sg;
-  part_h[threadIdx.x] = sh;
-  __syncthreads();
-  long long og = 0, oh = 0, tg = 0, th = 0;
-  for (int c = 0; c < nchunks; ++c) {
-    const long long g = part_g[c * TW + lane], h = part_h[c * TW + lane];
-    if (c < chunk) {
-      og += g;
-      oh += h;
-    }
-    tg += g;
-    th += h;
-  }
-  if (tile == 0 && threadIdx.x == 0) {
-    rec[node].tg = tg;
-    rec[node].th = th;
-  }
-  float bgain = 0.0f;
-  int bbin = -1;
-  const bool active = f < F && feature_active[f];
-  if (active && th != 0) {
-    const double isg = qs->inv_sg, ish = qs->inv_sh;
-    const double dtg = double(tg) * isg, dth = double(th) * ish;
-    long long rg = og, rh = oh;
-#pragma unroll 2
-    for (int k = 0; k < kBinsPerThread; ++k) {
-      const int bin = bin0 + k;
-      if (bin >= hist_size) break;  // ids >= hist_size hold missing values: never a threshold
-      const longlong2 v = *reinterpret_cast<const longlong2 *>(base + (size_t(bin) * TW + lane) * 2);
-      rg += v.x;
-      rh += v.y;
-      unsigned long long lc, tc;
-      if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
-        lc = rh > 0;
-        tc = lc + ((th - rh) > 0);
-      } else {  // h_q == 1 for every row: the sum is the row count
-        lc = (unsigned long long)rh;
-        tc = (unsigned long long)th;
-      }
-      const float gain = split_gain<PAIR>(double(rg) * isg, double(rh) * ish, dtg, dth, lc, tc, gp);
-      if (gain > 0.0f && gain >= bgain) {
-        bgain = gain;
-        bbin = bin;
-      }
-    }
-  }
-  best_gain[threadIdx.x] = bgain;
-  best_bin[threadIdx.x] = bbin;
-  __syncthreads();
-  if (chunk == 0 && active) {
-    for (int c = 1; c < nchunks; ++c) {
-      const float g = best_gain[c * TW + lane];
-      if (g > 0.0f && g >= bgain) {
-        bgain = g;
-        bbin = best_bin[c * TW + lane];
-      }
-    }
-    if (bgain > 0.0f) atomicMax(&keys[node], pack_key(bgain, f, bbin));
-  }
-}
-
-// One warp per node: decode the winner and sum its left side.
-__global__ void finalize_kernel(const long long *__restrict__ hist,
-                                const unsigned long long *__restrict__ keys,
-                                NodeRec *__restrict__ rec, const int TW, const int NT, const int L) {
-  const int node = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
-  const int lane = threadIdx.x & 31;
-  if (node >= L) return;
-  const unsigned long long key = keys[node];
+// Decode the winner of a node and sum its left side (one warp).
+__device__ void finalize_node(const long long *__restrict__ hist, unsigned long long key,
+                              NodeRec *__restrict__ rec, int node, int TW, int NT, int lane) {
   NodeRec r = rec[node];
   if (key == 0ull) {  // no positive gain: all rows stay left (hist_tree_grower.cu:84-93)
     r.gain = 0.0f;
@@ -145,24 +55,117 @@ __global__ void finalize_kernel(const long long *__restrict__ hist,
   if (lane == 0) rec[node] = r;
 }
 
+template <bool PAIR>
+__global__ void __launch_bounds__(kSplitThreads)
+split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict__ feature_active,
+             unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
+             NodeRec *__restrict__ rec, const QuantScale *__restrict__ qs, const GainParams gp,
+             const int TW, const int NT, const int F, const int hist_size) {
+  __shared__ long long part_g[kSplitThreads], part_h[kSplitThreads];
+  __shared__ float best_gain[kSplitThreads];
+  __shared__ int best_bin[kSplitThreads];
+  __shared__ bool is_last;
+  const int node = blockIdx.x, tile = blockIdx.y;
+  const int lane = threadIdx.x % TW;
+  const int chunk = threadIdx.x / TW;
+  const int nchunks = kSplitThreads / TW;
+  const int f = tile * TW + lane;
+  const long long *base = hist + (size_t(node) * NT + tile) * kHistWords * 2;
+  const int bin0 = chunk * kBinsPerThread;
+
+  longlong2 v[kBinsPerThread];
+  long long sg = 0, sh = 0;
+#pragma unroll
+  for (int k = 0; k < kBinsPerThread; ++k) {
+    v[k] = *reinterpret_cast<const longlong2 *>(base + (size_t(bin0 + k) * TW + lane) * 2);
+    sg += v[k].x;
+    sh += v[k].y;
+  }
+  part_g[threadIdx.x] = sg;
+  part_h[threadIdx.x] = sh;
+  __syncthreads();
+  long long og = 0, oh = 0, tg = 0, th = 0;
+  for (int c = 0; c < nchunks; ++c) {
+    const long long g = part_g[c * TW + lane], h = part_h[c * TW + lane];
+    if (c < chunk) {
+      og += g;
+      oh += h;
+    }
+    tg += g;
+    th += h;
+  }
+  if (tile == 0 && threadIdx.x == 0) {
+    rec[node].tg = tg;
+    rec[node].th = th;
+  }
+  float bgain = 0.0f;
+  int bbin = -1;
+  const bool active = f < F && feature_active[f];
+  if (active && th != 0) {
+    const double isg = qs->inv_sg, ish = qs->inv_sh;
+    const double dtg = double(tg) * isg, dth = double(th) * ish;
+    long long rg = og, rh = oh;
+#pragma unroll
+    for (int k = 0; k < kBinsPerThread; ++k) {
+      const int bin = bin0 + k;
+      rg += v[k].x;
+      rh += v[k].y;
+      if (bin >= hist_size) continue;  // ids >= hist_size hold missing values: never a threshold
+      unsigned long long lc, tc;
+      if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
+        lc = rh > 0;
+        tc = lc + ((th - rh) > 0);
+      } else {  // h_q == 1 for every row: the sum is the row count
+        lc = (unsigned long long)rh;
+        tc = (unsigned long long)th;
+      }
+      const float gain = split_gain<PAIR>(double(rg) * isg, double(rh) * ish, dtg, dth, lc, tc, gp);
+      if (gain > 0.0f && gain >= bgain) {
+        bgain = gain;
+        bbin = bin;
+      }
+    }
+  }
+  best_gain[threadIdx.x] = bgain;
+  best_bin[threadIdx.x] = bbin;
+  __syncthreads();
+  if (chunk == 0 && active) {
+    for (int c = 1; c < nchunks; ++c) {
+      const float g = best_gain[c * TW + lane];
+      if (g > 0.0f && g >= bgain) {
+        bgain = g;
+        bbin = best_bin[c * TW + lane];
+      }
+    }
+    if (bgain > 0.0f) atomicMax(&keys[node], pack_key(bgain, f, bbin));
+  }
+  // the last tile of the node to arrive turns the packed winner into the record
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&done[node], 1u) == unsigned(NT - 1);
+  __syncthreads();
+  if (is_last && threadIdx.x < 32) {
+    __threadfence();
+    const unsigned long long key = atomicMax(&keys[node], 0ull);
+    finalize_node(hist, key, rec, node, TW, NT, threadIdx.x);
+  }
+}
+
 }  // namespace
 
 void launch_split(const SplitLaunch &a, cudaStream_t s) {
-  ARB_CUDA(cudaMemsetAsync(a.keys, 0, sizeof(unsigned long long) * a.L, s));
+  // keys (u64 per node) and arrival counters (u32 per node) live in one buffer
+  ARB_CUDA(cudaMemsetAsync(a.keys, 0, (sizeof(unsigned long long) + sizeof(unsigned)) * a.max_nodes, s));
+  unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
   const dim3 grid(a.L, a.geo.NT);
   if (a.pair)
-    split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, a.rec, a.qs,
-                                                      a.gp, a.geo.TW, a.geo.NT, a.geo.F,
+    split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
+                                                      a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
                                                       a.geo.hist_size);
   else
-    split_kernel<false><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, a.rec,
+    split_kernel<false><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
                                                        a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
                                                        a.geo.hist_size);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-  const int threads = 128;
-  finalize_kernel<<<ceil_div(size_t(a.L) * 32, threads), threads, 0, s>>>(a.hist, a.keys, a.rec,
-                                                                         a.geo.TW, a.geo.NT, a.L);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
