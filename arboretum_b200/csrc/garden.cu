@@ -281,13 +281,21 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   };
   // events per level: 0 begin, 1 partition done, 2 plan + clear done, 3 histogram done,
   // 4 allreduce done, 5 subtraction done, 6 split search done
+  // One-tile uint8 data takes the fused step: the partition of level l-1 and the
+  // histogram of level l are one pass over the parents' rows.
+  const bool fused = cfg.internal.fused_step && geo_.NT == 1 && geo_.bin_bytes == 1 &&
+                     geo_.TW == 32 && use_trick;
   for (int l = 0; l < levels_; ++l) {
     const int L = 1 << l;
+    const bool trick_level = use_trick && l > 0;
+    const int n_build = trick_level ? L / 2 : L;
+    long long *hist = d_hist_[l & 1].as<long long>();
+    const unsigned *src_list = (l - 1 <= 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>();
     mark();
-    if (l > 0) {
+    if (l > 0 && !fused) {
       PartitionLaunch p;
       p.geo = geo_;
-      p.rowid_src = (l - 1 == 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>();
+      p.rowid_src = src_list;
       p.rowid_dst = d_rowid_[l & 1].as<unsigned>();
       p.cursors = d_cursors_.as<unsigned>();
       p.node_begin = node_begin(l - 1);
@@ -300,29 +308,49 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       launch_partition(p, s);
     }
     mark();
-    // rows scanned this level: all at the root, at most half with the trick
-    // (the hessian rule of multi-GPU runs has no such bound)
-    const bool trick_level = use_trick && l > 0;
-    const bool half = trick_level && !by_hessian;
-    const size_t level_rows = half ? n_ / 2 + 1 : n_;
-    const int n_build = trick_level ? L / 2 : L;
-    // items: about three per persistent CTA, at least 2048 rows, at most the int32 cap
     const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo_.NT));
-    int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
-    launch_plan_hist(node_begin(l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
-                     pb_, max_hist_items_, s);
-    long long *hist = d_hist_[l & 1].as<long long>();
-    mark();
-    HistLaunch h;
-    h.geo = geo_;
-    h.rowid = l == 0 ? nullptr : d_rowid_[l & 1].as<unsigned>();
-    h.grad = grad;
-    h.pair = pair_;
-    h.items = pb_.hist_items;
-    h.n_items = pb_.n_hist_items;
-    h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
-    h.partials = d_partials_.as<int>();
-    launch_hist(h, s);
+    if (l > 0 && fused) {
+      // every row of the level is read (the partition needs them all)
+      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (n_ + target_items - 1) / target_items)));
+      launch_plan_fused(node_begin(l - 1), rec(l - 1), L / 2, item_rows, pb_, max_hist_items_, s);
+      mark();
+      FusedLaunch f;
+      f.geo = geo_;
+      f.rowid_src = src_list;
+      f.rowid_dst = d_rowid_[l & 1].as<unsigned>();
+      f.grad = grad;
+      f.pair = pair_;
+      f.items = pb_.hist_items;
+      f.n_items = pb_.n_hist_items;
+      f.max_items = int(std::min<size_t>(max_hist_items_, n_ / item_rows + L / 2 + 1));
+      f.parent_rec = rec(l - 1);
+      f.built_child = pb_.built_child;
+      f.parent_begin = node_begin(l - 1);
+      f.cursors = d_cursors_.as<unsigned>();
+      f.n_parents = L / 2;
+      f.partials = d_partials_.as<int>();
+      launch_fused(f, s);
+      launch_partition_finish(d_cursors_.as<unsigned>(), node_begin(l - 1), node_begin(l), rec(l - 1), L / 2, s);
+    } else {
+      // rows scanned this level: all at the root, at most half with the trick
+      // (the hessian rule of multi-GPU runs has no such bound)
+      const bool half = trick_level && !by_hessian;
+      const size_t level_rows = half ? n_ / 2 + 1 : n_;
+      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
+      launch_plan_hist(node_begin(l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
+                       pb_, max_hist_items_, s);
+      mark();
+      HistLaunch h;
+      h.geo = geo_;
+      h.rowid = l == 0 ? nullptr : d_rowid_[l & 1].as<unsigned>();
+      h.grad = grad;
+      h.pair = pair_;
+      h.items = pb_.hist_items;
+      h.n_items = pb_.n_hist_items;
+      h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
+      h.partials = d_partials_.as<int>();
+      launch_hist(h, s);
+    }
     ReduceLaunch rd;
     rd.partials = d_partials_.as<int>();
     rd.item_first = pb_.hist_item_first;
@@ -442,7 +470,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       } else {
         for (int p = 0; p < L / 2; ++p) {
           const unsigned ls = nb[2 * p + 1] - nb[2 * p], rs = nb[2 * p + 2] - nb[2 * p + 1];
-          if (by_hessian) {
+          if (by_hessian || fused) {
             const NodeRec &pr = hrec[size_t(l - 1) * max_nodes_ + p];
             rows += (pr.lh <= pr.th - pr.lh) ? ls : rs;
           } else {
@@ -453,6 +481,9 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       t.hist_rows += rows;
       t.hist_features += double(F_);
       t.hist_bytes += rows * (double(F_) * geo_.bin_bytes + (pair_ ? 8.0 : 4.0));
+      // the fused step also does the level's row partition: split-feature bin read,
+      // row id read and write for every row
+      if (fused && l > 0) t.hist_bytes += double(n_) * (geo_.bin_bytes + 8.0);
       t.hist_launches += 1;
     }
     t.update += span(e - 1, e);

@@ -115,6 +115,32 @@ struct PartitionLaunch {
   unsigned n_rows;
 };
 void launch_partition(const PartitionLaunch &a, cudaStream_t s);
+// next level's prefix counts and the split records' left row counts from the cursors
+void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
+                             unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s);
+
+// --- fused level step (one-tile uint8 data): partition of level l-1 + histogram of level l
+// items are pieces of the parents' row lists; the built child of every parent is
+// chosen from the parent's split record (smaller hessian sum, ties left)
+void launch_plan_fused(const unsigned *parent_begin, const NodeRec *parent_rec, int n_parents,
+                       int item_rows, PlanBuffers pb, int max_items, cudaStream_t s);
+struct FusedLaunch {
+  Geometry geo;
+  const unsigned *rowid_src;  // nullptr: identity (parents are the root)
+  unsigned *rowid_dst;
+  const void *grad;
+  bool pair;
+  const WorkItem *items;
+  const int *n_items;
+  int max_items;
+  const NodeRec *parent_rec;
+  const int *built_child;
+  const unsigned *parent_begin;
+  unsigned *cursors;  // 2 per parent, zeroed by the launcher
+  int n_parents;
+  int *partials;
+};
+void launch_fused(const FusedLaunch &a, cudaStream_t s);
 
 // --- objective, leaves, prediction ----------------------------------------------
 // grad from (y, yhat); also tracks max|g|, max h in qs

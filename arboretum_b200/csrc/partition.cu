@@ -46,7 +46,7 @@ __device__ void make_items(const unsigned *begin, const unsigned *len, const int
     WorkItem w;
     w.begin = begin[lo] + off;
     w.len = min(unsigned(rows_per_item), len[lo] - off);
-    w.node = node_id[lo];
+    w.node = node_id ? node_id[lo] : lo;
     w.pad = 0;
     items[it] = w;
   }
@@ -97,6 +97,23 @@ __global__ void plan_hist_kernel(const unsigned *__restrict__ node_begin,
   }
   __syncthreads();
   make_items(sb, sl, sn, n_build, item_rows, first, pb.hist_items, pb.n_hist_items, max_items);
+}
+
+// items over the parents of a fused level step; built child = smaller hessian sum
+__global__ void plan_fused_kernel(const unsigned *__restrict__ parent_begin,
+                                  const NodeRec *__restrict__ parent_rec, int n_parents, int item_rows,
+                                  PlanBuffers pb, unsigned *sb, unsigned *sl, int *build_node,
+                                  int *first, int max_items) {
+  for (int p = threadIdx.x; p < n_parents; p += blockDim.x) {
+    const long long lh = parent_rec[p].lh, rh = parent_rec[p].th - parent_rec[p].lh;
+    const int built = lh <= rh ? 0 : 1;
+    pb.built_child[p] = built;
+    build_node[p] = 2 * p + built;
+    sb[p] = parent_begin[p];
+    sl[p] = parent_begin[p + 1] - parent_begin[p];
+  }
+  __syncthreads();
+  make_items(sb, sl, nullptr, n_parents, item_rows, first, pb.hist_items, pb.n_hist_items, max_items);
 }
 
 // One pass per level: every CTA takes one item (a piece of one node's row list),
@@ -217,6 +234,22 @@ void launch_plan_hist(const unsigned *node_begin, const NodeRec *parent_rec, int
   count_launch();
 }
 
+void launch_plan_fused(const unsigned *parent_begin, const NodeRec *parent_rec, int n_parents,
+                       int item_rows, PlanBuffers pb, int max_items, cudaStream_t s) {
+  plan_fused_kernel<<<1, 256, 0, s>>>(parent_begin, parent_rec, n_parents, item_rows, pb,
+                                      pb.scratch_begin, pb.scratch_len, pb.scratch_node,
+                                      pb.hist_item_first, max_items);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
+                             unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s) {
+  partition_finish_kernel<<<ceil_div(L, 128), 128, 0, s>>>(cursors, node_begin, node_begin_next, rec, L);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
 void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
   launch_plan_partition(a.node_begin, a.L, a.pb, a.max_items, s);
   ARB_CUDA(cudaMemsetAsync(a.cursors, 0, 2 * sizeof(unsigned) * a.L, s));
@@ -230,10 +263,7 @@ void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
       a.pb.part_items, a.pb.n_part_items);
   ARB_CUDA(cudaGetLastError());
   count_launch();
-  partition_finish_kernel<<<ceil_div(a.L, 128), 128, 0, s>>>(a.cursors, a.node_begin,
-                                                            a.node_begin_next, a.rec, a.L);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
+  launch_partition_finish(a.cursors, a.node_begin, a.node_begin_next, a.rec, a.L, s);
 }
 
 }  // namespace arb

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(kSplitThreads)
 split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict__ feature_active,
              unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
              NodeRec *__restrict__ rec, const QuantScale *__restrict__ qs, const GainParams gp,
-             const int TW, const int NT, const int F, const int hist_size) {
+             const int TW, const int NT, const int F, const int hist_size, const int parts) {
   __shared__ long long part_g[kSplitThreads], part_h[kSplitThreads];
   __shared__ float best_gain[kSplitThreads];
   __shared__ int best_bin[kSplitThreads];
@@ -94,14 +94,16 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
     tg += g;
     th += h;
   }
-  if (tile == 0 && threadIdx.x == 0) {
+  if (tile == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     rec[node].tg = tg;
     rec[node].th = th;
   }
   float bgain = 0.0f;
   int bbin = -1;
+  // the gain search of a (node, tile) is dealt to `parts` CTAs by bin chunk; all of
+  // them redo the cheap prefix sums above
   const bool active = f < F && feature_active[f];
-  if (active && th != 0) {
+  if (active && th != 0 && chunk % parts == int(blockIdx.z)) {
     const double isg = qs->inv_sg, ish = qs->inv_sh;
     const double dtg = double(tg) * isg, dth = double(th) * ish;
     long long rg = og, rh = oh;
@@ -142,7 +144,7 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
   // the last tile of the node to arrive turns the packed winner into the record
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) is_last = atomicAdd(&done[node], 1u) == unsigned(NT - 1);
+  if (threadIdx.x == 0) is_last = atomicAdd(&done[node], 1u) == unsigned(NT * parts - 1);
   __syncthreads();
   if (is_last && threadIdx.x < 32) {
     __threadfence();
@@ -157,15 +159,18 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   // keys (u64 per node) and arrival counters (u32 per node) live in one buffer
   ARB_CUDA(cudaMemsetAsync(a.keys, 0, (sizeof(unsigned long long) + sizeof(unsigned)) * a.max_nodes, s));
   unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
-  const dim3 grid(a.L, a.geo.NT);
+  // spread the double-precision gain arithmetic of small levels over the GPU
+  int parts = 1;
+  while (parts < 4 && a.L * a.geo.NT * parts < 148) parts <<= 1;
+  const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair)
     split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
                                                       a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
-                                                      a.geo.hist_size);
+                                                      a.geo.hist_size, parts);
   else
     split_kernel<false><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
                                                        a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
-                                                       a.geo.hist_size);
+                                                       a.geo.hist_size, parts);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
