@@ -1,0 +1,63 @@
+"""Worker of tests/test_gpu_multi.py: one process per GPU (torchrun).  Trains the same
+data sharded over all ranks and, on rank 0, unsharded on one GPU; the trees must be
+bit-identical because every histogram is an exact integer sum."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import arboretum_b200 as arboretum  # noqa: E402
+from arboretum_b200 import distributed as adist  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rng = np.random.default_rng(123)
+    n, F, rounds = 60000, 28, 4
+    X = rng.normal(size=(n, F)).astype(np.float32)
+    w = rng.normal(size=F)
+    y = (rng.random(n) < 1 / (1 + np.exp(-(X @ w * 0.5 + 0.3 * X[:, 0] * X[:, 1])))).astype(np.float32)
+    cfg = {"objective": 1, "method": 1,
+           "internals": {"hist_size": 255, "seed": 0, "device": local},
+           "verbose": {"gpu": False, "booster": False, "data": False},
+           "tree": {"eta": 0.1, "max_depth": 6, "lambda": 1.0, "min_child_weight": 1.0}}
+    # thresholds of the WHOLE matrix, computed on rank 0, shared with everybody
+    thr = size = None
+    if rank == 0:
+        thr, size, _ = arboretum.DMatrix(X).quantize(255, True, want_bins=False)
+    lo, hi = adist.shard_rows(n, rank, world)
+    data = arboretum.DMatrix(X[lo:hi], y=y[lo:hi])
+    thr, size = adist.share_thresholds(data, 255, rank, world, thresholds=thr, sizes=size)
+    model = arboretum.Garden(cfg)
+    model.data = data
+    adist.init_nccl(model, rank, world)
+    for _ in range(rounds):
+        model.grow_tree()
+    sharded = json.loads(model.dump())["model"]
+    ok = True
+    if rank == 0:
+        full = arboretum.DMatrix(X, y=y)
+        full.set_thresholds(thr, size)
+        single = json.loads(arboretum.train(cfg, full, rounds).dump())["model"]
+        ok = single == sharded
+        print("MULTI_GPU_TREES_IDENTICAL" if ok else "MULTI_GPU_TREES_DIFFER", flush=True)
+    # every rank must hold the same model
+    digest = torch.tensor([hash(json.dumps(sharded)) % (2 ** 31)], device="cuda")
+    gathered = [torch.zeros_like(digest) for _ in range(world)]
+    dist.all_gather(gathered, digest)
+    same = all(int(g.item()) == int(digest.item()) for g in gathered)
+    if rank == 0:
+        print("MULTI_GPU_RANKS_AGREE" if same else "MULTI_GPU_RANKS_DISAGREE", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if (ok and same) else 1)
+
+
+if __name__ == "__main__":
+    main()
