@@ -4,6 +4,7 @@ bit-identical because every histogram is an exact integer sum."""
 import json
 import os
 import sys
+import zlib
 
 import numpy as np
 import torch
@@ -49,7 +50,7 @@ def main():
         ok = single == sharded
         print("MULTI_GPU_TREES_IDENTICAL" if ok else "MULTI_GPU_TREES_DIFFER", flush=True)
     # every rank must hold the same model
-    digest = torch.tensor([hash(json.dumps(sharded)) % (2 ** 31)], device="cuda")
+    digest = torch.tensor([zlib.crc32(json.dumps(sharded).encode()) % (2 ** 31)], device="cuda")
     gathered = [torch.zeros_like(digest) for _ in range(world)]
     dist.all_gather(gathered, digest)
     same = all(int(g.item()) == int(digest.item()) for g in gathered)
