@@ -1,6 +1,6 @@
 """Builds ``libarboretum.so`` in-tree with nvcc for sm_100a.
 
-    python -m arboretum_b200.build [--force]
+    python arboretum_b200/build.py [--force]
 
 The library is the product: the C ABI the Python layer (and the reference's own
 ``core.py``) loads with ctypes.  nvcc cross-compiles without a GPU.
