@@ -25,7 +25,7 @@ def _load_lib():
     path = os.path.join(here, "libarboretum.so")
     if not os.path.exists(path):
         raise ImportError(
-            "%s is missing: build it with `python -m arboretum_b200.build` "
+            "%s is missing: build it with `python arboretum_b200/build.py` "
             "(there is no CPU fallback)" % path)
     lib = ctypes.cdll.LoadLibrary(path)
     for name in ("ACreateFromDenseMatrix", "ASetY", "AInitGarden", "AGrowTree", "APredict",
@@ -34,7 +34,7 @@ def _load_lib():
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
                  "AGetLevelStats", "ASetProfile", "AGetTimings", "ABuildHistogram",
-                 "ANcclUniqueId", "AInitNccl"):
+                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc"):
         getattr(lib, name).restype = ctypes.c_char_p
     lib.ADumpModel.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.c_void_p]
     lib.AFreeDMatrix.argtypes = [ctypes.c_void_p]
@@ -64,6 +64,8 @@ def _load_lib():
                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    lib.AThresholdsNoAlloc.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
+                                       ctypes.c_void_p, ctypes.c_void_p]
     lib.ANcclUniqueId.argtypes = [ctypes.c_void_p]
     lib.AInitNccl.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     return lib

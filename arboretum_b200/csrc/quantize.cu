@@ -208,4 +208,57 @@ void launch_binning(const float *X, size_t n, int F, const float *thr, const int
   count_launch();
 }
 
+// ---------------------------------------------------------------------------
+// Threshold search without any allocation.
+//
+// Some callers may not allocate device memory at all: a host that has handed the
+// whole GPU to one arena at start-up and forbids cudaMalloc afterwards, a service
+// that runs inside a fixed memory budget, or code that is called while an
+// allocation could not be tolerated (latency-critical sections, other libraries'
+// callbacks).  The border scan of the threshold search needs one word of scratch
+// per 2048 sorted values; here that scratch is a fixed array inside the library
+// image, so the call only launches kernels.  The price is a size limit and the
+// fact that every call on a device shares the one array.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr long long kStaticThresholdRows = 1ll << 26;  // 67,108,864 values per call
+constexpr size_t kStaticScratchWords = size_t(kStaticThresholdRows / kScanTile) + 1;
+// 128 KB of device memory per GPU that loads the library, held until exit
+static __device__ __align__(256) unsigned g_threshold_scratch[kStaticScratchWords];
+constexpr int kMaxDevices = 64;
+unsigned *g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
 }  // namespace arb
+
+extern "C" const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist_size,
+                                           float *thr_device, void *stream) {
+  using namespace arb;
+  static thread_local std::string error;
+  try {
+    ARB_CHECK(sorted_device && thr_device, "NULL argument");
+    ARB_CHECK(hist_size > 0 && hist_size < 2048, "hist_size must be in [1, 2047]");
+    ARB_CHECK(n >= 0, "negative row count");
+    if (n > kStaticThresholdRows)
+      throw std::runtime_error("AThresholdsNoAlloc: " + std::to_string(n) + " values exceed the limit of " +
+                               std::to_string(kStaticThresholdRows) +
+                               " of the built-in scratch array; use AQuantize for larger columns");
+    int dev = 0;
+    ARB_CUDA(cudaGetDevice(&dev));
+    ARB_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+    if (!g_scratch_ptr[dev]) {
+      // In host code the array's name is only a handle: the kernels need the address
+      // the symbol has on THIS device, which the runtime hands out here.
+      void *p = nullptr;
+      ARB_CUDA(cudaGetSymbolAddress(&p, g_threshold_scratch));
+      g_scratch_ptr[dev] = static_cast<unsigned *>(p);
+    }
+    // block counts are rewritten in full for the blocks of this call, so nothing of an
+    // earlier call's contents is read: no clearing is needed
+    launch_thresholds(sorted_device, size_t(n), hist_size, thr_device, g_scratch_ptr[dev],
+                      static_cast<cudaStream_t>(stream));
+    return nullptr;
+  } catch (const std::exception &e) {
+    error = e.what();
+    return error.c_str();
+  }
+}

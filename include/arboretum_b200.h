@@ -92,6 +92,22 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
 const char *ANcclUniqueId(char *id128);
 const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128);
 
+/* No counterpart in the reference.  Threshold search of ONE feature for callers that
+ * must not allocate device memory (a process whose GPU memory is owned by one
+ * arena, a fixed-budget service, a latency-critical section): `sorted_device` holds
+ * the column's n values in ascending fp32 radix order in device memory,
+ * `thr_device` receives hist_size thresholds (device memory), `stream` is a
+ * cudaStream_t (NULL = default stream).  The call only launches kernels; its
+ * scratch is a 128 KB array inside the library image, which every GPU that loads
+ * the library holds until the process exits.  n may not exceed 67,108,864 (2^26):
+ * larger columns return an error and should go through AQuantize.  The first call on
+ * a device looks the array's address up (cudaGetSymbolAddress); make that first
+ * call before any stream capture.  All calls on a device share the array, so two
+ * calls that overlap on the GPU (different streams, different threads) race; calls
+ * on one stream are safe.  Nothing of an earlier call's scratch contents is read. */
+const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist_size,
+                               float *thr_device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
