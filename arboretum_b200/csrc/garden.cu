@@ -17,8 +17,9 @@ long long g_kernel_launches = 0;
 // ---------------------------------------------------------------------------
 // DataMatrix
 // ---------------------------------------------------------------------------
-void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s) {
+void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows) {
   if (binned) return;
+  out_of_core = chunk_rows > 0 && chunk_rows < rows;
   const int F = cols_dense;
   ARB_CHECK(hs > 0 && hs < 2048, "hist_size must be in [1, 2047]");
   ARB_CHECK(F > 0 && rows > 0, "empty data matrix");
@@ -64,7 +65,23 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
     launch_binning(d_x.as<float>(), n, F, d_thr.as<float>(), d_fsize.as<int>(), hs, missing_bin,
                    d_bins.as<unsigned char>(), pitch, bin_bytes, s);
+    if (out_of_core) {  // the bins live in pinned host memory and are streamed per level
+      h_bins.alloc(n * pitch);
+      ARB_CUDA(cudaMemcpyAsync(h_bins.p, d_bins.p, n * pitch, cudaMemcpyDeviceToHost, s));
+    }
     ARB_CUDA(cudaStreamSynchronize(s));
+    if (out_of_core) d_bins.release();
+  } else if (out_of_core) {
+    ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
+    h_bins.alloc(n * pitch);
+    std::memset(h_bins.p, 0, n * pitch);
+    ARB_CUDA(cudaMemcpy2D(h_bins.p, pitch, host_bins.data(), size_t(F), size_t(F), n, cudaMemcpyHostToHost));
+    if (thr.empty()) {
+      thr.resize(size_t(F) * hs);
+      fsize.assign(F, hs);
+      for (int f = 0; f < F; ++f)
+        for (int q = 0; q < hs; ++q) thr[size_t(f) * hs + q] = q + 0.5f;
+    }
   } else {
     // rows arrive already binned: copy them into the padded row-major layout
     ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
@@ -118,12 +135,32 @@ class Builder {
     d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_cursors_;
   DevBuf d_partials_, d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
+  std::vector<unsigned> h_nb_total_;
   PlanBuffers pb_;
   cudaEvent_t ev_[2 * 8 * kMaxLevels];
+  // Row chunks (out-of-core): a chunk is a contiguous range of rows whose bins are
+  // either resident in HBM or streamed from pinned host memory into one of two
+  // staging buffers once per level.  In-core training is one resident chunk.
+  struct Chunk {
+    size_t begin, rows;
+    const unsigned char *resident;  // device bins of the chunk, or nullptr (streamed)
+  };
+  std::vector<Chunk> chunks_;
+  DevBuf d_stage_[2], d_resident_;
+  cudaStream_t copy_stream_ = nullptr;
+  cudaEvent_t stage_ready_[2], stage_free_[2];
+  int stage_of_next_ = 0;
+  std::vector<int> streamed_;       // indices of the streamed chunks, in visiting order
+  size_t issued_ = 0, consumed_ = 0;  // position in the endless cyclic sequence of `streamed_`
+  const unsigned char *Acquire(int chunk);
+  void Release(int chunk);
+  void IssueCopy();
   friend class Garden;
   friend struct BuilderView;
 
-  unsigned *node_begin(int level) { return d_node_begin_.as<unsigned>() + size_t(level) * nb_stride_; }
+  unsigned *node_begin(int chunk, int level) {
+    return d_node_begin_.as<unsigned>() + (size_t(chunk) * (levels_ + 1) + level) * nb_stride_;
+  }
   NodeRec *rec(int level) { return d_rec_.as<NodeRec>() + size_t(level) * max_nodes_; }
 };
 
@@ -186,10 +223,17 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_rowid_[0].alloc(n_ * sizeof(unsigned));
   d_rowid_[1].alloc(n_ * sizeof(unsigned));
   // level state
-  d_node_begin_.alloc(size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
+  {
+    const size_t chunk_rows = d->out_of_core ? size_t(cfg.internal.chunk_rows) : n_;
+    for (size_t b = 0; b < n_; b += chunk_rows)
+      chunks_.push_back(Chunk{b, std::min(chunk_rows, n_ - b), nullptr});
+  }
+  d_node_begin_.alloc(chunks_.size() * size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
   ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
-  const unsigned root[2] = {0u, unsigned(n_)};
-  ARB_CUDA(cudaMemcpyAsync(d_node_begin_.p, root, sizeof root, cudaMemcpyHostToDevice, s));
+  for (size_t c = 0; c < chunks_.size(); ++c) {
+    const unsigned root[2] = {0u, unsigned(chunks_[c].rows)};
+    ARB_CUDA(cudaMemcpyAsync(node_begin(int(c), 0), root, sizeof root, cudaMemcpyHostToDevice, s));
+  }
   d_rec_.alloc(size_t(levels_) * max_nodes_ * sizeof(NodeRec));
   ARB_CUDA(cudaMemsetAsync(d_rec_.p, 0, d_rec_.bytes, s));
   const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
@@ -228,6 +272,69 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   active_host_.resize(size_t(levels_) * F_);
   for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
   ARB_CUDA(cudaStreamSynchronize(s));
+  if (!d->out_of_core) {
+    chunks_[0].resident = d->d_bins.as<unsigned char>();
+  } else {
+    // as many leading chunks as fit stay in HBM; the rest cycle through two buffers
+    const size_t chunk_bytes = chunks_[0].rows * d->pitch;
+    int resident = cfg.internal.resident_chunks;
+    if (resident < 0) {
+      size_t free_b = 0, total_b = 0;
+      ARB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+      const size_t budget = free_b / 10 * 8;
+      resident = budget > 2 * chunk_bytes ? int((budget - 2 * chunk_bytes) / chunk_bytes) : 0;
+    }
+    resident = std::min<int>(resident, int(chunks_.size()));
+    size_t resident_rows = 0;
+    for (int c = 0; c < resident; ++c) resident_rows += chunks_[c].rows;
+    if (resident_rows) {
+      d_resident_.alloc(resident_rows * d->pitch);
+      ARB_CUDA(cudaMemcpyAsync(d_resident_.p, d->h_bins.p, resident_rows * d->pitch,
+                               cudaMemcpyHostToDevice, s));
+      for (int c = 0; c < resident; ++c)
+        chunks_[c].resident = d_resident_.as<unsigned char>() + chunks_[c].begin * d->pitch;
+    }
+    for (size_t c = resident; c < chunks_.size(); ++c) streamed_.push_back(int(c));
+    if (!streamed_.empty()) {
+      d_stage_[0].alloc(chunk_bytes);
+      d_stage_[1].alloc(chunk_bytes);
+      ARB_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+      for (int i = 0; i < 2; ++i) {
+        ARB_CUDA(cudaEventCreateWithFlags(&stage_ready_[i], cudaEventDisableTiming));
+        ARB_CUDA(cudaEventCreateWithFlags(&stage_free_[i], cudaEventDisableTiming));
+      }
+    }
+    ARB_CUDA(cudaStreamSynchronize(s));
+  }
+}
+
+// Copy the next chunk of the endless cyclic visiting sequence into its staging buffer.
+void Builder::IssueCopy() {
+  const Chunk &ch = chunks_[streamed_[issued_ % streamed_.size()]];
+  const int buf = int(issued_ & 1);
+  ARB_CUDA(cudaStreamWaitEvent(copy_stream_, stage_free_[buf], 0));  // kernels done with it
+  ARB_CUDA(cudaMemcpyAsync(d_stage_[buf].p, data->h_bins.as<unsigned char>() + ch.begin * data->pitch,
+                           ch.rows * data->pitch, cudaMemcpyHostToDevice, copy_stream_));
+  ARB_CUDA(cudaEventRecord(stage_ready_[buf], copy_stream_));
+  ++issued_;
+}
+
+// Device address of a chunk's bins for the kernels about to be enqueued; streamed
+// chunks must be visited in the cyclic order of `streamed_`.
+const unsigned char *Builder::Acquire(int chunk) {
+  if (chunks_[chunk].resident) return chunks_[chunk].resident;
+  ARB_CHECK(streamed_[consumed_ % streamed_.size()] == chunk, "row chunks visited out of order");
+  while (issued_ <= consumed_) IssueCopy();
+  if (issued_ == consumed_ + 1) IssueCopy();  // the next chunk travels while this one is used
+  const int buf = int(consumed_ & 1);
+  ARB_CUDA(cudaStreamWaitEvent(g_->stream, stage_ready_[buf], 0));
+  return d_stage_[buf].as<unsigned char>();
+}
+
+void Builder::Release(int chunk) {
+  if (chunks_[chunk].resident) return;
+  ARB_CUDA(cudaEventRecord(stage_free_[int(consumed_ & 1)], g_->stream));
+  ++consumed_;
 }
 
 void Builder::UpdateGrad() {  // objective.cu:28-56
@@ -273,97 +380,113 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
                            cudaMemcpyHostToDevice, s));
 
   const bool use_trick = cfg.internal.use_hist_subtraction_trick;
-  const bool by_hessian = g_->allreduce != nullptr;
+  const int n_chunks = int(chunks_.size());
+  const bool multi = n_chunks > 1;  // row chunks add their histograms like GPUs do
+  const bool by_hessian = g_->allreduce != nullptr || multi;
+  const size_t gsz = pair_ ? sizeof(float2) : sizeof(float);
   int ev = 0;
   auto mark = [&]() {
-    if (prof) ARB_CUDA(cudaEventRecord(ev_[ev], s));
+    if (prof && !multi) ARB_CUDA(cudaEventRecord(ev_[ev], s));
     ++ev;
   };
   // events per level: 0 begin, 1 partition done, 2 plan + clear done, 3 histogram done,
   // 4 allreduce done, 5 subtraction done, 6 split search done
-  // One-tile uint8 data takes the fused step: the partition of level l-1 and the
+  // One-tile uint8 data may take the fused step: the partition of level l-1 and the
   // histogram of level l are one pass over the parents' rows.
   const bool fused = cfg.internal.fused_step && geo_.NT == 1 && geo_.bin_bytes == 1 &&
-                     geo_.TW == 32 && use_trick;
+                     geo_.TW == 32 && use_trick && !multi;
   for (int l = 0; l < levels_; ++l) {
     const int L = 1 << l;
     const bool trick_level = use_trick && l > 0;
     const int n_build = trick_level ? L / 2 : L;
     long long *hist = d_hist_[l & 1].as<long long>();
-    const unsigned *src_list = (l - 1 <= 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>();
-    mark();
-    if (l > 0 && !fused) {
-      PartitionLaunch p;
-      p.geo = geo_;
-      p.rowid_src = src_list;
-      p.rowid_dst = d_rowid_[l & 1].as<unsigned>();
-      p.cursors = d_cursors_.as<unsigned>();
-      p.node_begin = node_begin(l - 1);
-      p.node_begin_next = node_begin(l);
-      p.rec = rec(l - 1);
-      p.pb = pb_;
-      p.L = L / 2;
-      p.max_items = max_part_items_;
-      p.n_rows = unsigned(n_);
-      launch_partition(p, s);
+    if (multi)
+      ARB_CUDA(cudaMemsetAsync(hist, 0, size_t(L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+    for (int c = 0; c < n_chunks; ++c) {
+      const Chunk &ch = chunks_[c];
+      const bool last = c + 1 == n_chunks;
+      Geometry geo = geo_;
+      geo.bins = Acquire(c);
+      const size_t rows = ch.rows;
+      const void *grad_c = static_cast<const char *>(grad) + ch.begin * gsz;
+      unsigned *list_cur = d_rowid_[l & 1].as<unsigned>() + ch.begin;
+      const unsigned *src_list = (l - 1 <= 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>() + ch.begin;
+      if (c == 0) mark();
+      if (l > 0 && !fused) {
+        PartitionLaunch p;
+        p.geo = geo;
+        p.rowid_src = src_list;
+        p.rowid_dst = list_cur;
+        p.cursors = d_cursors_.as<unsigned>();
+        p.node_begin = node_begin(c, l - 1);
+        p.node_begin_next = node_begin(c, l);
+        p.rec = rec(l - 1);
+        p.pb = pb_;
+        p.L = L / 2;
+        p.max_items = int(rows / kPartRows) + L / 2 + 1;
+        p.n_rows = unsigned(rows);
+        launch_partition(p, s);
+      }
+      if (last) mark();
+      const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo.NT));
+      if (l > 0 && fused) {
+        // every row of the level is read (the partition needs them all)
+        const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (rows + target_items - 1) / target_items)));
+        launch_plan_fused(node_begin(c, l - 1), rec(l - 1), L / 2, item_rows, pb_, max_hist_items_, s);
+        if (last) mark();
+        FusedLaunch f;
+        f.geo = geo;
+        f.rowid_src = src_list;
+        f.rowid_dst = list_cur;
+        f.grad = grad_c;
+        f.pair = pair_;
+        f.items = pb_.hist_items;
+        f.n_items = pb_.n_hist_items;
+        f.max_items = int(std::min<size_t>(max_hist_items_, rows / item_rows + L / 2 + 1));
+        f.parent_rec = rec(l - 1);
+        f.built_child = pb_.built_child;
+        f.parent_begin = node_begin(c, l - 1);
+        f.cursors = d_cursors_.as<unsigned>();
+        f.n_parents = L / 2;
+        f.partials = d_partials_.as<int>();
+        launch_fused(f, s);
+        launch_partition_finish(d_cursors_.as<unsigned>(), node_begin(c, l - 1), node_begin(c, l), rec(l - 1), L / 2, s);
+      } else {
+        // rows scanned this level: all at the root, at most half with the trick
+        // (the hessian rule of multi-GPU / multi-chunk runs has no such bound)
+        const bool half = trick_level && !by_hessian;
+        const size_t level_rows = half ? rows / 2 + 1 : rows;
+        const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
+        launch_plan_hist(node_begin(c, l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
+                         pb_, max_hist_items_, s);
+        if (last) mark();
+        HistLaunch h;
+        h.geo = geo;
+        h.rowid = l == 0 ? nullptr : list_cur;
+        h.grad = grad_c;
+        h.pair = pair_;
+        h.items = pb_.hist_items;
+        h.n_items = pb_.n_hist_items;
+        h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
+        h.partials = d_partials_.as<int>();
+        launch_hist(h, s);
+      }
+      ReduceLaunch rd;
+      rd.partials = d_partials_.as<int>();
+      rd.item_first = pb_.hist_item_first;
+      rd.build_node = pb_.scratch_node;
+      rd.n_build = n_build;
+      rd.NT = geo.NT;
+      rd.level_hist = hist;
+      rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
+      rd.subtract = trick_level && !g_->allreduce && !multi;
+      rd.zero_sibling = trick_level && g_->allreduce && !multi;
+      rd.level_nodes = L;
+      rd.built_child = pb_.built_child;
+      rd.accumulate = multi;
+      launch_reduce(rd, s);
+      Release(c);
     }
-    mark();
-    const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo_.NT));
-    if (l > 0 && fused) {
-      // every row of the level is read (the partition needs them all)
-      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (n_ + target_items - 1) / target_items)));
-      launch_plan_fused(node_begin(l - 1), rec(l - 1), L / 2, item_rows, pb_, max_hist_items_, s);
-      mark();
-      FusedLaunch f;
-      f.geo = geo_;
-      f.rowid_src = src_list;
-      f.rowid_dst = d_rowid_[l & 1].as<unsigned>();
-      f.grad = grad;
-      f.pair = pair_;
-      f.items = pb_.hist_items;
-      f.n_items = pb_.n_hist_items;
-      f.max_items = int(std::min<size_t>(max_hist_items_, n_ / item_rows + L / 2 + 1));
-      f.parent_rec = rec(l - 1);
-      f.built_child = pb_.built_child;
-      f.parent_begin = node_begin(l - 1);
-      f.cursors = d_cursors_.as<unsigned>();
-      f.n_parents = L / 2;
-      f.partials = d_partials_.as<int>();
-      launch_fused(f, s);
-      launch_partition_finish(d_cursors_.as<unsigned>(), node_begin(l - 1), node_begin(l), rec(l - 1), L / 2, s);
-    } else {
-      // rows scanned this level: all at the root, at most half with the trick
-      // (the hessian rule of multi-GPU runs has no such bound)
-      const bool half = trick_level && !by_hessian;
-      const size_t level_rows = half ? n_ / 2 + 1 : n_;
-      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
-      launch_plan_hist(node_begin(l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
-                       pb_, max_hist_items_, s);
-      mark();
-      HistLaunch h;
-      h.geo = geo_;
-      h.rowid = l == 0 ? nullptr : d_rowid_[l & 1].as<unsigned>();
-      h.grad = grad;
-      h.pair = pair_;
-      h.items = pb_.hist_items;
-      h.n_items = pb_.n_hist_items;
-      h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
-      h.partials = d_partials_.as<int>();
-      launch_hist(h, s);
-    }
-    ReduceLaunch rd;
-    rd.partials = d_partials_.as<int>();
-    rd.item_first = pb_.hist_item_first;
-    rd.build_node = pb_.scratch_node;
-    rd.n_build = n_build;
-    rd.NT = geo_.NT;
-    rd.level_hist = hist;
-    rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
-    rd.subtract = trick_level && !g_->allreduce;
-    rd.zero_sibling = trick_level && g_->allreduce;
-    rd.level_nodes = L;
-    rd.built_child = pb_.built_child;
-    launch_reduce(rd, s);
     mark();
     if (g_->allreduce) {
       const size_t count = size_t(L) * geo_.NT * kHistWords * 2;
@@ -371,13 +494,13 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         throw std::runtime_error("histogram allreduce failed");
     }
     mark();
-    if (trick_level && g_->allreduce)
+    if (trick_level && (g_->allreduce || multi))
       launch_subtract(hist, d_hist_[(l - 1) & 1].as<long long>(), pb_.built_child, L / 2, geo_.NT, s);
     mark();
     SplitLaunch sp;
     sp.geo = geo_;
     sp.hist = hist;
-    sp.node_begin = node_begin(l);
+    sp.node_begin = node_begin(0, l);
     sp.feature_active = d_active_.as<unsigned char>() + size_t(l) * F_;
     sp.feature_size = d_fsize_.as<int>();
     sp.keys = d_keys_.as<unsigned long long>();
@@ -405,14 +528,26 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   lf.eta = tp.eta;
   lf.pair = pair_;
   launch_leaf_weights(lf, s);
-  launch_update_yhat(geo_, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(),
-                     d_yhat_.as<float>() + size_t(label) * n_, n_, s);
+  for (int c = 0; c < n_chunks; ++c) {  // the tree walk needs the bins once more
+    Geometry geo = geo_;
+    geo.bins = Acquire(c);
+    launch_update_yhat(geo, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(),
+                       d_yhat_.as<float>() + size_t(label) * n_ + chunks_[c].begin, chunks_[c].rows, s);
+    Release(c);
+  }
   mark();
   ARB_CUDA(cudaMemcpyAsync(h_rec_.p, d_rec_.p, d_rec_.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaMemcpyAsync(h_leaf_w_.p, d_leaf_w_.p, d_leaf_w_.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
                            cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaStreamSynchronize(s));
+  {  // per-level prefix counts of the whole data set = sums over the row chunks
+    const size_t per_chunk = size_t(levels_ + 1) * nb_stride_;
+    h_nb_total_.assign(per_chunk, 0u);
+    const unsigned *all = h_node_begin_.as<unsigned>();
+    for (int c = 0; c < n_chunks; ++c)
+      for (size_t i = 0; i < per_chunk; ++i) h_nb_total_[i] += all[size_t(c) * per_chunk + i];
+  }
 
   // ---- UpdateTree garden.cu:447-485 -----------------------------------------------
   const int depth = int(tp.depth);
@@ -444,9 +579,10 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   const float *hw = h_leaf_w_.as<float>();
   for (int i = 0; i < 2 * max_nodes_; ++i) tree->weights[i] = hw[i];
 
-  if (prof) {
+  if (prof && multi) g_->times.trees += 1;
+  if (prof && !multi) {
     PhaseTimes &t = g_->times;
-    const unsigned *hnb = h_node_begin_.as<unsigned>();
+    const unsigned *hnb = h_nb_total_.data();
     int e = 0;
     auto span = [&](int a, int b) {
       float ms;
@@ -500,7 +636,7 @@ const NodeRec *BuilderView::host_rec(const Garden *g, int *max_nodes, int *level
 const unsigned *BuilderView::host_node_begin(const Garden *g, int *stride) {
   ARB_CHECK(g->builder && !g->trees.empty(), "no tree has been grown yet");
   *stride = g->builder->nb_stride_;
-  return g->builder->h_node_begin_.as<unsigned>();
+  return g->builder->h_nb_total_.data();
 }
 void BuilderView::scales(Garden *g, QuantScale *out) {
   ARB_CHECK(g->builder, "no tree has been grown yet");
@@ -542,7 +678,8 @@ float Garden::InternalInitialY() const {  // objective.h:19,55-57
 
 void Garden::GrowTree(DataMatrix *data, const float *grad) {
   (void)grad;  // custom gradients are ignored by the reference as well (garden.cu:609-614)
-  data->InitHist(cfg.internal.hist_size, cfg.internal.missing_bin, cfg.verbose.data, stream);
+  data->InitHist(cfg.internal.hist_size, cfg.internal.missing_bin, cfg.verbose.data, stream,
+                 cfg.internal.chunk_rows);
   if (!builder) {
     builder = new Builder(this, data);
   } else if (builder->data != data) {

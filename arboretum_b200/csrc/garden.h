@@ -36,6 +36,8 @@ class DataMatrix {
   int bin_bytes = 1;
   size_t pitch = 0;
   DevBuf d_bins;
+  PinnedBuf h_bins;  // out-of-core: the padded row-major bin matrix in pinned host memory
+  bool out_of_core = false;
   std::vector<float> thr;  // [F][hist_size] data_reduced_mapping
   std::vector<int> fsize;  // bins in use per feature
   int max_reduced_bits = 0;
@@ -45,7 +47,7 @@ class DataMatrix {
   DevBuf d_yhat;
   int yhat_planes = 0;
 
-  void InitHist(int hist_size, bool missing_bin, bool verbose, cudaStream_t s);
+  void InitHist(int hist_size, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows = 0);
   static size_t PitchFor(int F, int bin_bytes) {
     return (size_t(F) * bin_bytes + 31) / 32 * 32;
   }

@@ -391,7 +391,7 @@ template <bool SUBTRACT>
 __global__ void reduce_kernel(const int *__restrict__ partials, const int *__restrict__ item_first,
                               const int *__restrict__ build_node, long long *__restrict__ level_hist,
                               const long long *__restrict__ parent_hist, const int NT,
-                              const int slices, const bool zero_sibling) {
+                              const int slices, const bool zero_sibling, const bool atomic) {
   const int b = blockIdx.z / slices, slice = blockIdx.z - b * slices, tile = blockIdx.y;
   const int w = blockIdx.x * blockDim.x + threadIdx.x;
   const int first = item_first[b], last = item_first[b + 1];
@@ -404,7 +404,7 @@ __global__ void reduce_kernel(const int *__restrict__ partials, const int *__res
   }
   const int node = build_node[b];
   const size_t off = (size_t(node) * NT + tile) * kHistWords + w;
-  if (slices > 1) {
+  if (slices > 1 || atomic) {
     if (g) atomicAdd(reinterpret_cast<unsigned long long *>(level_hist) + 2 * off, (unsigned long long)g);
     if (h) atomicAdd(reinterpret_cast<unsigned long long *>(level_hist) + 2 * off + 1, (unsigned long long)h);
     return;
@@ -529,11 +529,11 @@ void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   int slices = 1;
   while (slices < 64 && a.n_build * a.NT * slices < 64) slices <<= 1;
   const dim3 grid(kHistWords / threads, a.NT, a.n_build * slices);
-  if (slices > 1) {
+  if (slices > 1 || a.accumulate) {
     const size_t bytes = size_t(a.level_nodes) * a.NT * kHistWords * 2 * sizeof(long long);
-    ARB_CUDA(cudaMemsetAsync(a.level_hist, 0, bytes, s));
+    if (!a.accumulate) ARB_CUDA(cudaMemsetAsync(a.level_hist, 0, bytes, s));
     reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, slices, false);
+                                                  a.level_hist, nullptr, a.NT, slices, false, true);
     ARB_CUDA(cudaGetLastError());
     count_launch();
     if (a.subtract) launch_subtract(a.level_hist, a.parent_hist, a.built_child, a.level_nodes / 2, a.NT, s);
@@ -541,10 +541,10 @@ void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   }
   if (a.subtract)
     reduce_kernel<true><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node, a.level_hist,
-                                                 a.parent_hist, a.NT, 1, false);
+                                                 a.parent_hist, a.NT, 1, false, false);
   else
     reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, 1, a.zero_sibling);
+                                                  a.level_hist, nullptr, a.NT, 1, a.zero_sibling, false);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

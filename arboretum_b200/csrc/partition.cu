@@ -211,7 +211,7 @@ __global__ void partition_finish_kernel(const unsigned *__restrict__ cursors,
   node_begin_next[2 * node] = node_begin[node];
   node_begin_next[2 * node + 1] = node_begin[node] + nl;
   if (node == L - 1) node_begin_next[2 * L] = node_begin[L];
-  rec[node].left_count = nl;
+  rec[node].left_count += nl;  // cleared by the split search; row chunks add up
 }
 
 }  // namespace

@@ -366,3 +366,49 @@ def test_bad_calls_return_errors():
         arboretum.train(make_config(0, 3, colsample_bytree=0.01), arboretum.DMatrix(X, y=y), 1)
     with pytest.raises(arboretum.ArboretumError):
         arboretum.train(make_config(0, 3), arboretum.DMatrix(X), 1)  # no labels
+
+
+# ---------------------------------------------------------------------------------
+# out-of-core: row chunks streamed from pinned host memory
+# ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("resident", [0, 1, -1])
+@pytest.mark.parametrize("kind,objective", [("logistic", 1), ("linear", 0)])
+def test_out_of_core_chunks_give_identical_trees(resident, kind, objective):
+    """Histograms are exact integer sums, so cutting the rows into streamed chunks
+    must not change a single bit of the model."""
+    arboretum = arb()
+    X, y = synth(kind, 30011, 28, seed=31)
+    base = make_config(objective, 6)
+    ref = arboretum.train(base, arboretum.DMatrix(X, y=y), 4)
+    cfg = make_config(objective, 6)
+    cfg["internals"]["chunk_rows"] = 7000
+    cfg["internals"]["resident_chunks"] = resident
+    data = arboretum.DMatrix(X, y=y)
+    model = arboretum.train(cfg, data, 4)
+    assert json.loads(model.dump())["model"] == json.loads(ref.dump())["model"]
+    assert np.array_equal(model.train_yhat(), ref.train_yhat())
+    assert (model.level_stats(3)["node_begin"] == ref.level_stats(3)["node_begin"]).all()
+
+
+def test_out_of_core_prebinned_input():
+    arboretum = arb()
+    rng = np.random.default_rng(77)
+    n, F = 40000, 100  # the pre-binned configuration's shape: 100 uint8 features
+    bins = rng.integers(0, 255, size=(n, F)).astype(np.uint8)
+    active = rng.choice(F, 10, replace=False)
+    logit = ((bins[:, active] / 255.0 - 0.5) * rng.normal(0, 2, 10)).sum(axis=1)
+    y = (rng.random(n) < 1 / (1 + np.exp(-logit))).astype(np.float32)
+    base = make_config(1, 5)
+    ref = arboretum.train(base, arboretum.DMatrix(bins, y=y, binned_hist_size=255), 3)
+    cfg = make_config(1, 5)
+    cfg["internals"]["chunk_rows"] = 9000
+    cfg["internals"]["resident_chunks"] = 1
+    ooc = arboretum.train(cfg, arboretum.DMatrix(bins, y=y, binned_hist_size=255), 3)
+    assert json.loads(ooc.dump())["model"] == json.loads(ref.dump())["model"]
+    o = orc.Oracle(base, missing_bin=True)
+    thr = np.tile(np.arange(255, dtype=np.float32) + 0.5, (F, 1))
+    o.set_binned(bins.T.astype(np.uint16), thr, np.full(F, 255, dtype=np.int32)).set_y(y).grow(3)
+    got, exp = json.loads(ref.dump())["model"], o.model_dict()
+    for a, b in zip(got, exp):
+        assert [nd.get("fid") for nd in a["nodes"]] == [nd.get("fid") for nd in b["nodes"]]
+        assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
