@@ -134,7 +134,9 @@ class DMatrix(object):
             raise ValueError('Input numpy.ndarray must be 2 dimensional')
         if category is not None and not np.issubdtype(category.dtype, np.integer):
             raise ValueError('Categoty''s type must be int like')
-        data = np.array(mat.reshape(mat.size), dtype=np.float32)
+        # no host copy when the caller's matrix is already C-contiguous float32 (the library
+        # copies it to the device during this call and does not keep the pointer)
+        data = np.ascontiguousarray(mat, dtype=np.float32).reshape(mat.size)
         self.handle = ctypes.c_void_p()
         if category is None:
             data_category = None
@@ -156,7 +158,7 @@ class DMatrix(object):
             ctypes.c_int(hist_size), ctypes.byref(self.handle)))
 
     def _init_y(self, y):
-        data = np.array(np.asarray(y).reshape(self.rows), dtype=np.float32)
+        data = np.ascontiguousarray(np.asarray(y).reshape(self.rows), dtype=np.float32)
         _call_and_throw_if_error(_LIB.ASetY(self.handle, _ptr(data)))
 
     def _init_labels(self, labels):

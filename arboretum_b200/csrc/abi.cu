@@ -95,7 +95,26 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
   ARB_CHECK(data != nullptr, "data is NULL");
   ARB_CHECK(ccol == 0, "categorical columns are not supported by this build");
   std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, ccol));
-  m->x.assign(data, data + size_t(nrow) * ncol);
+  // The matrix goes straight into HBM (one host->device copy from the caller's buffer,
+  // no staging copy on the host); quantisation and inference read it there.  Without a
+  // usable device, or when it does not fit beside the training state, a host copy is kept.
+  const size_t bytes = size_t(nrow) * ncol * sizeof(float);
+  size_t free_b = 0, total_b = 0;
+  bool on_device = false;
+  if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && bytes < free_b / 2) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) == cudaSuccess) {
+      m->d_x.p = p;
+      m->d_x.bytes = bytes;
+      on_device = cudaMemcpy(p, data, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+                  cudaGetDevice(&m->device) == cudaSuccess;
+      if (!on_device) m->d_x.release();
+    }
+  }
+  if (!on_device) {
+    cudaGetLastError();  // clear the error state: the host copy below is the fallback storage
+    m->x.assign(data, data + size_t(nrow) * ncol);
+  }
   *out = m.release();
   ARB_CATCH
 }

@@ -29,9 +29,12 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
   pitch = PitchFor(F, bin_bytes);
   const size_t n = size_t(rows);
   if (!prebinned) {
-    DevBuf d_x, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
-    d_x.alloc(n * F * sizeof(float));
-    ARB_CUDA(cudaMemcpyAsync(d_x.p, x.data(), n * F * sizeof(float), cudaMemcpyHostToDevice, s));
+    DevBuf d_x_tmp, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
+    if (!d_x.p) {
+      d_x_tmp.alloc(n * F * sizeof(float));
+      ARB_CUDA(cudaMemcpyAsync(d_x_tmp.p, x.data(), n * F * sizeof(float), cudaMemcpyHostToDevice, s));
+    }
+    const DevBuf &d_x = this->d_x.p ? this->d_x : d_x_tmp;
     if (!thresholds_given) {
       d_col.alloc(n * sizeof(float));
       d_sorted.alloc(n * sizeof(float));
@@ -173,6 +176,11 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   K_ = int(tp.labels_count);
   ARB_CHECK(tp.depth >= 2 && tp.depth <= kMaxLevels, "max_depth must be in [1, 15]");
   ARB_CHECK(n_ < (size_t(1) << 31), "row count must be below 2^31");
+  if (d->device >= 0) {
+    int cur = -1;
+    ARB_CUDA(cudaGetDevice(&cur));
+    ARB_CHECK(cur == d->device, "the DMatrix was created on another CUDA device than the Garden uses");
+  }
   levels_ = int(tp.depth) - 1;
   max_nodes_ = 1 << (levels_ - 1);
   nb_stride_ = 2 * max_nodes_ + 1;
@@ -213,12 +221,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     ARB_CUDA(cudaMemcpyAsync(d_y_.p, d->y.data(), n_ * sizeof(float), cudaMemcpyHostToDevice, s));
   }
   d_yhat_.alloc(n_ * K_ * sizeof(float));
-  {  // garden.cu:105: y_hat starts at IntoInternal(initial_y)
-    std::vector<float> init(n_ * K_, g->InternalInitialY());
-    ARB_CUDA(cudaMemcpyAsync(d_yhat_.p, init.data(), init.size() * sizeof(float),
-                             cudaMemcpyHostToDevice, s));
-    ARB_CUDA(cudaStreamSynchronize(s));
-  }
+  // garden.cu:105: y_hat starts at IntoInternal(initial_y)
+  launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
   d_rowid_[0].alloc(n_ * sizeof(unsigned));
   d_rowid_[1].alloc(n_ * sizeof(unsigned));
@@ -730,10 +734,11 @@ struct RowFeeder {
   explicit RowFeeder(DataMatrix *dm) : d(dm) {
     const size_t row_bytes = size_t(d->cols_dense) * sizeof(float);
     chunk = std::max<size_t>(1, std::min<size_t>(size_t(d->rows), (size_t(1) << 30) / row_bytes));
-    buf.alloc(chunk * row_bytes);
+    if (!d->d_x.p) buf.alloc(chunk * row_bytes);
   }
   const float *load(size_t first, size_t count, cudaStream_t s) {
     const int F = d->cols_dense;
+    if (d->d_x.p) return d->d_x.as<float>() + first * F;  // already in HBM
     if (d->prebinned) {  // pre-binned rows predict on their bin ids as values
       staged.resize(count * F);
       for (size_t i = 0; i < count * F; ++i) staged[i] = float(d->host_bins[first * F + i]);
@@ -759,12 +764,10 @@ void Garden::Predict(DataMatrix *data, std::vector<float> &out, int n_rounds) {
   d_int.alloc(feed.chunk * K * sizeof(float));
   d_out.alloc(feed.chunk * K * sizeof(float));
   const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>()};
-  std::vector<float> init;
   for (size_t first = 0; first < n; first += feed.chunk) {
     const size_t count = std::min(feed.chunk, n - first);
     const float *X = feed.load(first, count, stream);
-    init.assign(count * K, InternalInitialY());
-    ARB_CUDA(cudaMemcpyAsync(d_int.p, init.data(), count * K * sizeof(float), cudaMemcpyHostToDevice, stream));
+    launch_fill(d_int.as<float>(), count * K, InternalInitialY(), stream);
     launch_predict(X, count, data->cols_dense, pt, 0, use, int(cfg.tree.depth), d_int.as<float>(), stream);
     launch_link(cfg.objective, K, count, d_int.as<float>(), d_out.as<float>(), stream);
     ARB_CUDA(cudaMemcpyAsync(out.data() + first * K, d_out.p, count * K * sizeof(float),
@@ -782,10 +785,7 @@ void Garden::UpdateByLastTree(DataMatrix *data) {
   if (!data->d_yhat.p || data->yhat_planes != K) {
     data->d_yhat.alloc(n * K * sizeof(float));
     data->yhat_planes = K;
-    std::vector<float> init(n * K, InternalInitialY());
-    ARB_CUDA(cudaMemcpyAsync(data->d_yhat.p, init.data(), init.size() * sizeof(float),
-                             cudaMemcpyHostToDevice, stream));
-    ARB_CUDA(cudaStreamSynchronize(stream));
+    launch_fill(data->d_yhat.as<float>(), n * K, InternalInitialY(), stream);
   }
   SyncForest();
   RowFeeder feed(data);

@@ -23,7 +23,10 @@ class DataMatrix {
   int64_t rows;
   int cols_dense;
   int cols_cat;
-  std::vector<float> x;  // dense features, row-major copy of the caller's matrix
+  std::vector<float> x;  // dense features, row-major copy of the caller's matrix (only when
+                         // the device copy below could not be made)
+  DevBuf d_x;            // the same matrix in HBM, uploaded at construction
+  int device = -1;       // device that holds d_x
   std::vector<float> y;
   std::vector<unsigned char> labels;
   std::vector<float> weights;

@@ -177,6 +177,7 @@ struct PackedTree {  // device arrays of one forest
 };
 void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tree, int n_trees,
                     int depth, float *out /*[K][n]*/, cudaStream_t s);
+void launch_fill(float *dst, size_t n, float value, cudaStream_t s);
 void launch_link(int objective, int K, size_t n, const float *internal /*[K][n]*/,
                  float *out /*[n][K]*/, cudaStream_t s);
 

@@ -186,6 +186,12 @@ __global__ void link_kernel(int objective, int K, size_t n, const float *__restr
   }
 }
 
+__global__ void fill_kernel(float *dst, size_t n, float v) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = v;
+}
+
 inline int grid_for(size_t n, int threads) {
   return int(std::min<size_t>((n + threads - 1) / threads, size_t(148) * 16));
 }
@@ -255,6 +261,13 @@ void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tre
   if (n_trees <= 0 || n == 0) return;
   const int threads = 256;
   predict_kernel<<<grid_for(n, threads), threads, 0, s>>>(X, n, F, t, first_tree, n_trees, depth, out);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_fill(float *dst, size_t n, float value, cudaStream_t s) {
+  if (n == 0) return;
+  fill_kernel<<<grid_for(n, 256), 256, 0, s>>>(dst, n, value);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
