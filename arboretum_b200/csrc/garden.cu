@@ -100,6 +100,12 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     }
     ARB_CUDA(cudaStreamSynchronize(s));
   }
+  if (!out_of_core) {  // feature-major copy: F x N bins more, cheap next to the row-major matrix
+    d_bins_cm.alloc(size_t(F) * n * bin_bytes);
+    launch_transpose_bins(d_bins.as<unsigned char>(), pitch, bin_bytes, n, F,
+                          d_bins_cm.as<unsigned char>(), s);
+    ARB_CUDA(cudaStreamSynchronize(s));
+  }
   max_reduced_bits = 0;
   for (int f = 0; f < F; ++f) {
     int bits = 0;
@@ -202,6 +208,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   geo_.BINS = bins_pad;
   geo_.TW = kHistWords / bins_pad;
   geo_.NT = (F_ + geo_.TW - 1) / geo_.TW;
+  geo_.bins_cm = d->d_bins_cm.as<unsigned char>();
+  geo_.cm_rows = n_;
 
   const int qb = cfg.internal.quant_bits;
   ARB_CHECK(qb >= 10 && qb <= 20, "internals.quant_bits must be in [10, 20]");

@@ -39,6 +39,7 @@ class DataMatrix {
   int bin_bytes = 1;
   size_t pitch = 0;
   DevBuf d_bins;
+  DevBuf d_bins_cm;  // feature-major copy for the row partition (in-core only)
   PinnedBuf h_bins;  // out-of-core: the padded row-major bin matrix in pinned host memory
   bool out_of_core = false;
   std::vector<float> thr;  // [F][hist_size] data_reduced_mapping

@@ -28,6 +28,10 @@ struct Geometry {
   int F;
   int TW, NT, BINS;
   int hist_size;  // bins a split may use (config value); id hist_size = missing
+  // optional feature-major copy bins_cm[f * cm_rows + row] (nullptr: absent): the row
+  // partition reads one feature of many rows, which is sequential in this layout
+  const unsigned char *bins_cm = nullptr;
+  size_t cm_rows = 0;
 };
 
 struct HistLaunch {
@@ -190,6 +194,9 @@ size_t thresholds_scratch_words(size_t n);
 void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist_size]*/,
                     const int *fsize, int hist_size, bool missing_bin, unsigned char *bins,
                     size_t pitch, int bin_bytes, cudaStream_t s);
+// row-major padded bins -> feature-major copy
+void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
+                           unsigned char *bins_cm, cudaStream_t s);
 void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s);
 // sorts n fp32 keys (radix order); tmp sizes itself on first use
 void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s);

@@ -127,6 +127,7 @@ __global__ void plan_fused_kernel(const unsigned *__restrict__ parent_begin,
 template <typename BIN_T>
 __global__ void __launch_bounds__(kPartThreads)
 partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
+                 const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
                  const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
                  const NodeRec *__restrict__ rec, const unsigned *__restrict__ node_begin,
                  unsigned *__restrict__ cursors, const WorkItem *__restrict__ items,
@@ -153,7 +154,11 @@ partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
     if (valid) {
       rid[k] = rowid_src ? rowid_src[item.begin + off] : item.begin + off;
       left = true;
-      if (fid >= 0) left = int(reinterpret_cast<const BIN_T *>(bins + size_t(rid[k]) * pitch)[fid]) <= split_bin;
+      if (fid >= 0) {
+        const int b = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fid) * cm_rows + rid[k]])
+                              : int(reinterpret_cast<const BIN_T *>(bins + size_t(rid[k]) * pitch)[fid]);
+        left = b <= split_bin;
+      }
     }
     const unsigned bal = __ballot_sync(0xffffffffu, left);
     before[k] = __popc(bal & ((1u << lane) - 1));
@@ -255,11 +260,13 @@ void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
   ARB_CUDA(cudaMemsetAsync(a.cursors, 0, 2 * sizeof(unsigned) * a.L, s));
   if (a.geo.bin_bytes == 1)
     partition_kernel<unsigned char><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.rowid_src, a.rowid_dst, a.rec, a.node_begin, a.cursors,
+      a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
+      a.node_begin, a.cursors,
       a.pb.part_items, a.pb.n_part_items);
   else
     partition_kernel<unsigned short><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.rowid_src, a.rowid_dst, a.rec, a.node_begin, a.cursors,
+      a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
+      a.node_begin, a.cursors,
       a.pb.part_items, a.pb.n_part_items);
   ARB_CUDA(cudaGetLastError());
   count_launch();

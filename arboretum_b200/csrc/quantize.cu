@@ -139,6 +139,27 @@ __device__ __forceinline__ unsigned lower_bound_thr(const float *thr, int size, 
   return l;
 }
 
+// 32 rows x 32 features per CTA through shared memory: coalesced on both sides
+template <typename BIN_T>
+__global__ void transpose_bins_kernel(const unsigned char *__restrict__ bins, size_t pitch, size_t n,
+                                      int F, BIN_T *__restrict__ out) {
+  __shared__ BIN_T tile[32][33];
+  const size_t r0 = size_t(blockIdx.x) * 32;
+  const int f0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+  for (int j = ty; j < 32; j += 8) {
+    const size_t r = r0 + j;
+    const int f = f0 + tx;
+    tile[j][tx] = (r < n && f < F) ? reinterpret_cast<const BIN_T *>(bins + r * pitch)[f] : BIN_T(0);
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int f = f0 + j;
+    const size_t r = r0 + tx;
+    if (f < F && r < n) out[size_t(f) * n + r] = tile[tx][j];
+  }
+}
+
 template <typename BIN_T>
 __global__ void binning_kernel(const float *__restrict__ X, size_t n, int F,
                                const float *__restrict__ thr, const int *__restrict__ fsize,
@@ -174,6 +195,18 @@ void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr,
   border_apply_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, seg, hist_size, scratch, thr);
   ARB_CUDA(cudaGetLastError());
   count_launch(4);
+}
+
+void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
+                           unsigned char *bins_cm, cudaStream_t s) {
+  const dim3 grid(unsigned((n + 31) / 32), unsigned((F + 31) / 32));
+  if (bin_bytes == 1)
+    transpose_bins_kernel<unsigned char><<<grid, 256, 0, s>>>(bins, pitch, n, F, bins_cm);
+  else
+    transpose_bins_kernel<unsigned short><<<grid, 256, 0, s>>>(bins, pitch, n, F,
+                                                               reinterpret_cast<unsigned short *>(bins_cm));
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
 }
 
 void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s) {
