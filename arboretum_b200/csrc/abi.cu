@@ -70,6 +70,12 @@ int nccl_allreduce(void *ctx, long long *buf, size_t count, cudaStream_t s) {
   return r == ncclSuccess ? 0 : 1;
 }
 
+int nccl_allreduce_max(void *ctx, unsigned *buf, size_t count, cudaStream_t s) {
+  NcclCtx *c = static_cast<NcclCtx *>(ctx);
+  const ncclResult_t r = g_nccl.AllReduce(buf, buf, count, ncclUint32, ncclMax, c->comm, s);
+  return r == ncclSuccess ? 0 : 1;
+}
+
 void host_scales(float max_g, float max_h, int qb, bool pair, QuantScale *q) {
   int eg = 0, eh = 0;
   if (max_g > 0.0f && std::isfinite(max_g)) std::frexp(max_g, &eg);
@@ -504,6 +510,7 @@ const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128
   const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
   if (r != ncclSuccess) throw std::runtime_error(std::string("ncclCommInitRank: ") + g_nccl.GetErrorString(r));
   g->allreduce = nccl_allreduce;
+  g->allreduce_max = nccl_allreduce_max;
   g->allreduce_ctx = c.release();
   ARB_CATCH
 }

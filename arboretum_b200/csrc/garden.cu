@@ -354,6 +354,10 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   if (g_->profile) ARB_CUDA(cudaEventRecord(ev_[0], s));
   launch_gradients(g_->cfg.objective, K_, n_, d_y_.as<float>(), d_label_.as<unsigned char>(),
                    d_yhat_.as<float>(), d_grad_.p, d_qs_.as<QuantScale>(), s);
+  // row shards must share one fixed-point scale: take the maxima over all ranks
+  if (g_->allreduce_max &&
+      g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
+    throw std::runtime_error("gradient-scale allreduce failed");
   launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
   launch_quantize_grads(d_grad_.p, n_ * K_, pair_, d_qs_.as<QuantScale>(), s);
   if (g_->profile) {

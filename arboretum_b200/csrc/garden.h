@@ -72,6 +72,10 @@ struct Tree {  // reg_tree.h:40-45 + RegTree::label
 // Optional exchange step of multi-GPU training: sums `count` int64 values in
 // place across all ranks, ordered on `stream`.  Returns 0 on success.
 typedef int (*AllreduceFn)(void *ctx, long long *device_buf, size_t count, cudaStream_t stream);
+// The other exchange: element-wise maximum of `count` uint32 values over all ranks (the
+// bit patterns of the round's largest |gradient| and hessian, which fix the fixed-point
+// scale: every rank must quantise with the same one).
+typedef int (*AllreduceMaxFn)(void *ctx, unsigned *device_buf, size_t count, cudaStream_t stream);
 
 struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
   double grad = 0, hist = 0, subtract = 0, split = 0, partition = 0, plan = 0, update = 0, allreduce = 0;
@@ -109,6 +113,7 @@ class Garden {
 
   std::vector<Tree> trees;
   AllreduceFn allreduce = nullptr;
+  AllreduceMaxFn allreduce_max = nullptr;
   void *allreduce_ctx = nullptr;
   bool profile = false;
   PhaseTimes times;

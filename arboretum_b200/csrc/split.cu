@@ -100,10 +100,11 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
   }
   float bgain = 0.0f;
   int bbin = -1;
-  // the gain search of a (node, tile) is dealt to `parts` CTAs by bin chunk; all of
-  // them redo the cheap prefix sums above
+  // the gain search of a (node, tile) is dealt to `parts` CTAs (a power of two): bin k of
+  // every thread's 8 goes to CTA k % parts; all of them redo the cheap prefix sums above,
+  // so the long double-precision chains run side by side instead of one after another
   const bool active = f < F && feature_active[f];
-  if (active && th != 0 && chunk % parts == int(blockIdx.z)) {
+  if (active && th != 0) {
     const double isg = qs->inv_sg, ish = qs->inv_sh;
     const double dtg = double(tg) * isg, dth = double(th) * ish;
     long long rg = og, rh = oh;
@@ -113,6 +114,7 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
       rg += v[k].x;
       rh += v[k].y;
       if (bin >= hist_size) continue;  // ids >= hist_size hold missing values: never a threshold
+      if ((k & (parts - 1)) != int(blockIdx.z)) continue;  // another CTA's candidate
       unsigned long long lc, tc;
       if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
         lc = rh > 0;
@@ -160,8 +162,7 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   ARB_CUDA(cudaMemsetAsync(a.keys, 0, (sizeof(unsigned long long) + sizeof(unsigned)) * a.max_nodes, s));
   unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
   // spread the double-precision gain arithmetic of small levels over the GPU
-  int parts = 1;
-  while (parts < 4 && a.L * a.geo.NT * parts < 148) parts <<= 1;
+  const int parts = kBinsPerThread;
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair)
     split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,

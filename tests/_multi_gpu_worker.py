@@ -15,17 +15,17 @@ import arboretum_b200 as arboretum  # noqa: E402
 from arboretum_b200 import distributed as adist  # noqa: E402
 
 
-def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+def run_case(rank, world, local, objective):
     rng = np.random.default_rng(123)
     n, F, rounds = 60000, 28, 4
     X = rng.normal(size=(n, F)).astype(np.float32)
     w = rng.normal(size=F)
-    y = (rng.random(n) < 1 / (1 + np.exp(-(X @ w * 0.5 + 0.3 * X[:, 0] * X[:, 1])))).astype(np.float32)
-    cfg = {"objective": 1, "method": 1,
+    if objective == 1:
+        y = (rng.random(n) < 1 / (1 + np.exp(-(X @ w * 0.5 + 0.3 * X[:, 0] * X[:, 1])))).astype(np.float32)
+    else:
+        y = (X @ w + rng.normal(0, 0.1, n)).astype(np.float32)
+        y[-5:] += 300.0  # the largest |gradient| lives in the last shard only
+    cfg = {"objective": objective, "method": 1,
            "internals": {"hist_size": 255, "seed": 0, "device": local},
            "verbose": {"gpu": False, "booster": False, "data": False},
            "tree": {"eta": 0.1, "max_depth": 6, "lambda": 1.0, "min_child_weight": 1.0}}
@@ -48,13 +48,25 @@ def main():
         full.set_thresholds(thr, size)
         single = json.loads(arboretum.train(cfg, full, rounds).dump())["model"]
         ok = single == sharded
-        print("MULTI_GPU_TREES_IDENTICAL" if ok else "MULTI_GPU_TREES_DIFFER", flush=True)
     # every rank must hold the same model
     digest = torch.tensor([zlib.crc32(json.dumps(sharded).encode()) % (2 ** 31)], device="cuda")
     gathered = [torch.zeros_like(digest) for _ in range(world)]
     dist.all_gather(gathered, digest)
     same = all(int(g.item()) == int(digest.item()) for g in gathered)
+    return ok, same
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ok = same = True
+    for objective in (1, 0):
+        o, s = run_case(rank, world, local, objective)
+        ok, same = ok and o, same and s
     if rank == 0:
+        print("MULTI_GPU_TREES_IDENTICAL" if ok else "MULTI_GPU_TREES_DIFFER", flush=True)
         print("MULTI_GPU_RANKS_AGREE" if same else "MULTI_GPU_RANKS_DISAGREE", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if (ok and same) else 1)
