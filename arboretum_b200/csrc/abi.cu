@@ -87,6 +87,32 @@ void host_scales(float max_g, float max_h, int qb, bool pair, QuantScale *q) {
   q->max_g_bits = q->max_h_bits = 0;
 }
 
+// Targets follow the matrix: when it sits in HBM they are copied straight from the
+// caller's buffer to the same device (no host copy is kept); false = keep them on the host.
+bool upload_beside_matrix(DataMatrix *d, DevBuf &dst, const void *src, size_t bytes) {
+  if (d->device < 0) return false;
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return false;
+  if (cur != d->device && cudaSetDevice(d->device) != cudaSuccess) return false;
+  bool ok = true;
+  if (dst.bytes != bytes) {
+    dst.release();
+    void *p = nullptr;
+    ok = cudaMalloc(&p, bytes) == cudaSuccess;
+    if (ok) {
+      dst.p = p;
+      dst.bytes = bytes;
+    }
+  }
+  ok = ok && cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    dst.release();
+  }
+  if (cur != d->device) cudaSetDevice(cur);
+  return ok;
+}
+
 }  // namespace
 
 extern "C" {
@@ -101,6 +127,7 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
   ARB_CHECK(data != nullptr, "data is NULL");
   ARB_CHECK(ccol == 0, "categorical columns are not supported by this build");
   std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, ccol));
+  StageTrace trace("ACreateFromDenseMatrix");
   // The matrix goes straight into HBM (one host->device copy from the caller's buffer,
   // no staging copy on the host); quantisation and inference read it there.  Without a
   // usable device, or when it does not fit beside the training state, a host copy is kept.
@@ -121,6 +148,7 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
     cudaGetLastError();  // clear the error state: the host copy below is the fallback storage
     m->x.assign(data, data + size_t(nrow) * ncol);
   }
+  trace.lap("matrix to HBM");
   *out = m.release();
   ARB_CATCH
 }
@@ -134,7 +162,26 @@ const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol,
   std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, 0));
   m->prebinned = true;
   m->hist_size = hist_size;
-  m->host_bins.assign(bins, bins + size_t(nrow) * ncol);
+  // Like the dense constructor: the rows go to HBM right away when they take at most a
+  // quarter of the free memory (training needs the padded copy and its transpose too);
+  // larger inputs stay on the host, for out-of-core training.
+  const size_t bytes = size_t(nrow) * ncol;
+  size_t free_b = 0, total_b = 0;
+  bool on_device = false;
+  if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && bytes <= free_b / 4) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) == cudaSuccess) {
+      m->d_raw.p = p;
+      m->d_raw.bytes = bytes;
+      on_device = cudaMemcpy(p, bins, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+                  cudaGetDevice(&m->device) == cudaSuccess;
+      if (!on_device) m->d_raw.release();
+    }
+  }
+  if (!on_device) {
+    cudaGetLastError();
+    m->host_bins.assign(bins, bins + bytes);
+  }
   *out = m.release();
   ARB_CATCH
 }
@@ -143,7 +190,7 @@ const char *ASetY(VoidPointer data, const float *y) {
   ARB_TRY
   ARB_CHECK(data && y, "NULL argument");
   DataMatrix *d = static_cast<DataMatrix *>(data);
-  d->y.assign(y, y + d->rows);
+  if (!upload_beside_matrix(d, d->d_y, y, size_t(d->rows) * sizeof(float))) d->y.assign(y, y + d->rows);
   ARB_CATCH
 }
 
@@ -151,7 +198,8 @@ const char *ASetLabel(VoidPointer data, const unsigned char *labels) {
   ARB_TRY
   ARB_CHECK(data && labels, "NULL argument");
   DataMatrix *d = static_cast<DataMatrix *>(data);
-  d->labels.assign(labels, labels + d->rows);
+  if (!upload_beside_matrix(d, d->d_labels, labels, size_t(d->rows)))
+    d->labels.assign(labels, labels + d->rows);
   ARB_CATCH
 }
 
@@ -351,6 +399,8 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   j["hist_rows"] = Json::number(t.hist_rows);
   j["hist_row_features"] = Json::number(t.hist_features);
   j["hist_bytes"] = Json::number(t.hist_bytes);
+  j["tree_ms"] = Json::number(t.tree);
+  j["h2d_bytes"] = Json::number(t.h2d_bytes);
   j["kernel_launches"] = Json::integer(g_kernel_launches);
   static thread_local std::string text;
   text.clear();

@@ -2,6 +2,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+
 #include <cstdint>
 #include <cstdio>
 #include <stdexcept>
@@ -83,6 +87,24 @@ static inline int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); 
 // Kernels of this library launched so far in this process (reported by AGetTimings).
 extern long long g_kernel_launches;
 static inline void count_launch(int n = 1) { g_kernel_launches += n; }
+
+// Host-side stage timer of the set-up paths: with ARBORETUM_TRACE set in the environment,
+// lap("name") synchronises the device and prints the wall time since the previous lap.
+struct StageTrace {
+  bool on;
+  std::chrono::steady_clock::time_point t;
+  const char *scope;
+  explicit StageTrace(const char *scope_name)
+      : on(std::getenv("ARBORETUM_TRACE") != nullptr), t(std::chrono::steady_clock::now()), scope(scope_name) {}
+  void lap(const char *what) {
+    if (!on) return;
+    cudaDeviceSynchronize();
+    const auto now = std::chrono::steady_clock::now();
+    std::fprintf(stderr, "[arboretum] %s: %s %.3f ms\n", scope, what,
+                 std::chrono::duration<double, std::milli>(now - t).count());
+    t = now;
+  }
+};
 
 // ---------------------------------------------------------------------------
 // Device-side records of the level loop.

@@ -9,6 +9,8 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <thread>
+#include <vector>
 
 namespace arb {
 
@@ -17,6 +19,26 @@ long long g_kernel_launches = 0;
 // ---------------------------------------------------------------------------
 // DataMatrix
 // ---------------------------------------------------------------------------
+namespace {
+// unpadded rows -> padded rows on the host, rows dealt to a few threads
+void pad_rows_host(const unsigned char *src, size_t F, size_t n, unsigned char *dst, size_t pitch) {
+  const unsigned hw = std::max(1u, std::min(16u, std::thread::hardware_concurrency()));
+  const size_t per = (n + hw - 1) / hw;
+  std::vector<std::thread> pool;
+  for (unsigned t = 0; t < hw; ++t) {
+    const size_t lo = std::min(n, t * per), hi = std::min(n, lo + per);
+    if (lo == hi) break;
+    pool.emplace_back([=]() {
+      for (size_t r = lo; r < hi; ++r) {
+        std::memcpy(dst + r * pitch, src + r * F, F);
+        std::memset(dst + r * pitch + F, 0, pitch - F);
+      }
+    });
+  }
+  for (auto &th : pool) th.join();
+}
+}  // namespace
+
 void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows) {
   if (binned) return;
   out_of_core = chunk_rows > 0 && chunk_rows < rows;
@@ -28,6 +50,7 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
   bin_bytes = hs < 256 ? 1 : 2;
   pitch = PitchFor(F, bin_bytes);
   const size_t n = size_t(rows);
+  StageTrace trace("InitHist");
   if (!prebinned) {
     DevBuf d_x_tmp, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
     if (!d_x.p) {
@@ -36,16 +59,21 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     }
     const DevBuf &d_x = this->d_x.p ? this->d_x : d_x_tmp;
     if (!thresholds_given) {
-      d_col.alloc(n * sizeof(float));
+      const int block_cols = std::min(F, 32);  // columns made contiguous at a time
+      d_col.alloc(n * block_cols * sizeof(float));
       d_sorted.alloc(n * sizeof(float));
       d_scratch.alloc(thresholds_scratch_words(n) * sizeof(unsigned));
       d_thr_f.alloc(size_t(F) * hs * sizeof(float));
-      for (int f = 0; f < F; ++f) {
-        launch_extract_column(d_x.as<float>(), n, F, f, d_col.as<float>(), s);
-        sort_floats(d_col.as<float>(), d_sorted.as<float>(), n, d_tmp, s);
-        launch_thresholds(d_sorted.as<float>(), n, hs, d_thr_f.as<float>() + size_t(f) * hs,
-                          d_scratch.as<unsigned>(), s);
+      for (int f0 = 0; f0 < F; f0 += block_cols) {
+        const int nf = std::min(block_cols, F - f0);
+        launch_transpose_columns(d_x.as<float>(), n, F, f0, nf, d_col.as<float>(), s);
+        for (int f = f0; f < f0 + nf; ++f) {
+          sort_floats(d_col.as<float>() + size_t(f - f0) * n, d_sorted.as<float>(), n, d_tmp, s);
+          launch_thresholds(d_sorted.as<float>(), n, hs, d_thr_f.as<float>() + size_t(f) * hs,
+                            d_scratch.as<unsigned>(), s);
+        }
       }
+      trace.lap("column sorts + thresholds");
       thr.resize(size_t(F) * hs);
       ARB_CUDA(cudaMemcpyAsync(thr.data(), d_thr_f.p, thr.size() * sizeof(float),
                                cudaMemcpyDeviceToHost, s));
@@ -74,11 +102,24 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     }
     ARB_CUDA(cudaStreamSynchronize(s));
     if (out_of_core) d_bins.release();
+    trace.lap("binning");
   } else if (out_of_core) {
     ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
     h_bins.alloc(n * pitch);
-    std::memset(h_bins.p, 0, n * pitch);
-    ARB_CUDA(cudaMemcpy2D(h_bins.p, pitch, host_bins.data(), size_t(F), size_t(F), n, cudaMemcpyHostToHost));
+    if (d_raw.p) {  // pad on the device, a slab of rows at a time, and bring the slabs back
+      const size_t slab = std::min<size_t>(n, size_t(1) << 24);
+      DevBuf d_slab;
+      d_slab.alloc(slab * pitch);
+      for (size_t first = 0; first < n; first += slab) {
+        const size_t count = std::min(slab, n - first);
+        launch_pad_rows(d_raw.as<unsigned char>() + first * F, F, count, d_slab.as<unsigned char>(), pitch, s);
+        ARB_CUDA(cudaMemcpyAsync(h_bins.as<unsigned char>() + first * pitch, d_slab.p, count * pitch,
+                                 cudaMemcpyDeviceToHost, s));
+      }
+      ARB_CUDA(cudaStreamSynchronize(s));
+    } else {
+      pad_rows_host(host_bins.data(), size_t(F), n, h_bins.as<unsigned char>(), pitch);
+    }
     if (thr.empty()) {
       thr.resize(size_t(F) * hs);
       fsize.assign(F, hs);
@@ -89,9 +130,13 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     // rows arrive already binned: copy them into the padded row-major layout
     ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
     d_bins.alloc(n * pitch);
-    ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
-    ARB_CUDA(cudaMemcpy2DAsync(d_bins.p, pitch, host_bins.data(), size_t(F), size_t(F), n,
-                               cudaMemcpyHostToDevice, s));
+    if (d_raw.p) {
+      launch_pad_rows(d_raw.as<unsigned char>(), F, n, d_bins.as<unsigned char>(), pitch, s);
+    } else {
+      ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
+      ARB_CUDA(cudaMemcpy2DAsync(d_bins.p, pitch, host_bins.data(), size_t(F), size_t(F), n,
+                                 cudaMemcpyHostToDevice, s));
+    }
     if (thr.empty()) {  // threshold of bin q is q + 0.5: "bin <= q" <=> "value < q + 0.5"
       thr.resize(size_t(F) * hs);
       fsize.assign(F, hs);
@@ -106,6 +151,7 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
                           d_bins_cm.as<unsigned char>(), s);
     ARB_CUDA(cudaStreamSynchronize(s));
   }
+  trace.lap("feature-major copy (and temporaries freed)");
   max_reduced_bits = 0;
   for (int f = 0; f < F; ++f) {
     int bits = 0;
@@ -123,6 +169,9 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
 class Builder {
  public:
   Builder(Garden *g, DataMatrix *d);
+  ~Builder();
+  Builder(const Builder &) = delete;
+  Builder &operator=(const Builder &) = delete;
   void UpdateGrad();
   void GrowTree(int label, Tree *tree);
   DataMatrix *data;
@@ -147,6 +196,7 @@ class Builder {
   std::vector<unsigned> h_nb_total_;
   PlanBuffers pb_;
   cudaEvent_t ev_[2 * 8 * kMaxLevels];
+  cudaEvent_t ev_tree_[2];
   // Row chunks (out-of-core): a chunk is a contiguous range of rows whose bins are
   // either resident in HBM or streamed from pinned host memory into one of two
   // staging buffers once per level.  In-core training is one resident chunk.
@@ -177,6 +227,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const Configuration &cfg = g->cfg;
   const TreeParam &tp = cfg.tree;
   cudaStream_t s = g->stream;
+  StageTrace trace("Builder");
   n_ = size_t(d->rows);
   F_ = d->cols_dense;
   K_ = int(tp.labels_count);
@@ -194,9 +245,9 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   ARB_CHECK(!(pair_ && tp.min_leaf_size > 1),
             "min_leaf_size > 1 with a (gradient, hessian) objective is not supported by this build");
   if (cfg.objective == kSoftMaxOneVsAll)
-    ARB_CHECK(d->labels.size() == n_, "multi:softmax needs labels (ASetLabel)");
+    ARB_CHECK(d->has_labels(), "multi:softmax needs labels (ASetLabel)");
   else
-    ARB_CHECK(d->y.size() == n_, "labels are not set (ASetY)");
+    ARB_CHECK(d->has_y(), "labels are not set (ASetY)");
 
   geo_.bins = d->d_bins.as<unsigned char>();
   geo_.pitch = d->pitch;
@@ -222,11 +273,15 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
 
   // per-row state
   if (cfg.objective == kSoftMaxOneVsAll) {
-    d_label_.alloc(n_);
-    ARB_CUDA(cudaMemcpyAsync(d_label_.p, d->labels.data(), n_, cudaMemcpyHostToDevice, s));
+    if (!d->d_labels.p) {
+      d_label_.alloc(n_);
+      ARB_CUDA(cudaMemcpyAsync(d_label_.p, d->labels.data(), n_, cudaMemcpyHostToDevice, s));
+    }
   } else {
-    d_y_.alloc(n_ * sizeof(float));
-    ARB_CUDA(cudaMemcpyAsync(d_y_.p, d->y.data(), n_ * sizeof(float), cudaMemcpyHostToDevice, s));
+    if (!d->d_y.p) {
+      d_y_.alloc(n_ * sizeof(float));
+      ARB_CUDA(cudaMemcpyAsync(d_y_.p, d->y.data(), n_ * sizeof(float), cudaMemcpyHostToDevice, s));
+    }
   }
   d_yhat_.alloc(n_ * K_ * sizeof(float));
   // garden.cu:105: y_hat starts at IntoInternal(initial_y)
@@ -234,6 +289,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
   d_rowid_[0].alloc(n_ * sizeof(unsigned));
   d_rowid_[1].alloc(n_ * sizeof(unsigned));
+  trace.lap("per-row state");
   // level state
   {
     const size_t chunk_rows = d->out_of_core ? size_t(cfg.internal.chunk_rows) : n_;
@@ -277,13 +333,16 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   pb_.scratch_begin = d_scratch_.as<unsigned>();
   pb_.scratch_len = d_scratch_.as<unsigned>() + max_nodes_;
   pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * max_nodes_);
+  trace.lap("level buffers");
   h_rec_.alloc(d_rec_.bytes);
   h_leaf_w_.alloc(d_leaf_w_.bytes);
   h_node_begin_.alloc(d_node_begin_.bytes);
   active_fids_.resize(F_);
   active_host_.resize(size_t(levels_) * F_);
   for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
+  for (auto &e : ev_tree_) ARB_CUDA(cudaEventCreate(&e));
   ARB_CUDA(cudaStreamSynchronize(s));
+  trace.lap("pinned read-back buffers + events");
   if (!d->out_of_core) {
     chunks_[0].resident = d->d_bins.as<unsigned char>();
   } else {
@@ -320,6 +379,19 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   }
 }
 
+Builder::~Builder() {
+  for (auto &e : ev_) cudaEventDestroy(e);
+  for (auto &e : ev_tree_) cudaEventDestroy(e);
+  if (copy_stream_) {
+    cudaStreamSynchronize(copy_stream_);
+    for (int i = 0; i < 2; ++i) {
+      cudaEventDestroy(stage_ready_[i]);
+      cudaEventDestroy(stage_free_[i]);
+    }
+    cudaStreamDestroy(copy_stream_);
+  }
+}
+
 // Copy the next chunk of the endless cyclic visiting sequence into its staging buffer.
 void Builder::IssueCopy() {
   const Chunk &ch = chunks_[streamed_[issued_ % streamed_.size()]];
@@ -328,6 +400,7 @@ void Builder::IssueCopy() {
   ARB_CUDA(cudaMemcpyAsync(d_stage_[buf].p, data->h_bins.as<unsigned char>() + ch.begin * data->pitch,
                            ch.rows * data->pitch, cudaMemcpyHostToDevice, copy_stream_));
   ARB_CUDA(cudaEventRecord(stage_ready_[buf], copy_stream_));
+  if (g_->profile) g_->times.h2d_bytes += double(ch.rows * data->pitch);
   ++issued_;
 }
 
@@ -352,7 +425,10 @@ void Builder::Release(int chunk) {
 void Builder::UpdateGrad() {  // objective.cu:28-56
   cudaStream_t s = g_->stream;
   if (g_->profile) ARB_CUDA(cudaEventRecord(ev_[0], s));
-  launch_gradients(g_->cfg.objective, K_, n_, d_y_.as<float>(), d_label_.as<unsigned char>(),
+  // targets uploaded with the matrix are read where they are (a later ASetY is seen too)
+  const float *y = data->d_y.p ? data->d_y.as<float>() : d_y_.as<float>();
+  const unsigned char *labels = data->d_labels.p ? data->d_labels.as<unsigned char>() : d_label_.as<unsigned char>();
+  launch_gradients(g_->cfg.objective, K_, n_, y, labels,
                    d_yhat_.as<float>(), d_grad_.p, d_qs_.as<QuantScale>(), s);
   // row shards must share one fixed-point scale: take the maxima over all ranks
   if (g_->allreduce_max &&
@@ -394,6 +470,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   }
   ARB_CUDA(cudaMemcpyAsync(d_active_.p, active_host_.data(), active_host_.size(),
                            cudaMemcpyHostToDevice, s));
+  if (prof) ARB_CUDA(cudaEventRecord(ev_tree_[0], s));
 
   const bool use_trick = cfg.internal.use_hist_subtraction_trick;
   const int n_chunks = int(chunks_.size());
@@ -552,6 +629,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     Release(c);
   }
   mark();
+  if (prof) ARB_CUDA(cudaEventRecord(ev_tree_[1], s));
   ARB_CUDA(cudaMemcpyAsync(h_rec_.p, d_rec_.p, d_rec_.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaMemcpyAsync(h_leaf_w_.p, d_leaf_w_.p, d_leaf_w_.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
@@ -595,6 +673,11 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   const float *hw = h_leaf_w_.as<float>();
   for (int i = 0; i < 2 * max_nodes_; ++i) tree->weights[i] = hw[i];
 
+  if (prof) {
+    float ms;
+    ARB_CUDA(cudaEventElapsedTime(&ms, ev_tree_[0], ev_tree_[1]));
+    g_->times.tree += ms;
+  }
   if (prof && multi) g_->times.trees += 1;
   if (prof && !multi) {
     PhaseTimes &t = g_->times;
@@ -751,7 +834,9 @@ struct RowFeeder {
   const float *load(size_t first, size_t count, cudaStream_t s) {
     const int F = d->cols_dense;
     if (d->d_x.p) return d->d_x.as<float>() + first * F;  // already in HBM
-    if (d->prebinned) {  // pre-binned rows predict on their bin ids as values
+    if (d->prebinned && d->d_raw.p) {  // pre-binned rows predict on their bin ids as values
+      launch_u8_to_f32(d->d_raw.as<unsigned char>() + first * F, buf.as<float>(), count * F, s);
+    } else if (d->prebinned) {
       staged.resize(count * F);
       for (size_t i = 0; i < count * F; ++i) staged[i] = float(d->host_bins[first * F + i]);
       ARB_CUDA(cudaMemcpyAsync(buf.p, staged.data(), count * F * sizeof(float), cudaMemcpyHostToDevice, s));

@@ -27,8 +27,11 @@ class DataMatrix {
                          // the device copy below could not be made)
   DevBuf d_x;            // the same matrix in HBM, uploaded at construction
   int device = -1;       // device that holds d_x
-  std::vector<float> y;
+  std::vector<float> y;  // targets on the host (only when the matrix is not in HBM)
   std::vector<unsigned char> labels;
+  DevBuf d_y, d_labels;  // targets in HBM, uploaded by ASetY / ASetLabel beside the matrix
+  bool has_y() const { return d_y.p || y.size() == size_t(rows); }
+  bool has_labels() const { return d_labels.p || labels.size() == size_t(rows); }
   std::vector<float> weights;
 
   // quantised form (built by the first AGrowTree, like DataMatrix::InitHist)
@@ -45,7 +48,9 @@ class DataMatrix {
   std::vector<float> thr;  // [F][hist_size] data_reduced_mapping
   std::vector<int> fsize;  // bins in use per feature
   int max_reduced_bits = 0;
-  std::vector<unsigned char> host_bins;  // caller's pre-binned rows (row-major), if any
+  std::vector<unsigned char> host_bins;  // caller's pre-binned rows (row-major), if they were not
+                                         // uploaded at construction
+  DevBuf d_raw;  // caller's pre-binned rows in HBM, unpadded [rows][cols]
 
   // predictions accumulated by AAppendLastTree, internal scale, [K][rows]
   DevBuf d_yhat;
@@ -84,6 +89,8 @@ struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
   double hist_features = 0;  // features per scanned row (summed per launch)
   double hist_bytes = 0;     // algorithmic bytes of those launches
   long long trees = 0;
+  double tree = 0;       // whole GrowTree calls, device time
+  double h2d_bytes = 0;  // bins streamed from pinned host memory (out-of-core)
 };
 
 class Builder;

@@ -197,7 +197,13 @@ void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist
 // row-major padded bins -> feature-major copy
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
                            unsigned char *bins_cm, cudaStream_t s);
-void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s);
+// caller's unpadded uint8 rows -> the padded row-major layout (pitch a multiple of 4)
+void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *bins, size_t pitch,
+                     cudaStream_t s);
+void launch_u8_to_f32(const unsigned char *src, float *dst, size_t count, cudaStream_t s);
+// columns [f0, f0 + nf) of a row-major fp32 matrix as contiguous columns out[(f - f0) * n + row]
+void launch_transpose_columns(const float *X, size_t n, int F, int f0, int nf, float *out,
+                              cudaStream_t s);
 // sorts n fp32 keys (radix order); tmp sizes itself on first use
 void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s);
 

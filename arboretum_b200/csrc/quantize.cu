@@ -99,16 +99,27 @@ __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_
   __syncthreads();
   unsigned run = block_off[blockIdx.x] + incl - c;
   for (int w = 0; w < warp; ++w) run += warp_sums[w];
+  // Midpoints grow with the position, so a slot keeps the midpoint of its first border.
+  // Only that one is sent to the atomic minimum: a thread drops a border that falls in
+  // the slot of its previous one, and among the lanes of a warp that hold the same slot
+  // in the same step the lowest lane (the smallest position) speaks for all.
+  long long last_slot = -1;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
-    if (!flag[k]) continue;
-    ++run;  // inclusive border count of position i (io.cu:144-153)
-    const size_t i = base + k;
-    const float mid = float((s[i] + s[i - 1]) * 0.5);  // io.cu:72-79
-    const long long a = (long long)run + 1, b = (long long)(i / seg) + 1;
-    const long long slot = (a < b ? a : b) - 2;  // io.cu:257
-    // slots past the table are a defect of the reference (out-of-range write); skipped
-    if (slot >= 0 && slot < hist_size) atomic_min_float(thr + slot, mid);
+    long long slot = -1;
+    float mid = 0.0f;
+    if (flag[k]) {
+      ++run;  // inclusive border count of position i (io.cu:144-153)
+      const size_t i = base + k;
+      mid = float((s[i] + s[i - 1]) * 0.5);  // io.cu:72-79
+      const long long a = (long long)run + 1, b = (long long)(i / seg) + 1;
+      slot = (a < b ? a : b) - 2;  // io.cu:257
+      // slots past the table are a defect of the reference (out-of-range write); skipped
+      if (slot >= hist_size || slot == last_slot) slot = -1;
+      if (slot >= 0) last_slot = slot;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, slot);
+    if (slot >= 0 && (peers & ((1u << lane) - 1)) == 0) atomic_min_float(thr + slot, mid);
   }
 }
 
@@ -117,14 +128,26 @@ __global__ void fill_inf_kernel(float *thr, int n) {
   if (i < n) thr[i] = INFINITY;
 }
 
-__global__ void extract_column_kernel(const float *__restrict__ X, size_t n, int F, int f,
-                                      float *__restrict__ col) {
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += size_t(gridDim.x) * blockDim.x) {
-    float v = X[i * F + f];
-    // every NaN sorts last, as the positive quiet NaN does in the reference's sort
+// columns [f0, f0 + nf) of the row-major matrix -> column-major out[(f - f0) * n + row];
+// 32 x 32 tiles through shared memory, every NaN becomes the positive quiet NaN, which sorts last as in the reference's sort
+__global__ void transpose_f32_kernel(const float *__restrict__ X, size_t n, int F, int f0, int nf,
+                                     float *__restrict__ out) {
+  __shared__ float tile[32][33];
+  const size_t r0 = size_t(blockIdx.x) * 32;
+  const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+  for (int j = ty; j < 32; j += 8) {
+    const size_t r = r0 + j;
+    const int c = c0 + tx;
+    float v = (r < n && c < nf) ? X[r * F + f0 + c] : 0.0f;
     if (v != v) v = __int_as_float(0x7fc00000);
-    col[i] = v;
+    tile[j][tx] = v;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int c = c0 + j;
+    const size_t r = r0 + tx;
+    if (c < nf && r < n) out[size_t(c) * n + r] = tile[tx][j];
   }
 }
 
@@ -158,6 +181,31 @@ __global__ void transpose_bins_kernel(const unsigned char *__restrict__ bins, si
     const size_t r = r0 + tx;
     if (f < F && r < n) out[size_t(f) * n + r] = tile[tx][j];
   }
+}
+
+// unpadded uint8 rows [n][F] -> padded rows [n][pitch] (padding bytes zero), one
+// 32-bit word of the padded row per thread
+__global__ void pad_rows_kernel(const unsigned char *__restrict__ raw, int F, size_t n,
+                                unsigned *__restrict__ out, int words_per_row) {
+  const size_t total = n * size_t(words_per_row);
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = e / words_per_row;
+    const int f0 = int(e - r * words_per_row) * 4;
+    const unsigned char *src = raw + r * F;
+    unsigned w = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (f0 + k < F) w |= unsigned(src[f0 + k]) << (8 * k);
+    out[e] = w;
+  }
+}
+
+__global__ void u8_to_f32_kernel(const unsigned char *__restrict__ src, float *__restrict__ dst,
+                                 size_t count) {
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < count;
+       e += size_t(gridDim.x) * blockDim.x)
+    dst[e] = float(src[e]);
 }
 
 template <typename BIN_T>
@@ -209,10 +257,29 @@ void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_byte
   count_launch();
 }
 
-void launch_extract_column(const float *X, size_t n, int F, int f, float *col, cudaStream_t s) {
-  const int threads = 256;
-  const int grid = int(std::min<size_t>((n + threads - 1) / threads, size_t(148) * 16));
-  extract_column_kernel<<<grid, threads, 0, s>>>(X, n, F, f, col);
+void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *bins, size_t pitch,
+                     cudaStream_t s) {
+  if (n == 0) return;
+  const int words = int(pitch / 4);
+  const size_t total = n * size_t(words);
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
+  pad_rows_kernel<<<grid, 256, 0, s>>>(raw, F, n, reinterpret_cast<unsigned *>(bins), words);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_u8_to_f32(const unsigned char *src, float *dst, size_t count, cudaStream_t s) {
+  if (count == 0) return;
+  const int grid = int(std::min<size_t>((count + 255) / 256, size_t(148) * 32));
+  u8_to_f32_kernel<<<grid, 256, 0, s>>>(src, dst, count);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_transpose_columns(const float *X, size_t n, int F, int f0, int nf, float *out,
+                              cudaStream_t s) {
+  const dim3 grid(unsigned((n + 31) / 32), unsigned((nf + 31) / 32));
+  transpose_f32_kernel<<<grid, 256, 0, s>>>(X, n, F, f0, nf, out);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

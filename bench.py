@@ -63,6 +63,91 @@ def make_rows(n, seed):
     return X, y
 
 
+def _cfg(objective, max_depth, eta, **kw):
+    c = json.loads(json.dumps(CONFIG))
+    c["objective"] = objective
+    c["tree"]["max_depth"] = max_depth
+    c["tree"]["eta"] = eta
+    for k, v in kw.items():
+        (c["internals"] if k in ("chunk_rows", "resident_chunks") else c["tree"])[k] = v
+    return c
+
+
+def make_c1(n, seed):  # small regression: y = w.x + 0.5 x0 x1 + N(0, 0.1)
+    rng = np.random.default_rng([1, seed])
+    X = rng.standard_normal((n, 28), dtype=np.float32)
+    w = np.random.default_rng(1).normal(size=28).astype(np.float32)
+    y = X @ w + 0.5 * X[:, 0] * X[:, 1] + rng.normal(0, 0.1, n).astype(np.float32)
+    return X, y.astype(np.float32), None
+
+
+def make_c3(n, seed):  # wide table, 20 % missing; the 10 categorical columns enter as numbers
+    rng = np.random.default_rng([3, seed])
+    F = 2000
+    prm = np.random.default_rng(3)
+    cols = prm.choice(F, 30, replace=False)
+    coef = prm.normal(size=30).astype(np.float32)
+    cards = prm.integers(50, 1001, size=10)
+    X = np.empty((n, F), dtype=np.float32)
+    y = rng.normal(0, 0.5, n).astype(np.float32)
+    for lo in range(0, F, 100):  # column blocks keep the temporaries small
+        blk = np.exp(rng.standard_normal((n, 100), dtype=np.float32))
+        if lo == F - 100:
+            for j in range(10):
+                blk[:, 90 + j] = np.minimum(rng.zipf(1.2, n), cards[j]).astype(np.float32)
+        for k, c in enumerate(cols):
+            if lo <= c < lo + 100:
+                y += coef[k] * np.log1p(blk[:, c - lo])
+        blk[rng.random((n, 100), dtype=np.float32) < 0.2] = np.nan
+        X[:, lo:lo + 100] = blk
+    return X, y.astype(np.float32), None
+
+
+def make_c4(n, seed):  # 10 classes by argmax of random projections plus Gumbel noise
+    rng = np.random.default_rng([4, seed])
+    X = rng.standard_normal((n, 50), dtype=np.float32)
+    W = np.random.default_rng(4).normal(size=(50, 10)).astype(np.float32)
+    labels = np.argmax(X @ W + rng.gumbel(size=(n, 10)).astype(np.float32), axis=1).astype(np.uint8)
+    return X, None, labels
+
+
+def make_c5(n, seed):  # pre-binned uint8, uniform bins, logistic label from 10 active features
+    rng = np.random.default_rng([5, seed])
+    bins = rng.integers(0, 255, size=(n, 100), dtype=np.uint8)
+    prm = np.random.default_rng(5)
+    active = prm.choice(100, 10, replace=False)
+    c = prm.normal(0, 2, 10).astype(np.float32)
+    logit = ((bins[:, active].astype(np.float32) / 255.0 - 0.5) * c).sum(axis=1)
+    y = (rng.random(n, dtype=np.float32) < 1.0 / (1.0 + np.exp(-logit))).astype(np.float32)
+    return bins, y, None
+
+
+def make_c2(n, seed):
+    X, y = make_rows(n, seed)
+    return X, y, None
+
+
+# name -> (default rows, features, generator, configuration, description); the bench
+# line of the driver is c2; the others are the remaining configurations at full size
+WORKLOADS = {
+    "c1": (100_000, 28, make_c1, _cfg(0, 6, 0.1),
+           "regression %d x 28 fp32, reg:linear, max_depth 6, eta 0.1 (configs[0])"),
+    "c2": (FULL_ROWS, FEATURES, make_c2, CONFIG,
+           "binary classification %d x 28 fp32, hist_size 255, reg:logistic, max_depth 8, eta 0.1 "
+           "(configs[1])"),
+    "c3": (1_000_000, 2000, make_c3, _cfg(0, 6, 0.1, colsample_bytree=0.5),
+           "wide table %d x 2000 fp32, 20%% NaN, colsample_bytree 0.5, max_depth 6 (configs[2], "
+           "categorical columns as numbers)"),
+    "c4": (5_000_000, 50, make_c4, _cfg(3, 6, 0.2, labels_count=10),
+           "multi:softmax %d x 50 fp32, 10 classes, max_depth 6, eta 0.2 (configs[3])"),
+    "c5": (50_000_000, 100, make_c5, _cfg(1, 8, 0.1),
+           "pre-binned uint8 %d x 100, reg:logistic, max_depth 8, in HBM (configs[4] shape)"),
+    "c5a": (50_000_000, 100, make_c5, _cfg(1, 8, 0.1, chunk_rows=8_000_000, resident_chunks=0),
+            "pre-binned uint8 %d x 100, reg:logistic, max_depth 8, every chunk streamed from pinned "
+            "host memory (configs[4] mode a)"),
+}
+
+
 class ClockSampler(object):
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -125,11 +210,21 @@ def measured_peak():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-def oracle_rounds_per_s(rows, rounds, warmup):
+def oracle_rounds_per_s(rows, rounds, warmup, workload="c2"):
     """The CPU port of the path on a bounded sample: rounds/s at `rows` rows."""
     from oracle import oracle as orc
-    X, y = make_rows(rows, seed=1000)
-    o = orc.Oracle(CONFIG, missing_bin=True).set_dense(X).set_y(y)
+    _, features, gen, cfg, _ = WORKLOADS[workload]
+    X, y, labels = gen(rows, 1000)
+    o = orc.Oracle(cfg, missing_bin=True)
+    if X.dtype == np.uint8:
+        thr = np.tile(np.arange(255, dtype=np.float32) + 0.5, (features, 1))
+        o.set_binned(np.ascontiguousarray(X.T).astype(np.uint16), thr, np.full(features, 255, dtype=np.int32))
+    else:
+        o.set_dense(X)
+    if labels is not None:
+        o.set_label(labels)
+    else:
+        o.set_y(y)
     o.grow(warmup)
     t0 = time.perf_counter()
     o.grow(rounds)
@@ -143,7 +238,7 @@ def run_reference(args, rank, world):
         return
     sample = min(args.rows, 1_000_000)
     cores = os.cpu_count() or 1
-    rps_sample = oracle_rounds_per_s(sample, max(1, args.steps), max(0, args.warmup))
+    rps_sample = oracle_rounds_per_s(sample, max(1, args.steps), max(0, args.warmup), args.workload)
     value = rps_sample * sample / args.rows  # cost is linear in rows
     line = {"impl": "reference", "metric": "boosting_rounds_per_sec", "value": value,
             "unit": "rounds/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -159,12 +254,13 @@ def run_reference(args, rank, world):
 
 
 def workload_config(args, world):
-    return {"workload": "binary classification %d x %d fp32, hist_size 255, reg:logistic, "
-                        "max_depth 8, eta 0.1 (configs[1])" % (args.rows, FEATURES),
-            "rows": args.rows, "features": FEATURES, "max_depth": 8,
+    _, features, _, cfg, desc = WORKLOADS[args.workload]
+    pitch = (features + 31) // 32 * 32
+    return {"workload": desc % args.rows, "rows": args.rows, "features": features,
+            "max_depth": cfg["tree"]["max_depth"],
             "rows_per_gpu": args.rows // world, "parallelism": "rows sharded x%d" % world,
             "l2": "inputs (bins %.0f MB + gradients %.0f MB per GPU) exceed the 126 MB L2"
-                  % (args.rows // world * 32 / 1e6, args.rows // world * 8 / 1e6)}
+                  % (args.rows // world * pitch / 1e6, args.rows // world * 8 / 1e6)}
 
 
 def main():
@@ -173,9 +269,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--rows", type=int, default=FULL_ROWS)
+    ap.add_argument("--rows", type=int, default=0)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.rows <= 0:
+        args.rows = WORKLOADS[args.workload][0]
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -195,11 +294,15 @@ def main():
 
     args.warmup = max(args.warmup, 3)
     n_local = args.rows // world
-    X, y = make_rows(n_local, seed=rank)
+    _, features, gen, base_cfg, _ = WORKLOADS[args.workload]
+    X, y, labels = gen(n_local, rank)
+    binned = X.dtype == np.uint8
     xp = torch.from_numpy(X).pin_memory()  # the job's host buffers are pinned
-    yp = torch.from_numpy(y).pin_memory()
-    Xh, yh = xp.numpy(), yp.numpy()
-    cfg = json.loads(json.dumps(CONFIG))
+    Xh = xp.numpy()
+    target = labels if labels is not None else y
+    yp = torch.from_numpy(target).pin_memory()
+    yh = yp.numpy()
+    cfg = json.loads(json.dumps(base_cfg))
     cfg["internals"]["device"] = local_rank
 
     def barrier():
@@ -208,11 +311,17 @@ def main():
             dist.barrier()
 
     def new_model():
-        data = arboretum.DMatrix(Xh, y=yh)
+        kw = {"binned_hist_size": 255} if binned else {}
+        if labels is not None:
+            data = arboretum.DMatrix(Xh, labels=yh, **kw)
+        else:
+            data = arboretum.DMatrix(Xh, y=yh, **kw)
         model = arboretum.Garden(cfg)
         model.data = data
-        if world > 1:
+        model.labels_count = data.labels_count
+        if world > 1 and not binned:
             adist.share_thresholds(data, cfg["internals"]["hist_size"], rank, world)
+        if world > 1:
             adist.init_nccl(model, rank, world)
         return model, data
 
@@ -266,19 +375,31 @@ def main():
     t = model.timings()
     model.set_profile(False)
     peak, peak_src = measured_peak()
-    hist_gbs = t["hist_bytes"] / (t["hist_ms"] * 1e-3) / 1e9
-    per_launch_bytes = t["hist_bytes"] / max(1, t["hist_launches"])
-    roofline = {"bound": "hbm", "kernel": "hist_u8_kernel", "achieved": hist_gbs, "peak": peak,
-                "unit": "GB/s", "frac": hist_gbs / peak, "peak_source": peak_src,
-                "frac_of_nominal_8TBs": hist_gbs / 8000.0,
-                "traffic": None if HIST_TRAFFIC_RATIO is None else per_launch_bytes * HIST_TRAFFIC_RATIO,
-                "algorithmic_bytes_per_launch": per_launch_bytes,
-                "avg_launch_ms": t["hist_ms"] / max(1, t["hist_launches"]),
-                "rows_x_features_per_s_per_gpu": t["hist_rows"] * FEATURES / (t["hist_ms"] * 1e-3),
-                "smem_atomic_updates_per_s": 2.0 * t["hist_rows"] * FEATURES / (t["hist_ms"] * 1e-3),
-                "phase_ms_per_round": {k: t[k] / prof_rounds for k in
-                                       ("grad_ms", "partition_ms", "plan_ms", "hist_ms", "allreduce_ms",
-                                        "subtract_ms", "split_ms", "update_ms")}}
+    if t["hist_ms"] > 0:
+        hist_gbs = t["hist_bytes"] / (t["hist_ms"] * 1e-3) / 1e9
+        per_launch_bytes = t["hist_bytes"] / max(1, t["hist_launches"])
+        roofline = {"bound": "hbm", "kernel": "hist_u8_kernel", "achieved": hist_gbs, "peak": peak,
+                    "unit": "GB/s", "frac": hist_gbs / peak, "peak_source": peak_src,
+                    "frac_of_nominal_8TBs": hist_gbs / 8000.0,
+                    "traffic": None if HIST_TRAFFIC_RATIO is None or args.workload != "c2"
+                    else per_launch_bytes * HIST_TRAFFIC_RATIO,
+                    "algorithmic_bytes_per_launch": per_launch_bytes,
+                    "avg_launch_ms": t["hist_ms"] / max(1, t["hist_launches"]),
+                    "rows_x_features_per_s_per_gpu": t["hist_rows"] * features / (t["hist_ms"] * 1e-3),
+                    "smem_atomic_updates_per_s": 2.0 * t["hist_rows"] * features / (t["hist_ms"] * 1e-3),
+                    "tree_ms": t["tree_ms"] / max(1, t["trees"]),
+                    "phase_ms_per_round": {k: t[k] / prof_rounds for k in
+                                           ("grad_ms", "partition_ms", "plan_ms", "hist_ms", "allreduce_ms",
+                                            "subtract_ms", "split_ms", "update_ms")}}
+    else:
+        # row chunks streamed from the host: the level loop is bound by the host link, and
+        # the phases of the chunks interleave, so only the whole tree is timed
+        link_gbs = t["h2d_bytes"] / (t["tree_ms"] * 1e-3) / 1e9
+        roofline = {"bound": "host link", "kernel": "chunk copies + hist_u8_kernel", "achieved": link_gbs,
+                    "peak": None, "unit": "GB/s", "frac": None, "traffic": None,
+                    "h2d_bytes_per_round": t["h2d_bytes"] / prof_rounds,
+                    "tree_ms": t["tree_ms"] / max(1, t["trees"]),
+                    "rows_streamed_per_s": t["h2d_bytes"] / ((features + 31) // 32 * 32) / (t["tree_ms"] * 1e-3)}
 
     if rank == 0:
         line = {"metric": "boosting_rounds_per_sec", "value": args.steps / step_s, "unit": "rounds/s",
@@ -289,9 +410,9 @@ def main():
                 "e2e": e2e, "gpu_launches": int(launches), "wall_ms_per_step": 1000.0 * wall_s / args.steps,
                 "roofline": roofline}
         if world == 1 and not args.no_cpu_baseline:
-            sample = min(args.rows, 500_000)
+            sample = min(args.rows, max(20_000, 14_000_000 // features))
             cores = os.cpu_count() or 1
-            rps = oracle_rounds_per_s(sample, 2, 1) * sample / args.rows
+            rps = oracle_rounds_per_s(sample, 2, 1, args.workload) * sample / args.rows
             line["cpu_baseline"] = {"value": rps, "unit": "rounds/s", "cores": cores, "kind": "port",
                                     "sample": "%d of %d rows, 2 rounds timed after 1, rounds/s scaled "
                                               "by rows" % (sample, args.rows)}
