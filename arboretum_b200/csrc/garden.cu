@@ -191,6 +191,8 @@ class Builder {
 
   DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_node_begin_, d_rec_, d_hist_[2],
     d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_cursors_;
+  DevBuf d_node_of_, d_go_right_;  // per row: node inside the current level; last step's direction bit
+  size_t bit_words_per_chunk_ = 0;
   DevBuf d_partials_, d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
   std::vector<unsigned> h_nb_total_;
@@ -265,7 +267,10 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const int qb = cfg.internal.quant_bits;
   ARB_CHECK(qb >= 10 && qb <= 20, "internals.quant_bits must be in [10, 20]");
   item_cap_ = 1 << (31 - qb);
-  max_hist_items_ = int(n_ / kMinItemRows) + max_nodes_ + 1;
+  // items of one level: sum over nodes of ceil(len / item_rows) <= rows / item_rows + nodes, and
+  // item_rows is ceil(rows / target) unless kMinItemRows (fewer items) or item_cap_ binds
+  max_hist_items_ = std::max(std::max(max_nodes_, 3 * hist_grid_x(1 << 30, geo_.NT)), int(n_ / item_cap_) + 1) +
+                    max_nodes_ + 2;
   max_part_items_ = int(n_ / kPartRows) + max_nodes_ + 1;
 
   gp_ = GainParams{tp.min_leaf_size, tp.min_child_weight, tp.gamma_absolute, tp.gamma_relative,
@@ -289,6 +294,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
   d_rowid_[0].alloc(n_ * sizeof(unsigned));
   d_rowid_[1].alloc(n_ * sizeof(unsigned));
+  d_node_of_.alloc(n_ * sizeof(unsigned short));
   trace.lap("per-row state");
   // level state
   {
@@ -296,6 +302,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     for (size_t b = 0; b < n_; b += chunk_rows)
       chunks_.push_back(Chunk{b, std::min(chunk_rows, n_ - b), nullptr});
   }
+  bit_words_per_chunk_ = (chunks_[0].rows + 31) / 32;
+  d_go_right_.alloc(chunks_.size() * bit_words_per_chunk_ * sizeof(unsigned));
   d_node_begin_.alloc(chunks_.size() * size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
   ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
   for (size_t c = 0; c < chunks_.size(); ++c) {
@@ -506,7 +514,20 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       const unsigned *src_list = (l - 1 <= 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>() + ch.begin;
       if (c == 0) mark();
       if (l > 0 && !fused) {
+        // every row of the chunk steps from its node of level l - 1 to the child, then the
+        // row lists are partitioned from the direction bits
+        DescendLaunch d;
+        d.geo = geo;
+        d.rec = rec(l - 1);
+        d.L = L / 2;
+        d.node_of = d_node_of_.as<unsigned short>() + ch.begin;
+        d.go_right = d_go_right_.as<unsigned>() + size_t(c) * bit_words_per_chunk_;
+        d.leaf_w = nullptr;
+        d.yhat = nullptr;
+        d.n = rows;
+        launch_descend(d, s);
         PartitionLaunch p;
+        p.go_right = d.go_right;
         p.geo = geo;
         p.rowid_src = src_list;
         p.rowid_dst = list_cur;
@@ -624,8 +645,22 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   for (int c = 0; c < n_chunks; ++c) {  // the tree walk needs the bins once more
     Geometry geo = geo_;
     geo.bins = Acquire(c);
-    launch_update_yhat(geo, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(),
-                       d_yhat_.as<float>() + size_t(label) * n_ + chunks_[c].begin, chunks_[c].rows, s);
+    float *yhat_c = d_yhat_.as<float>() + size_t(label) * n_ + chunks_[c].begin;
+    if (fused) {  // the fused step keeps no per-row node numbers: walk the whole tree
+      launch_update_yhat(geo, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(), yhat_c,
+                         chunks_[c].rows, s);
+    } else {  // one more step down from the last level, straight into the prediction
+      DescendLaunch d;
+      d.geo = geo;
+      d.rec = rec(levels_ - 1);
+      d.L = max_nodes_;
+      d.node_of = d_node_of_.as<unsigned short>() + chunks_[c].begin;
+      d.go_right = nullptr;
+      d.leaf_w = d_leaf_w_.as<float>();
+      d.yhat = yhat_c;
+      d.n = chunks_[c].rows;
+      launch_descend(d, s);
+    }
     Release(c);
   }
   mark();

@@ -118,8 +118,24 @@ struct PartitionLaunch {
   int L;
   int max_items;
   unsigned n_rows;
+  const unsigned *go_right = nullptr;  // bit per row from launch_descend (nullptr: the kernel
+                                       // reads the split feature's bin itself)
 };
 void launch_partition(const PartitionLaunch &a, cudaStream_t s);
+
+// One step of every row down the tree, in row order (see descend_kernel).
+struct DescendLaunch {
+  Geometry geo;
+  const NodeRec *rec;        // split records of the level the rows stand on
+  int L;                     // nodes of that level
+  unsigned short *node_of;   // per row: its node inside the level; becomes the child's (L == 1:
+                             // not read, every row stands on the root)
+  unsigned *go_right;        // bit per row, written here; nullptr = the final step, which adds
+  const float *leaf_w;       //   leaf_w[child] to
+  float *yhat;               //   yhat[row] instead
+  size_t n;
+};
+void launch_descend(const DescendLaunch &a, cudaStream_t s);
 // next level's prefix counts and the split records' left row counts from the cursors
 void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
                              unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s);

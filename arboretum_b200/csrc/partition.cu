@@ -12,6 +12,8 @@
 // observable contract of the reference -- per-level node row counts and the leaf
 // every row ends in -- is the same; its physical order (rights reversed) is not
 // observable and is not reproduced.
+#include <algorithm>
+
 #include "kernels.cuh"
 
 namespace arb {
@@ -131,7 +133,7 @@ partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
                  const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
                  const NodeRec *__restrict__ rec, const unsigned *__restrict__ node_begin,
                  unsigned *__restrict__ cursors, const WorkItem *__restrict__ items,
-                 const int *__restrict__ n_items) {
+                 const int *__restrict__ n_items, const unsigned *__restrict__ go_right) {
   constexpr int kWarps = kPartThreads / 32;
   __shared__ unsigned buf[kPartRows];
   __shared__ int cnt[kRowsPerThread * kWarps];
@@ -154,7 +156,9 @@ partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
     if (valid) {
       rid[k] = rowid_src ? rowid_src[item.begin + off] : item.begin + off;
       left = true;
-      if (fid >= 0) {
+      if (go_right) {  // decided by the descend step; the bit array stays in L2
+        left = ((go_right[rid[k] >> 5] >> (rid[k] & 31)) & 1u) == 0;
+      } else if (fid >= 0) {
         const int b = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fid) * cm_rows + rid[k]])
                               : int(reinterpret_cast<const BIN_T *>(bins + size_t(rid[k]) * pitch)[fid]);
         left = b <= split_bin;
@@ -204,6 +208,72 @@ partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
     rowid_dst[int(i) < nl ? ldst + i : rdst + (i - unsigned(nl))] = buf[i];
 }
 
+// Every row takes one step down the tree, in row order: its node's split decides left or
+// right (left <=> bin of the split feature <= split bin, builder.h:113-120; a node without
+// a split keeps its rows on the left).  The step reads each row's node number and one bin
+// of the feature-major matrix, both in row order, so DRAM lines are used whole however
+// deep the tree is; the row lists are then partitioned from the bit array written here,
+// which is small enough to stay in L2.  A warp takes 256 consecutive rows per turn, row
+// base + 32 k + lane in pass k, so that every access is coalesced and a lane has eight
+// independent loads in flight.
+// FINAL: the step below the last level; instead of storing the child, the row's
+// prediction receives the child's leaf weight (garden.cu:45-76 of the reference).
+constexpr int kDescendPasses = 8;
+constexpr int kDescendTable = 2048;
+
+template <typename BIN_T, bool FINAL>
+__global__ void __launch_bounds__(256)
+descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
+               const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
+               const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
+               unsigned *__restrict__ go_right, const float *__restrict__ leaf_w,
+               float *__restrict__ yhat, const size_t n) {
+  __shared__ int2 table[kDescendTable];  // (fid, bin) of the level's nodes
+  const bool cached = L <= kDescendTable;
+  if (cached) {
+    for (int i = threadIdx.x; i < L; i += blockDim.x) table[i] = make_int2(rec[i].fid, rec[i].bin);
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const size_t warps = size_t(gridDim.x) * (blockDim.x >> 5);
+  const size_t span = size_t(32) * kDescendPasses;
+  for (size_t base = (size_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * span; base < n;
+       base += warps * span) {
+    int node[kDescendPasses];
+#pragma unroll
+    for (int k = 0; k < kDescendPasses; ++k) {
+      const size_t r = base + size_t(k) * 32 + lane;
+      node[k] = (L > 1 && r < n) ? int(node_of[r]) : 0;
+    }
+    int binv[kDescendPasses], split_bin[kDescendPasses];
+#pragma unroll
+    for (int k = 0; k < kDescendPasses; ++k) {
+      const size_t r = base + size_t(k) * 32 + lane;
+      const int2 fb = cached ? table[node[k]] : make_int2(rec[node[k]].fid, rec[node[k]].bin);
+      split_bin[k] = fb.y;
+      binv[k] = -1;  // no split, or past the end: left
+      if (fb.x >= 0 && r < n)
+        binv[k] = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fb.x) * cm_rows + r])
+                          : int(reinterpret_cast<const BIN_T *>(bins + r * pitch)[fb.x]);
+    }
+    unsigned mine = 0;
+#pragma unroll
+    for (int k = 0; k < kDescendPasses; ++k) {
+      const size_t r = base + size_t(k) * 32 + lane;
+      const int right = binv[k] > split_bin[k];
+      const int child = 2 * node[k] + right;
+      if (FINAL) {
+        if (r < n) yhat[r] += leaf_w[child];
+      } else {
+        if (r < n) node_of[r] = (unsigned short)child;
+        const unsigned word = __ballot_sync(0xffffffffu, right);
+        if (lane == k) mine = word;
+      }
+    }
+    if (!FINAL && lane < kDescendPasses && base + size_t(lane) * 32 < n) go_right[base / 32 + lane] = mine;
+  }
+}
+
 // next level's prefix counts (count_next[2n+1] = left end, [2n+2] = node end:
 // hist_tree_grower.cu:80-83) and the left row count of every split record
 __global__ void partition_finish_kernel(const unsigned *__restrict__ cursors,
@@ -248,6 +318,25 @@ void launch_plan_fused(const unsigned *parent_begin, const NodeRec *parent_rec, 
   count_launch();
 }
 
+void launch_descend(const DescendLaunch &a, cudaStream_t s) {
+  if (a.n == 0) return;
+  const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
+  const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(148) * 8));
+  const Geometry &g = a.geo;
+  const bool fin = a.go_right == nullptr;
+#define ARB_LAUNCH(T, FIN)                                                                        \
+  descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L, \
+                                              a.node_of, a.go_right, a.leaf_w, a.yhat, a.n)
+  if (g.bin_bytes == 1) {
+    if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
+  } else {
+    if (fin) ARB_LAUNCH(unsigned short, true); else ARB_LAUNCH(unsigned short, false);
+  }
+#undef ARB_LAUNCH
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
 void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
                              unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s) {
   partition_finish_kernel<<<ceil_div(L, 128), 128, 0, s>>>(cursors, node_begin, node_begin_next, rec, L);
@@ -262,12 +351,12 @@ void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
     partition_kernel<unsigned char><<<a.max_items, kPartThreads, 0, s>>>(
       a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
       a.node_begin, a.cursors,
-      a.pb.part_items, a.pb.n_part_items);
+      a.pb.part_items, a.pb.n_part_items, a.go_right);
   else
     partition_kernel<unsigned short><<<a.max_items, kPartThreads, 0, s>>>(
       a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
       a.node_begin, a.cursors,
-      a.pb.part_items, a.pb.n_part_items);
+      a.pb.part_items, a.pb.n_part_items, a.go_right);
   ARB_CUDA(cudaGetLastError());
   count_launch();
   launch_partition_finish(a.cursors, a.node_begin, a.node_begin_next, a.rec, a.L, s);

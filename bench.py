@@ -272,6 +272,7 @@ def main():
     ap.add_argument("--rows", type=int, default=0)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--internals", default="", help='JSON merged into the "internals" configuration')
     args = ap.parse_args()
     if args.rows <= 0:
         args.rows = WORKLOADS[args.workload][0]
@@ -304,6 +305,8 @@ def main():
     yh = yp.numpy()
     cfg = json.loads(json.dumps(base_cfg))
     cfg["internals"]["device"] = local_rank
+    if args.internals:
+        cfg["internals"].update(json.loads(args.internals))
 
     def barrier():
         torch.cuda.synchronize()
