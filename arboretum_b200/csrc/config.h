@@ -49,7 +49,6 @@ struct Internals {  // param.h:52-62 (defaults :54-57)
   int device = -1;       // CUDA device ordinal, -1 = current device
   bool missing_bin = true;  // NaN -> dedicated bin id hist_size (always right)
   long long chunk_rows = 0;  // out-of-core: rows per streamed chunk, 0 = in-core
-  bool fused_step = false;   // one pass for partition + histogram (one-tile uint8 data)
   int resident_chunks = -1;  // out-of-core: chunks kept in HBM (-1 = as many as fit)
 };
 
@@ -123,7 +122,6 @@ struct Configuration {
       if (i.has("device")) c.internal.device = int(i.at("device").as_num());
       if (i.has("missing_bin")) c.internal.missing_bin = i.at("missing_bin").as_bool();
       if (i.has("chunk_rows")) c.internal.chunk_rows = (long long)i.at("chunk_rows").as_num();
-      if (i.has("fused_step")) c.internal.fused_step = i.at("fused_step").as_bool();
       if (i.has("resident_chunks")) c.internal.resident_chunks = int(i.at("resident_chunks").as_num());
     }
     return c;

@@ -183,17 +183,18 @@ class Builder {
   bool pair_;
   Geometry geo_;
   int item_cap_;       // rows an int32 sub-histogram may take (2^(31 - quant_bits))
-  int max_hist_items_, max_part_items_;
+  int max_hist_items_;
   std::default_random_engine rnd_;  // garden.cu:87
   std::vector<unsigned> active_fids_;
   std::vector<unsigned char> active_host_;
   GainParams gp_;
 
-  DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_rowid_[2], d_node_begin_, d_rec_, d_hist_[2],
-    d_keys_, d_qs_, d_leaf_w_, d_active_, d_fsize_, d_cursors_;
-  DevBuf d_node_of_, d_go_right_;  // per row: node inside the current level; last step's direction bit
-  size_t bit_words_per_chunk_ = 0;
-  DevBuf d_partials_, d_part_items_, d_hist_items_, d_counters_, d_first_[2], d_built_, d_scratch_;
+  DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_node_begin_, d_rec_, d_hist_[2], d_keys_, d_qs_,
+    d_leaf_w_, d_active_, d_fsize_;
+  DevBuf d_node_of_;  // per row: the node (inside the current level) it stands on
+  DevBuf d_list_;     // row lists of the built nodes of the current level, back to back
+  DevBuf d_partials_, d_hist_items_, d_counters_, d_first_, d_built_, d_scratch_, d_list_base_,
+    d_cursor_, d_child_count_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
   std::vector<unsigned> h_nb_total_;
   PlanBuffers pb_;
@@ -235,6 +236,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   K_ = int(tp.labels_count);
   ARB_CHECK(tp.depth >= 2 && tp.depth <= kMaxLevels, "max_depth must be in [1, 15]");
   ARB_CHECK(n_ < (size_t(1) << 31), "row count must be below 2^31");
+  ARB_CHECK(F_ < 65535, "more than 65534 features");
   if (d->device >= 0) {
     int cur = -1;
     ARB_CUDA(cudaGetDevice(&cur));
@@ -271,7 +273,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   // item_rows is ceil(rows / target) unless kMinItemRows (fewer items) or item_cap_ binds
   max_hist_items_ = std::max(std::max(max_nodes_, 3 * hist_grid_x(1 << 30, geo_.NT)), int(n_ / item_cap_) + 1) +
                     max_nodes_ + 2;
-  max_part_items_ = int(n_ / kPartRows) + max_nodes_ + 1;
 
   gp_ = GainParams{tp.min_leaf_size, tp.min_child_weight, tp.gamma_absolute, tp.gamma_relative,
                    tp.lambda,        tp.alpha,            tp.max_leaf_weight};
@@ -292,8 +293,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   // garden.cu:105: y_hat starts at IntoInternal(initial_y)
   launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
-  d_rowid_[0].alloc(n_ * sizeof(unsigned));
-  d_rowid_[1].alloc(n_ * sizeof(unsigned));
+  d_list_.alloc(n_ * sizeof(unsigned));
   d_node_of_.alloc(n_ * sizeof(unsigned short));
   trace.lap("per-row state");
   // level state
@@ -302,8 +302,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     for (size_t b = 0; b < n_; b += chunk_rows)
       chunks_.push_back(Chunk{b, std::min(chunk_rows, n_ - b), nullptr});
   }
-  bit_words_per_chunk_ = (chunks_[0].rows + 31) / 32;
-  d_go_right_.alloc(chunks_.size() * bit_words_per_chunk_ * sizeof(unsigned));
   d_node_begin_.alloc(chunks_.size() * size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
   ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
   for (size_t c = 0; c < chunks_.size(); ++c) {
@@ -323,24 +321,23 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   d_active_.alloc(size_t(levels_) * F_);
   d_fsize_.alloc(F_ * sizeof(int));
   ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
-  d_cursors_.alloc(2 * size_t(max_nodes_) * sizeof(unsigned));
-  d_part_items_.alloc(max_part_items_ * sizeof(WorkItem));
   d_hist_items_.alloc(max_hist_items_ * sizeof(WorkItem));
-  d_counters_.alloc(2 * sizeof(int));
-  d_first_[0].alloc((max_nodes_ + 1) * sizeof(int));
-  d_first_[1].alloc((max_nodes_ + 1) * sizeof(int));
+  d_counters_.alloc(sizeof(int));
+  d_first_.alloc((max_nodes_ + 2) * sizeof(int));
   d_built_.alloc(max_nodes_ * sizeof(int));
-  d_scratch_.alloc(3 * size_t(max_nodes_) * sizeof(unsigned));
-  pb_.part_items = d_part_items_.as<WorkItem>();
-  pb_.n_part_items = d_counters_.as<int>();
-  pb_.part_item_first = d_first_[0].as<int>();
+  d_scratch_.alloc(3 * size_t(max_nodes_ + 1) * sizeof(unsigned));
+  d_list_base_.alloc(max_nodes_ * sizeof(unsigned));
+  d_cursor_.alloc(size_t(max_nodes_) * kCounterStride * sizeof(unsigned));
+  d_child_count_.alloc(size_t(max_nodes_) * kCounterStride * sizeof(unsigned));
   pb_.hist_items = d_hist_items_.as<WorkItem>();
-  pb_.n_hist_items = d_counters_.as<int>() + 1;
-  pb_.hist_item_first = d_first_[1].as<int>();
+  pb_.n_hist_items = d_counters_.as<int>();
+  pb_.hist_item_first = d_first_.as<int>();
   pb_.built_child = d_built_.as<int>();
+  pb_.list_base = d_list_base_.as<unsigned>();
+  pb_.cursor = d_cursor_.as<unsigned>();
   pb_.scratch_begin = d_scratch_.as<unsigned>();
-  pb_.scratch_len = d_scratch_.as<unsigned>() + max_nodes_;
-  pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * max_nodes_);
+  pb_.scratch_len = d_scratch_.as<unsigned>() + (max_nodes_ + 1);
+  pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * (max_nodes_ + 1));
   trace.lap("level buffers");
   h_rec_.alloc(d_rec_.bytes);
   h_leaf_w_.alloc(d_leaf_w_.bytes);
@@ -490,12 +487,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     if (prof && !multi) ARB_CUDA(cudaEventRecord(ev_[ev], s));
     ++ev;
   };
-  // events per level: 0 begin, 1 partition done, 2 plan + clear done, 3 histogram done,
+  // events per level: 0 begin, 1 descend done, 2 plan + lists done, 3 histogram done,
   // 4 allreduce done, 5 subtraction done, 6 split search done
-  // One-tile uint8 data may take the fused step: the partition of level l-1 and the
-  // histogram of level l are one pass over the parents' rows.
-  const bool fused = cfg.internal.fused_step && geo_.NT == 1 && geo_.bin_bytes == 1 &&
-                     geo_.TW == 32 && use_trick && !multi;
   for (int l = 0; l < levels_; ++l) {
     const int L = 1 << l;
     const bool trick_level = use_trick && l > 0;
@@ -510,81 +503,52 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       geo.bins = Acquire(c);
       const size_t rows = ch.rows;
       const void *grad_c = static_cast<const char *>(grad) + ch.begin * gsz;
-      unsigned *list_cur = d_rowid_[l & 1].as<unsigned>() + ch.begin;
-      const unsigned *src_list = (l - 1 <= 0) ? nullptr : d_rowid_[(l - 1) & 1].as<unsigned>() + ch.begin;
+      unsigned short *node_of = d_node_of_.as<unsigned short>() + ch.begin;
+      unsigned *list = d_list_.as<unsigned>() + ch.begin;
       if (c == 0) mark();
-      if (l > 0 && !fused) {
-        // every row of the chunk steps from its node of level l - 1 to the child, then the
-        // row lists are partitioned from the direction bits
+      if (l > 0) {  // every row of the chunk steps from its node of level l - 1 to a child
         DescendLaunch d;
         d.geo = geo;
         d.rec = rec(l - 1);
         d.L = L / 2;
-        d.node_of = d_node_of_.as<unsigned short>() + ch.begin;
-        d.go_right = d_go_right_.as<unsigned>() + size_t(c) * bit_words_per_chunk_;
+        d.node_of = node_of;
+        d.child_count = d_child_count_.as<unsigned>();
         d.leaf_w = nullptr;
         d.yhat = nullptr;
         d.n = rows;
         launch_descend(d, s);
-        PartitionLaunch p;
-        p.go_right = d.go_right;
-        p.geo = geo;
-        p.rowid_src = src_list;
-        p.rowid_dst = list_cur;
-        p.cursors = d_cursors_.as<unsigned>();
-        p.node_begin = node_begin(c, l - 1);
-        p.node_begin_next = node_begin(c, l);
-        p.rec = rec(l - 1);
-        p.pb = pb_;
-        p.L = L / 2;
-        p.max_items = int(rows / kPartRows) + L / 2 + 1;
-        p.n_rows = unsigned(rows);
-        launch_partition(p, s);
       }
       if (last) mark();
+      // rows scanned this level: all at the root, at most half with the trick (the hessian
+      // rule of multi-GPU / multi-chunk runs has no such bound)
+      const bool half = trick_level && !by_hessian;
+      const size_t level_rows = half ? rows / 2 + 1 : rows;
       const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo.NT));
-      if (l > 0 && fused) {
-        // every row of the level is read (the partition needs them all)
-        const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (rows + target_items - 1) / target_items)));
-        launch_plan_fused(node_begin(c, l - 1), rec(l - 1), L / 2, item_rows, pb_, max_hist_items_, s);
-        if (last) mark();
-        FusedLaunch f;
-        f.geo = geo;
-        f.rowid_src = src_list;
-        f.rowid_dst = list_cur;
-        f.grad = grad_c;
-        f.pair = pair_;
-        f.items = pb_.hist_items;
-        f.n_items = pb_.n_hist_items;
-        f.max_items = int(std::min<size_t>(max_hist_items_, rows / item_rows + L / 2 + 1));
-        f.parent_rec = rec(l - 1);
-        f.built_child = pb_.built_child;
-        f.parent_begin = node_begin(c, l - 1);
-        f.cursors = d_cursors_.as<unsigned>();
-        f.n_parents = L / 2;
-        f.partials = d_partials_.as<int>();
-        launch_fused(f, s);
-        launch_partition_finish(d_cursors_.as<unsigned>(), node_begin(c, l - 1), node_begin(c, l), rec(l - 1), L / 2, s);
-      } else {
-        // rows scanned this level: all at the root, at most half with the trick
-        // (the hessian rule of multi-GPU / multi-chunk runs has no such bound)
-        const bool half = trick_level && !by_hessian;
-        const size_t level_rows = half ? rows / 2 + 1 : rows;
-        const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
-        launch_plan_hist(node_begin(c, l), l > 0 ? rec(l - 1) : nullptr, L, item_rows, use_trick, by_hessian,
-                         pb_, max_hist_items_, s);
-        if (last) mark();
-        HistLaunch h;
-        h.geo = geo;
-        h.rowid = l == 0 ? nullptr : list_cur;
-        h.grad = grad_c;
-        h.pair = pair_;
-        h.items = pb_.hist_items;
-        h.n_items = pb_.n_hist_items;
-        h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
-        h.partials = d_partials_.as<int>();
-        launch_hist(h, s);
-      }
+      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
+      LevelPlanLaunch pl;
+      pl.child_count = l > 0 ? d_child_count_.as<unsigned>() : nullptr;
+      pl.parent_begin = l > 0 ? node_begin(c, l - 1) : nullptr;
+      pl.node_begin = node_begin(c, l);
+      pl.parent_rec = l > 0 ? rec(l - 1) : nullptr;
+      pl.L = L;
+      pl.item_rows = item_rows;
+      pl.use_trick = use_trick;
+      pl.by_hessian = by_hessian;
+      pl.pb = pb_;
+      pl.max_items = max_hist_items_;
+      launch_plan_level(pl, s);
+      if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, s);
+      if (last) mark();
+      HistLaunch h;
+      h.geo = geo;
+      h.rowid = l == 0 ? nullptr : list;
+      h.grad = grad_c;
+      h.pair = pair_;
+      h.items = pb_.hist_items;
+      h.n_items = pb_.n_hist_items;
+      h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
+      h.partials = d_partials_.as<int>();
+      launch_hist(h, s);
       ReduceLaunch rd;
       rd.partials = d_partials_.as<int>();
       rd.item_first = pb_.hist_item_first;
@@ -646,21 +610,17 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     Geometry geo = geo_;
     geo.bins = Acquire(c);
     float *yhat_c = d_yhat_.as<float>() + size_t(label) * n_ + chunks_[c].begin;
-    if (fused) {  // the fused step keeps no per-row node numbers: walk the whole tree
-      launch_update_yhat(geo, d_rec_.as<NodeRec>(), levels_, max_nodes_, d_leaf_w_.as<float>(), yhat_c,
-                         chunks_[c].rows, s);
-    } else {  // one more step down from the last level, straight into the prediction
-      DescendLaunch d;
-      d.geo = geo;
-      d.rec = rec(levels_ - 1);
-      d.L = max_nodes_;
-      d.node_of = d_node_of_.as<unsigned short>() + chunks_[c].begin;
-      d.go_right = nullptr;
-      d.leaf_w = d_leaf_w_.as<float>();
-      d.yhat = yhat_c;
-      d.n = chunks_[c].rows;
-      launch_descend(d, s);
-    }
+    // one more step down from the last level, straight into the prediction
+    DescendLaunch d;
+    d.geo = geo;
+    d.rec = rec(levels_ - 1);
+    d.L = max_nodes_;
+    d.node_of = d_node_of_.as<unsigned short>() + chunks_[c].begin;
+    d.child_count = nullptr;
+    d.leaf_w = d_leaf_w_.as<float>();
+    d.yhat = yhat_c;
+    d.n = chunks_[c].rows;
+    launch_descend(d, s);
     Release(c);
   }
   mark();
@@ -740,7 +700,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       } else {
         for (int p = 0; p < L / 2; ++p) {
           const unsigned ls = nb[2 * p + 1] - nb[2 * p], rs = nb[2 * p + 2] - nb[2 * p + 1];
-          if (by_hessian || fused) {
+          if (by_hessian) {
             const NodeRec &pr = hrec[size_t(l - 1) * max_nodes_ + p];
             rows += (pr.lh <= pr.th - pr.lh) ? ls : rs;
           } else {
@@ -751,9 +711,6 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       t.hist_rows += rows;
       t.hist_features += double(F_);
       t.hist_bytes += rows * (double(F_) * geo_.bin_bytes + (pair_ ? 8.0 : 4.0));
-      // the fused step also does the level's row partition: split-feature bin read,
-      // row id read and write for every row
-      if (fused && l > 0) t.hist_bytes += double(n_) * (geo_.bin_bytes + 8.0);
       t.hist_launches += 1;
     }
     t.update += span(e - 1, e);

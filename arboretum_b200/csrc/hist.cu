@@ -164,180 +164,6 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
   }
 }
 
-// Fused level step for one-tile uint8 data (rows P + H of the hot path in one pass):
-// the items are pieces of the PARENT nodes' row lists.  Every row is fetched once;
-// its staged bins give (a) the left / right decision of the parent's split
-// (left <=> bin <= split bin, builder.h:113-120), which sends its row id to the
-// child's list, and (b) if the row falls into the child whose histogram is built,
-// the 2.5-wavefront update of the planes.  Row ids leave through a 2048-entry
-// shared buffer: lefts fill it from the front, rights from the back, and per
-// 2048 rows the CTA reserves room in both children with one atomicAdd per side
-// (lefts grow up from the parent's begin, rights down from its end).
-constexpr int kFusedStageBytes = 1024 + 256 + 128;  // bins, gradient records, row ids
-constexpr int kOutRows = 2048;
-
-template <bool PAIR>
-__global__ void __launch_bounds__(kHistThreads, 2)
-fused_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
-                const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
-                const void *__restrict__ grad, const WorkItem *__restrict__ items,
-                const int *__restrict__ n_items, const NodeRec *__restrict__ parent_rec,
-                const int *__restrict__ built_child, const unsigned *__restrict__ parent_begin,
-                unsigned *__restrict__ cursors, int *__restrict__ partials) {
-  extern __shared__ __align__(16) int smem[];
-  int *G = smem;
-  constexpr int kWarps = kHistThreads / 32;
-  unsigned char *stage0 = reinterpret_cast<unsigned char *>(smem + 2 * kHistWords);
-  unsigned *sout = reinterpret_cast<unsigned *>(stage0 + kWarps * kStages * kFusedStageBytes);
-  unsigned char *sidx_all = reinterpret_cast<unsigned char *>(sout + kOutRows);
-  unsigned *ctl = reinterpret_cast<unsigned *>(sidx_all + kWarps * 32);  // lcnt, rcnt, gl, gr
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned char *my = stage0 + warp * kStages * kFusedStageBytes;
-  unsigned char *sidx = sidx_all + warp * 32;
-  const int q = lane >> 3, m = lane & 7;
-  int foff[4], sh[4];
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int r = (k + q) & 3;
-    foff[k] = 4 * m + r;
-    sh[k] = 8 * r;
-  }
-  constexpr int GSZ = PAIR ? 8 : 4;
-  const unsigned lt_mask = (1u << lane) - 1u;
-  const int total_items = *n_items;
-  constexpr int kBatchesPerBlock = kOutRows / 32;  // batches between two row-id flushes
-
-  for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
-    const WorkItem item = items[it];
-    const int parent = item.node;
-    const int fid = parent_rec[parent].fid;
-    const int split_bin = parent_rec[parent].bin;
-    const bool build_right = built_child[parent] != 0;
-    const unsigned pbeg = parent_begin[parent], pend = parent_begin[parent + 1];
-    for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
-    if (threadIdx.x < 2) ctl[threadIdx.x] = 0;
-    __syncthreads();
-    const unsigned len = item.len;
-    const int nb = int((len + 31) / 32);
-
-    auto rid_of = [&](int b) -> unsigned {
-      const unsigned pos = min(unsigned(b * 32 + lane), len - 1);
-      return rowid_src ? __ldg(rowid_src + item.begin + pos) : item.begin + pos;
-    };
-    auto issue = [&](int b, int stage, unsigned rid_lane) {
-      unsigned char *sb = my + stage * kFusedStageBytes;
-      const unsigned r0 = __shfl_sync(0xffffffffu, rid_lane, lane >> 1);
-      const unsigned r1 = __shfl_sync(0xffffffffu, rid_lane, 16 + (lane >> 1));
-      cp_async16(sb + (lane >> 1) * 32 + (lane & 1) * 16, bins + size_t(r0) * pitch + (lane & 1) * 16);
-      cp_async16(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
-                 bins + size_t(r1) * pitch + (lane & 1) * 16);
-      const bool valid = unsigned(b * 32 + lane) < len;
-      cp_async_zfill<GSZ>(sb + 1024 + lane * GSZ, static_cast<const char *>(grad) + size_t(rid_lane) * GSZ,
-                          valid ? GSZ : 0);
-      cp_async_commit();
-      reinterpret_cast<unsigned *>(sb + 1280)[lane] = rid_lane;
-    };
-
-    int b_issue = warp;
-    unsigned rid_next = 0;
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      if (b_issue < nb) issue(b_issue, s, rid_of(b_issue)); else cp_async_commit();
-      b_issue += kWarps;
-    }
-    if (b_issue < nb) rid_next = rid_of(b_issue);
-    int stage = 0;
-    // all warps walk the same number of sub-blocks so that the barriers match
-    const int n_blocks = (nb + kBatchesPerBlock - 1) / kBatchesPerBlock;
-    for (int blk = 0; blk < n_blocks; ++blk) {
-      const int b_end = min(nb, (blk + 1) * kBatchesPerBlock);
-      for (int b = blk * kBatchesPerBlock + warp; b < b_end; b += kWarps) {
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
-        const unsigned char *sb = my + stage * kFusedStageBytes;
-        // ---- decision of my row, destinations of the row ids ----------------------
-        const bool valid = unsigned(b * 32 + lane) < len;
-        const bool left = valid && (fid < 0 || int(sb[lane * 32 + fid]) <= split_bin);
-        const unsigned bl = __ballot_sync(0xffffffffu, left);
-        const unsigned bv = __ballot_sync(0xffffffffu, valid);
-        const unsigned br = bv & ~bl;
-        unsigned lb = 0, rb = 0;
-        if (lane == 0) {
-          lb = atomicAdd(&ctl[0], unsigned(__popc(bl)));
-          rb = atomicAdd(&ctl[1], unsigned(__popc(br)));
-        }
-        lb = __shfl_sync(0xffffffffu, lb, 0);
-        rb = __shfl_sync(0xffffffffu, rb, 0);
-        const unsigned rid = reinterpret_cast<const unsigned *>(sb + 1280)[lane];
-        if (left)
-          sout[lb + __popc(bl & lt_mask)] = rid;
-        else if (valid)
-          sout[kOutRows - 1 - (rb + __popc(br & lt_mask))] = rid;
-        // ---- rows of the child being built, compacted ------------------------------
-        const unsigned bm = build_right ? br : bl;
-        if ((bm >> lane) & 1u) sidx[__popc(bm & lt_mask)] = (unsigned char)lane;
-        __syncwarp();
-        const int nbuilt = __popc(bm);
-        const int steps = (nbuilt + 3) >> 2;
-        for (int s = 0; s < steps; ++s) {
-          const int idx = 4 * s + q;
-          const bool ok = idx < nbuilt;
-          const int row = ok ? int(sidx[idx]) : 0;
-          const unsigned wv = *reinterpret_cast<const unsigned *>(sb + row * 32 + 4 * m);
-          int gq = 0, hq = 0;
-          if (ok) {
-            if (PAIR) {
-              const int2 gh = *reinterpret_cast<const int2 *>(sb + 1024 + row * 8);
-              gq = gh.x;
-              hq = gh.y;
-            } else {
-              gq = *reinterpret_cast<const int *>(sb + 1024 + row * 4);
-              hq = 1;
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int bin = (wv >> sh[k]) & 255;
-            int *p = G + bin * 32 + foff[k];
-            red_shared(p, gq);
-            red_shared(p + kHistWords, hq);
-          }
-        }
-        __syncwarp();
-        if (b_issue < nb) {
-          const unsigned rid_c = rid_next;
-          const int bn = b_issue + kWarps;
-          if (bn < nb) rid_next = rid_of(bn);
-          issue(b_issue, stage, rid_c);
-        } else {
-          cp_async_commit();
-        }
-        b_issue += kWarps;
-        stage = (stage + 1 == kStages) ? 0 : stage + 1;
-      }
-      // ---- hand the sub-block's row ids to the two children ---------------------------
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        ctl[2] = atomicAdd(&cursors[2 * parent], ctl[0]);
-        ctl[3] = atomicAdd(&cursors[2 * parent + 1], ctl[1]);
-      }
-      __syncthreads();
-      const unsigned nl = ctl[0], nr = ctl[1];
-      const unsigned ldst = pbeg + ctl[2];
-      const unsigned rdst = pend - ctl[3] - nr;
-      for (unsigned i = threadIdx.x; i < nl; i += kHistThreads) rowid_dst[ldst + i] = sout[i];
-      for (unsigned i = threadIdx.x; i < nr; i += kHistThreads)
-        rowid_dst[rdst + i] = sout[kOutRows - nr + i];
-      __syncthreads();
-      if (threadIdx.x < 2) ctl[threadIdx.x] = 0;
-      __syncthreads();
-    }
-    cp_async_wait<0>();
-    store_planes(smem, partials + size_t(it) * 2 * kHistWords);
-    __syncthreads();
-  }
-}
-
 // Any bin width / tile width: thread = (row in group, feature in tile).
 template <bool PAIR, bool IDENT, typename BIN_T>
 __global__ void __launch_bounds__(kHistThreads, 2)
@@ -496,28 +322,6 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
     if (g.bin_bytes == 1) ARB_LAUNCH_T(unsigned char); else ARB_LAUNCH_T(unsigned short);
 #undef ARB_LAUNCH_T
 #undef ARB_LAUNCH
-  }
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-}
-
-void launch_fused(const FusedLaunch &a, cudaStream_t s) {
-  const Geometry &g = a.geo;
-  ARB_CHECK(g.bin_bytes == 1 && g.TW == 32 && g.NT == 1, "fused level step needs one uint8 tile");
-  ARB_CUDA(cudaMemsetAsync(a.cursors, 0, 2 * sizeof(unsigned) * a.n_parents, s));
-  const size_t smem = 2 * kHistWords * 4 + (kHistThreads / 32) * kStages * kFusedStageBytes +
-                      kOutRows * 4 + (kHistThreads / 32) * 32 + 16;
-  const int grid = hist_grid_x(a.max_items, 1);
-  if (a.pair) {
-    ARB_SET_SMEM((fused_u8_kernel<true>), smem);
-    fused_u8_kernel<true><<<grid, kHistThreads, smem, s>>>(
-      g.bins, g.pitch, a.rowid_src, a.rowid_dst, a.grad, a.items, a.n_items, a.parent_rec,
-      a.built_child, a.parent_begin, a.cursors, a.partials);
-  } else {
-    ARB_SET_SMEM((fused_u8_kernel<false>), smem);
-    fused_u8_kernel<false><<<grid, kHistThreads, smem, s>>>(
-      g.bins, g.pitch, a.rowid_src, a.rowid_dst, a.grad, a.items, a.n_items, a.parent_rec,
-      a.built_child, a.parent_begin, a.cursors, a.partials);
   }
   ARB_CUDA(cudaGetLastError());
   count_launch();

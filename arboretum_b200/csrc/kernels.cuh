@@ -11,9 +11,8 @@ namespace arb {
 
 constexpr int kHistWords = 8192;      // words of one shared-memory histogram plane
 constexpr int kHistThreads = 256;     // threads of a histogram CTA
-constexpr int kPartRows = 2048;       // rows of one partition work item
-constexpr int kPartThreads = 256;
 constexpr int kMaxLevels = 16;
+constexpr int kCounterStride = 32;    // words between two counters that many CTAs add to
 constexpr int kMinItemRows = 2048;    // smallest piece a node's row list is cut into
 
 // Geometry of the binned matrix and of the histograms built from it.
@@ -86,82 +85,53 @@ struct SplitLaunch {
 };
 void launch_split(const SplitLaunch &a, cudaStream_t s);
 
-// --- row partition ----------------------------------------------------------
+// --- node assignment and row lists ---------------------------------------------
 struct PlanBuffers {
-  WorkItem *part_items;
-  int *n_part_items;
-  int *part_item_first;  // per node of the level: first item, L+1 entries
   WorkItem *hist_items;
   int *n_hist_items;
-  int *hist_item_first;  // scratch, max_nodes + 1
-  int *built_child;  // per parent: 0 = left child built, 1 = right child
-  unsigned *scratch_begin, *scratch_len;  // scratch, max_nodes each
-  int *scratch_node;
+  int *hist_item_first;   // per built node: its first item; max_nodes + 1 entries
+  int *built_child;       // per parent: 0 = left child built, 1 = right child
+  unsigned *list_base;    // per node of the level: where its row list starts (0xffffffff: none)
+  unsigned *cursor;       // per node of the level, kCounterStride words apart: rows written to
+                          // its list so far
+  unsigned *scratch_begin, *scratch_len;  // per built node: list start / length; max_nodes + 1
+  int *scratch_node;      // per built node: its node index inside the level
 };
-// items of the partition pass over the nodes of `level`
-void launch_plan_partition(const unsigned *node_begin, int L, PlanBuffers pb, int max_items,
-                           cudaStream_t s);
-// choose which child of every parent to build and cut those children into items
-void launch_plan_hist(const unsigned *node_begin, const NodeRec *parent_rec, int L, int item_rows,
-                      bool use_trick, bool by_hessian, PlanBuffers pb, int max_items,
-                      cudaStream_t s);
 
-struct PartitionLaunch {
-  Geometry geo;
-  const unsigned *rowid_src;  // nullptr: identity (root)
-  unsigned *rowid_dst;
-  unsigned *cursors;          // 2 per node: rows placed so far in the left / right child
-  const unsigned *node_begin; // level L prefix counts
-  unsigned *node_begin_next;  // 2L+1 prefix counts out
-  NodeRec *rec;               // split records of the level (left_count filled)
-  PlanBuffers pb;
-  int L;
-  int max_items;
-  unsigned n_rows;
-  const unsigned *go_right = nullptr;  // bit per row from launch_descend (nullptr: the kernel
-                                       // reads the split feature's bin itself)
-};
-void launch_partition(const PartitionLaunch &a, cudaStream_t s);
-
-// One step of every row down the tree, in row order (see descend_kernel).
+// Every row steps from its node to a child (or, below the last level, into a leaf).
 struct DescendLaunch {
   Geometry geo;
   const NodeRec *rec;        // split records of the level the rows stand on
   int L;                     // nodes of that level
   unsigned short *node_of;   // per row: its node inside the level; becomes the child's (L == 1:
                              // not read, every row stands on the root)
-  unsigned *go_right;        // bit per row, written here; nullptr = the final step, which adds
-  const float *leaf_w;       //   leaf_w[child] to
+  unsigned *child_count;     // per node (kCounterStride words apart): its rows that went right;
+                             // cleared and filled here; nullptr = the final step,
+  const float *leaf_w;       //   which adds leaf_w[child] to
   float *yhat;               //   yhat[row] instead
   size_t n;
 };
 void launch_descend(const DescendLaunch &a, cudaStream_t s);
-// next level's prefix counts and the split records' left row counts from the cursors
-void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
-                             unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s);
 
-// --- fused level step (one-tile uint8 data): partition of level l-1 + histogram of level l
-// items are pieces of the parents' row lists; the built child of every parent is
-// chosen from the parent's split record (smaller hessian sum, ties left)
-void launch_plan_fused(const unsigned *parent_begin, const NodeRec *parent_rec, int n_parents,
-                       int item_rows, PlanBuffers pb, int max_items, cudaStream_t s);
-struct FusedLaunch {
-  Geometry geo;
-  const unsigned *rowid_src;  // nullptr: identity (parents are the root)
-  unsigned *rowid_dst;
-  const void *grad;
-  bool pair;
-  const WorkItem *items;
-  const int *n_items;
+// Prefix counts of a level, the children to build, their lists and the histogram work items.
+struct LevelPlanLaunch {
+  const unsigned *child_count;  // per parent (kCounterStride apart): rows that went right, from
+                                // launch_descend; nullptr at the root
+  const unsigned *parent_begin; // L / 2 + 1 prefix counts of the level above
+  unsigned *node_begin;         // L + 1 prefix counts, written here (read at the root)
+  NodeRec *parent_rec;          // L / 2 records of the level above: left_count += lefts
+  int L;
+  int item_rows;                // rows per work item
+  bool use_trick;               // build one child per parent, the other is parent - built
+  bool by_hessian;              // choose it by the hessian sums (row shards, row chunks)
+  PlanBuffers pb;
   int max_items;
-  const NodeRec *parent_rec;
-  const int *built_child;
-  const unsigned *parent_begin;
-  unsigned *cursors;  // 2 per parent, zeroed by the launcher
-  int n_parents;
-  int *partials;
 };
-void launch_fused(const FusedLaunch &a, cudaStream_t s);
+void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s);
+
+// rows of the built nodes -> list[pb.list_base[node] + ...]
+void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const PlanBuffers &pb,
+                         unsigned *list, cudaStream_t s);
 
 // --- objective, leaves, prediction ----------------------------------------------
 // grad from (y, yhat); also tracks max|g|, max h in qs
@@ -182,11 +152,6 @@ struct LeafLaunch {
   bool pair;
 };
 void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s);
-
-// yhat[row] += leaf weight of the tree just grown, walking the tree over bins
-void launch_update_yhat(const Geometry &geo, const NodeRec *rec /*[levels][max_nodes]*/,
-                        int levels, int max_nodes, const float *leaf_w, float *yhat, size_t n,
-                        cudaStream_t s);
 
 // inference over raw fp32 rows (RegTree::Predict of the reference, on the device)
 struct PackedTree {  // device arrays of one forest

@@ -120,35 +120,6 @@ __global__ void leaf_weights_kernel(LeafLaunch a) {
                                           a.lambda, a.alpha, a.mlw) * a.eta;
 }
 
-// garden.cu:45-76 restated over the immutable bin matrix: every row walks the
-// tree that was just grown (left <=> bin <= split bin, builder.h:113-120).
-template <typename BIN_T>
-__global__ void update_yhat_kernel(const unsigned char *__restrict__ bins, size_t pitch,
-                                   const NodeRec *__restrict__ rec, int levels, int max_nodes,
-                                   const float *__restrict__ leaf_w, float *__restrict__ yhat,
-                                   size_t n) {
-  extern __shared__ int2 snode[];  // (fid, bin) per (level, node) when it fits
-  const int total = levels * max_nodes;
-  const bool cached = total * sizeof(int2) <= 40 * 1024;
-  if (cached) {
-    for (int i = threadIdx.x; i < total; i += blockDim.x)
-      snode[i] = make_int2(rec[i].fid, rec[i].bin);
-    __syncthreads();
-  }
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += size_t(gridDim.x) * blockDim.x) {
-    const BIN_T *row = reinterpret_cast<const BIN_T *>(bins + i * pitch);
-    int node = 0;
-    for (int l = 0; l < levels; ++l) {
-      const int2 fb = cached ? snode[l * max_nodes + node]
-                             : make_int2(rec[l * max_nodes + node].fid, rec[l * max_nodes + node].bin);
-      const int right = fb.x >= 0 && int(row[fb.x]) > fb.y;
-      node = 2 * node + right;
-    }
-    yhat[i] += leaf_w[node];
-  }
-}
-
 // RegTree::Predict garden.h:70-90 (dense features): x < threshold goes left, so
 // NaN goes right; trees are added in order, in float, like the reference's loop
 // in Garden::Predict garden.cu:643-657.
@@ -236,22 +207,6 @@ void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s) {
     leaf_weights_kernel<true><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
   else
     leaf_weights_kernel<false><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-}
-
-void launch_update_yhat(const Geometry &geo, const NodeRec *rec, int levels, int max_nodes,
-                        const float *leaf_w, float *yhat, size_t n, cudaStream_t s) {
-  const int threads = 256;
-  const int grid = grid_for(n, threads);
-  size_t smem = size_t(levels) * max_nodes * sizeof(int2);
-  if (smem > 40 * 1024) smem = 0;
-  if (geo.bin_bytes == 1)
-    update_yhat_kernel<unsigned char><<<grid, threads, smem, s>>>(geo.bins, geo.pitch, rec, levels,
-                                                                  max_nodes, leaf_w, yhat, n);
-  else
-    update_yhat_kernel<unsigned short><<<grid, threads, smem, s>>>(geo.bins, geo.pitch, rec, levels,
-                                                                   max_nodes, leaf_w, yhat, n);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

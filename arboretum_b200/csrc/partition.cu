@@ -1,17 +1,24 @@
-// Row partition / node assignment (row P of the hot path; replaces set_segment,
+// Node assignment and row lists (row P of the hot path; replaces set_segment,
 // CreatePartitioningIndexes + scatter_kernel and apply_split of the reference:
 // src/core/garden.cu:32-43,255-294, src/core/partition.cuh:20-206,
 // src/core/builder.h:51-59,107-123,287-300).
 //
-// The binned matrix never moves.  Each level keeps a list of row ids grouped by
-// node (`node_begin` are the prefix counts, like parent_node_count in the
-// reference) and a level step splits every node's piece of the list into its two
-// children: rows whose bin of the split feature is <= the split bin go left
-// (builder.h:113-120); inside every 2048-row piece both sides keep their order,
-// so row ids stay ascending in long runs and gathers stay local.  The
-// observable contract of the reference -- per-level node row counts and the leaf
-// every row ends in -- is the same; its physical order (rights reversed) is not
-// observable and is not reproduced.
+// The binned matrix never moves and no list is carried from level to level.  Every
+// row keeps the number of the node it stands on (`node_of`), and a level step is three
+// passes in row order, each of them a stream over whole DRAM lines whatever the depth:
+//   1. descend: every row steps to a child of its node (left <=> bin of the split
+//      feature <= split bin, builder.h:113-120) and the children are counted;
+//   2. plan (one CTA): prefix counts of the level (`node_begin`, like parent_node_count
+//      in the reference), which child of every parent gets a histogram of its own (the
+//      other is parent - built), where the row list of every built node starts, and the
+//      work items of the histogram pass;
+//   3. lists: the rows of the built nodes -- the only ones a histogram pass reads --
+//      are written to their node's list; a CTA reserves room for its rows with one
+//      atomicAdd per node it meets.
+// The order of the rows inside a list depends on scheduling; nothing observable does,
+// because every sum over rows is an exact integer sum.  The observable contract of the
+// reference -- per-level node row counts and the leaf every row ends in -- is the same;
+// its physical row order is not observable and is not reproduced.
 #include <algorithm>
 
 #include "kernels.cuh"
@@ -20,26 +27,61 @@ namespace arb {
 
 namespace {
 
-constexpr int kRowsPerThread = kPartRows / kPartThreads;  // 8
+constexpr unsigned kNoList = 0xffffffffu;
+constexpr int kDescendPasses = 8;   // a warp takes 32 * 8 consecutive rows per turn
+constexpr int kSmemNodes = 2048;    // nodes of a level whose tables fit in shared memory
+constexpr int kListRows = 4096;     // rows of one CTA of the list pass
+constexpr int kListThreads = 256;
+// Counters that many CTAs add to (children counts, list cursors) sit one per 128-byte line:
+// atomics on one line are served one after the other by a single L2 slice, so packed
+// counters would serialise every CTA's updates of a whole level.
+constexpr int kPad = kCounterStride;
+constexpr int kFewNodes = 2;        // descend: up to here a level's right-goers are counted from ballots
+constexpr int kFewLists = 4;        // lists: up to here lanes are grouped by node before they take ranks
 
-// first[n] = first item of node n, items of `rows_per_item` rows; one CTA.
+// out[i] = sum of in[0..i) for i <= n (n + 1 values); one CTA; in place allowed
+__device__ void block_exclusive_scan(const unsigned *in, unsigned *out, int n) {
+  __shared__ unsigned warp_sums[32];
+  const int per = (n + int(blockDim.x) - 1) / int(blockDim.x);
+  const int lo = min(n, int(threadIdx.x) * per), hi = min(n, lo + per);
+  unsigned sum = 0;
+  for (int i = lo; i < hi; ++i) sum += in[i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned incl = sum;
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  unsigned run = incl - sum;
+  for (int w = 0; w < warp; ++w) run += warp_sums[w];
+  for (int i = lo; i < hi; ++i) {  // a thread reads its own elements before it overwrites them
+    const unsigned v = in[i];
+    out[i] = run;
+    run += v;
+  }
+  if (hi == n) out[n] = run;  // every thread at or past the end holds the total
+  __syncthreads();
+}
+
+// first[b] = first item of list b, items of `rows_per_item` rows; one CTA.
 __device__ void make_items(const unsigned *begin, const unsigned *len, const int *node_id,
-                           int n_nodes, int rows_per_item, int *first, WorkItem *items,
+                           int n_lists, int rows_per_item, int *first, WorkItem *items,
                            int *n_items, int max_items) {
   __shared__ int total;
+  unsigned *ufirst = reinterpret_cast<unsigned *>(first);
+  for (int i = threadIdx.x; i < n_lists; i += blockDim.x)
+    ufirst[i] = (len[i] + unsigned(rows_per_item) - 1) / unsigned(rows_per_item);
+  __syncthreads();
+  block_exclusive_scan(ufirst, ufirst, n_lists);
   if (threadIdx.x == 0) {
-    int run = 0;
-    for (int i = 0; i < n_nodes; ++i) {
-      first[i] = run;
-      run += int((len[i] + rows_per_item - 1) / rows_per_item);
-    }
-    first[n_nodes] = run;
-    total = run < max_items ? run : max_items;
+    total = first[n_lists] < max_items ? first[n_lists] : max_items;
     *n_items = total;
   }
   __syncthreads();
   for (int it = threadIdx.x; it < total; it += blockDim.x) {
-    int lo = 0, hi = n_nodes;  // last node with first[node] <= it
+    int lo = 0, hi = n_lists;  // last list with first[list] <= it
     while (hi - lo > 1) {
       const int mid = (lo + hi) / 2;
       if (first[mid] <= it) lo = mid; else hi = mid;
@@ -48,28 +90,37 @@ __device__ void make_items(const unsigned *begin, const unsigned *len, const int
     WorkItem w;
     w.begin = begin[lo] + off;
     w.len = min(unsigned(rows_per_item), len[lo] - off);
-    w.node = node_id ? node_id[lo] : lo;
+    w.node = node_id[lo];
     w.pad = 0;
     items[it] = w;
   }
 }
 
-__global__ void plan_partition_kernel(const unsigned *__restrict__ node_begin, int L, PlanBuffers pb,
-                                      unsigned *sb, unsigned *sl, int *sn, int max_items) {
-  for (int i = threadIdx.x; i < L; i += blockDim.x) {
-    sb[i] = node_begin[i];
-    sl[i] = node_begin[i + 1] - node_begin[i];
-    sn[i] = i;
+// One CTA per level: prefix counts, the children that get a histogram of their own, their
+// row lists and the work items of the histogram pass.
+//   child_count : per parent, the rows that stepped to its right child (nullptr at the
+//                 root, whose prefix counts {0, rows} are already in node_begin)
+//   parent_begin: prefix counts of the level above
+//   parent_rec  : split records of the level above; left_count += rows that went left
+//                 (cleared by the split search; row chunks add up)
+__global__ void plan_level_kernel(const unsigned *__restrict__ child_count,
+                                  const unsigned *__restrict__ parent_begin,
+                                  unsigned *__restrict__ node_begin, NodeRec *__restrict__ parent_rec,
+                                  int L, int item_rows, bool use_trick, bool by_hessian,
+                                  PlanBuffers pb, int max_items) {
+  unsigned *sb = pb.scratch_begin, *sl = pb.scratch_len;
+  int *sn = pb.scratch_node;
+  if (child_count) {  // rows that went right, per parent; the others of the parent went left
+    for (int p = threadIdx.x; p < L / 2; p += blockDim.x) {
+      const unsigned size = parent_begin[p + 1] - parent_begin[p], rights = child_count[size_t(p) * kPad];
+      sl[2 * p] = size - rights;
+      sl[2 * p + 1] = rights;
+    }
+    __syncthreads();
+    block_exclusive_scan(sl, node_begin, L);
+    for (int p = threadIdx.x; p < L / 2; p += blockDim.x) parent_rec[p].left_count += sl[2 * p];
   }
   __syncthreads();
-  make_items(sb, sl, sn, L, kPartRows, pb.part_item_first, pb.part_items, pb.n_part_items,
-             max_items);
-}
-
-__global__ void plan_hist_kernel(const unsigned *__restrict__ node_begin,
-                                 const NodeRec *__restrict__ parent_rec, int L, int item_rows,
-                                 bool use_trick, bool by_hessian, PlanBuffers pb, unsigned *sb,
-                                 unsigned *sl, int *sn, int *first, int max_items) {
   int n_build;
   if (use_trick && L > 1) {
     n_build = L / 2;
@@ -77,164 +128,73 @@ __global__ void plan_hist_kernel(const unsigned *__restrict__ node_begin,
       const unsigned ls = node_begin[2 * p + 1] - node_begin[2 * p];
       const unsigned rs = node_begin[2 * p + 2] - node_begin[2 * p + 1];
       int built;
-      if (by_hessian) {  // identical on every rank: decided from the global sums
+      if (by_hessian) {  // identical on every rank and for every row chunk: from the global sums
         const long long lh = parent_rec[p].lh, rh = parent_rec[p].th - parent_rec[p].lh;
         built = lh <= rh ? 0 : 1;
       } else {  // smaller child, ties build the left one (hist_grad_sum.cu:288-290)
         built = ls <= rs ? 0 : 1;
       }
       pb.built_child[p] = built;
-      const int node = 2 * p + built;
-      sb[p] = node_begin[node];
       sl[p] = built ? rs : ls;
-      sn[p] = node;
+      sn[p] = 2 * p + built;
+      pb.list_base[2 * p + 1 - built] = kNoList;
     }
   } else {
     n_build = L;
     for (int i = threadIdx.x; i < L; i += blockDim.x) {
-      sb[i] = node_begin[i];
       sl[i] = node_begin[i + 1] - node_begin[i];
       sn[i] = i;
     }
   }
   __syncthreads();
-  make_items(sb, sl, sn, n_build, item_rows, first, pb.hist_items, pb.n_hist_items, max_items);
+  block_exclusive_scan(sl, sb, n_build);  // the lists of the built nodes lie back to back
+  for (int b = threadIdx.x; b < n_build; b += blockDim.x) {
+    pb.list_base[sn[b]] = sb[b];
+    pb.cursor[size_t(sn[b]) * kPad] = 0;
+  }
+  __syncthreads();
+  make_items(sb, sl, sn, n_build, item_rows, pb.hist_item_first, pb.hist_items, pb.n_hist_items,
+             max_items);
 }
 
-// items over the parents of a fused level step; built child = smaller hessian sum
-__global__ void plan_fused_kernel(const unsigned *__restrict__ parent_begin,
-                                  const NodeRec *__restrict__ parent_rec, int n_parents, int item_rows,
-                                  PlanBuffers pb, unsigned *sb, unsigned *sl, int *build_node,
-                                  int *first, int max_items) {
-  for (int p = threadIdx.x; p < n_parents; p += blockDim.x) {
-    const long long lh = parent_rec[p].lh, rh = parent_rec[p].th - parent_rec[p].lh;
-    const int built = lh <= rh ? 0 : 1;
-    pb.built_child[p] = built;
-    build_node[p] = 2 * p + built;
-    sb[p] = parent_begin[p];
-    sl[p] = parent_begin[p + 1] - parent_begin[p];
-  }
-  __syncthreads();
-  make_items(sb, sl, nullptr, n_parents, item_rows, first, pb.hist_items, pb.n_hist_items, max_items);
+__device__ __forceinline__ void red_shared_u32(unsigned *p, unsigned v) {
+  const unsigned a = unsigned(__cvta_generic_to_shared(p));
+  asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
-// One pass per level: every CTA takes one item (a piece of one node's row list),
-// decides left / right for its rows (left <=> bin of the split feature <= split
-// bin, builder.h:113-120), orders them in shared memory (lefts first, both sides
-// in list order) and reserves room in the two children with one atomicAdd per
-// side: lefts grow upwards from the node's begin, rights downwards from its end,
-// so both children are contiguous without knowing their sizes in advance.  The
-// order of the items inside a child depends on scheduling; nothing observable
-// does, because every sum over rows is an exact integer sum.
-template <typename BIN_T>
-__global__ void __launch_bounds__(kPartThreads)
-partition_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
-                 const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
-                 const unsigned *__restrict__ rowid_src, unsigned *__restrict__ rowid_dst,
-                 const NodeRec *__restrict__ rec, const unsigned *__restrict__ node_begin,
-                 unsigned *__restrict__ cursors, const WorkItem *__restrict__ items,
-                 const int *__restrict__ n_items, const unsigned *__restrict__ go_right) {
-  constexpr int kWarps = kPartThreads / 32;
-  __shared__ unsigned buf[kPartRows];
-  __shared__ int cnt[kRowsPerThread * kWarps];
-  __shared__ int pre[kRowsPerThread * kWarps + 1];
-  __shared__ unsigned base_l, base_r;
-  if (int(blockIdx.x) >= *n_items) return;
-  const WorkItem item = items[blockIdx.x];
-  const int fid = rec[item.node].fid;
-  const int split_bin = rec[item.node].bin;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned rid[kRowsPerThread];
-  int before[kRowsPerThread];  // lefts before this element inside its warp round
-  unsigned left_bits = 0;
-#pragma unroll
-  for (int k = 0; k < kRowsPerThread; ++k) {
-    const unsigned off = k * kPartThreads + threadIdx.x;
-    const bool valid = off < item.len;
-    rid[k] = 0;
-    bool left = false;
-    if (valid) {
-      rid[k] = rowid_src ? rowid_src[item.begin + off] : item.begin + off;
-      left = true;
-      if (go_right) {  // decided by the descend step; the bit array stays in L2
-        left = ((go_right[rid[k] >> 5] >> (rid[k] & 31)) & 1u) == 0;
-      } else if (fid >= 0) {
-        const int b = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fid) * cm_rows + rid[k]])
-                              : int(reinterpret_cast<const BIN_T *>(bins + size_t(rid[k]) * pitch)[fid]);
-        left = b <= split_bin;
-      }
-    }
-    const unsigned bal = __ballot_sync(0xffffffffu, left);
-    before[k] = __popc(bal & ((1u << lane) - 1));
-    if (lane == 0) cnt[k * kWarps + warp] = __popc(bal);
-    left_bits |= unsigned(left) << k;
-  }
-  __syncthreads();
-  if (warp == 0) {  // exclusive scan of the 64 (round, warp) counts
-    constexpr int kN = kRowsPerThread * kWarps;
-    const int a = cnt[2 * lane], b = cnt[2 * lane + 1];
-    int incl = a + b;
-    for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    static_assert(kN == 64, "two counts per lane");
-    pre[2 * lane] = incl - a - b;
-    pre[2 * lane + 1] = incl - b;
-    if (lane == 31) pre[kN] = incl;
-  }
-  __syncthreads();
-  const int nl = pre[kRowsPerThread * kWarps];
-  const int nr = int(item.len) - nl;
-#pragma unroll
-  for (int k = 0; k < kRowsPerThread; ++k) {
-    const unsigned off = k * kPartThreads + threadIdx.x;
-    if (off < item.len) {
-      const int lefts_before = pre[k * kWarps + warp] + before[k];
-      if ((left_bits >> k) & 1u)
-        buf[lefts_before] = rid[k];
-      else
-        buf[nl + int(off) - lefts_before] = rid[k];
-    }
-  }
-  if (threadIdx.x == 0) {
-    base_l = atomicAdd(&cursors[2 * item.node], unsigned(nl));
-    base_r = atomicAdd(&cursors[2 * item.node + 1], unsigned(nr));
-  }
-  __syncthreads();
-  const unsigned ldst = node_begin[item.node] + base_l;
-  const unsigned rdst = node_begin[item.node + 1] - base_r - unsigned(nr);
-  for (unsigned i = threadIdx.x; i < item.len; i += kPartThreads)
-    rowid_dst[int(i) < nl ? ldst + i : rdst + (i - unsigned(nl))] = buf[i];
-}
-
-// Every row takes one step down the tree, in row order: its node's split decides left or
-// right (left <=> bin of the split feature <= split bin, builder.h:113-120; a node without
-// a split keeps its rows on the left).  The step reads each row's node number and one bin
-// of the feature-major matrix, both in row order, so DRAM lines are used whole however
-// deep the tree is; the row lists are then partitioned from the bit array written here,
-// which is small enough to stay in L2.  A warp takes 256 consecutive rows per turn, row
-// base + 32 k + lane in pass k, so that every access is coalesced and a lane has eight
-// independent loads in flight.
-// FINAL: the step below the last level; instead of storing the child, the row's
-// prediction receives the child's leaf weight (garden.cu:45-76 of the reference).
-constexpr int kDescendPasses = 8;
-constexpr int kDescendTable = 2048;
-
+// Every row takes one step down the tree, in row order.  A warp takes 256 consecutive rows
+// per turn, row base + 32 k + lane in pass k, so that every access is coalesced and a lane
+// has eight independent loads in flight; the bin comes from the feature-major copy when
+// there is one (neighbouring rows share its lines whatever their nodes are).  The rows that
+// go right are counted per node: in registers (lane c counts for node c, from ballots) while
+// the level has at most kFewNodes nodes, with shared-memory atomics beyond that, where lanes
+// rarely meet on a node.
+// FINAL: the step below the last level; instead of storing and counting the child, the
+// row's prediction receives the child's leaf weight (garden.cu:45-76 of the reference).
 template <typename BIN_T, bool FINAL>
 __global__ void __launch_bounds__(256)
 descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
                const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
                const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
-               unsigned *__restrict__ go_right, const float *__restrict__ leaf_w,
+               unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
                float *__restrict__ yhat, const size_t n) {
-  __shared__ int2 table[kDescendTable];  // (fid, bin) of the level's nodes
-  const bool cached = L <= kDescendTable;
+  __shared__ unsigned table[kSmemNodes];  // feature << 16 | split bin; feature 0xffff: no split
+  __shared__ unsigned cnt[kSmemNodes];    // rows of this CTA that went right, per node
+  const bool cached = L <= kSmemNodes;
+  auto packed = [&](int i) {
+    const int fid = rec[i].fid;
+    return fid < 0 ? 0xffff0000u : (unsigned(fid) << 16) | unsigned(rec[i].bin);
+  };
   if (cached) {
-    for (int i = threadIdx.x; i < L; i += blockDim.x) table[i] = make_int2(rec[i].fid, rec[i].bin);
+    for (int i = threadIdx.x; i < L; i += blockDim.x) {
+      table[i] = packed(i);
+      cnt[i] = 0;
+    }
     __syncthreads();
   }
   const int lane = threadIdx.x & 31;
+  const bool few = L <= kFewNodes;
+  unsigned mine = 0;  // few nodes: lane c < L counts the right-goers of node c
   const size_t warps = size_t(gridDim.x) * (blockDim.x >> 5);
   const size_t span = size_t(32) * kDescendPasses;
   for (size_t base = (size_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * span; base < n;
@@ -249,84 +209,130 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
 #pragma unroll
     for (int k = 0; k < kDescendPasses; ++k) {
       const size_t r = base + size_t(k) * 32 + lane;
-      const int2 fb = cached ? table[node[k]] : make_int2(rec[node[k]].fid, rec[node[k]].bin);
-      split_bin[k] = fb.y;
+      const unsigned e = cached ? table[node[k]] : packed(node[k]);
+      const int fid = int(e >> 16);
+      split_bin[k] = int(e & 0xffffu);
       binv[k] = -1;  // no split, or past the end: left
-      if (fb.x >= 0 && r < n)
-        binv[k] = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fb.x) * cm_rows + r])
-                          : int(reinterpret_cast<const BIN_T *>(bins + r * pitch)[fb.x]);
+      if (fid != 0xffff && r < n)
+        binv[k] = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fid) * cm_rows + r])
+                          : int(reinterpret_cast<const BIN_T *>(bins + r * pitch)[fid]);
     }
-    unsigned mine = 0;
 #pragma unroll
     for (int k = 0; k < kDescendPasses; ++k) {
       const size_t r = base + size_t(k) * 32 + lane;
-      const int right = binv[k] > split_bin[k];
-      const int child = 2 * node[k] + right;
+      const bool right = binv[k] > split_bin[k];
+      const int child = 2 * node[k] + (right ? 1 : 0);
       if (FINAL) {
         if (r < n) yhat[r] += leaf_w[child];
       } else {
         if (r < n) node_of[r] = (unsigned short)child;
-        const unsigned word = __ballot_sync(0xffffffffu, right);
-        if (lane == k) mine = word;
+        if (!cached) {
+          if (right) atomicAdd(&right_count[size_t(node[k]) * kPad], 1u);
+        } else if (few) {
+          for (int c = 0; c < L; ++c) {
+            const unsigned m = __ballot_sync(0xffffffffu, right && node[k] == c);
+            if (lane == c) mine += unsigned(__popc(m));
+          }
+        } else if (right) {
+          red_shared_u32(&cnt[node[k]], 1u);
+        }
       }
     }
-    if (!FINAL && lane < kDescendPasses && base + size_t(lane) * 32 < n) go_right[base / 32 + lane] = mine;
+  }
+  if (!FINAL && cached) {
+    if (few && lane < L && mine) red_shared_u32(&cnt[lane], mine);
+    __syncthreads();
+    for (int i = threadIdx.x; i < L; i += blockDim.x)
+      if (cnt[i]) atomicAdd(&right_count[size_t(i) * kPad], cnt[i]);
   }
 }
 
-// next level's prefix counts (count_next[2n+1] = left end, [2n+2] = node end:
-// hist_tree_grower.cu:80-83) and the left row count of every split record
-__global__ void partition_finish_kernel(const unsigned *__restrict__ cursors,
-                                        const unsigned *__restrict__ node_begin,
-                                        unsigned *__restrict__ node_begin_next,
-                                        NodeRec *__restrict__ rec, int L) {
-  const int node = blockIdx.x * blockDim.x + threadIdx.x;
-  if (node >= L) return;
-  const unsigned nl = cursors[2 * node];
-  node_begin_next[2 * node] = node_begin[node];
-  node_begin_next[2 * node + 1] = node_begin[node] + nl;
-  if (node == L - 1) node_begin_next[2 * L] = node_begin[L];
-  rec[node].left_count += nl;  // cleared by the split search; row chunks add up
+// The rows of the built nodes go to their node's list.  A CTA takes kListRows consecutive
+// rows: every row gets a rank among the CTA's rows of its node from a shared-memory counter
+// (one atomic per group of lanes with the same node while the level has at most kFewLists
+// nodes: there the lanes of a warp would all meet on the same few counters), the CTA reserves room in every list it has rows for
+// with one global atomicAdd, and the rows are written at list start + CTA base + rank.
+__global__ void __launch_bounds__(kListThreads)
+gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, const int L,
+                    const unsigned *__restrict__ list_base, unsigned *__restrict__ cursor,
+                    unsigned *__restrict__ list) {
+  // per node: first the CTA's row count, then where the CTA's rows of the node go (kNoList:
+  // the node has no list)
+  __shared__ unsigned s_at[kSmemNodes];
+  constexpr int kPer = kListRows / kListThreads;
+  const bool cached = L <= kSmemNodes;
+  const bool few = L <= kFewLists;
+  const size_t base = size_t(blockIdx.x) * kListRows;
+  const int lane = threadIdx.x & 31;
+  if (cached) {
+    for (int i = threadIdx.x; i < L; i += kListThreads) s_at[i] = 0;
+    __syncthreads();
+  }
+  int node[kPer];
+  unsigned rank[kPer];
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const size_t r = base + size_t(k) * kListThreads + threadIdx.x;
+    node[k] = r < n ? int(node_of[r]) : -1;
+  }
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    rank[k] = 0;
+    if (!cached) {  // too many nodes for the table: row by row, straight to the list position
+      if (node[k] >= 0) {
+        const unsigned lb = list_base[node[k]];
+        if (lb == kNoList) node[k] = -1;
+        else rank[k] = lb + atomicAdd(&cursor[size_t(node[k]) * kPad], 1u);
+      }
+    } else if (few) {  // the lanes that hold the same node take their ranks from one atomic
+      const unsigned peers = __match_any_sync(0xffffffffu, node[k]);
+      if (node[k] >= 0) {
+        const int leader = __ffs(peers) - 1;
+        unsigned first = 0;
+        if (lane == leader) first = atomicAdd(&s_at[node[k]], unsigned(__popc(peers)));
+        first = __shfl_sync(peers, first, leader);
+        rank[k] = first + unsigned(__popc(peers & ((1u << lane) - 1)));
+      }
+    } else if (node[k] >= 0) {
+      rank[k] = atomicAdd(&s_at[node[k]], 1u);
+    }
+  }
+  if (cached) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < L; i += kListThreads) {
+      const unsigned c = s_at[i], lb = list_base[i];
+      s_at[i] = lb == kNoList ? kNoList : (c ? lb + atomicAdd(&cursor[size_t(i) * kPad], c) : lb);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    if (node[k] < 0) continue;
+    const size_t r = base + size_t(k) * kListThreads + threadIdx.x;
+    const unsigned at = cached ? s_at[node[k]] : 0u;
+    if (at != kNoList) list[at + rank[k]] = unsigned(r);
+  }
 }
 
 }  // namespace
 
-void launch_plan_partition(const unsigned *node_begin, int L, PlanBuffers pb, int max_items,
-                           cudaStream_t s) {
-  plan_partition_kernel<<<1, 256, 0, s>>>(node_begin, L, pb, pb.scratch_begin, pb.scratch_len,
-                                          pb.scratch_node, max_items);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-}
-
-void launch_plan_hist(const unsigned *node_begin, const NodeRec *parent_rec, int L, int item_rows,
-                      bool use_trick, bool by_hessian, PlanBuffers pb, int max_items,
-                      cudaStream_t s) {
-  plan_hist_kernel<<<1, 256, 0, s>>>(node_begin, parent_rec, L, item_rows, use_trick, by_hessian,
-                                     pb, pb.scratch_begin, pb.scratch_len, pb.scratch_node,
-                                     pb.hist_item_first, max_items);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-}
-
-void launch_plan_fused(const unsigned *parent_begin, const NodeRec *parent_rec, int n_parents,
-                       int item_rows, PlanBuffers pb, int max_items, cudaStream_t s) {
-  plan_fused_kernel<<<1, 256, 0, s>>>(parent_begin, parent_rec, n_parents, item_rows, pb,
-                                      pb.scratch_begin, pb.scratch_len, pb.scratch_node,
-                                      pb.hist_item_first, max_items);
+void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
+  plan_level_kernel<<<1, 256, 0, s>>>(a.child_count, a.parent_begin, a.node_begin, a.parent_rec, a.L, a.item_rows,
+                                      a.use_trick, a.by_hessian, a.pb, a.max_items);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
 
 void launch_descend(const DescendLaunch &a, cudaStream_t s) {
   if (a.n == 0) return;
+  const bool fin = a.child_count == nullptr;
+  if (!fin) ARB_CUDA(cudaMemsetAsync(a.child_count, 0, sizeof(unsigned) * a.L * kPad, s));
   const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
   const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(148) * 8));
   const Geometry &g = a.geo;
-  const bool fin = a.go_right == nullptr;
 #define ARB_LAUNCH(T, FIN)                                                                        \
   descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L, \
-                                              a.node_of, a.go_right, a.leaf_w, a.yhat, a.n)
+                                              a.node_of, a.child_count, a.leaf_w, a.yhat, a.n)
   if (g.bin_bytes == 1) {
     if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
   } else {
@@ -337,29 +343,13 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
   count_launch();
 }
 
-void launch_partition_finish(const unsigned *cursors, const unsigned *node_begin,
-                             unsigned *node_begin_next, NodeRec *rec, int L, cudaStream_t s) {
-  partition_finish_kernel<<<ceil_div(L, 128), 128, 0, s>>>(cursors, node_begin, node_begin_next, rec, L);
+void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const PlanBuffers &pb,
+                         unsigned *list, cudaStream_t s) {
+  if (n == 0) return;
+  const unsigned grid = unsigned((n + kListRows - 1) / kListRows);
+  gather_lists_kernel<<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list);
   ARB_CUDA(cudaGetLastError());
   count_launch();
-}
-
-void launch_partition(const PartitionLaunch &a, cudaStream_t s) {
-  launch_plan_partition(a.node_begin, a.L, a.pb, a.max_items, s);
-  ARB_CUDA(cudaMemsetAsync(a.cursors, 0, 2 * sizeof(unsigned) * a.L, s));
-  if (a.geo.bin_bytes == 1)
-    partition_kernel<unsigned char><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
-      a.node_begin, a.cursors,
-      a.pb.part_items, a.pb.n_part_items, a.go_right);
-  else
-    partition_kernel<unsigned short><<<a.max_items, kPartThreads, 0, s>>>(
-      a.geo.bins, a.geo.pitch, a.geo.bins_cm, a.geo.cm_rows, a.rowid_src, a.rowid_dst, a.rec,
-      a.node_begin, a.cursors,
-      a.pb.part_items, a.pb.n_part_items, a.go_right);
-  ARB_CUDA(cudaGetLastError());
-  count_launch();
-  launch_partition_finish(a.cursors, a.node_begin, a.node_begin_next, a.rec, a.L, s);
 }
 
 }  // namespace arb

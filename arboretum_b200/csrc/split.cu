@@ -161,8 +161,11 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   // keys (u64 per node) and arrival counters (u32 per node) live in one buffer
   ARB_CUDA(cudaMemsetAsync(a.keys, 0, (sizeof(unsigned long long) + sizeof(unsigned)) * a.max_nodes, s));
   unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
-  // spread the double-precision gain arithmetic of small levels over the GPU
-  const int parts = kBinsPerThread;
+  // Small levels: the double-precision gain arithmetic of a (node, tile) is spread over up
+  // to 8 CTAs, which all re-read the tile.  Large levels have enough (node, tile) pairs to
+  // fill the GPU, and the re-reads would only multiply the traffic.
+  int parts = kBinsPerThread;
+  while (parts > 1 && a.L * a.geo.NT * parts > 2 * 148) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair)
     split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
