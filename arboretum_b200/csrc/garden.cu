@@ -433,14 +433,17 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   // targets uploaded with the matrix are read where they are (a later ASetY is seen too)
   const float *y = data->d_y.p ? data->d_y.as<float>() : d_y_.as<float>();
   const unsigned char *labels = data->d_labels.p ? data->d_labels.as<unsigned char>() : d_label_.as<unsigned char>();
-  launch_gradients(g_->cfg.objective, K_, n_, y, labels,
-                   d_yhat_.as<float>(), d_grad_.p, d_qs_.as<QuantScale>(), s);
+  // pass 1: the round's largest |gradient| and hessian (they fix the fixed-point scale)
+  launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
+                   d_qs_.as<QuantScale>(), false, s);
   // row shards must share one fixed-point scale: take the maxima over all ranks
   if (g_->allreduce_max &&
       g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
     throw std::runtime_error("gradient-scale allreduce failed");
   launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
-  launch_quantize_grads(d_grad_.p, n_ * K_, pair_, d_qs_.as<QuantScale>(), s);
+  // pass 2: the gradients as fixed-point integers
+  launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
+                   d_qs_.as<QuantScale>(), true, s);
   if (g_->profile) {
     ARB_CUDA(cudaEventRecord(ev_[1], s));
     ARB_CUDA(cudaEventSynchronize(ev_[1]));

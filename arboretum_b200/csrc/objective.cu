@@ -11,39 +11,80 @@ namespace arb {
 namespace {
 
 // objective.h:66-68: the exponential is evaluated in float, the rest in double.
-__device__ __forceinline__ float sigmoid(float x) { return float(1.0 / (1.0 + expf(-x))); }
+// (1.0 / d and the correctly rounded reciprocal are the same number)
+__device__ __forceinline__ float sigmoid(float x) { return float(__drcp_rn(1.0 + double(expf(-x)))); }
+// single-precision stand-in, good to a few units in the last place: only used to bound the
+// round's largest |gradient| and hessian, never for a gradient that is summed
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+constexpr float kMaxSlack = 1.0f + 1.0f / 1024.0f;  // the bound errs upwards by far more than that error
 
-__device__ __forceinline__ void block_max_to(unsigned *dst, float v) {
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0 && v > 0.0f) atomicMax(dst, __float_as_uint(v));
+// The round's largest |gradient| and hessian: one atomicMax per CTA and value, and only
+// when the CTA's maximum beats what is already there (the counters share a cache line, so
+// thousands of unconditional atomics would queue up behind one another).
+__device__ __forceinline__ void block_max_to(QuantScale *qs, float mg, float mh) {
+  __shared__ float warp_g[32], warp_h[32];
+  for (int o = 16; o > 0; o >>= 1) {
+    mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+    mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, o));
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    warp_g[warp] = mg;
+    warp_h[warp] = mh;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    mg = lane < nw ? warp_g[lane] : 0.0f;
+    mh = lane < nw ? warp_h[lane] : 0.0f;
+    for (int o = 16; o > 0; o >>= 1) {
+      mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+      mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, o));
+    }
+    if (lane == 0) {
+      const volatile unsigned *seen_g = &qs->max_g_bits, *seen_h = &qs->max_h_bits;
+      if (mg > 0.0f && __float_as_uint(mg) > *seen_g) atomicMax(&qs->max_g_bits, __float_as_uint(mg));
+      if (mh > 0.0f && __float_as_uint(mh) > *seen_h) atomicMax(&qs->max_h_bits, __float_as_uint(mh));
+    }
+  }
 }
 
 // Sign convention of the reference: grad = negative gradient (objective.cu:31,45).
+// Two passes over (y, yhat): EMIT = false finds the maxima that fix the round's fixed-point
+// scale, EMIT = true computes the same floats again and stores them as integers
+// (g_q = rint(g * sg), h_q = max(1, rint(h * sh))): the float gradients never touch memory.
+template <bool EMIT>
 __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
-                                   float *__restrict__ grad, QuantScale *qs, size_t n) {
+                                   int *__restrict__ grad, QuantScale *qs, size_t n) {
   float m = 0.0f;
+  const float sg = EMIT ? qs->sg : 0.0f;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x) {
     const float g = y[i] - yhat[i];
-    grad[i] = g;
-    m = fmaxf(m, fabsf(g));
+    if (EMIT) grad[i] = __float2int_rn(g * sg);
+    else m = fmaxf(m, fabsf(g));
   }
-  block_max_to(&qs->max_g_bits, m);
+  if (!EMIT) block_max_to(qs, m, 0.0f);
 }
 
+template <bool EMIT>
 __global__ void grad_logistic_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
-                                     float2 *__restrict__ grad, QuantScale *qs, size_t n) {
+                                     int2 *__restrict__ grad, QuantScale *qs, size_t n) {
   float mg = 0.0f, mh = 0.0f;
+  const float sg = EMIT ? qs->sg : 0.0f, sh = EMIT ? qs->sh : 0.0f;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x) {
-    const float s = sigmoid(yhat[i]);
+    const float s = EMIT ? sigmoid(yhat[i]) : sigmoid_fast(yhat[i]);
     const float2 g = make_float2(y[i] - s, s * (1.0f - s));
-    grad[i] = g;
-    mg = fmaxf(mg, fabsf(g.x));
-    mh = fmaxf(mh, g.y);
+    if (EMIT) {
+      // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
+      grad[i] = make_int2(__float2int_rn(g.x * sg), max(1, __float2int_rn(g.y * sh)));
+    } else {
+      mg = fmaxf(mg, fabsf(g.x));
+      mh = fmaxf(mh, g.y);
+    }
   }
-  block_max_to(&qs->max_g_bits, mg);
-  block_max_to(&qs->max_h_bits, mh);
+  if (!EMIT) block_max_to(qs, mg * kMaxSlack, mh * kMaxSlack);
 }
 
 // multi:softmax as the reference intends it (objective.cu:60-89, objective.h:100-112):
@@ -65,8 +106,7 @@ __global__ void grad_softmax_kernel(const unsigned char *__restrict__ label,
       mh = fmaxf(mh, g.y);
     }
   }
-  block_max_to(&qs->max_g_bits, mg);
-  block_max_to(&qs->max_h_bits, mh);
+  block_max_to(qs, mg, mh);
 }
 
 __global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) {
@@ -170,16 +210,21 @@ inline int grid_for(size_t n, int threads) {
 }  // namespace
 
 void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
-                      const float *yhat, void *grad, QuantScale *qs, cudaStream_t s) {
-  ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
+                      const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s) {
+  if (!emit) ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
   const int threads = 256;
   const int grid = grid_for(n, threads);
-  if (objective == 0)
-    grad_linear_kernel<<<grid, threads, 0, s>>>(y, yhat, static_cast<float *>(grad), qs, n);
-  else if (objective == 1)
-    grad_logistic_kernel<<<grid, threads, 0, s>>>(y, yhat, static_cast<float2 *>(grad), qs, n);
-  else
+  if (objective == 0) {
+    if (emit) grad_linear_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n);
+    else grad_linear_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n);
+  } else if (objective == 1) {
+    if (emit) grad_logistic_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n);
+    else grad_logistic_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n);
+  } else if (!emit) {  // the K double-precision exponentials per row are not computed twice:
     grad_softmax_kernel<<<grid, threads, 0, s>>>(label, yhat, static_cast<float2 *>(grad), qs, n, K);
+  } else {             // the floats are stored by the first pass and turned into integers in place
+    quantize_pair_kernel<<<grid_for(n * K, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n * K, qs);
+  }
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
