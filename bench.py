@@ -336,19 +336,36 @@ def main():
         return float(t.item())
 
     # ---- end to end: host buffers -> model -> predictions on the host --------------
-    barrier()
-    t0 = time.perf_counter()
-    model, data = new_model()
-    for _ in range(args.steps):
-        model.grow_tree()
-    yhat = model.train_yhat()
-    barrier()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    # A small job first, so that the timed runs do not pay for loading the kernels and for
+    # the allocator's first calls; then the whole job three times, the median is reported.
+    warm_rows = min(n_local, 200_000)
+    Xw, yw, lw = gen(warm_rows, 10_000 + rank)
+    kw = {"binned_hist_size": 255} if binned else {}
+    wd = arboretum.DMatrix(Xw, labels=lw, **kw) if lw is not None else arboretum.DMatrix(Xw, y=yw, **kw)
+    wm = arboretum.Garden(cfg)
+    wm.data = wd
+    wm.labels_count = wd.labels_count
+    wm.grow_tree()
+    wm.train_yhat()
+    del wm, wd
+    e2e_runs = []
+    for _ in range(3 if world == 1 else 1):  # (a rank set-up per run would dominate N > 1)
+        model = data = None
+        barrier()
+        t0 = time.perf_counter()
+        model, data = new_model()
+        for _ in range(args.steps):
+            model.grow_tree()
+        yhat = model.train_yhat()
+        barrier()
+        e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
+    e2e_s = sorted(e2e_runs)[len(e2e_runs) // 2]
     e2e = {"value": args.steps / e2e_s, "unit": "rounds/s",
            "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) * world / args.steps),
            "d2h_bytes_per_step": int(yhat.nbytes * world / args.steps),
-           "what": "DMatrix from pinned host fp32 + quantise + %d rounds + predictions to host"
-                   % args.steps}
+           "runs_s": [round(t, 4) for t in e2e_runs],
+           "what": "median of %d: DMatrix from pinned host memory + quantise + %d rounds + "
+                   "predictions to host" % (len(e2e_runs), args.steps)}
 
     # ---- device-resident rounds (the model above is already bound and warm) ---------
     for _ in range(args.warmup):
