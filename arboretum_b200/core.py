@@ -34,7 +34,7 @@ def _load_lib():
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
                  "AGetLevelStats", "ASetProfile", "AGetTimings", "ABuildHistogram",
-                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc"):
+                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak"):
         getattr(lib, name).restype = ctypes.c_char_p
     lib.ADumpModel.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.c_void_p]
     lib.AFreeDMatrix.argtypes = [ctypes.c_void_p]
@@ -64,6 +64,7 @@ def _load_lib():
                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    lib.ASharedAtomicPeak.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     lib.AThresholdsNoAlloc.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
                                        ctypes.c_void_p, ctypes.c_void_p]
     lib.ANcclUniqueId.argtypes = [ctypes.c_void_p]
@@ -307,6 +308,14 @@ def load(json_model_str):
     model = Garden(config)
     model.load(json_model_str)
     return model
+
+
+def shared_atomic_peak(steps=2000):
+    """(g, h) pair updates per second of the histogram kernels' shared-memory reductions alone
+    (``ASharedAtomicPeak``): the ceiling the histogram pass is measured against."""
+    out = ctypes.c_double(0)
+    _call_and_throw_if_error(_LIB.ASharedAtomicPeak(int(steps), ctypes.byref(out)))
+    return out.value
 
 
 def build_histogram(bins, grad, hist_size, rowid=None, node_begin=None, quant_bits=17, reps=0):

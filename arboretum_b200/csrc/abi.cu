@@ -409,6 +409,14 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   ARB_CATCH
 }
 
+const char *ASharedAtomicPeak(int steps, double *pair_updates_per_s) {
+  ARB_TRY
+  ARB_CHECK(pair_updates_per_s != nullptr, "NULL argument");
+  ARB_CHECK(steps > 0 && steps <= (1 << 20), "steps must be in [1, 2^20]");
+  *pair_updates_per_s = measure_shared_atomic_peak(steps, nullptr);
+  ARB_CATCH
+}
+
 const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
                             const float *grad, int pair, const unsigned *rowid,
                             const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,

@@ -327,6 +327,58 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
   count_launch();
 }
 
+namespace {
+// Ceiling of the histogram kernels' inner loop: every lane adds one (g, h) pair per step to
+// its own column of the two int32 planes at a pseudo-random bin -- the same two conflict-free
+// red.shared instructions per 32 (row, feature) pairs, with no loads, no staging and no
+// stores around them.
+__global__ void __launch_bounds__(kHistThreads, 2) shared_atomic_peak_kernel(int steps, int *sink) {
+  extern __shared__ __align__(16) int smem[];
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  unsigned state = threadIdx.x * 2654435761u + blockIdx.x * 97u + 1u;
+  for (int i = 0; i < steps; ++i) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      state = state * 1664525u + 1013904223u;
+      const int bin = int(state >> 24);
+      red_shared(smem + bin * 32 + lane, int(state & 0xffffu) - 32768);
+      red_shared(smem + kHistWords + bin * 32 + lane, 1 + int(state & 0xffu));
+    }
+  }
+  __syncthreads();
+  int acc = 0;
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) acc ^= smem[w];
+  if (acc == 0x7fffffff) sink[0] = acc;  // keeps the adds alive
+}
+}  // namespace
+
+double measure_shared_atomic_peak(int steps, cudaStream_t s) {
+  const size_t smem = 2 * kHistWords * 4;
+  ARB_SET_SMEM(shared_atomic_peak_kernel, smem);
+  DevBuf sink;
+  sink.alloc(sizeof(int));
+  const int grid = 2 * 148;
+  cudaEvent_t e0, e1;
+  ARB_CUDA(cudaEventCreate(&e0));
+  ARB_CUDA(cudaEventCreate(&e1));
+  float best = 0.0f;
+  for (int rep = 0; rep < 4; ++rep) {  // the first launch warms up
+    ARB_CUDA(cudaEventRecord(e0, s));
+    shared_atomic_peak_kernel<<<grid, kHistThreads, smem, s>>>(steps, sink.as<int>());
+    ARB_CUDA(cudaEventRecord(e1, s));
+    ARB_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.0f;
+    ARB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    if (rep > 0 && (best == 0.0f || ms < best)) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  count_launch(4);
+  return double(grid) * kHistThreads * double(steps) * 8.0 / (double(best) * 1e-3);
+}
+
 void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   const int threads = 256;
   // few built nodes: cut every node's item list into slices so the GPU is filled

@@ -46,6 +46,10 @@ struct HistLaunch {
 void launch_hist(const HistLaunch &a, cudaStream_t s);
 int hist_grid_x(int max_items, int NT);
 
+// (g, h) pair updates per second of the histogram kernels' two shared-memory reductions
+// alone, on the current device: the ceiling their inner loop runs against
+double measure_shared_atomic_peak(int steps, cudaStream_t s);
+
 // planes of the items of every built node -> the level's int64 histogram
 struct ReduceLaunch {
   const int *partials;

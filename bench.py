@@ -253,6 +253,18 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def shared_atomics(t, features):
+    """The histogram pass against the ceiling of its inner loop: (g, h) pair updates per
+    second of the two shared-memory reductions alone, measured by the library on this GPU
+    (every scanned row updates one pair per feature slot, 32 slots per tile of features)."""
+    from arboretum_b200 import core
+    peak = core.shared_atomic_peak(2000)
+    slots = (features + 31) // 32 * 32
+    achieved = t["hist_rows"] * slots / (t["hist_ms"] * 1e-3)
+    return {"achieved": achieved, "peak": peak, "frac": achieved / peak, "unit": "(g, h) updates/s",
+            "note": "histogram + reduce time of all levels; feature slots padded to 32 per tile"}
+
+
 def workload_config(args, world):
     _, features, _, cfg, desc = WORKLOADS[args.workload]
     pitch = (features + 31) // 32 * 32
@@ -408,6 +420,7 @@ def main():
                     "rows_x_features_per_s_per_gpu": t["hist_rows"] * features / (t["hist_ms"] * 1e-3),
                     "smem_atomic_updates_per_s": 2.0 * t["hist_rows"] * features / (t["hist_ms"] * 1e-3),
                     "tree_ms": t["tree_ms"] / max(1, t["trees"]),
+                    "shared_atomics": shared_atomics(t, features),
                     "phase_ms_per_round": {k: t[k] / prof_rounds for k in
                                            ("grad_ms", "partition_ms", "plan_ms", "hist_ms", "allreduce_ms",
                                             "subtract_ms", "split_ms", "update_ms")}}

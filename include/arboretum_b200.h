@@ -108,6 +108,13 @@ const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128
 const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist_size,
                                float *thr_device, void *stream);
 
+/* Additive (no counterpart in the reference): measures, on the current device, how many
+ * (gradient, hessian) pair updates per second the histogram kernels' two shared-memory
+ * reductions sustain when nothing else is done (no loads, staging or stores) -- the
+ * ceiling of their inner loop.  `steps` x 8 updates per thread of a full grid; a few
+ * thousand steps run for a millisecond. */
+const char *ASharedAtomicPeak(int steps, double *pair_updates_per_s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -210,7 +210,7 @@ def synth(kind, n, F, seed):
     return X, y.astype(np.float32)
 
 
-def compare_with_oracle(cfg, X, y, rounds, labels=None):
+def compare_with_oracle(cfg, X, y, rounds, labels=None, max_level=None):
     """Grow `rounds` rounds on both sides, comparing level by level."""
     arboretum = arb()
     if labels is None:
@@ -231,7 +231,7 @@ def compare_with_oracle(cfg, X, y, rounds, labels=None):
         if K > 1:
             continue  # per-level records exist for the last tree of a round only
         diverged = False
-        for l in range(depth):
+        for l in range(min(depth, max_level or depth)):
             g = model.level_stats(l)
             e = o.level(o.num_trees() - 1, l)
             if l > 0 and not diverged:
@@ -310,6 +310,33 @@ def test_missing_values_go_right():
     model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 3)
     if ambiguous == 0:
         assert np.allclose(model.predict(data), o.predict(X), atol=PRED_ATOL, rtol=0)
+
+
+@pytest.mark.parametrize("kind,objective", [("linear", 0), ("logistic", 1)])
+def test_deep_tree_beyond_the_shared_memory_node_tables(kind, objective):
+    # 4096 nodes on the last level: the descend and list kernels leave their 2048-entry
+    # shared-memory tables and count / rank through global memory
+    X, y = synth(kind, 20000, 12, seed=31)
+    cfg = make_config(objective, 14)
+    # level by level against the oracle down to the nodes of a few hundred rows; below that
+    # a node's gain is a small difference of large terms and the fixed-point step of the
+    # gradients (half a step per row) shows in it
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 2, max_level=7)
+    # the leaf every training row was counted into is the leaf the finished trees send its
+    # raw feature values to: the per-row node numbers against the fp32 tree walk
+    internal = model.train_yhat()[0]
+    pred = model.predict(data)
+    if objective == 1:
+        internal = 1.0 / (1.0 + np.exp(-internal.astype(np.float64)))
+    assert np.allclose(internal, pred, atol=1e-5, rtol=0)
+    # the same trees without the subtraction trick (every node gets a list)
+    arboretum = arb()
+    out = []
+    for trick in (True, False):
+        c = make_config(objective, 14)
+        c["internals"]["use_hist_subtraction_trick"] = trick
+        out.append(json.loads(arboretum.train(c, arboretum.DMatrix(X, y=y), 2).dump())["model"])
+    assert out[0] == out[1]
 
 
 def test_uint16_bins_training():
