@@ -193,6 +193,7 @@ class Builder {
     d_leaf_w_, d_active_, d_fsize_;
   DevBuf d_node_of_;  // per row: the node (inside the current level) it stands on
   DevBuf d_list_;     // row lists of the built nodes of the current level, back to back
+  DevBuf d_list_grad_;  // their gradient records in the same order (uint8 data)
   DevBuf d_partials_, d_hist_items_, d_counters_, d_first_, d_built_, d_scratch_, d_list_base_,
     d_cursor_, d_child_count_;
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
@@ -294,6 +295,9 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
   d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
   d_list_.alloc(n_ * sizeof(unsigned));
+  // the histogram kernel of uint8 data reads the gradient records in list order
+  if (geo_.bin_bytes == 1 && geo_.TW == 32)
+    d_list_grad_.alloc(n_ * (pair_ ? sizeof(int2) : sizeof(int)));
   d_node_of_.alloc(n_ * sizeof(unsigned short));
   trace.lap("per-row state");
   // level state
@@ -540,7 +544,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       pl.pb = pb_;
       pl.max_items = max_hist_items_;
       launch_plan_level(pl, s);
-      if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, s);
+      void *list_grad = d_list_grad_.p ? static_cast<char *>(d_list_grad_.p) + ch.begin * gsz : nullptr;
+      if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
       if (last) mark();
       HistLaunch h;
       h.geo = geo;
@@ -551,6 +556,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       h.n_items = pb_.n_hist_items;
       h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
       h.partials = d_partials_.as<int>();
+      h.list_grad = l == 0 ? nullptr : list_grad;
       launch_hist(h, s);
       ReduceLaunch rd;
       rd.partials = d_partials_.as<int>();

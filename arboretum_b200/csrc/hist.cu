@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kHistThreads, 2)
 hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
-               int *__restrict__ partials) {
+               int *__restrict__ partials, const void *__restrict__ list_grad) {
   extern __shared__ __align__(16) int smem[];
   int *G = smem;
   constexpr int kWarps = kHistThreads / 32;
@@ -105,8 +105,13 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
                  tile_base + size_t(r1) * pitch + (lane & 1) * 16);
       // rows past the end of the item get a zero gradient record: they add nothing
       const bool valid = unsigned(b * 32 + lane) < len;
-      cp_async_zfill<GSZ>(sb + 1024 + lane * GSZ, static_cast<const char *>(grad) + size_t(rid_lane) * GSZ,
-                          valid ? GSZ : 0);
+      // the gradient records lie in list order beside the row ids when the list pass copied
+      // them (a sequential read); otherwise they are gathered by row id like the bins
+      const char *gsrc = list_grad
+                           ? static_cast<const char *>(list_grad) +
+                               size_t(item.begin + min(unsigned(b * 32 + lane), len - 1)) * GSZ
+                           : static_cast<const char *>(grad) + size_t(rid_lane) * GSZ;
+      cp_async_zfill<GSZ>(sb + 1024 + lane * GSZ, gsrc, valid ? GSZ : 0);
       cp_async_commit();
     };
 
@@ -295,7 +300,7 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
     ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                               \
     hist_u8_kernel<P, I><<<grid, kHistThreads, smem, s>>>(g.bins, g.pitch, g.NT, a.rowid,     \
                                                           a.grad, a.items, a.n_items,         \
-                                                          a.partials);                        \
+                                                          a.partials, a.list_grad);           \
   } while (0)
     if (a.pair) {
       if (ident) ARB_LAUNCH(true, true); else ARB_LAUNCH(true, false);

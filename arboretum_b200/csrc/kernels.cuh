@@ -42,6 +42,9 @@ struct HistLaunch {
   const int *n_items;
   int max_items;
   int *partials;  // [item][tile][2][kHistWords] int32 planes, written here
+  const void *list_grad = nullptr;  // gradient records in list order (position p of `rowid` <->
+                                    // record p), or nullptr: gathered from `grad` by row id.
+                                    // Read by the uint8 kernel only.
 };
 void launch_hist(const HistLaunch &a, cudaStream_t s);
 int hist_grid_x(int max_items, int NT);
@@ -133,9 +136,11 @@ struct LevelPlanLaunch {
 };
 void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s);
 
-// rows of the built nodes -> list[pb.list_base[node] + ...]
+// rows of the built nodes -> list[pb.list_base[node] + ...]; with list_grad != nullptr their
+// gradient records (int2 if pair, else int) are copied to the same positions of list_grad
 void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const PlanBuffers &pb,
-                         unsigned *list, cudaStream_t s);
+                         unsigned *list, const void *grad, void *list_grad, bool pair,
+                         cudaStream_t s);
 
 // --- objective, leaves, prediction ----------------------------------------------
 // Gradients of the round in two passes over (y, yhat).  emit = false: the largest |g| and h

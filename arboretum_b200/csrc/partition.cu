@@ -30,7 +30,7 @@ namespace {
 constexpr unsigned kNoList = 0xffffffffu;
 constexpr int kDescendPasses = 8;   // a warp takes 32 * 8 consecutive rows per turn
 constexpr int kSmemNodes = 2048;    // nodes of a level whose tables fit in shared memory
-constexpr int kListRows = 4096;     // rows of one CTA of the list pass
+constexpr int kListRows = 2048;     // rows of one CTA of the list pass
 constexpr int kListThreads = 256;
 // Counters that many CTAs add to (children counts, list cursors) sit one per 128-byte line:
 // atomics on one line are served one after the other by a single L2 slice, so packed
@@ -252,10 +252,12 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
 // (one atomic per group of lanes with the same node while the level has at most kFewLists
 // nodes: there the lanes of a warp would all meet on the same few counters), the CTA reserves room in every list it has rows for
 // with one global atomicAdd, and the rows are written at list start + CTA base + rank.
+template <typename GRAD_T>  // int2 / int: the gradient record copied along; char: none
 __global__ void __launch_bounds__(kListThreads)
 gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, const int L,
                     const unsigned *__restrict__ list_base, unsigned *__restrict__ cursor,
-                    unsigned *__restrict__ list) {
+                    unsigned *__restrict__ list, const GRAD_T *__restrict__ grad,
+                    GRAD_T *__restrict__ list_grad) {
   // per node: first the CTA's row count, then where the CTA's rows of the node go (kNoList:
   // the node has no list)
   __shared__ unsigned s_at[kSmemNodes];
@@ -270,10 +272,12 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
   }
   int node[kPer];
   unsigned rank[kPer];
+  GRAD_T gv[kPer];  // the rows' gradient records, fetched with the node numbers: one more stream
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
     const size_t r = base + size_t(k) * kListThreads + threadIdx.x;
     node[k] = r < n ? int(node_of[r]) : -1;
+    if (sizeof(GRAD_T) > 1 && r < n) gv[k] = grad[r];
   }
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
@@ -310,7 +314,10 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
     if (node[k] < 0) continue;
     const size_t r = base + size_t(k) * kListThreads + threadIdx.x;
     const unsigned at = cached ? s_at[node[k]] : 0u;
-    if (at != kNoList) list[at + rank[k]] = unsigned(r);
+    if (at != kNoList) {
+      list[at + rank[k]] = unsigned(r);
+      if (sizeof(GRAD_T) > 1) list_grad[at + rank[k]] = gv[k];
+    }
   }
 }
 
@@ -344,10 +351,21 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
 }
 
 void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const PlanBuffers &pb,
-                         unsigned *list, cudaStream_t s) {
+                         unsigned *list, const void *grad, void *list_grad, bool pair,
+                         cudaStream_t s) {
   if (n == 0) return;
   const unsigned grid = unsigned((n + kListRows - 1) / kListRows);
-  gather_lists_kernel<<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list);
+  if (!list_grad)
+    gather_lists_kernel<char><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
+                                                            nullptr, nullptr);
+  else if (pair)
+    gather_lists_kernel<int2><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
+                                                            static_cast<const int2 *>(grad),
+                                                            static_cast<int2 *>(list_grad));
+  else
+    gather_lists_kernel<int><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
+                                                           static_cast<const int *>(grad),
+                                                           static_cast<int *>(list_grad));
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
