@@ -60,7 +60,15 @@ struct NcclApi {
 };
 NcclApi g_nccl;
 
+// The first communicator a process makes is kept for the life of the process and can be
+// attached to later Gardens (AInitNccl with a NULL id): bringing one up takes a second or
+// more, far longer than a short training job.  It is never destroyed (at exit the CUDA
+// context may already be gone).
+ncclComm_t g_process_comm = nullptr;
+int g_process_world = 0, g_process_rank = -1;
+
 struct NcclCtx {
+  bool shared = false;  // comm is g_process_comm: not destroyed with the Garden
   ncclComm_t comm = nullptr;
 };
 
@@ -323,7 +331,7 @@ const char *AFreeGarden(VoidPointer ptr) {
   Garden *g = static_cast<Garden *>(ptr);
   if (g && g->allreduce_ctx) {
     NcclCtx *c = static_cast<NcclCtx *>(g->allreduce_ctx);
-    if (c->comm) g_nccl.CommDestroy(c->comm);
+    if (c->comm && !c->shared) g_nccl.CommDestroy(c->comm);
     delete c;
     g->allreduce_ctx = nullptr;
   }
@@ -557,16 +565,31 @@ const char *ANcclUniqueId(char *id128) {
 
 const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128) {
   ARB_TRY
-  ARB_CHECK(garden && id128, "NULL argument");
+  ARB_CHECK(garden, "NULL argument");
   ARB_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank / world size");
   Garden *g = static_cast<Garden *>(garden);
   ARB_CHECK(g->builder == nullptr, "AInitNccl must precede the first AGrowTree");
+  ARB_CHECK(g->allreduce_ctx == nullptr, "the Garden already has a communicator");
   g_nccl.load();
-  ncclUniqueId id;
-  std::memcpy(&id, id128, 128);
   std::unique_ptr<NcclCtx> c(new NcclCtx());
-  const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
-  if (r != ncclSuccess) throw std::runtime_error(std::string("ncclCommInitRank: ") + g_nccl.GetErrorString(r));
+  if (id128 == nullptr) {  // attach the communicator this process already has
+    ARB_CHECK(g_process_comm != nullptr, "no communicator to reuse: pass the ncclUniqueId");
+    ARB_CHECK(g_process_world == world && g_process_rank == rank,
+              "the process's communicator was made for another rank / world size");
+    c->comm = g_process_comm;
+    c->shared = true;
+  } else {
+    ncclUniqueId id;
+    std::memcpy(&id, id128, 128);
+    const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
+    if (r != ncclSuccess) throw std::runtime_error(std::string("ncclCommInitRank: ") + g_nccl.GetErrorString(r));
+    if (g_process_comm == nullptr) {
+      g_process_comm = c->comm;
+      g_process_world = world;
+      g_process_rank = rank;
+      c->shared = true;
+    }
+  }
   g->allreduce = nccl_allreduce;
   g->allreduce_max = nccl_allreduce_max;
   g->allreduce_ctx = c.release();

@@ -60,13 +60,27 @@ def share_thresholds(data, hist_size, rank, world, thresholds=None, sizes=None, 
     return thr, size
 
 
-def init_nccl(garden, rank, world, src=0):
-    """Create the Garden's communicator; must precede its first grow_tree."""
+_PROCESS_COMM = None  # (rank, world) of the communicator this process keeps
+
+
+def init_nccl(garden, rank, world, src=0, reuse=True):
+    """Give the Garden a communicator; must precede its first grow_tree.
+
+    The first call of a process makes one (rank ``src`` draws the ncclUniqueId, the others
+    receive it through torch.distributed) and the library keeps it; later calls with the
+    same rank and world size attach that one (``reuse=False`` makes a new one).  Every rank
+    must take the same path, which they do when they make the same sequence of calls."""
+    global _PROCESS_COMM
     from . import core
     garden._ensure_init()
+    if reuse and _PROCESS_COMM == (rank, world):
+        core._call_and_throw_if_error(core.lib().AInitNccl(garden.handle, rank, world, None))
+        return
     uid = np.zeros(128, dtype=np.uint8)
     if rank == src:
         core._call_and_throw_if_error(core.lib().ANcclUniqueId(uid.ctypes.data_as(ctypes.c_void_p)))
     _broadcast_bytes(uid, src)
     core._call_and_throw_if_error(core.lib().AInitNccl(garden.handle, rank, world,
                                                       uid.ctypes.data_as(ctypes.c_void_p)))
+    if _PROCESS_COMM is None:
+        _PROCESS_COMM = (rank, world)

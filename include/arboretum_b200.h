@@ -88,7 +88,11 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
                             double *out_h, int reps, float *ms);
 /* Multi-GPU: rows are sharded over one process per GPU; every level's histogram
  * is summed over the ranks with ncclAllReduce.  `id` is the 128-byte
- * ncclUniqueId made by rank 0 (ANcclUniqueId) and sent to the others by the host. */
+ * ncclUniqueId made by rank 0 (ANcclUniqueId) and sent to the others by the host.
+ * The first communicator of a process is kept until the process exits; a later Garden
+ * of the same rank and world size attaches it when AInitNccl is given id128 == NULL
+ * (no bootstrap, no host traffic).  Gardens that share a communicator must not train at
+ * the same time. */
 const char *ANcclUniqueId(char *id128);
 const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128);
 
