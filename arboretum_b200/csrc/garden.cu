@@ -191,6 +191,7 @@ class Builder {
 
   DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_node_begin_, d_rec_, d_hist_[2], d_keys_, d_qs_,
     d_leaf_w_, d_active_, d_fsize_;
+  DevBuf d_compact_;  // row shards: the built nodes' histograms of a level, the part the ranks sum
   DevBuf d_node_of_;  // per row: the node (inside the current level) it stands on
   DevBuf d_list_;     // row lists of the built nodes of the current level, back to back
   DevBuf d_list_grad_;  // their gradient records in the same order (uint8 data)
@@ -501,8 +502,15 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     const bool trick_level = use_trick && l > 0;
     const int n_build = trick_level ? L / 2 : L;
     long long *hist = d_hist_[l & 1].as<long long>();
+    // Row shards sum only what they built: below the root that is one child per parent, so
+    // the exchanged buffer holds those alone and the siblings follow from the parents after
+    // the exchange.
+    const bool compact = trick_level && g_->allreduce != nullptr;
+    if (compact && !d_compact_.p)
+      d_compact_.alloc(size_t(std::max(1, max_nodes_ / 2)) * geo_.NT * kHistWords * 2 * sizeof(long long));
+    long long *reduce_to = compact ? d_compact_.as<long long>() : hist;
     if (multi)
-      ARB_CUDA(cudaMemsetAsync(hist, 0, size_t(L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+      ARB_CUDA(cudaMemsetAsync(reduce_to, 0, size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
     for (int c = 0; c < n_chunks; ++c) {
       const Chunk &ch = chunks_[c];
       const bool last = c + 1 == n_chunks;
@@ -561,14 +569,14 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       ReduceLaunch rd;
       rd.partials = d_partials_.as<int>();
       rd.item_first = pb_.hist_item_first;
-      rd.build_node = pb_.scratch_node;
+      rd.build_node = compact ? nullptr : pb_.scratch_node;
       rd.n_build = n_build;
       rd.NT = geo.NT;
-      rd.level_hist = hist;
+      rd.level_hist = reduce_to;
       rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
       rd.subtract = trick_level && !g_->allreduce && !multi;
-      rd.zero_sibling = trick_level && g_->allreduce && !multi;
-      rd.level_nodes = L;
+      rd.zero_sibling = false;
+      rd.level_nodes = compact ? n_build : L;
       rd.built_child = pb_.built_child;
       rd.accumulate = multi;
       launch_reduce(rd, s);
@@ -576,12 +584,15 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     }
     mark();
     if (g_->allreduce) {
-      const size_t count = size_t(L) * geo_.NT * kHistWords * 2;
-      if (g_->allreduce(g_->allreduce_ctx, hist, count, s) != 0)
+      const size_t count = size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2;
+      if (g_->allreduce(g_->allreduce_ctx, reduce_to, count, s) != 0)
         throw std::runtime_error("histogram allreduce failed");
     }
     mark();
-    if (trick_level && (g_->allreduce || multi))
+    if (compact)
+      launch_expand(d_compact_.as<long long>(), d_hist_[(l - 1) & 1].as<long long>(), hist, pb_.built_child,
+                    L / 2, geo_.NT, s);
+    else if (trick_level && multi)
       launch_subtract(hist, d_hist_[(l - 1) & 1].as<long long>(), pb_.built_child, L / 2, geo_.NT, s);
     mark();
     SplitLaunch sp;

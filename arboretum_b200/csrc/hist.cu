@@ -233,7 +233,7 @@ __global__ void reduce_kernel(const int *__restrict__ partials, const int *__res
     g += p[w];
     h += p[kHistWords + w];
   }
-  const int node = build_node[b];
+  const int node = build_node ? build_node[b] : b;  // no map: the output holds the built nodes only
   const size_t off = (size_t(node) * NT + tile) * kHistWords + w;
   if (slices > 1 || atomic) {
     if (g) atomicAdd(reinterpret_cast<unsigned long long *>(level_hist) + 2 * off, (unsigned long long)g);
@@ -267,6 +267,24 @@ __global__ void subtract_kernel(long long *__restrict__ level_hist,
   }
 }
 
+// built nodes only (in build order) -> both children of every parent:
+// built child = compact, sibling = parent - compact
+__global__ void expand_kernel(const long long *__restrict__ compact,
+                              const long long *__restrict__ parent_hist,
+                              long long *__restrict__ level_hist,
+                              const int *__restrict__ built_child, const size_t words_per_node,
+                              const size_t total) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t p = i / words_per_node;
+    const size_t w = i - p * words_per_node;
+    const int built = built_child[p];
+    const long long v = compact[i];
+    level_hist[(2 * p + built) * words_per_node + w] = v;
+    level_hist[(2 * p + (1 - built)) * words_per_node + w] = parent_hist[i] - v;
+  }
+}
+
 // opt in to more than 48 KB of dynamic shared memory, once per call site
 #define ARB_SET_SMEM(kernel, bytes)                                                        \
   do {                                                                                     \
@@ -279,6 +297,18 @@ __global__ void subtract_kernel(long long *__restrict__ level_hist,
   } while (0)
 
 }  // namespace
+
+void launch_expand(const long long *compact, const long long *parent_hist, long long *level_hist,
+                   const int *built_child, int n_parents, int NT, cudaStream_t s) {
+  const size_t words_per_node = size_t(NT) * kHistWords * 2;
+  const size_t total = size_t(n_parents) * words_per_node;
+  const int threads = 256;
+  const int blocks = int(std::min<size_t>((total + threads - 1) / threads, size_t(148) * 16));
+  expand_kernel<<<blocks, threads, 0, s>>>(compact, parent_hist, level_hist, built_child, words_per_node,
+                                           total);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
 
 void launch_subtract(long long *level_hist, const long long *parent_hist, const int *built_child,
                      int n_parents, int NT, cudaStream_t s);

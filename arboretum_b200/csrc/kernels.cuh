@@ -57,7 +57,8 @@ double measure_shared_atomic_peak(int steps, cudaStream_t s);
 struct ReduceLaunch {
   const int *partials;
   const int *item_first;  // n_build + 1: items of built node b are [first[b], first[b+1])
-  const int *build_node;  // node index (inside the level) of built node b
+  const int *build_node;  // node index (inside the level) of built node b; nullptr: level_hist
+                          // holds the built nodes only, in build order
   int n_build;
   int NT;
   long long *level_hist;
@@ -69,6 +70,11 @@ struct ReduceLaunch {
   bool accumulate = false;  // add into level_hist (cleared by the caller): row chunks of one level
 };
 void launch_reduce(const ReduceLaunch &a, cudaStream_t s);
+
+// The built nodes' histograms alone (what row shards exchange) -> the level's buffer:
+// built child = compact[parent], sibling = parent - compact[parent]
+void launch_expand(const long long *compact, const long long *parent_hist, long long *level_hist,
+                   const int *built_child, int n_parents, int NT, cudaStream_t s);
 
 // sibling = parent - built child, for every parent of the level above
 void launch_subtract(long long *level_hist, const long long *parent_hist, const int *built_child,
