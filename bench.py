@@ -39,7 +39,7 @@ CONFIG = {"objective": 1, "method": 1,
                    "lambda": 1.0, "alpha": 0.0, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}}
 # DRAM bytes per algorithmic byte of the histogram kernel, from the ncu capture
 # summarised in profiles/ (None until a capture exists for this kernel version).
-HIST_TRAFFIC_RATIO = 2.08
+HIST_TRAFFIC_RATIO = 2.45
 
 
 def make_rows(n, seed):
@@ -349,7 +349,7 @@ def main():
 
     # ---- end to end: host buffers -> model -> predictions on the host --------------
     # A small job first, so that the timed runs do not pay for loading the kernels and for
-    # the allocator's first calls; then the whole job three times, the median is reported.
+    # the allocator's first calls; then the whole job five times, the median is reported.
     warm_rows = min(n_local, 200_000)
     Xw, yw, lw = gen(warm_rows, 10_000 + rank)
     kw = {"binned_hist_size": 255} if binned else {}
@@ -365,7 +365,7 @@ def main():
     wm.train_yhat()
     del wm, wd
     e2e_runs = []
-    for _ in range(3):
+    for _ in range(5):
         model = data = None
         barrier()
         t0 = time.perf_counter()
