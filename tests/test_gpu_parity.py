@@ -203,9 +203,9 @@ def synth(kind, n, F, seed):
     X = rng.normal(size=(n, F)).astype(np.float32)
     w = rng.normal(size=F)
     if kind == "linear":  # the small regression config: y = w.x + 0.5 x0 x1 + noise
-        y = X @ w + 0.5 * X[:, 0] * X[:, 1] + rng.normal(0, 0.1, n)
+        y = X @ w + 0.5 * X[:, 0] * X[:, min(1, F - 1)] + rng.normal(0, 0.1, n)
     else:
-        logit = X @ w * 0.5 + 0.3 * X[:, 0] * X[:, 1]
+        logit = X @ w * 0.5 + 0.3 * X[:, 0] * X[:, min(1, F - 1)]
         y = (rng.random(n) < 1 / (1 + np.exp(-logit))).astype(np.float64)
     return X, y.astype(np.float32)
 
@@ -337,6 +337,27 @@ def test_deep_tree_beyond_the_shared_memory_node_tables(kind, objective):
         c["internals"]["use_hist_subtraction_trick"] = trick
         out.append(json.loads(arboretum.train(c, arboretum.DMatrix(X, y=y), 2).dump())["model"])
     assert out[0] == out[1]
+
+
+@pytest.mark.parametrize("n,F,hist_size,depth,objective", [
+    (33, 1, 255, 2, 0),        # fewer rows than a warp, one feature, a single split
+    (2049, 3, 15, 3, 1),       # one row past a work item, 16 bins
+    (5000, 33, 255, 4, 1),     # one feature past a tile of 32: two tiles, the second nearly empty
+    (5000, 65, 255, 5, 0),     # three tiles
+    (3000, 7, 2047, 4, 0),     # the largest table: uint16 bins, 4 features per tile
+    (4000, 5, 256, 4, 1),      # the smallest uint16 table
+    (70000, 28, 255, 9, 1),    # more rows than one CTA of any pass, 256 nodes on the last level
+])
+def test_edge_shapes_match_oracle(n, F, hist_size, depth, objective):
+    X, y = synth("linear" if objective == 0 else "logistic", n, F, seed=n + F)
+    cfg = make_config(objective, depth, hist_size=hist_size)
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 3, max_level=7)
+    internal = model.train_yhat()[0]
+    if objective == 1:
+        internal = 1.0 / (1.0 + np.exp(-internal.astype(np.float64)))
+    assert np.allclose(internal, model.predict(data), atol=1e-5, rtol=0)
+    if ambiguous == 0 and depth <= 7:
+        assert np.allclose(model.train_yhat()[0], o.yhat()[0], atol=PRED_ATOL, rtol=0)
 
 
 def test_uint16_bins_training():
