@@ -364,22 +364,33 @@ def main():
     wm.grow_tree()
     wm.train_yhat()
     del wm, wd
-    e2e_runs = []
+    e2e_runs, e2e_parts = [], []
     for _ in range(5):
         model = data = None
         barrier()
         t0 = time.perf_counter()
         model, data = new_model()
-        for _ in range(args.steps):
+        t1 = time.perf_counter()
+        model.grow_tree()  # quantises the matrix first
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        for _ in range(args.steps - 1):
             model.grow_tree()
+        torch.cuda.synchronize()
+        t3 = time.perf_counter()
         yhat = model.train_yhat()
+        t4 = time.perf_counter()
         barrier()
         e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
+        e2e_parts.append([round(b - a, 4) for a, b in ((t0, t1), (t1, t2), (t2, t3), (t3, t4))])
     e2e_s = sorted(e2e_runs)[len(e2e_runs) // 2]
     e2e = {"value": args.steps / e2e_s, "unit": "rounds/s",
            "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) * world / args.steps),
            "d2h_bytes_per_step": int(yhat.nbytes * world / args.steps),
            "runs_s": [round(t, 4) for t in e2e_runs],
+           "parts_s": {"order": ["DMatrix (host to device)", "quantise + first round", "other rounds",
+                                 "predictions to host"],
+                       "per_run": e2e_parts},
            "what": "median of %d: DMatrix from pinned host memory + quantise + %d rounds + "
                    "predictions to host; CUDA context, kernel images and (N > 1) the NCCL "
                    "communicator exist before the timed jobs" % (len(e2e_runs), args.steps)}
