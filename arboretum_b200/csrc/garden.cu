@@ -753,10 +753,53 @@ void BuilderView::scales(Garden *g, QuantScale *out) {
   ARB_CHECK(g->builder, "no tree has been grown yet");
   ARB_CUDA(cudaMemcpy(out, g->builder->d_qs_.p, sizeof(QuantScale), cudaMemcpyDeviceToHost));
 }
+namespace {
+// Device -> pageable host memory for large results.  A plain cudaMemcpy into memory the
+// caller has just allocated spends most of its time in one thread that takes the page
+// faults of the destination; here a few threads each bring their share through their own
+// small pinned buffer (kept for the life of the process) and copy it out, so the faults
+// and the copies run side by side with the DMA.
+void copy_to_host(void *dst, const void *src_device, size_t bytes) {
+  constexpr int kThreads = 4;
+  constexpr size_t kPiece = size_t(2) << 20;
+  if (bytes < 4 * kPiece) {
+    ARB_CUDA(cudaMemcpy(dst, src_device, bytes, cudaMemcpyDeviceToHost));
+    return;
+  }
+  static void *bounce[kThreads] = {nullptr, nullptr, nullptr, nullptr};
+  for (void *&b : bounce)
+    if (!b) ARB_CUDA(cudaMallocHost(&b, kPiece));
+  int device = 0;
+  ARB_CUDA(cudaGetDevice(&device));
+  const size_t pieces = (bytes + kPiece - 1) / kPiece;
+  cudaError_t status[kThreads];
+  std::vector<std::thread> pool;
+  for (int t = 0; t < kThreads; ++t) {
+    status[t] = cudaSuccess;
+    pool.emplace_back([=, &status]() {
+      cudaError_t e = cudaSetDevice(device);
+      cudaStream_t st = nullptr;
+      if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+      for (size_t p = size_t(t); p < pieces && e == cudaSuccess; p += kThreads) {
+        const size_t off = p * kPiece, len = std::min(kPiece, bytes - off);
+        e = cudaMemcpyAsync(bounce[t], static_cast<const char *>(src_device) + off, len,
+                            cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e == cudaSuccess) std::memcpy(static_cast<char *>(dst) + off, bounce[t], len);
+      }
+      if (st) cudaStreamDestroy(st);
+      status[t] = e;
+    });
+  }
+  for (auto &th : pool) th.join();
+  for (cudaError_t e : status) ARB_CUDA(e);
+}
+}  // namespace
+
 void BuilderView::train_yhat(Garden *g, float *out) {
   ARB_CHECK(g->builder, "no tree has been grown yet");
   ARB_CUDA(cudaStreamSynchronize(g->stream));
-  ARB_CUDA(cudaMemcpy(out, g->builder->d_yhat_.p, g->builder->d_yhat_.bytes, cudaMemcpyDeviceToHost));
+  copy_to_host(out, g->builder->d_yhat_.p, g->builder->d_yhat_.bytes);
 }
 
 // ---------------------------------------------------------------------------
