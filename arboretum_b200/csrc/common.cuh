@@ -36,6 +36,7 @@ namespace arb {
 struct DevBuf {
   void *p = nullptr;
   size_t bytes = 0;
+  bool owned = true;  // false: a window on another buffer's memory (see view)
   DevBuf() {}
   DevBuf(const DevBuf &) = delete;
   DevBuf &operator=(const DevBuf &) = delete;
@@ -46,10 +47,18 @@ struct DevBuf {
     ARB_CUDA(cudaMalloc(&p, n));
     bytes = n;
   }
+  // n bytes at `ptr`, owned by someone else who outlives this object
+  void view(void *ptr, size_t n) {
+    release();
+    p = ptr;
+    bytes = n;
+    owned = false;
+  }
   void release() {
-    if (p) cudaFree(p);
+    if (p && owned) cudaFree(p);
     p = nullptr;
     bytes = 0;
+    owned = true;
   }
   template <typename T>
   T *as() const {
@@ -61,6 +70,7 @@ struct DevBuf {
 struct PinnedBuf {
   void *p = nullptr;
   size_t bytes = 0;
+  bool owned = true;
   PinnedBuf() {}
   PinnedBuf(const PinnedBuf &) = delete;
   PinnedBuf &operator=(const PinnedBuf &) = delete;
@@ -71,10 +81,17 @@ struct PinnedBuf {
     ARB_CUDA(cudaMallocHost(&p, n));
     bytes = n;
   }
+  void view(void *ptr, size_t n) {
+    release();
+    p = ptr;
+    bytes = n;
+    owned = false;
+  }
   void release() {
-    if (p) cudaFreeHost(p);
+    if (p && owned) cudaFreeHost(p);
     p = nullptr;
     bytes = 0;
+    owned = true;
   }
   template <typename T>
   T *as() const {

@@ -52,7 +52,7 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
   const size_t n = size_t(rows);
   StageTrace trace("InitHist");
   if (!prebinned) {
-    DevBuf d_x_tmp, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
+    DevBuf d_quant_arena, d_x_tmp, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
     if (!d_x.p) {
       d_x_tmp.alloc(n * F * sizeof(float));
       ARB_CUDA(cudaMemcpyAsync(d_x_tmp.p, x.data(), n * F * sizeof(float), cudaMemcpyHostToDevice, s));
@@ -60,10 +60,27 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     const DevBuf &d_x = this->d_x.p ? this->d_x : d_x_tmp;
     if (!thresholds_given) {
       const int block_cols = std::min(F, 32);  // columns made contiguous at a time
-      d_col.alloc(n * block_cols * sizeof(float));
-      d_sorted.alloc(n * sizeof(float));
-      d_scratch.alloc(thresholds_scratch_words(n) * sizeof(unsigned));
-      d_thr_f.alloc(size_t(F) * hs * sizeof(float));
+      {  // one allocation (and later one free) for the quantizer's temporaries
+        struct Want {
+          DevBuf *buf;
+          size_t bytes;
+        };
+        const Want wants[] = {
+          {&d_col, n * block_cols * sizeof(float)},
+          {&d_sorted, n * sizeof(float)},
+          {&d_tmp, sort_floats_temp_bytes(n)},
+          {&d_scratch, thresholds_scratch_words(n) * sizeof(unsigned)},
+          {&d_thr_f, size_t(F) * hs * sizeof(float)},
+        };
+        size_t total = 0;
+        for (const Want &w : wants) total += (w.bytes + 255) / 256 * 256;
+        d_quant_arena.alloc(total);
+        size_t at = 0;
+        for (const Want &w : wants) {
+          w.buf->view(static_cast<char *>(d_quant_arena.p) + at, w.bytes);
+          at += (w.bytes + 255) / 256 * 256;
+        }
+      }
       for (int f0 = 0; f0 < F; f0 += block_cols) {
         const int nf = std::min(block_cols, F - f0);
         launch_transpose_columns(d_x.as<float>(), n, F, f0, nf, d_col.as<float>(), s);
@@ -87,9 +104,13 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       }
     }
     ARB_CHECK(int(thr.size()) == F * hs && int(fsize.size()) == F, "threshold table has the wrong shape");
-    DevBuf d_thr, d_fsize;
-    d_thr.alloc(thr.size() * sizeof(float));
-    d_fsize.alloc(F * sizeof(int));
+    DevBuf d_thr_arena, d_thr, d_fsize;
+    {
+      const size_t a = (thr.size() * sizeof(float) + 255) / 256 * 256;
+      d_thr_arena.alloc(a + F * sizeof(int));
+      d_thr.view(d_thr_arena.p, thr.size() * sizeof(float));
+      d_fsize.view(static_cast<char *>(d_thr_arena.p) + a, F * sizeof(int));
+    }
     ARB_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), thr.size() * sizeof(float), cudaMemcpyHostToDevice, s));
     ARB_CUDA(cudaMemcpyAsync(d_fsize.p, fsize.data(), F * sizeof(int), cudaMemcpyHostToDevice, s));
     d_bins.alloc(n * pitch);
@@ -197,6 +218,11 @@ class Builder {
   DevBuf d_list_grad_;  // their gradient records in the same order (uint8 data)
   DevBuf d_partials_, d_hist_items_, d_counters_, d_first_, d_built_, d_scratch_, d_list_base_,
     d_cursor_, d_child_count_;
+  DevBuf d_arena_;      // backs the small per-level arrays below
+  DevBuf d_rows_arena_; // backs the per-row arrays
+  bool events_made_ = false;
+  void EnsureEvents();
+  PinnedBuf h_arena_;   // backs the read-back buffers
   PinnedBuf h_rec_, h_leaf_w_, h_node_begin_;
   std::vector<unsigned> h_nb_total_;
   PlanBuffers pb_;
@@ -291,15 +317,31 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
       ARB_CUDA(cudaMemcpyAsync(d_y_.p, d->y.data(), n_ * sizeof(float), cudaMemcpyHostToDevice, s));
     }
   }
-  d_yhat_.alloc(n_ * K_ * sizeof(float));
+  {  // one allocation for the per-row arrays
+    struct Want {
+      DevBuf *buf;
+      size_t bytes;
+    };
+    // the histogram kernel of uint8 data reads the gradient records in list order
+    const bool listed_grads = geo_.bin_bytes == 1 && geo_.TW == 32;
+    const Want wants[] = {
+      {&d_yhat_, n_ * K_ * sizeof(float)},
+      {&d_grad_, n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float))},
+      {&d_list_, n_ * sizeof(unsigned)},
+      {&d_list_grad_, listed_grads ? n_ * (pair_ ? sizeof(int2) : sizeof(int)) : 0},
+      {&d_node_of_, n_ * sizeof(unsigned short)},
+    };
+    size_t total = 0;
+    for (const Want &w : wants) total += (w.bytes + 255) / 256 * 256;
+    d_rows_arena_.alloc(total);
+    size_t at = 0;
+    for (const Want &w : wants) {
+      if (w.bytes) w.buf->view(static_cast<char *>(d_rows_arena_.p) + at, w.bytes);
+      at += (w.bytes + 255) / 256 * 256;
+    }
+  }
   // garden.cu:105: y_hat starts at IntoInternal(initial_y)
   launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
-  d_grad_.alloc(n_ * K_ * (pair_ ? sizeof(float2) : sizeof(float)));
-  d_list_.alloc(n_ * sizeof(unsigned));
-  // the histogram kernel of uint8 data reads the gradient records in list order
-  if (geo_.bin_bytes == 1 && geo_.TW == 32)
-    d_list_grad_.alloc(n_ * (pair_ ? sizeof(int2) : sizeof(int)));
-  d_node_of_.alloc(n_ * sizeof(unsigned short));
   trace.lap("per-row state");
   // level state
   {
@@ -307,33 +349,48 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     for (size_t b = 0; b < n_; b += chunk_rows)
       chunks_.push_back(Chunk{b, std::min(chunk_rows, n_ - b), nullptr});
   }
-  d_node_begin_.alloc(chunks_.size() * size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned));
-  ARB_CUDA(cudaMemsetAsync(d_node_begin_.p, 0, d_node_begin_.bytes, s));
+  // the small per-level arrays share one allocation (a cudaMalloc costs far more than they do)
+  {
+    struct Want {
+      DevBuf *buf;
+      size_t bytes;
+    };
+    const Want wants[] = {
+      {&d_node_begin_, chunks_.size() * size_t(levels_ + 1) * nb_stride_ * sizeof(unsigned)},
+      {&d_rec_, size_t(levels_) * max_nodes_ * sizeof(NodeRec)},
+      {&d_keys_, max_nodes_ * (sizeof(unsigned long long) + sizeof(unsigned))},
+      {&d_qs_, sizeof(QuantScale)},
+      {&d_leaf_w_, 2 * max_nodes_ * sizeof(float)},
+      {&d_active_, size_t(levels_) * F_},
+      {&d_fsize_, F_ * sizeof(int)},
+      {&d_hist_items_, max_hist_items_ * sizeof(WorkItem)},
+      {&d_counters_, sizeof(int)},
+      {&d_first_, (max_nodes_ + 2) * sizeof(int)},
+      {&d_built_, max_nodes_ * sizeof(int)},
+      {&d_scratch_, 3 * size_t(max_nodes_ + 1) * sizeof(unsigned)},
+      {&d_list_base_, max_nodes_ * sizeof(unsigned)},
+      {&d_cursor_, size_t(max_nodes_) * kCounterStride * sizeof(unsigned)},
+      {&d_child_count_, size_t(max_nodes_) * kCounterStride * sizeof(unsigned)},
+    };
+    size_t total = 0;
+    for (const Want &w : wants) total += (w.bytes + 255) / 256 * 256;
+    d_arena_.alloc(total);
+    ARB_CUDA(cudaMemsetAsync(d_arena_.p, 0, total, s));  // node_begin, rec and qs start as zeros
+    size_t at = 0;
+    for (const Want &w : wants) {
+      w.buf->view(static_cast<char *>(d_arena_.p) + at, w.bytes);
+      at += (w.bytes + 255) / 256 * 256;
+    }
+  }
   for (size_t c = 0; c < chunks_.size(); ++c) {
     const unsigned root[2] = {0u, unsigned(chunks_[c].rows)};
     ARB_CUDA(cudaMemcpyAsync(node_begin(int(c), 0), root, sizeof root, cudaMemcpyHostToDevice, s));
   }
-  d_rec_.alloc(size_t(levels_) * max_nodes_ * sizeof(NodeRec));
-  ARB_CUDA(cudaMemsetAsync(d_rec_.p, 0, d_rec_.bytes, s));
+  ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
   const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
   d_hist_[0].alloc(level_hist_bytes);
   d_hist_[1].alloc(level_hist_bytes);
   d_partials_.alloc(size_t(max_hist_items_) * geo_.NT * 2 * kHistWords * sizeof(int));
-  d_keys_.alloc(max_nodes_ * (sizeof(unsigned long long) + sizeof(unsigned)));
-  d_qs_.alloc(sizeof(QuantScale));
-  ARB_CUDA(cudaMemsetAsync(d_qs_.p, 0, sizeof(QuantScale), s));
-  d_leaf_w_.alloc(2 * max_nodes_ * sizeof(float));
-  d_active_.alloc(size_t(levels_) * F_);
-  d_fsize_.alloc(F_ * sizeof(int));
-  ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
-  d_hist_items_.alloc(max_hist_items_ * sizeof(WorkItem));
-  d_counters_.alloc(sizeof(int));
-  d_first_.alloc((max_nodes_ + 2) * sizeof(int));
-  d_built_.alloc(max_nodes_ * sizeof(int));
-  d_scratch_.alloc(3 * size_t(max_nodes_ + 1) * sizeof(unsigned));
-  d_list_base_.alloc(max_nodes_ * sizeof(unsigned));
-  d_cursor_.alloc(size_t(max_nodes_) * kCounterStride * sizeof(unsigned));
-  d_child_count_.alloc(size_t(max_nodes_) * kCounterStride * sizeof(unsigned));
   pb_.hist_items = d_hist_items_.as<WorkItem>();
   pb_.n_hist_items = d_counters_.as<int>();
   pb_.hist_item_first = d_first_.as<int>();
@@ -344,15 +401,17 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   pb_.scratch_len = d_scratch_.as<unsigned>() + (max_nodes_ + 1);
   pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * (max_nodes_ + 1));
   trace.lap("level buffers");
-  h_rec_.alloc(d_rec_.bytes);
-  h_leaf_w_.alloc(d_leaf_w_.bytes);
-  h_node_begin_.alloc(d_node_begin_.bytes);
+  {  // one pinned allocation for the three read-back buffers
+    const size_t a = (d_rec_.bytes + 255) / 256 * 256, b = (d_leaf_w_.bytes + 255) / 256 * 256;
+    h_arena_.alloc(a + b + d_node_begin_.bytes);
+    h_rec_.view(h_arena_.p, d_rec_.bytes);
+    h_leaf_w_.view(static_cast<char *>(h_arena_.p) + a, d_leaf_w_.bytes);
+    h_node_begin_.view(static_cast<char *>(h_arena_.p) + a + b, d_node_begin_.bytes);
+  }
   active_fids_.resize(F_);
   active_host_.resize(size_t(levels_) * F_);
-  for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
-  for (auto &e : ev_tree_) ARB_CUDA(cudaEventCreate(&e));
   ARB_CUDA(cudaStreamSynchronize(s));
-  trace.lap("pinned read-back buffers + events");
+  trace.lap("pinned read-back buffers");
   if (!d->out_of_core) {
     chunks_[0].resident = d->d_bins.as<unsigned char>();
   } else {
@@ -390,8 +449,10 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
 }
 
 Builder::~Builder() {
-  for (auto &e : ev_) cudaEventDestroy(e);
-  for (auto &e : ev_tree_) cudaEventDestroy(e);
+  if (events_made_) {
+    for (auto &e : ev_) cudaEventDestroy(e);
+    for (auto &e : ev_tree_) cudaEventDestroy(e);
+  }
   if (copy_stream_) {
     cudaStreamSynchronize(copy_stream_);
     for (int i = 0; i < 2; ++i) {
@@ -432,8 +493,18 @@ void Builder::Release(int chunk) {
   ++consumed_;
 }
 
+// the profiling events are made on first use: two hundred cudaEventCreate calls are
+// not free, and most trainings never profile
+void Builder::EnsureEvents() {
+  if (events_made_) return;
+  for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
+  for (auto &e : ev_tree_) ARB_CUDA(cudaEventCreate(&e));
+  events_made_ = true;
+}
+
 void Builder::UpdateGrad() {  // objective.cu:28-56
   cudaStream_t s = g_->stream;
+  if (g_->profile) EnsureEvents();
   if (g_->profile) ARB_CUDA(cudaEventRecord(ev_[0], s));
   // targets uploaded with the matrix are read where they are (a later ASetY is seen too)
   const float *y = data->d_y.p ? data->d_y.as<float>() : d_y_.as<float>();
@@ -463,6 +534,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   const TreeParam &tp = cfg.tree;
   cudaStream_t s = g_->stream;
   const bool prof = g_->profile;
+  if (prof) EnsureEvents();
   QuantScale *qs = d_qs_.as<QuantScale>();
   const void *grad = static_cast<const char *>(d_grad_.p) +
                      size_t(label) * n_ * (pair_ ? sizeof(float2) : sizeof(float));

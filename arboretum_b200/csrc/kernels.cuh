@@ -202,7 +202,9 @@ void launch_u8_to_f32(const unsigned char *src, float *dst, size_t count, cudaSt
 // columns [f0, f0 + nf) of a row-major fp32 matrix as contiguous columns out[(f - f0) * n + row]
 void launch_transpose_columns(const float *X, size_t n, int F, int f0, int nf, float *out,
                               cudaStream_t s);
-// sorts n fp32 keys (radix order); tmp sizes itself on first use
+// sorts n fp32 keys (radix order); tmp sizes itself on first use unless it already holds
+// sort_floats_temp_bytes(n) bytes
+size_t sort_floats_temp_bytes(size_t n);
 void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s);
 
 }  // namespace arb

@@ -26,11 +26,13 @@ __device__ __forceinline__ bool is_border(const float *s, size_t i) { return i >
 
 __global__ void border_count_kernel(const float *__restrict__ s, size_t n, unsigned *block_count) {
   __shared__ unsigned warp_sums[kScanThreads / 32];
-  const size_t base = size_t(blockIdx.x) * kScanTile + size_t(threadIdx.x) * kScanItems;
+  const size_t base = size_t(blockIdx.x) * kScanTile;
   unsigned c = 0;
 #pragma unroll
-  for (int k = 0; k < kScanItems; ++k)
-    if (base + k < n) c += is_border(s, base + k);
+  for (int k = 0; k < kScanItems; ++k) {  // any order will do for a count: coalesced
+    const size_t i = base + size_t(k) * kScanThreads + threadIdx.x;
+    if (i < n) c += is_border(s, i);
+  }
   for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
   if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = c;
   __syncthreads();
@@ -81,12 +83,24 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {  // io.
 __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_t seg, int hist_size,
                                     const unsigned *__restrict__ block_off, float *thr) {
   __shared__ unsigned warp_sums[kScanThreads / 32];
-  const size_t base = size_t(blockIdx.x) * kScanTile + size_t(threadIdx.x) * kScanItems;
+  // the tile and the value before it, read coalesced; a thread then walks 8 consecutive
+  // values, so slot p is kept at p + p / 32: the 32 lanes' strides of 8 fall on 32 banks
+  __shared__ float tile[kScanTile + 1 + (kScanTile + 1) / 32 + 1];
+  const size_t tile_base = size_t(blockIdx.x) * kScanTile;
+  for (int p = threadIdx.x; p < kScanTile + 1; p += kScanThreads) {
+    const size_t i = tile_base + size_t(p);  // tile[p] = s[i - 1]
+    tile[p + (p >> 5)] = (i >= 1 && i - 1 < n) ? s[i - 1] : 0.0f;
+  }
+  __syncthreads();
+  auto at = [&](int p) { return tile[p + (p >> 5)]; };
+  const int first = threadIdx.x * kScanItems;
+  const size_t base = tile_base + size_t(first);
   bool flag[kScanItems];
   unsigned c = 0;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
-    flag[k] = base + k < n && is_border(s, base + k);
+    const size_t i = base + k;
+    flag[k] = i > 0 && i < n && at(first + k + 1) != at(first + k);
     c += flag[k];
   }
   unsigned incl = c;
@@ -111,7 +125,7 @@ __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_
     if (flag[k]) {
       ++run;  // inclusive border count of position i (io.cu:144-153)
       const size_t i = base + k;
-      mid = float((s[i] + s[i - 1]) * 0.5);  // io.cu:72-79
+      mid = float((at(first + k + 1) + at(first + k)) * 0.5);  // io.cu:72-79
       const long long a = (long long)run + 1, b = (long long)(i / seg) + 1;
       slot = (a < b ? a : b) - 2;  // io.cu:257
       // slots past the table are a defect of the reference (out-of-range write); skipped
@@ -214,10 +228,18 @@ __global__ void binning_kernel(const float *__restrict__ X, size_t n, int F,
                                int hist_size, bool missing_bin, unsigned char *__restrict__ bins,
                                size_t pitch) {
   const size_t total = n * size_t(F);
-  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
-       e += size_t(gridDim.x) * blockDim.x) {
-    const size_t r = e / F;
-    const int f = int(e - r * F);
+  // (row, feature) of the element are carried along instead of divided out every time
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  const size_t stride_rows = stride / F;
+  const int stride_f = int(stride - stride_rows * F);
+  size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  size_t r = e / F;
+  int f = int(e - r * F);
+  for (; e < total; e += stride, r += stride_rows, f += stride_f) {
+    if (f >= F) {
+      f -= F;
+      ++r;
+    }
     const float x = X[e];
     unsigned b;
     if (missing_bin && x != x)
@@ -282,6 +304,13 @@ void launch_transpose_columns(const float *X, size_t n, int F, int f0, int nf, f
   transpose_f32_kernel<<<grid, 256, 0, s>>>(X, n, F, f0, nf, out);
   ARB_CUDA(cudaGetLastError());
   count_launch();
+}
+
+size_t sort_floats_temp_bytes(size_t n) {
+  size_t bytes = 0;
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes, static_cast<const float *>(nullptr),
+                                          static_cast<float *>(nullptr), n, 0, 32, nullptr));
+  return bytes;
 }
 
 void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s) {

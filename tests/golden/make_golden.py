@@ -1,7 +1,7 @@
 """Extract the golden vectors of the reference's own Python tests into JSON.
 
 Run in a checkout that has the reference mounted:
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 It reads ``tests/py/test_hist_logregression.py`` and
 ``tests/py/test_sklearn_classification.py`` as text (nothing is executed), pulls
 the expected prediction vectors and the expected model JSON out of the
