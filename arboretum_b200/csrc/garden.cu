@@ -400,6 +400,9 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   pb_.scratch_begin = d_scratch_.as<unsigned>();
   pb_.scratch_len = d_scratch_.as<unsigned>() + (max_nodes_ + 1);
   pb_.scratch_node = reinterpret_cast<int *>(d_scratch_.as<unsigned>() + 2 * (max_nodes_ + 1));
+  pb_.right_count = d_child_count_.as<unsigned>();
+  pb_.split_scratch = d_keys_.as<unsigned>();
+  pb_.split_scratch_words = int(d_keys_.bytes / sizeof(unsigned));
   trace.lap("level buffers");
   {  // one pinned allocation for the three read-back buffers
     const size_t a = (d_rec_.bytes + 255) / 256 * 256, b = (d_leaf_w_.bytes + 255) / 256 * 256;

@@ -87,7 +87,8 @@ struct SplitLaunch {
   const unsigned char *feature_active;  // F flags: evaluated at this level
   const int *feature_size;     // bins in use per feature
   unsigned long long *keys;    // max_nodes packed (gain, feature, bin) maxima followed by
-                               // max_nodes u32 arrival counters; zeroed here
+                               // max_nodes u32 arrival counters; zeroed by the plan kernel of the
+                               // level (PlanBuffers::split_scratch)
   int max_nodes;
   NodeRec *rec;                // L records out
   const NodeRec *parent_rec;   // level above (nullptr at the root)
@@ -109,6 +110,10 @@ struct PlanBuffers {
                           // its list so far
   unsigned *scratch_begin, *scratch_len;  // per built node: list start / length; max_nodes + 1
   int *scratch_node;      // per built node: its node index inside the level
+  // cleared by the plan kernel for the kernels that follow it (instead of memsets of their own):
+  unsigned *right_count;  //   the descend step's counters, one per node, kCounterStride apart
+  unsigned *split_scratch;  // the split search's keys and arrival counters
+  int split_scratch_words;
 };
 
 // Every row steps from its node to a child (or, below the last level, into a leaf).
@@ -119,7 +124,8 @@ struct DescendLaunch {
   unsigned short *node_of;   // per row: its node inside the level; becomes the child's (L == 1:
                              // not read, every row stands on the root)
   unsigned *child_count;     // per node (kCounterStride words apart): its rows that went right;
-                             // cleared and filled here; nullptr = the final step,
+                             // added to here, cleared by the plan kernel before (PlanBuffers::
+                             // right_count); nullptr = the final step,
   const float *leaf_w;       //   which adds leaf_w[child] to
   float *yhat;               //   yhat[row] instead
   size_t n;

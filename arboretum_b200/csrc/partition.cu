@@ -120,6 +120,10 @@ __global__ void plan_level_kernel(const unsigned *__restrict__ child_count,
     block_exclusive_scan(sl, node_begin, L);
     for (int p = threadIdx.x; p < L / 2; p += blockDim.x) parent_rec[p].left_count += sl[2 * p];
   }
+  // the next descend step counts into L counters at most; the level's split search starts
+  // from cleared keys
+  for (int i = threadIdx.x; i < L; i += blockDim.x) pb.right_count[size_t(i) * kPad] = 0;
+  for (int i = threadIdx.x; i < pb.split_scratch_words; i += blockDim.x) pb.split_scratch[i] = 0;
   __syncthreads();
   int n_build;
   if (use_trick && L > 1) {
@@ -333,7 +337,6 @@ void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
 void launch_descend(const DescendLaunch &a, cudaStream_t s) {
   if (a.n == 0) return;
   const bool fin = a.child_count == nullptr;
-  if (!fin) ARB_CUDA(cudaMemsetAsync(a.child_count, 0, sizeof(unsigned) * a.L * kPad, s));
   const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
   const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(148) * 8));
   const Geometry &g = a.geo;

@@ -158,8 +158,8 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
 }  // namespace
 
 void launch_split(const SplitLaunch &a, cudaStream_t s) {
-  // keys (u64 per node) and arrival counters (u32 per node) live in one buffer
-  ARB_CUDA(cudaMemsetAsync(a.keys, 0, (sizeof(unsigned long long) + sizeof(unsigned)) * a.max_nodes, s));
+  // keys (u64 per node) and arrival counters (u32 per node) live in one buffer, cleared by
+  // the level's plan kernel
   unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
   // Small levels: the double-precision gain arithmetic of a (node, tile) is spread over up
   // to 8 CTAs, which all re-read the tile.  Large levels have enough (node, tile) pairs to
