@@ -162,7 +162,7 @@ class ClockSampler(object):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -197,7 +197,8 @@ class ClockSampler(object):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(np.max(smax)) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "span": "every 50 ms from the end-to-end jobs through the timed and the profiled rounds"}
 
 
 def measured_peak():
@@ -364,6 +365,11 @@ def main():
     wm.grow_tree()
     wm.train_yhat()
     del wm, wd
+    # clocks and throttle reasons are sampled from here to the end of the profiled rounds: the
+    # timed region alone (tens of milliseconds) is shorter than the sampler's start-up
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     e2e_runs, e2e_parts = [], []
     for _ in range(5):
         model = data = None
@@ -398,11 +404,8 @@ def main():
     # ---- device-resident rounds (the model above is already bound and warm) ---------
     for _ in range(args.warmup):
         model.grow_tree()
-    sampler = ClockSampler(local_rank)
     launches0 = model.timings()["kernel_launches"]
     barrier()
-    if rank == 0:
-        sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     t0 = time.perf_counter()
@@ -411,7 +414,6 @@ def main():
     ev1.record()
     barrier()
     wall_s = time.perf_counter() - t0
-    clocks = sampler.stop() if rank == 0 else None
     step_s = max_over_ranks(ev0.elapsed_time(ev1) / 1000.0)
     launches = model.timings()["kernel_launches"] - launches0
 
@@ -422,6 +424,7 @@ def main():
         model.grow_tree()
     t = model.timings()
     model.set_profile(False)
+    clocks = sampler.stop() if rank == 0 else None
     peak, peak_src = measured_peak()
     if t["hist_ms"] > 0:
         hist_gbs = t["hist_bytes"] / (t["hist_ms"] * 1e-3) / 1e9
