@@ -513,7 +513,6 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   rd.level_hist = d_hist.as<long long>();
   rd.parent_hist = nullptr;
   rd.subtract = false;
-  rd.zero_sibling = false;
   rd.level_nodes = n_nodes;
   rd.built_child = nullptr;
   if (reps > 0) {

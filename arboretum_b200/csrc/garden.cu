@@ -650,7 +650,6 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       rd.level_hist = reduce_to;
       rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
       rd.subtract = trick_level && !g_->allreduce && !multi;
-      rd.zero_sibling = false;
       rd.level_nodes = compact ? n_build : L;
       rd.built_child = pb_.built_child;
       rd.accumulate = multi;

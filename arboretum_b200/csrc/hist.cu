@@ -17,7 +17,13 @@
 //    4m..4m+3 of row 4s+q, and in pass k updates feature 4m + ((k + q) & 3).  The
 //    32 lanes of every red.shared instruction therefore hit 32 different banks
 //    whatever the bin values are -- no bank conflicts, also for skewed or sorted
-//    columns -- at 2.5 shared-memory wavefronts per row.
+//    columns -- at 2.5 shared-memory wavefronts per row.  The two red.shared per 32
+//    (row, feature) pairs are what bounds the kernel on consecutive rows:
+//    measure_shared_atomic_peak() times them alone.
+//  * Below the root a row list (row ids, and the gradient records in the same order)
+//    says which rows a node has: ids and gradients are read in list order, the bins
+//    are gathered with the 64-byte L2 fetch qualifier, since a plain copy would pull
+//    the whole 128-byte line (four rows) for the one row the node wants.
 //  * The CTA stores its planes with plain coalesced stores; reduce_kernel then
 //    sums the planes of every built node into the level's int64 histogram and, in
 //    the same pass, derives the sibling as parent - built (the subtraction trick).
@@ -237,7 +243,7 @@ template <bool SUBTRACT>
 __global__ void reduce_kernel(const int *__restrict__ partials, const int *__restrict__ item_first,
                               const int *__restrict__ build_node, long long *__restrict__ level_hist,
                               const long long *__restrict__ parent_hist, const int NT,
-                              const int slices, const bool zero_sibling, const bool atomic) {
+                              const int slices, const bool atomic) {
   const int b = blockIdx.z / slices, slice = blockIdx.z - b * slices, tile = blockIdx.y;
   const int w = blockIdx.x * blockDim.x + threadIdx.x;
   const int first = item_first[b], last = item_first[b + 1];
@@ -261,9 +267,6 @@ __global__ void reduce_kernel(const int *__restrict__ partials, const int *__res
     const longlong2 pv = reinterpret_cast<const longlong2 *>(parent_hist)[poff];
     const size_t soff = (size_t(node ^ 1) * NT + tile) * kHistWords + w;
     reinterpret_cast<longlong2 *>(level_hist)[soff] = make_longlong2(pv.x - g, pv.y - h);
-  } else if (zero_sibling) {
-    const size_t soff = (size_t(node ^ 1) * NT + tile) * kHistWords + w;
-    reinterpret_cast<longlong2 *>(level_hist)[soff] = make_longlong2(0, 0);
   }
 }
 
@@ -439,7 +442,7 @@ void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
     const size_t bytes = size_t(a.level_nodes) * a.NT * kHistWords * 2 * sizeof(long long);
     if (!a.accumulate) ARB_CUDA(cudaMemsetAsync(a.level_hist, 0, bytes, s));
     reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, slices, false, true);
+                                                  a.level_hist, nullptr, a.NT, slices, true);
     ARB_CUDA(cudaGetLastError());
     count_launch();
     if (a.subtract) launch_subtract(a.level_hist, a.parent_hist, a.built_child, a.level_nodes / 2, a.NT, s);
@@ -447,10 +450,10 @@ void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   }
   if (a.subtract)
     reduce_kernel<true><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node, a.level_hist,
-                                                 a.parent_hist, a.NT, 1, false, false);
+                                                 a.parent_hist, a.NT, 1, false);
   else
     reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, 1, a.zero_sibling, false);
+                                                  a.level_hist, nullptr, a.NT, 1, false);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

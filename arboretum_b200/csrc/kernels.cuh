@@ -64,7 +64,6 @@ struct ReduceLaunch {
   long long *level_hist;
   const long long *parent_hist;  // level above, for the subtraction
   bool subtract;      // also write sibling = parent - built
-  bool zero_sibling;  // (no subtract) clear the sibling so the buffer can be all-reduced
   int level_nodes;    // nodes of the level (size of level_hist)
   const int *built_child;  // per parent: which child was built (for the subtraction)
   bool accumulate = false;  // add into level_hist (cleared by the caller): row chunks of one level
