@@ -41,6 +41,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                             cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
   void load() {
@@ -52,9 +53,10 @@ struct NcclApi {
     GetUniqueId = reinterpret_cast<decltype(GetUniqueId)>(dlsym(handle, "ncclGetUniqueId"));
     CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(handle, "ncclCommInitRank"));
     AllReduce = reinterpret_cast<decltype(AllReduce)>(dlsym(handle, "ncclAllReduce"));
+    AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(handle, "ncclAllGather"));
     CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(handle, "ncclCommDestroy"));
     GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(handle, "ncclGetErrorString"));
-    if (!GetUniqueId || !CommInitRank || !AllReduce || !CommDestroy || !GetErrorString)
+    if (!GetUniqueId || !CommInitRank || !AllReduce || !AllGather || !CommDestroy || !GetErrorString)
       throw std::runtime_error("libnccl.so.2 lacks a required symbol");
   }
 };
@@ -75,6 +77,12 @@ struct NcclCtx {
 int nccl_allreduce(void *ctx, long long *buf, size_t count, cudaStream_t s) {
   NcclCtx *c = static_cast<NcclCtx *>(ctx);
   const ncclResult_t r = g_nccl.AllReduce(buf, buf, count, ncclInt64, ncclSum, c->comm, s);
+  return r == ncclSuccess ? 0 : 1;
+}
+
+int nccl_allgather(void *ctx, const void *send, void *recv, size_t bytes, cudaStream_t s) {
+  NcclCtx *c = static_cast<NcclCtx *>(ctx);
+  const ncclResult_t r = g_nccl.AllGather(send, recv, bytes, ncclChar, c->comm, s);
   return r == ncclSuccess ? 0 : 1;
 }
 
@@ -591,6 +599,10 @@ const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128
   }
   g->allreduce = nccl_allreduce;
   g->allreduce_max = nccl_allreduce_max;
+  g->shards.rank = rank;
+  g->shards.world = world;
+  g->shards.allgather = nccl_allgather;
+  g->shards.ctx = c.get();
   g->allreduce_ctx = c.release();
   ARB_CATCH
 }

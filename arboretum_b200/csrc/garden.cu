@@ -39,7 +39,94 @@ void pad_rows_host(const unsigned char *src, size_t F, size_t n, unsigned char *
 }
 }  // namespace
 
-void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows) {
+// Thresholds of the whole data set when every rank holds a shard of the rows (same result
+// as InitHist on the unsharded matrix, bit for bit).  A block of 32 columns at a time: every
+// rank makes its rows' columns contiguous, pads them with NaN (which sorts last) to the
+// longest shard and all ranks all-gather the block; rank r then sorts the whole columns
+// f with f % world == r and scans them for thresholds, so the sorts are spread over the
+// GPUs; the threshold tables are all-gathered at the end.
+void DataMatrix::ShardedThresholds(const float *d_x_local, int hs, const ShardInfo &sh, cudaStream_t s) {
+  const int F = cols_dense, world = sh.world;
+  const size_t n = size_t(rows);
+  // row counts of all ranks
+  DevBuf d_cnt;
+  d_cnt.alloc(sizeof(unsigned long long) * (world + 1));
+  const unsigned long long mine = n;
+  ARB_CUDA(cudaMemcpyAsync(d_cnt.as<unsigned long long>() + world, &mine, sizeof mine, cudaMemcpyHostToDevice, s));
+  if (sh.allgather(sh.ctx, d_cnt.as<unsigned long long>() + world, d_cnt.p, sizeof mine, s) != 0)
+    throw std::runtime_error("row-count all-gather failed");
+  std::vector<unsigned long long> counts(world);
+  ARB_CUDA(cudaMemcpyAsync(counts.data(), d_cnt.p, sizeof(unsigned long long) * world, cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaStreamSynchronize(s));
+  size_t n_total = 0, n_max = 0;
+  for (unsigned long long c : counts) {
+    n_total += size_t(c);
+    n_max = std::max(n_max, size_t(c));
+  }
+  const int block_cols = std::min(F, 32);
+  const size_t whole = size_t(world) * n_max;  // a whole column with its padding
+  DevBuf arena, d_local, d_send, d_recv, d_full, d_sorted, d_tmp, d_scratch, d_thr_f, d_thr_all;
+  {
+    struct Want {
+      DevBuf *buf;
+      size_t bytes;
+    };
+    const Want wants[] = {
+      {&d_local, n * block_cols * sizeof(float)},
+      {&d_send, n_max * block_cols * sizeof(float)},
+      {&d_recv, whole * block_cols * sizeof(float)},
+      {&d_full, whole * sizeof(float)},
+      {&d_sorted, whole * sizeof(float)},
+      {&d_tmp, sort_floats_temp_bytes(whole)},
+      {&d_scratch, thresholds_scratch_words(n_total) * sizeof(unsigned)},
+      {&d_thr_f, size_t(F) * hs * sizeof(float)},
+      {&d_thr_all, size_t(world) * F * hs * sizeof(float)},
+    };
+    size_t total = 0;
+    for (const Want &w : wants) total += (w.bytes + 255) / 256 * 256;
+    arena.alloc(total);
+    size_t at = 0;
+    for (const Want &w : wants) {
+      w.buf->view(static_cast<char *>(arena.p) + at, w.bytes);
+      at += (w.bytes + 255) / 256 * 256;
+    }
+  }
+  ARB_CUDA(cudaMemsetAsync(d_thr_f.p, 0, d_thr_f.bytes, s));
+  const float pad = std::numeric_limits<float>::quiet_NaN();  // 0x7fc00000, like the transposed NaNs
+  for (int f0 = 0; f0 < F; f0 += block_cols) {
+    const int nf = std::min(block_cols, F - f0);
+    launch_transpose_columns(d_x_local, n, F, f0, nf, d_local.as<float>(), s);
+    launch_fill(d_send.as<float>(), n_max * nf, pad, s);
+    ARB_CUDA(cudaMemcpy2DAsync(d_send.p, n_max * sizeof(float), d_local.p, n * sizeof(float), n * sizeof(float),
+                               nf, cudaMemcpyDeviceToDevice, s));
+    const size_t block_bytes = n_max * nf * sizeof(float);
+    if (sh.allgather(sh.ctx, d_send.p, d_recv.p, block_bytes, s) != 0)
+      throw std::runtime_error("column all-gather failed");
+    for (int c = 0; c < nf; ++c) {
+      const int f = f0 + c;
+      if (f % world != sh.rank) continue;
+      // column c of every rank's block, rank after rank
+      ARB_CUDA(cudaMemcpy2DAsync(d_full.p, n_max * sizeof(float), d_recv.as<float>() + size_t(c) * n_max,
+                                 block_bytes, n_max * sizeof(float), world, cudaMemcpyDeviceToDevice, s));
+      sort_floats(d_full.as<float>(), d_sorted.as<float>(), whole, d_tmp, s);
+      launch_thresholds(d_sorted.as<float>(), n_total, hs, d_thr_f.as<float>() + size_t(f) * hs,
+                        d_scratch.as<unsigned>(), s);
+    }
+  }
+  if (sh.allgather(sh.ctx, d_thr_f.p, d_thr_all.p, d_thr_f.bytes, s) != 0)
+    throw std::runtime_error("threshold all-gather failed");
+  std::vector<float> all(size_t(world) * F * hs);
+  ARB_CUDA(cudaMemcpyAsync(all.data(), d_thr_all.p, d_thr_all.bytes, cudaMemcpyDeviceToHost, s));
+  ARB_CUDA(cudaStreamSynchronize(s));
+  thr.resize(size_t(F) * hs);
+  for (int f = 0; f < F; ++f) {
+    const float *src = all.data() + (size_t(f % world) * F + f) * hs;
+    std::copy(src, src + hs, thr.begin() + size_t(f) * hs);
+  }
+}
+
+void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows,
+                          const ShardInfo *shards) {
   if (binned) return;
   out_of_core = chunk_rows > 0 && chunk_rows < rows;
   const int F = cols_dense;
@@ -58,7 +145,10 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       ARB_CUDA(cudaMemcpyAsync(d_x_tmp.p, x.data(), n * F * sizeof(float), cudaMemcpyHostToDevice, s));
     }
     const DevBuf &d_x = this->d_x.p ? this->d_x : d_x_tmp;
-    if (!thresholds_given) {
+    if (!thresholds_given && shards && shards->world > 1 && shards->allgather) {
+      ShardedThresholds(d_x.as<float>(), hs, *shards, s);
+      trace.lap("sharded column sorts + thresholds");
+    } else if (!thresholds_given) {
       const int block_cols = std::min(F, 32);  // columns made contiguous at a time
       {  // one allocation (and later one free) for the quantizer's temporaries
         struct Want {
@@ -95,6 +185,8 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       ARB_CUDA(cudaMemcpyAsync(thr.data(), d_thr_f.p, thr.size() * sizeof(float),
                                cudaMemcpyDeviceToHost, s));
       ARB_CUDA(cudaStreamSynchronize(s));
+    }
+    if (!thresholds_given) {
       fsize.resize(F);
       for (int f = 0; f < F; ++f) {  // io.cu:403-410
         int unique = 0;
@@ -907,7 +999,7 @@ float Garden::InternalInitialY() const {  // objective.h:19,55-57
 void Garden::GrowTree(DataMatrix *data, const float *grad) {
   (void)grad;  // custom gradients are ignored by the reference as well (garden.cu:609-614)
   data->InitHist(cfg.internal.hist_size, cfg.internal.missing_bin, cfg.verbose.data, stream,
-                 cfg.internal.chunk_rows);
+                 cfg.internal.chunk_rows, &shards);
   if (!builder) {
     builder = new Builder(this, data);
   } else if (builder->data != data) {

@@ -15,6 +15,16 @@
 
 namespace arb {
 
+// Row shards (one process per GPU): what InitHist needs to find the thresholds of the WHOLE
+// data set.  allgather(ctx, send, recv, bytes, stream): every rank contributes `bytes`
+// bytes from device memory; recv (device) receives world x bytes in rank order.
+typedef int (*AllgatherFn)(void *ctx, const void *send, void *recv, size_t bytes, cudaStream_t stream);
+struct ShardInfo {
+  int rank = 0, world = 1;
+  AllgatherFn allgather = nullptr;
+  void *ctx = nullptr;
+};
+
 class DataMatrix {
  public:
   DataMatrix(int64_t rows, int cols_dense, int cols_cat)
@@ -56,7 +66,9 @@ class DataMatrix {
   DevBuf d_yhat;
   int yhat_planes = 0;
 
-  void InitHist(int hist_size, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows = 0);
+  void InitHist(int hist_size, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows = 0,
+                const ShardInfo *shards = nullptr);
+  void ShardedThresholds(const float *d_x_local, int hs, const ShardInfo &sh, cudaStream_t s);
   static size_t PitchFor(int F, int bin_bytes) {
     return (size_t(F) * bin_bytes + 31) / 32 * 32;
   }
@@ -121,6 +133,7 @@ class Garden {
   std::vector<Tree> trees;
   AllreduceFn allreduce = nullptr;
   AllreduceMaxFn allreduce_max = nullptr;
+  ShardInfo shards;  // rank, world and the all-gather of the sharded quantizer
   void *allreduce_ctx = nullptr;
   bool profile = false;
   PhaseTimes times;

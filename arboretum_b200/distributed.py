@@ -1,14 +1,16 @@
 """Host-side plumbing of row-sharded multi-GPU training (one process per GPU).
 
-The data path needs exactly one exchange: the per-level histogram sum, done by the
-library with ncclAllReduce on its own stream.  What this module does on the host,
-through ``torch.distributed`` (NCCL or gloo), is the set-up around it:
+Every exchange of the data path is done by the library with NCCL on its own stream: the
+per-level histogram sums, the per-round gradient scale and, at the first round, the
+all-gather of the quantizer (the ranks find the thresholds of the whole data set together,
+each sorting its share of the columns).  What this module does on the host, through
+``torch.distributed`` (NCCL or gloo), is the set-up around it:
 
 * ``shard_rows``      -- the contiguous row range of a rank;
-* ``share_thresholds``-- one rank quantises, everybody bins with the same thresholds
-                         (bins must not depend on the number of GPUs);
 * ``init_nccl``       -- rank 0 creates the ncclUniqueId, the others receive it, and
-                         every rank joins the communicator of its Garden.
+                         every rank joins the communicator of its Garden;
+* ``share_thresholds``-- optional: hand thresholds computed elsewhere to every rank
+                         (the Gardens then skip their own quantizer).
 """
 import ctypes
 

@@ -335,9 +335,7 @@ def main():
         model = arboretum.Garden(cfg)
         model.data = data
         model.labels_count = data.labels_count
-        if world > 1 and not binned:
-            adist.share_thresholds(data, cfg["internals"]["hist_size"], rank, world)
-        if world > 1:
+        if world > 1:  # the ranks then quantise their shards together, at the first round
             adist.init_nccl(model, rank, world)
         return model, data
 
@@ -359,8 +357,6 @@ def main():
     wm.data = wd
     wm.labels_count = wd.labels_count
     if world > 1:  # the process's communicator is made here, once; the timed jobs attach it
-        if not binned:
-            adist.share_thresholds(wd, cfg["internals"]["hist_size"], rank, world)
         adist.init_nccl(wm, rank, world)
     wm.grow_tree()
     wm.train_yhat()

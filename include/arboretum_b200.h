@@ -87,7 +87,9 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
                             const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
                             double *out_h, int reps, float *ms);
 /* Multi-GPU: rows are sharded over one process per GPU; every level's histogram
- * is summed over the ranks with ncclAllReduce.  `id` is the 128-byte
+ * is summed over the ranks with ncclAllReduce, and the first AGrowTree finds the
+ * thresholds of the whole data set with the other ranks (unless ASetThresholds gave
+ * them), so bins and trees equal those of the unsharded matrix.  `id` is the 128-byte
  * ncclUniqueId made by rank 0 (ANcclUniqueId) and sent to the others by the host.
  * The first communicator of a process is kept until the process exits; a later Garden
  * of the same rank and world size attaches it when AInitNccl is given id128 == NULL
