@@ -39,7 +39,7 @@ CONFIG = {"objective": 1, "method": 1,
                    "lambda": 1.0, "alpha": 0.0, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}}
 # DRAM bytes per algorithmic byte of the histogram kernel, from the ncu capture
 # summarised in profiles/ (None until a capture exists for this kernel version).
-HIST_TRAFFIC_RATIO = 2.45
+HIST_TRAFFIC_RATIO = 1.82
 
 
 def make_rows(n, seed):
