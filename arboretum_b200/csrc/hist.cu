@@ -73,7 +73,7 @@ __device__ __forceinline__ void store_planes(const int *smem, int *dst) {
 
 // uint8 bins, 32 features per tile, 256 bins.
 template <bool PAIR, bool IDENT>
-__global__ void __launch_bounds__(kHistThreads, 2)
+__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
 hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
@@ -192,7 +192,7 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
 
 // Any bin width / tile width: thread = (row in group, feature in tile).
 template <bool PAIR, bool IDENT, typename BIN_T>
-__global__ void __launch_bounds__(kHistThreads, 2)
+__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
 hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                     const int TW, const int F, const unsigned *__restrict__ rowid,
                     const void *__restrict__ grad, const WorkItem *__restrict__ items,
@@ -332,8 +332,8 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
                      int n_parents, int NT, cudaStream_t s);
 
 int hist_grid_x(int max_items, int NT) {
-  // persistent CTAs: two per SM over all tiles
-  const int per_tile = std::max(8, (2 * 148 + NT - 1) / NT);
+  // persistent CTAs: kHistCtasPerSm per SM over all tiles
+  const int per_tile = std::max(8, (kHistCtasPerSm * 148 + NT - 1) / NT);
   return std::max(1, std::min(max_items, per_tile));
 }
 
@@ -384,10 +384,12 @@ namespace {
 // Ceiling of the histogram kernels' inner loop: every lane adds one (g, h) pair per step to
 // its own column of the two int32 planes at a pseudo-random bin -- the same two conflict-free
 // red.shared instructions per 32 (row, feature) pairs, with no loads, no staging and no
-// stores around them.
-__global__ void __launch_bounds__(kHistThreads, 2) shared_atomic_peak_kernel(int steps, int *sink) {
+// stores around them, and with all 64 warps an SM can hold (the rate grows with the warps
+// in flight: 2.6 T pairs/s with 32 warps, 2.9 T with 64).
+constexpr int kPeakThreads = 1024;
+__global__ void __launch_bounds__(kPeakThreads, 2) shared_atomic_peak_kernel(int steps, int *sink) {
   extern __shared__ __align__(16) int smem[];
-  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kPeakThreads) smem[w] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31;
   unsigned state = threadIdx.x * 2654435761u + blockIdx.x * 97u + 1u;
@@ -402,7 +404,7 @@ __global__ void __launch_bounds__(kHistThreads, 2) shared_atomic_peak_kernel(int
   }
   __syncthreads();
   int acc = 0;
-  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) acc ^= smem[w];
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kPeakThreads) acc ^= smem[w];
   if (acc == 0x7fffffff) sink[0] = acc;  // keeps the adds alive
 }
 }  // namespace
@@ -419,7 +421,7 @@ double measure_shared_atomic_peak(int steps, cudaStream_t s) {
   float best = 0.0f;
   for (int rep = 0; rep < 4; ++rep) {  // the first launch warms up
     ARB_CUDA(cudaEventRecord(e0, s));
-    shared_atomic_peak_kernel<<<grid, kHistThreads, smem, s>>>(steps, sink.as<int>());
+    shared_atomic_peak_kernel<<<grid, kPeakThreads, smem, s>>>(steps, sink.as<int>());
     ARB_CUDA(cudaEventRecord(e1, s));
     ARB_CUDA(cudaEventSynchronize(e1));
     float ms = 0.0f;
@@ -429,7 +431,7 @@ double measure_shared_atomic_peak(int steps, cudaStream_t s) {
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   count_launch(4);
-  return double(grid) * kHistThreads * double(steps) * 8.0 / (double(best) * 1e-3);
+  return double(grid) * kPeakThreads * double(steps) * 8.0 / (double(best) * 1e-3);
 }
 
 void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {

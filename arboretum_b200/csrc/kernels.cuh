@@ -11,6 +11,8 @@ namespace arb {
 
 constexpr int kHistWords = 8192;      // words of one shared-memory histogram plane
 constexpr int kHistThreads = 512;     // threads of a histogram CTA
+constexpr int kHistCtasPerSm = 2;     // resident histogram CTAs per SM (32 warps: the row gather
+                                      // of the levels below the root needs them to hide its latency)
 constexpr int kMaxLevels = 16;
 constexpr int kCounterStride = 32;    // words between two counters that many CTAs add to
 constexpr int kMinItemRows = 2048;    // smallest piece a node's row list is cut into
