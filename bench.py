@@ -285,6 +285,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="skip the end-to-end jobs (profiling runs: fewer launches before the timed rounds)")
     ap.add_argument("--internals", default="", help='JSON merged into the "internals" configuration')
     args = ap.parse_args()
     if args.rows <= 0:
@@ -367,7 +369,7 @@ def main():
     if rank == 0:
         sampler.start()
     e2e_runs, e2e_parts = [], []
-    for _ in range(5):
+    for _ in range(0 if args.no_e2e else 5):
         model = data = None
         barrier()
         t0 = time.perf_counter()
@@ -385,11 +387,16 @@ def main():
         barrier()
         e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
         e2e_parts.append([round(b - a, 4) for a, b in ((t0, t1), (t1, t2), (t2, t3), (t3, t4))])
+    if args.no_e2e:
+        model, data = new_model()
+        model.grow_tree()
+        yhat = model.train_yhat()
+        e2e_runs = [float("nan")]
     e2e_s = sorted(e2e_runs)[len(e2e_runs) // 2]
-    e2e = {"value": args.steps / e2e_s, "unit": "rounds/s",
+    e2e = {"value": None if args.no_e2e else args.steps / e2e_s, "unit": "rounds/s",
            "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) * world / args.steps),
            "d2h_bytes_per_step": int(yhat.nbytes * world / args.steps),
-           "runs_s": [round(t, 4) for t in e2e_runs],
+           "runs_s": [] if args.no_e2e else [round(t, 4) for t in e2e_runs],
            "parts_s": {"order": ["DMatrix (host to device)", "quantise + first round", "other rounds",
                                  "predictions to host"],
                        "per_run": e2e_parts},
