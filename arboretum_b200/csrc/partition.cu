@@ -338,11 +338,23 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
   if (a.n == 0) return;
   const bool fin = a.child_count == nullptr;
   const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
-  const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(148) * 8));
   const Geometry &g = a.geo;
-#define ARB_LAUNCH(T, FIN)                                                                        \
-  descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L, \
-                                              a.node_of, a.child_count, a.leaf_w, a.yhat, a.n)
+  // exactly as many CTAs as are resident at once: a second, partly filled wave would cost
+  // as much as a full one
+#define ARB_LAUNCH(T, FIN)                                                                          \
+  do {                                                                                              \
+    static int resident = 0;                                                                        \
+    if (!resident) {                                                                                \
+      int per_sm = 0, dev = 0, sms = 0;                                                             \
+      ARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, descend_kernel<T, FIN>, 256, 0)); \
+      ARB_CUDA(cudaGetDevice(&dev));                                                                \
+      ARB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));                  \
+      resident = std::max(1, per_sm * sms);                                                         \
+    }                                                                                               \
+    const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
+    descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L,  \
+                                                a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);   \
+  } while (0)
   if (g.bin_bytes == 1) {
     if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
   } else {
