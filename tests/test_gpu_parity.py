@@ -226,6 +226,16 @@ def compare_with_oracle(cfg, X, y, rounds, labels=None, max_level=None):
     depth = cfg["tree"]["max_depth"]
     ambiguous = 0
     for r in range(rounds):
+        # the largest |gradient| of the round, from the predictions before it
+        before = o.yhat()[0].astype(np.float64) if K == 1 and o.num_trees() > 0 else None
+        if K == 1 and y is not None:
+            if before is None:
+                iy = cfg["tree"].get("initial_y", 0.5)
+                before = np.full(len(y), np.log(iy / (1 - iy)) if cfg["objective"] == 1 else iy)
+            g_all = (y - 1 / (1 + np.exp(-before))) if cfg["objective"] == 1 else (y - before)
+            step = 2.0 ** (np.frexp(float(np.abs(g_all).max()) * (1 + 2.0 ** -9))[1] - 18)
+        else:
+            step = 0.0
         model.grow_tree()
         o.grow(1)
         if K > 1:
@@ -247,10 +257,24 @@ def compare_with_oracle(cfg, X, y, rounds, labels=None, max_level=None):
                     diverged = True
                 else:
                     # sums agree to 1e-5 of the node's sum of |g|
-                    tol = HIST_RTOL * max(e["abs_g"][i], 1e-3)
+                    # ... or to the rigorous bound of the fixed-point sums: half a step per row, the
+                    # step being 2^(e - 18) with 2^e the power of two above the round's largest |g|
+                    rows_i = float(e["node_begin"][i + 1] - e["node_begin"][i]) if l > 0 else float(len(X))
+                    tol = max(HIST_RTOL * max(e["abs_g"][i], 1e-3), 0.5 * step * rows_i)
                     assert abs(g["tot_g"][i] - e["tot_g"][i]) <= tol
                     assert abs(g["left_g"][i] - e["left_g"][i]) <= tol
-                    assert g["gain"][i] == pytest.approx(e["gain"][i], rel=1e-4, abs=1e-6)
+                    # the gain is a difference of terms G^2 / (H + lambda): an error of `tol` in a
+                    # sum G moves a term by 2 |w| tol, with w = G / (H + lambda) the term's weight
+                    lam = cfg["tree"].get("lambda", 1.0)
+                    hs = (e["tot_h"][i], e["left_h"][i], e["tot_h"][i] - e["left_h"][i])
+                    gs = (e["tot_g"][i], e["left_g"][i], e["tot_g"][i] - e["left_g"][i])
+                    if cfg["objective"] == 0:  # reg:linear: the hessian sum is the row count
+                        cnt = float(e["node_begin"][i + 1] - e["node_begin"][i]) if l > 0 else float(len(X))
+                        lc = float(e["left_count"][i])
+                        hs = (cnt, lc, cnt - lc)
+                    wmax = max(abs(a) / (max(b, 0.0) + lam) for a, b in zip(gs, hs))
+                    gain_tol = max(1e-4 * abs(e["gain"][i]), 1e-6, 8.0 * wmax * tol)
+                    assert abs(g["gain"][i] - e["gain"][i]) <= gain_tol
         if diverged:
             break
     return model, data, o, ambiguous
@@ -271,6 +295,30 @@ def test_training_matches_oracle(kind, objective, n, depth, rounds):
         for a, b in zip(md, od):
             assert a["nodes"] == b["nodes"]
             assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("objective,tree", [
+    (0, {"alpha": 0.5, "lambda": 3.0}),                      # L1 and a stronger L2 term
+    (1, {"alpha": 0.05, "lambda": 0.1, "min_child_weight": 5.0}),
+    (0, {"gamma_absolute": 2.0}),                            # splits must gain at least this much
+    (1, {"gamma_relative": 0.05}),                           # ... or this share of the parent's gain
+    (0, {"max_leaf_weight": 0.5}),                           # clamped leaf weights
+    (1, {"max_leaf_weight": 0.3, "initial_y": 0.2}),
+    (0, {"min_leaf_size": 40, "min_child_weight": 40.0}),    # reg:linear has a count plane
+])
+def test_regularisation_parameters_match_oracle(objective, tree):
+    kind = "linear" if objective == 0 else "logistic"
+    X, y = synth(kind, 12000, 16, seed=77 + objective)
+    cfg = make_config(objective, 5, eta=0.3, **tree)
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 4)
+    if ambiguous == 0:
+        assert np.allclose(model.train_yhat()[0], o.yhat()[0], atol=PRED_ATOL, rtol=0)
+        md, od = json.loads(model.dump())["model"], o.model_dict()
+        for a, b in zip(md, od):
+            assert a["nodes"] == b["nodes"]
+            # (|G| - alpha) / (H + lambda) of a leaf of a few rows cancels when |G| is near
+            # alpha: absolute agreement, at a tenth of the predictions' tolerance
+            assert np.allclose(a["weights"], b["weights"], rtol=1e-3, atol=0.1 * PRED_ATOL)
 
 
 def test_training_is_deterministic():
