@@ -478,7 +478,7 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   host_scales(max_g, max_h, quant_bits, pair != 0, &q);
   d_qs.alloc(sizeof q);
   ARB_CUDA(cudaMemcpyAsync(d_qs.p, &q, sizeof q, cudaMemcpyHostToDevice, s));
-  launch_quantize_grads(d_grad.p, n, pair != 0, d_qs.as<QuantScale>(), s);
+  launch_quantize_grads(d_grad.p, n, pair != 0, d_qs.as<QuantScale>(), quant_bits, s);
   const unsigned cap = 1u << (31 - quant_bits);
   std::vector<WorkItem> items;
   std::vector<int> first(n_nodes + 1, 0), ids(n_nodes);

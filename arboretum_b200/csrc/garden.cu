@@ -312,6 +312,8 @@ class Builder {
     d_cursor_, d_child_count_;
   DevBuf d_arena_;      // backs the small per-level arrays below
   DevBuf d_rows_arena_; // backs the per-row arrays
+  unsigned long long row_offset_ = 0;  // index of this shard's first row in the whole data set
+  unsigned round_ = 0;                 // boosting rounds so far (keys the gradients' dither)
   bool events_made_ = false;
   void EnsureEvents();
   PinnedBuf h_arena_;   // backs the read-back buffers
@@ -434,6 +436,20 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   }
   // garden.cu:105: y_hat starts at IntoInternal(initial_y)
   launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
+  if (g->shards.world > 1 && g->shards.allgather) {
+    // where this shard's rows lie in the whole data set (shards are contiguous, in rank order)
+    const int world = g->shards.world;
+    DevBuf d_cnt;
+    d_cnt.alloc(sizeof(unsigned long long) * (world + 1));
+    const unsigned long long mine = n_;
+    ARB_CUDA(cudaMemcpyAsync(d_cnt.as<unsigned long long>() + world, &mine, sizeof mine, cudaMemcpyHostToDevice, s));
+    if (g->shards.allgather(g->shards.ctx, d_cnt.as<unsigned long long>() + world, d_cnt.p, sizeof mine, s) != 0)
+      throw std::runtime_error("row-count all-gather failed");
+    std::vector<unsigned long long> counts(world);
+    ARB_CUDA(cudaMemcpyAsync(counts.data(), d_cnt.p, sizeof(unsigned long long) * world, cudaMemcpyDeviceToHost, s));
+    ARB_CUDA(cudaStreamSynchronize(s));
+    for (int r = 0; r < g->shards.rank; ++r) row_offset_ += counts[r];
+  }
   trace.lap("per-row state");
   // level state
   {
@@ -606,7 +622,7 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   const unsigned char *labels = data->d_labels.p ? data->d_labels.as<unsigned char>() : d_label_.as<unsigned char>();
   // pass 1: the round's largest |gradient| and hessian (they fix the fixed-point scale)
   launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
-                   d_qs_.as<QuantScale>(), false, s);
+                   d_qs_.as<QuantScale>(), false, s, row_offset_, round_, g_->cfg.internal.quant_bits);
   // row shards must share one fixed-point scale: take the maxima over all ranks
   if (g_->allreduce_max &&
       g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
@@ -614,7 +630,8 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
   // pass 2: the gradients as fixed-point integers
   launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
-                   d_qs_.as<QuantScale>(), true, s);
+                   d_qs_.as<QuantScale>(), true, s, row_offset_, round_, g_->cfg.internal.quant_bits);
+  ++round_;
   if (g_->profile) {
     ARB_CUDA(cudaEventRecord(ev_[1], s));
     ARB_CUDA(cudaEventSynchronize(ev_[1]));

@@ -159,11 +159,16 @@ void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const P
 // Gradients of the round in two passes over (y, yhat).  emit = false: the largest |g| and h
 // go to qs (multi:softmax also stores its float gradients); emit = true, after
 // launch_finish_scales: grad receives the fixed-point integers int2[N] (pair) or int[N].
+// The integers are dithered (see to_fixed in objective.cu): row0 = index of the first row in
+// the whole data set, round = the boosting round.
 void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
-                      const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s);
+                      const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s,
+                      unsigned long long row0, unsigned round, int quant_bits);
 void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s);
-// float gradients -> fixed-point integers, in place (g_q = rint(g * sg), h_q = max(1, rint(h * sh)))
-void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, cudaStream_t s);
+// float gradients -> fixed-point integers, in place, rounded to nearest
+// (g_q = rint(g * sg), h_q = max(1, rint(h * sh)))
+void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, int quant_bits,
+                           cudaStream_t s);
 
 struct LeafLaunch {
   const NodeRec *last_rec;

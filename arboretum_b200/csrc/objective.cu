@@ -18,6 +18,30 @@ __device__ __forceinline__ float sigmoid(float x) { return float(__drcp_rn(1.0 +
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 constexpr float kMaxSlack = 1.0f + 1.0f / 1024.0f;  // the bound errs upwards by far more than that error
 
+// Fixed-point conversion with a dither: floor(v * scale + u), u in [0, 1) a hash of (row of
+// the whole data set, round, salt).  Rounding to nearest would give every row with the same
+// gradient the same error -- and first rounds are full of equal gradients, so a node's sum
+// would be off by rows x error; with the dither the errors of equal values spread evenly
+// over one step and cancel like those of unequal ones.  The hash depends on the row's index
+// in the whole data set, so shards and row chunks quantise a row like one GPU does.
+// no_dither (round == 0xffffffff): plain round-to-nearest.
+constexpr unsigned kNoDither = 0xffffffffu;
+__device__ __forceinline__ float dither(unsigned long long row, unsigned round, unsigned salt) {
+  unsigned x = unsigned(row) ^ (unsigned(row >> 32) * 0x9E3779B1u) ^ (round * 0x85EBCA6Bu) ^ salt;
+  x ^= x >> 16;
+  x *= 0x7FEB352Du;
+  x ^= x >> 15;
+  x *= 0x846CA68Bu;
+  x ^= x >> 16;
+  return float(x >> 8) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ int to_fixed(float v, float scale, unsigned long long row, unsigned round,
+                                        unsigned salt, int lim) {
+  const int q = round == kNoDither ? __float2int_rn(v * scale)
+                                   : __float2int_rd(v * scale + dither(row, round, salt));
+  return max(-lim, min(lim, q));  // |q| < 2^quant_bits, whatever the dither adds at the largest value
+}
+
 // The round's largest |gradient| and hessian: one atomicMax per CTA and value, and only
 // when the CTA's maximum beats what is already there (the counters share a cache line, so
 // thousands of unconditional atomics would queue up behind one another).
@@ -55,13 +79,14 @@ __device__ __forceinline__ void block_max_to(QuantScale *qs, float mg, float mh)
 // (g_q = rint(g * sg), h_q = max(1, rint(h * sh))): the float gradients never touch memory.
 template <bool EMIT>
 __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
-                                   int *__restrict__ grad, QuantScale *qs, size_t n) {
+                                   int *__restrict__ grad, QuantScale *qs, size_t n,
+                                   unsigned long long row0, unsigned round, int lim) {
   float m = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x) {
     const float g = y[i] - yhat[i];
-    if (EMIT) grad[i] = __float2int_rn(g * sg);
+    if (EMIT) grad[i] = to_fixed(g, sg, row0 + i, round, 0u, lim);
     else m = fmaxf(m, fabsf(g));
   }
   if (!EMIT) block_max_to(qs, m, 0.0f);
@@ -69,7 +94,8 @@ __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__r
 
 template <bool EMIT>
 __global__ void grad_logistic_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
-                                     int2 *__restrict__ grad, QuantScale *qs, size_t n) {
+                                     int2 *__restrict__ grad, QuantScale *qs, size_t n,
+                                     unsigned long long row0, unsigned round, int lim) {
   float mg = 0.0f, mh = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f, sh = EMIT ? qs->sh : 0.0f;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -78,7 +104,8 @@ __global__ void grad_logistic_kernel(const float *__restrict__ y, const float *_
     const float2 g = make_float2(y[i] - s, s * (1.0f - s));
     if (EMIT) {
       // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
-      grad[i] = make_int2(__float2int_rn(g.x * sg), max(1, __float2int_rn(g.y * sh)));
+      grad[i] = make_int2(to_fixed(g.x, sg, row0 + i, round, 0u, lim),
+                          max(1, to_fixed(g.y, sh, row0 + i, round, 0x68E31DA4u, lim)));
     } else {
       mg = fmaxf(mg, fabsf(g.x));
       mh = fmaxf(mh, g.y);
@@ -126,21 +153,27 @@ __global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) 
   }
 }
 
-__global__ void quantize_pair_kernel(float2 *grad, size_t n, const QuantScale *__restrict__ qs) {
+// `rows` rows per plane (several planes: multi:softmax); plane k of row r is element k * rows + r
+__global__ void quantize_pair_kernel(float2 *grad, size_t n, size_t rows, const QuantScale *__restrict__ qs,
+                                     unsigned long long row0, unsigned round, int lim) {
   const float sg = qs->sg, sh = qs->sh;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x) {
     const float2 g = grad[i];
+    const size_t plane = i / rows;
+    const unsigned long long row = row0 + (i - plane * rows);
+    const unsigned salt = unsigned(plane) * 0x27D4EB2Fu;
     // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
-    reinterpret_cast<int2 *>(grad)[i] = make_int2(__float2int_rn(g.x * sg), max(1, __float2int_rn(g.y * sh)));
+    reinterpret_cast<int2 *>(grad)[i] = make_int2(to_fixed(g.x, sg, row, round, salt, lim),
+                                                  max(1, to_fixed(g.y, sh, row, round, salt ^ 0x68E31DA4u, lim)));
   }
 }
 
-__global__ void quantize_single_kernel(float *grad, size_t n, const QuantScale *__restrict__ qs) {
+__global__ void quantize_single_kernel(float *grad, size_t n, const QuantScale *__restrict__ qs, int lim) {
   const float sg = qs->sg;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x)
-    reinterpret_cast<int *>(grad)[i] = __float2int_rn(grad[i] * sg);
+    reinterpret_cast<int *>(grad)[i] = to_fixed(grad[i], sg, i, kNoDither, 0u, lim);
 }
 
 template <bool PAIR>
@@ -210,20 +243,23 @@ inline int grid_for(size_t n, int threads) {
 }  // namespace
 
 void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
-                      const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s) {
+                      const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s,
+                      unsigned long long row0, unsigned round, int quant_bits) {
+  const int lim = (1 << quant_bits) - 1;
   if (!emit) ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
   const int threads = 256;
   const int grid = grid_for(n, threads);
   if (objective == 0) {
-    if (emit) grad_linear_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n);
-    else grad_linear_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n);
+    if (emit) grad_linear_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim);
+    else grad_linear_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim);
   } else if (objective == 1) {
-    if (emit) grad_logistic_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n);
-    else grad_logistic_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n);
+    if (emit) grad_logistic_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim);
+    else grad_logistic_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim);
   } else if (!emit) {  // the K double-precision exponentials per row are not computed twice:
     grad_softmax_kernel<<<grid, threads, 0, s>>>(label, yhat, static_cast<float2 *>(grad), qs, n, K);
   } else {             // the floats are stored by the first pass and turned into integers in place
-    quantize_pair_kernel<<<grid_for(n * K, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n * K, qs);
+    quantize_pair_kernel<<<grid_for(n * K, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n * K, n, qs,
+                                                                      row0, round, lim);
   }
   ARB_CUDA(cudaGetLastError());
   count_launch();
@@ -236,12 +272,15 @@ void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cuda
   count_launch();
 }
 
-void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, cudaStream_t s) {
+void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, int quant_bits,
+                           cudaStream_t s) {
   const int threads = 256;
+  const int lim = (1 << quant_bits) - 1;
   if (pair)
-    quantize_pair_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n, qs);
+    quantize_pair_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float2 *>(grad), n, n, qs, 0ull,
+                                                                  kNoDither, lim);
   else
-    quantize_single_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float *>(grad), n, qs);
+    quantize_single_kernel<<<grid_for(n, threads), threads, 0, s>>>(static_cast<float *>(grad), n, qs, lim);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

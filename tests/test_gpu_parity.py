@@ -257,10 +257,11 @@ def compare_with_oracle(cfg, X, y, rounds, labels=None, max_level=None):
                     diverged = True
                 else:
                     # sums agree to 1e-5 of the node's sum of |g|
-                    # ... or to the rigorous bound of the fixed-point sums: half a step per row, the
-                    # step being 2^(e - 18) with 2^e the power of two above the round's largest |g|
+                    # ... or to the rigorous bound of the dithered fixed-point sums: one step per row,
+                    # the step being 2^(e - 18) with 2^e the power of two above the round's largest
+                    # |g| (the typical error is a step times the square root of the rows)
                     rows_i = float(e["node_begin"][i + 1] - e["node_begin"][i]) if l > 0 else float(len(X))
-                    tol = max(HIST_RTOL * max(e["abs_g"][i], 1e-3), 0.5 * step * rows_i)
+                    tol = max(HIST_RTOL * max(e["abs_g"][i], 1e-3), step * rows_i)
                     assert abs(g["tot_g"][i] - e["tot_g"][i]) <= tol
                     assert abs(g["left_g"][i] - e["left_g"][i]) <= tol
                     # the gain is a difference of terms G^2 / (H + lambda): an error of `tol` in a
@@ -368,8 +369,11 @@ def test_deep_tree_beyond_the_shared_memory_node_tables(kind, objective):
     cfg = make_config(objective, 14)
     # level by level against the oracle down to the nodes of a few hundred rows; below that
     # a node's gain is a small difference of large terms and the fixed-point step of the
-    # gradients (half a step per row) shows in it
-    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 2, max_level=7)
+    # gradients shows in it.  One round: the leaves of a tree this deep hold one or two rows,
+    # their weights carry those rows' rounding whole, and a second round would start from
+    # predictions that already differ by it.
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 1, max_level=7)
+    model.grow_tree()
     # the leaf every training row was counted into is the leaf the finished trees send its
     # raw feature values to: the per-row node numbers against the fp32 tree walk
     internal = model.train_yhat()[0]
