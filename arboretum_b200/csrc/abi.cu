@@ -114,7 +114,7 @@ bool upload_beside_matrix(DataMatrix *d, DevBuf &dst, const void *src, size_t by
   if (dst.bytes != bytes) {
     dst.release();
     void *p = nullptr;
-    ok = cudaMalloc(&p, bytes) == cudaSuccess;
+    ok = dev_alloc(&p, bytes) == cudaSuccess;
     if (ok) {
       dst.p = p;
       dst.bytes = bytes;
@@ -148,11 +148,11 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
   // no staging copy on the host); quantisation and inference read it there.  Without a
   // usable device, or when it does not fit beside the training state, a host copy is kept.
   const size_t bytes = size_t(nrow) * ncol * sizeof(float);
-  size_t free_b = 0, total_b = 0;
+  size_t free_b = 0;
   bool on_device = false;
-  if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && bytes < free_b / 2) {
+  if (dev_available(&free_b) == cudaSuccess && bytes < free_b / 2) {
     void *p = nullptr;
-    if (cudaMalloc(&p, bytes) == cudaSuccess) {
+    if (dev_alloc(&p, bytes) == cudaSuccess) {
       m->d_x.p = p;
       m->d_x.bytes = bytes;
       on_device = cudaMemcpy(p, data, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -182,11 +182,11 @@ const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol,
   // quarter of the free memory (training needs the padded copy and its transpose too);
   // larger inputs stay on the host, for out-of-core training.
   const size_t bytes = size_t(nrow) * ncol;
-  size_t free_b = 0, total_b = 0;
+  size_t free_b = 0;
   bool on_device = false;
-  if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && bytes <= free_b / 4) {
+  if (dev_available(&free_b) == cudaSuccess && bytes <= free_b / 4) {
     void *p = nullptr;
-    if (cudaMalloc(&p, bytes) == cudaSuccess) {
+    if (dev_alloc(&p, bytes) == cudaSuccess) {
       m->d_raw.p = p;
       m->d_raw.bytes = bytes;
       on_device = cudaMemcpy(p, bins, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&

@@ -33,6 +33,16 @@ namespace arb {
   } while (0)
 
 // Owning device allocation.
+// Device memory comes from the device's stream-ordered pool, set to keep what is freed:
+// cudaMalloc / cudaFree of gigabytes cost milliseconds (and on a busy host tens of them)
+// every time a matrix or a model is built, the pool hands a freed block back in
+// microseconds.  dev_alloc returns only when the block may be used on any stream;
+// dev_free first waits for the device, like cudaFree does.
+cudaError_t dev_alloc(void **p, size_t bytes);
+void dev_free(void *p);
+// free device memory as cudaMemGetInfo reports it, plus what the pool holds unused
+cudaError_t dev_available(size_t *bytes);
+
 struct DevBuf {
   void *p = nullptr;
   size_t bytes = 0;
@@ -44,7 +54,7 @@ struct DevBuf {
   void alloc(size_t n) {
     release();
     if (n == 0) return;
-    ARB_CUDA(cudaMalloc(&p, n));
+    ARB_CUDA(dev_alloc(&p, n));
     bytes = n;
   }
   // n bytes at `ptr`, owned by someone else who outlives this object
@@ -55,7 +65,7 @@ struct DevBuf {
     owned = false;
   }
   void release() {
-    if (p && owned) cudaFree(p);
+    if (p && owned) dev_free(p);
     p = nullptr;
     bytes = 0;
     owned = true;

@@ -16,6 +16,56 @@ namespace arb {
 
 long long g_kernel_launches = 0;
 
+namespace {
+// one stream per device for the pool's allocations and frees; the pool keeps freed memory
+cudaStream_t pool_stream() {
+  constexpr int kMaxDevices = 64;
+  static cudaStream_t streams[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!streams[dev]) {
+    cudaMemPool_t pool = nullptr;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+      unsigned long long keep = ~0ull;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    if (cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking) != cudaSuccess) streams[dev] = nullptr;
+  }
+  return streams[dev];
+}
+}  // namespace
+
+cudaError_t dev_alloc(void **p, size_t bytes) {
+  cudaStream_t st = pool_stream();
+  if (!st) return cudaMalloc(p, bytes);
+  cudaError_t e = cudaMallocAsync(p, bytes, st);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(st);
+}
+
+void dev_free(void *p) {
+  if (!p) return;
+  cudaDeviceSynchronize();  // nothing on any stream may still use the block
+  cudaStream_t st = pool_stream();
+  if (!st || cudaFreeAsync(p, st) != cudaSuccess) cudaFree(p);
+}
+
+cudaError_t dev_available(size_t *bytes) {
+  size_t free_b = 0, total_b = 0;
+  cudaError_t e = cudaMemGetInfo(&free_b, &total_b);
+  if (e != cudaSuccess) return e;
+  int dev = 0;
+  cudaMemPool_t pool = nullptr;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    unsigned long long reserved = 0, used = 0;
+    if (cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &reserved) == cudaSuccess &&
+        cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &used) == cudaSuccess && reserved > used)
+      free_b += size_t(reserved - used);
+  }
+  *bytes = free_b;
+  return cudaSuccess;
+}
+
 // ---------------------------------------------------------------------------
 // DataMatrix
 // ---------------------------------------------------------------------------
@@ -530,8 +580,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     const size_t chunk_bytes = chunks_[0].rows * d->pitch;
     int resident = cfg.internal.resident_chunks;
     if (resident < 0) {
-      size_t free_b = 0, total_b = 0;
-      ARB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+      size_t free_b = 0;
+      ARB_CUDA(dev_available(&free_b));
       const size_t budget = free_b / 10 * 8;
       resident = budget > 2 * chunk_bytes ? int((budget - 2 * chunk_bytes) / chunk_bytes) : 0;
     }
