@@ -34,7 +34,8 @@ def _load_lib():
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
                  "AGetLevelStats", "ASetProfile", "AGetTimings", "ABuildHistogram",
-                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak"):
+                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak",
+                 "AReleaseCachedMemory"):
         getattr(lib, name).restype = ctypes.c_char_p
     lib.ADumpModel.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.c_void_p]
     lib.AFreeDMatrix.argtypes = [ctypes.c_void_p]
@@ -308,6 +309,11 @@ def load(json_model_str):
     model = Garden(config)
     model.load(json_model_str)
     return model
+
+
+def release_cached_memory():
+    """Hand the device memory the library has freed but kept (its pool) back to the driver."""
+    _call_and_throw_if_error(_LIB.AReleaseCachedMemory())
 
 
 def shared_atomic_peak(steps=2000):

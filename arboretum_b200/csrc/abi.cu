@@ -425,6 +425,12 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   ARB_CATCH
 }
 
+const char *AReleaseCachedMemory() {
+  ARB_TRY
+  ARB_CUDA(dev_trim());
+  ARB_CATCH
+}
+
 const char *ASharedAtomicPeak(int steps, double *pair_updates_per_s) {
   ARB_TRY
   ARB_CHECK(pair_updates_per_s != nullptr, "NULL argument");

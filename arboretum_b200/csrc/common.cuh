@@ -42,6 +42,8 @@ cudaError_t dev_alloc(void **p, size_t bytes);
 void dev_free(void *p);
 // free device memory as cudaMemGetInfo reports it, plus what the pool holds unused
 cudaError_t dev_available(size_t *bytes);
+// give the pool's unused memory back to the driver
+cudaError_t dev_trim();
 
 struct DevBuf {
   void *p = nullptr;

@@ -50,6 +50,16 @@ void dev_free(void *p) {
   if (!st || cudaFreeAsync(p, st) != cudaSuccess) cudaFree(p);
 }
 
+cudaError_t dev_trim() {
+  int dev = 0;
+  cudaMemPool_t pool = nullptr;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetDefaultMemPool(&pool, dev);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemPoolTrimTo(pool, 0);
+  return e;
+}
+
 cudaError_t dev_available(size_t *bytes) {
   size_t free_b = 0, total_b = 0;
   cudaError_t e = cudaMemGetInfo(&free_b, &total_b);

@@ -114,6 +114,12 @@ const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128
 const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist_size,
                                float *thr_device, void *stream);
 
+/* Additive (no counterpart in the reference): the library takes its device memory from the
+ * current device's stream-ordered pool and keeps what it frees, so that the next matrix or
+ * model does not pay for cudaMalloc again; this call hands the unused part back to the
+ * driver (for a process that shares the GPU with other allocators). */
+const char *AReleaseCachedMemory(void);
+
 /* Additive (no counterpart in the reference): measures, on the current device, how many
  * (gradient, hessian) pair updates per second the histogram kernels' two shared-memory
  * reductions sustain when nothing else is done (no loads, staging or stores) -- the

@@ -459,6 +459,24 @@ def test_prebinned_input_equals_dense_input():
         assert a["weights"] == b["weights"]
 
 
+def test_freed_memory_is_kept_and_can_be_released():
+    import torch
+    from arboretum_b200 import core
+    arboretum = arb()
+    core.release_cached_memory()
+    free0 = torch.cuda.mem_get_info()[0]
+    X, y = synth("logistic", 400000, 28, seed=4)
+    model = arboretum.train(make_config(1, 6), arboretum.DMatrix(X, y=y), 2)
+    first = model.dump()
+    del model
+    kept = free0 - torch.cuda.mem_get_info()[0]
+    assert kept > 50 * 2 ** 20  # the freed blocks stay with the pool ...
+    again = arboretum.train(make_config(1, 6), arboretum.DMatrix(X, y=y), 2).dump()
+    assert again == first  # ... a second model is built from them, to the same trees ...
+    core.release_cached_memory()
+    assert free0 - torch.cuda.mem_get_info()[0] < kept / 4  # ... and the driver gets them back on request
+
+
 def test_bad_calls_return_errors():
     arboretum = arb()
     X, y = synth("linear", 100, 4, seed=1)
