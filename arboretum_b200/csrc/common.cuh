@@ -146,15 +146,16 @@ struct NodeRec {
   float gain;
   int fid;
   int bin;
-  unsigned left_count;  // rows that went left (filled by the partition pass)
+  unsigned left_count;  // rows that went left (filled by the level's plan kernel from the
+                        // descend step's counts)
   long long lg, lh;     // left child sums
   long long tg, th;     // node totals
 };
 
 // A contiguous piece of one node's row list, the unit of work of the histogram
-// and partition kernels.
+// kernels.
 struct WorkItem {
-  unsigned begin;  // first position in the row-id list
+  unsigned begin;  // first position in the level's row list (or first row, at the root)
   unsigned len;
   int node;        // node index inside its level
   int pad;

@@ -52,7 +52,7 @@ class DataMatrix {
   int bin_bytes = 1;
   size_t pitch = 0;
   DevBuf d_bins;
-  DevBuf d_bins_cm;  // feature-major copy for the row partition (in-core only)
+  DevBuf d_bins_cm;  // feature-major copy for the descend step (in-core only)
   PinnedBuf h_bins;  // out-of-core: the padded row-major bin matrix in pinned host memory
   bool out_of_core = false;
   std::vector<float> thr;  // [F][hist_size] data_reduced_mapping
@@ -95,6 +95,7 @@ typedef int (*AllreduceFn)(void *ctx, long long *device_buf, size_t count, cudaS
 typedef int (*AllreduceMaxFn)(void *ctx, unsigned *device_buf, size_t count, cudaStream_t stream);
 
 struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
+  // (partition = the descend steps, plan = plan kernel + row lists, update = the final descend)
   double grad = 0, hist = 0, subtract = 0, split = 0, partition = 0, plan = 0, update = 0, allreduce = 0;
   long long hist_launches = 0;
   double hist_rows = 0;      // rows scanned by histogram launches

@@ -30,7 +30,7 @@ struct Geometry {
   int TW, NT, BINS;
   int hist_size;  // bins a split may use (config value); id hist_size = missing
   // optional feature-major copy bins_cm[f * cm_rows + row] (nullptr: absent): the row
-  // partition reads one feature of many rows, which is sequential in this layout
+  // descend step reads one feature of every row, which is sequential in this layout
   const unsigned char *bins_cm = nullptr;
   size_t cm_rows = 0;
 };
