@@ -459,6 +459,48 @@ def test_prebinned_input_equals_dense_input():
         assert a["weights"] == b["weights"]
 
 
+def test_full_size_level_records_are_consistent():
+    """The bench configuration at its full size (10 M x 28, depth 8), where the oracle is too slow
+    to follow: properties that hold whatever the size.  Every level's node totals add up to
+    the root's, a parent's left sum is its left child's total (all exact: the sums are
+    integers), the prefix counts match the rows that went left, and the node every training
+    row was counted into is where the finished trees send its raw values."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    arboretum = arb()
+    n = 10_000_000
+    X, y = bench.make_rows(n, 0)
+    cfg = json.loads(json.dumps(bench.CONFIG))
+    data = arboretum.DMatrix(X, y=y)
+    model = arboretum.Garden(cfg)
+    model.data = data
+    depth = cfg["tree"]["max_depth"]
+    for _ in range(2):
+        model.grow_tree()
+        prev = None
+        for l in range(depth):
+            g = model.level_stats(l)
+            nb = g["node_begin"].astype(np.int64)
+            assert nb[0] == 0 and nb[-1] == n and (np.diff(nb) >= 0).all()
+            if prev is not None:
+                pg, pnb = prev
+                for k in ("tot_g", "tot_h"):
+                    kids = g[k].reshape(-1, 2)
+                    assert np.array_equal(kids.sum(axis=1), pg[k])           # children add up
+                    assert np.array_equal(kids[:, 0], pg["left_" + k[-1]])   # left child = left sum
+                assert np.array_equal(nb[1::2] - nb[0:-1:2], pg["left_count"].astype(np.int64))
+                assert np.array_equal(nb[::2], pnb)
+            split = g["fid"] >= 0
+            assert (g["gain"][split] > 0).all() and (g["gain"][~split] == 0).all()
+            prev = (g, nb)
+    sl = slice(0, n, 10)  # every tenth row through the fp32 tree walk
+    internal = model.train_yhat()[0][sl].astype(np.float64)
+    pred_model = arboretum.load(model.dump())
+    out = pred_model.predict(arboretum.DMatrix(np.ascontiguousarray(X[sl])))
+    assert np.allclose(1.0 / (1.0 + np.exp(-internal)), out, atol=1e-5, rtol=0)
+
+
 def test_freed_memory_is_kept_and_can_be_released():
     import torch
     from arboretum_b200 import core
