@@ -251,11 +251,123 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
   }
 }
 
+// The same step for the common case (the level's table fits shared memory, a feature-major
+// copy of the bins exists, node_of and yhat start on 16-byte boundaries), laid out for more
+// rows in flight per register: a lane takes kWideRows consecutive rows, reads their eight
+// nodes with one 16-byte load (and, FINAL, their predictions with two, before anything
+// depends on them), keeps nodes and split bins packed two to a word beside the eight bins in
+// flight, and writes the children (FINAL: the predictions) with 16-byte stores.  A warp
+// still covers 256 consecutive rows per turn, so the bin reads of rows on one feature share
+// sectors.  The counts of the first two nodes are kept per lane while the level has at most
+// kFewNodes nodes.
+constexpr int kWideRows = 8;
+constexpr int kWideCtasPerSm = 6;  // 40 registers: no spills
+
+template <typename BIN_T, bool FINAL>
+__global__ void __launch_bounds__(256, FINAL ? 5 : kWideCtasPerSm)
+descend_wide_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
+                    const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
+                    unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
+                    float *__restrict__ yhat, const size_t n) {
+  __shared__ unsigned table[kSmemNodes];             // feature << 16 | split bin; feature 0xffff: no split
+  __shared__ unsigned cnt[FINAL ? 1 : kSmemNodes];   // rows of this CTA that went right, per node
+  for (int i = threadIdx.x; i < L; i += blockDim.x) {
+    const int fid = rec[i].fid;
+    table[i] = fid < 0 ? 0xffff0000u : (unsigned(fid) << 16) | unsigned(rec[i].bin);
+    if (!FINAL) cnt[i] = 0;
+  }
+  __syncthreads();
+  const bool few = L <= kFewNodes;
+  unsigned mine0 = 0, mine1 = 0;  // few nodes: this lane's right-goers of nodes 0 and 1
+  const BIN_T *__restrict__ cm = reinterpret_cast<const BIN_T *>(bins_cm);
+  const size_t threads = size_t(gridDim.x) * blockDim.x;
+  for (size_t r0 = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * kWideRows; r0 < n;
+       r0 += threads * kWideRows) {
+    const bool whole = r0 + kWideRows <= n;
+    uint4 nodes = make_uint4(0u, 0u, 0u, 0u);  // eight nodes, two to a word (low half first)
+    if (L > 1) nodes = *reinterpret_cast<const uint4 *>(node_of + r0);
+    float y[kWideRows];
+    if (FINAL) {
+      if (whole) {
+        const float4 a = *reinterpret_cast<const float4 *>(yhat + r0);
+        const float4 b = *reinterpret_cast<const float4 *>(yhat + r0 + 4);
+        y[0] = a.x, y[1] = a.y, y[2] = a.z, y[3] = a.w, y[4] = b.x, y[5] = b.y, y[6] = b.z, y[7] = b.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < kWideRows; ++k) y[k] = r0 + k < n ? yhat[r0 + k] : 0.0f;
+      }
+    }
+    unsigned nw[4] = {nodes.x, nodes.y, nodes.z, nodes.w};
+    if (!whole) {  // what lies past the last row is not a node number
+#pragma unroll
+      for (int k = 0; k < kWideRows; ++k)
+        if (r0 + k >= n) nw[k >> 1] &= ~(0xffffu << (16 * (k & 1)));
+    }
+    unsigned sb[4] = {0u, 0u, 0u, 0u};  // the eight split bins, packed the same way
+    int binv[kWideRows];
+#pragma unroll
+    for (int k = 0; k < kWideRows; ++k) {
+      const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+      const unsigned e = table[node];
+      const unsigned fid = e >> 16;
+      sb[k >> 1] |= (e & 0xffffu) << (16 * (k & 1));
+      binv[k] = -1;  // no split, or past the end: left
+      if (fid != 0xffffu && r0 + k < n) binv[k] = int(cm[size_t(fid) * cm_rows + r0 + k]);
+    }
+    unsigned out[4];
+#pragma unroll
+    for (int k = 0; k < kWideRows; ++k) {
+      const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+      const bool right = binv[k] > int((sb[k >> 1] >> (16 * (k & 1))) & 0xffffu);
+      const unsigned child = 2u * node + (right ? 1u : 0u);
+      if (FINAL) {
+        y[k] += leaf_w[child];
+      } else {
+        if (k & 1) out[k >> 1] |= child << 16; else out[k >> 1] = child;
+        if (few) {
+          mine0 += (right && node == 0u) ? 1u : 0u;
+          mine1 += (right && node == 1u) ? 1u : 0u;
+        } else if (right) {
+          red_shared_u32(&cnt[node], 1u);
+        }
+      }
+    }
+    if (FINAL) {
+      if (whole) {
+        *reinterpret_cast<float4 *>(yhat + r0) = make_float4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<float4 *>(yhat + r0 + 4) = make_float4(y[4], y[5], y[6], y[7]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < kWideRows; ++k)
+          if (r0 + k < n) yhat[r0 + k] = y[k];
+      }
+    } else if (whole) {
+      *reinterpret_cast<uint4 *>(node_of + r0) = make_uint4(out[0], out[1], out[2], out[3]);
+    } else {
+      for (int k = 0; r0 + k < n; ++k)
+        node_of[r0 + k] = (unsigned short)((out[k >> 1] >> (16 * (k & 1))) & 0xffffu);
+    }
+  }
+  if (FINAL) return;
+  if (few) {
+    mine0 = __reduce_add_sync(0xffffffffu, mine0);
+    mine1 = __reduce_add_sync(0xffffffffu, mine1);
+    if ((threadIdx.x & 31) == 0) {
+      if (mine0) red_shared_u32(&cnt[0], mine0);
+      if (mine1 && L > 1) red_shared_u32(&cnt[1], mine1);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < L; i += blockDim.x)
+    if (cnt[i]) atomicAdd(&right_count[size_t(i) * kPad], cnt[i]);
+}
+
 // The rows of the built nodes go to their node's list.  A CTA takes kListRows consecutive
 // rows: every row gets a rank among the CTA's rows of its node from a shared-memory counter
 // (one atomic per group of lanes with the same node while the level has at most kFewLists
-// nodes: there the lanes of a warp would all meet on the same few counters), the CTA reserves room in every list it has rows for
-// with one global atomicAdd, and the rows are written at list start + CTA base + rank.
+// nodes: there the lanes of a warp would all meet on the same few counters), the CTA
+// reserves room in every list it has rows for with one global atomicAdd, and the rows are
+// written at list start + CTA base + rank.
 template <typename GRAD_T>  // int2 / int: the gradient record copied along; char: none
 __global__ void __launch_bounds__(kListThreads)
 gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, const int L,
@@ -270,18 +382,37 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
   const bool few = L <= kFewLists;
   const size_t base = size_t(blockIdx.x) * kListRows;
   const int lane = threadIdx.x & 31;
-  if (cached) {
-    for (int i = threadIdx.x; i < L; i += kListThreads) s_at[i] = 0;
-    __syncthreads();
-  }
+  // bit i: node i has a list; the rows of the other nodes (about half of all rows under the
+  // subtraction trick) then take no rank
+  __shared__ unsigned s_has_list[kSmemNodes / 32];
   int node[kPer];
   unsigned rank[kPer];
-  GRAD_T gv[kPer];  // the rows' gradient records, fetched with the node numbers: one more stream
+  GRAD_T gv[kPer];  // the gradient records of the rows that go to a list
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
     const size_t r = base + size_t(k) * kListThreads + threadIdx.x;
     node[k] = r < n ? int(node_of[r]) : -1;
-    if (sizeof(GRAD_T) > 1 && r < n) gv[k] = grad[r];
+  }
+  if (cached) {
+    for (int i0 = 0; i0 < L; i0 += kListThreads) {  // a warp's 32 nodes make one word of the mask
+      const int i = i0 + threadIdx.x;
+      const unsigned m = __ballot_sync(0xffffffffu, i < L && list_base[i] != kNoList);
+      if (i < L) s_at[i] = 0;
+      if (lane == 0 && i < L) s_has_list[i >> 5] = m;
+    }
+    __syncthreads();
+    const unsigned first_word = s_has_list[0];
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+      if (node[k] < 0) continue;
+      const unsigned word = L <= 32 ? first_word : s_has_list[node[k] >> 5];
+      if (!((word >> (node[k] & 31)) & 1u)) node[k] = -1;
+    }
+  }
+  if (sizeof(GRAD_T) > 1) {  // in flight while the ranks are taken
+#pragma unroll
+    for (int k = 0; k < kPer; ++k)
+      if (node[k] >= 0) gv[k] = grad[base + size_t(k) * kListThreads + threadIdx.x];
   }
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
@@ -334,23 +465,53 @@ void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
   count_launch();
 }
 
+namespace {
+
+// CTAs of `kernel` that are resident on the current device at once
+template <typename K>
+int resident_ctas(K kernel, int threads) {
+  int per_sm = 0, dev = 0, sms = 0;
+  ARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+  ARB_CUDA(cudaGetDevice(&dev));
+  ARB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  return std::max(1, per_sm * sms);
+}
+
+}  // namespace
+
 void launch_descend(const DescendLaunch &a, cudaStream_t s) {
   if (a.n == 0) return;
   const bool fin = a.child_count == nullptr;
-  const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
   const Geometry &g = a.geo;
   // exactly as many CTAs as are resident at once: a second, partly filled wave would cost
   // as much as a full one
+  const bool wide = g.bins_cm && a.L <= kSmemNodes && reinterpret_cast<uintptr_t>(a.node_of) % 16 == 0 &&
+                    (!fin || reinterpret_cast<uintptr_t>(a.yhat) % 16 == 0);
+  if (wide) {
+    const size_t span = size_t(256) * kWideRows;  // rows of one CTA turn
 #define ARB_LAUNCH(T, FIN)                                                                          \
   do {                                                                                              \
     static int resident = 0;                                                                        \
-    if (!resident) {                                                                                \
-      int per_sm = 0, dev = 0, sms = 0;                                                             \
-      ARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, descend_kernel<T, FIN>, 256, 0)); \
-      ARB_CUDA(cudaGetDevice(&dev));                                                                \
-      ARB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));                  \
-      resident = std::max(1, per_sm * sms);                                                         \
-    }                                                                                               \
+    if (!resident) resident = resident_ctas(descend_wide_kernel<T, FIN>, 256);                      \
+    const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
+    descend_wide_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins_cm, g.cm_rows, a.rec, a.L, a.node_of,   \
+                                                     a.child_count, a.leaf_w, a.yhat, a.n);         \
+  } while (0)
+    if (g.bin_bytes == 1) {
+      if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
+    } else {
+      if (fin) ARB_LAUNCH(unsigned short, true); else ARB_LAUNCH(unsigned short, false);
+    }
+#undef ARB_LAUNCH
+    ARB_CUDA(cudaGetLastError());
+    count_launch();
+    return;
+  }
+  const size_t span = size_t(32) * kDescendPasses * (256 / 32);  // rows of one CTA turn
+#define ARB_LAUNCH(T, FIN)                                                                          \
+  do {                                                                                              \
+    static int resident = 0;                                                                        \
+    if (!resident) resident = resident_ctas(descend_kernel<T, FIN>, 256);                           \
     const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
     descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L,  \
                                                 a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);   \
