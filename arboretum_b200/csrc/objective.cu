@@ -77,17 +77,30 @@ __device__ __forceinline__ void block_max_to(QuantScale *qs, float mg, float mh)
 // Two passes over (y, yhat): EMIT = false finds the maxima that fix the round's fixed-point
 // scale, EMIT = true computes the same floats again and stores them as integers
 // (g_q = rint(g * sg), h_q = max(1, rint(h * sh))): the float gradients never touch memory.
+// n4: the rows taken four at a time with 16-byte loads and stores (a multiple of 4; 0 when
+// a pointer is not 16-byte aligned), so that a thread has enough bytes in flight to keep the
+// memory busy; the other rows go one at a time.
 template <bool EMIT>
 __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
                                    int *__restrict__ grad, QuantScale *qs, size_t n,
-                                   unsigned long long row0, unsigned round, int lim) {
+                                   unsigned long long row0, unsigned round, int lim, size_t n4) {
   float m = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += size_t(gridDim.x) * blockDim.x) {
-    const float g = y[i] - yhat[i];
-    if (EMIT) grad[i] = to_fixed(g, sg, row0 + i, round, 0u, lim);
-    else m = fmaxf(m, fabsf(g));
+  const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
+  auto row = [&](float yi, float yh, size_t i) -> int {
+    const float g = yi - yh;
+    if (EMIT) return to_fixed(g, sg, row0 + i, round, 0u, lim);
+    m = fmaxf(m, fabsf(g));
+    return 0;
+  };
+  for (size_t i = tid * 4; i < n4; i += total * 4) {
+    const float4 a = *reinterpret_cast<const float4 *>(y + i), b = *reinterpret_cast<const float4 *>(yhat + i);
+    const int4 q = make_int4(row(a.x, b.x, i), row(a.y, b.y, i + 1), row(a.z, b.z, i + 2), row(a.w, b.w, i + 3));
+    if (EMIT) *reinterpret_cast<int4 *>(grad + i) = q;
+  }
+  for (size_t i = n4 + tid; i < n; i += total) {
+    const int q = row(y[i], yhat[i], i);
+    if (EMIT) grad[i] = q;
   }
   if (!EMIT) block_max_to(qs, m, 0.0f);
 }
@@ -95,21 +108,31 @@ __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__r
 template <bool EMIT>
 __global__ void grad_logistic_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
                                      int2 *__restrict__ grad, QuantScale *qs, size_t n,
-                                     unsigned long long row0, unsigned round, int lim) {
+                                     unsigned long long row0, unsigned round, int lim, size_t n4) {
   float mg = 0.0f, mh = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f, sh = EMIT ? qs->sh : 0.0f;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += size_t(gridDim.x) * blockDim.x) {
-    const float s = EMIT ? sigmoid(yhat[i]) : sigmoid_fast(yhat[i]);
-    const float2 g = make_float2(y[i] - s, s * (1.0f - s));
+  const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
+  auto row = [&](float yi, float yh, size_t i) -> int2 {
+    const float s = EMIT ? sigmoid(yh) : sigmoid_fast(yh);
+    const float2 g = make_float2(yi - s, s * (1.0f - s));
+    if (EMIT)  // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
+      return make_int2(to_fixed(g.x, sg, row0 + i, round, 0u, lim),
+                       max(1, to_fixed(g.y, sh, row0 + i, round, 0x68E31DA4u, lim)));
+    mg = fmaxf(mg, fabsf(g.x));
+    mh = fmaxf(mh, g.y);
+    return make_int2(0, 0);
+  };
+  for (size_t i = tid * 4; i < n4; i += total * 4) {
+    const float4 a = *reinterpret_cast<const float4 *>(y + i), b = *reinterpret_cast<const float4 *>(yhat + i);
+    const int2 q0 = row(a.x, b.x, i), q1 = row(a.y, b.y, i + 1), q2 = row(a.z, b.z, i + 2), q3 = row(a.w, b.w, i + 3);
     if (EMIT) {
-      // h_q >= 1 for every row, so that a zero hessian sum means "no rows"
-      grad[i] = make_int2(to_fixed(g.x, sg, row0 + i, round, 0u, lim),
-                          max(1, to_fixed(g.y, sh, row0 + i, round, 0x68E31DA4u, lim)));
-    } else {
-      mg = fmaxf(mg, fabsf(g.x));
-      mh = fmaxf(mh, g.y);
+      *reinterpret_cast<int4 *>(grad + i) = make_int4(q0.x, q0.y, q1.x, q1.y);
+      *reinterpret_cast<int4 *>(grad + i + 2) = make_int4(q2.x, q2.y, q3.x, q3.y);
     }
+  }
+  for (size_t i = n4 + tid; i < n; i += total) {
+    const int2 q = row(y[i], yhat[i], i);
+    if (EMIT) grad[i] = q;
   }
   if (!EMIT) block_max_to(qs, mg * kMaxSlack, mh * kMaxSlack);
 }
@@ -249,12 +272,16 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
   if (!emit) ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
   const int threads = 256;
   const int grid = grid_for(n, threads);
+  const bool aligned = (reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(yhat) |
+                        reinterpret_cast<uintptr_t>(grad)) % 16 == 0;
+  const size_t n4 = aligned ? n / 4 * 4 : 0;
+  const int grid4 = grid_for(n4 / 4 + (n - n4), threads);
   if (objective == 0) {
-    if (emit) grad_linear_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim);
-    else grad_linear_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim);
+    if (emit) grad_linear_kernel<true><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
+    else grad_linear_kernel<false><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
   } else if (objective == 1) {
-    if (emit) grad_logistic_kernel<true><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim);
-    else grad_logistic_kernel<false><<<grid, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim);
+    if (emit) grad_logistic_kernel<true><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
+    else grad_logistic_kernel<false><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
   } else if (!emit) {  // the K double-precision exponentials per row are not computed twice:
     grad_softmax_kernel<<<grid, threads, 0, s>>>(label, yhat, static_cast<float2 *>(grad), qs, n, K);
   } else {             // the floats are stored by the first pass and turned into integers in place
