@@ -117,6 +117,40 @@ static inline int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); 
 extern long long g_kernel_launches;
 static inline void count_launch(int n = 1) { g_kernel_launches += n; }
 
+// Programmatic dependent launch: a kernel launched with launch_overlapped() may be put on
+// the SMs while the kernel before it on the stream still runs, so that its launch latency
+// and whatever it does before overlap_wait() (clearing shared memory, index arithmetic)
+// hide behind that kernel's tail.  overlap_wait() returns once the earlier kernel has
+// finished and its writes are visible: every kernel launched this way calls it before its
+// first access to global memory.  overlap_release() lets the next kernel on the stream
+// start its own preamble; that kernel's overlap_wait() still waits for this whole grid.
+// ARBORETUM_NO_LAUNCH_OVERLAP in the environment turns the launches back into plain ones.
+#ifdef __CUDACC__
+__device__ __forceinline__ void overlap_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void overlap_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool launch_overlap_enabled() {
+  static const bool on = std::getenv("ARBORETUM_NO_LAUNCH_OVERLAP") == nullptr;
+  return on;
+}
+
+template <typename... P, typename... A>
+inline void launch_overlapped(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_overlap_enabled() ? 1 : 0;
+  ARB_CUDA(cudaLaunchKernelEx(&cfg, kernel, P(args)...));
+}
+#endif
+
 // Host-side stage timer of the set-up paths: with ARBORETUM_TRACE set in the environment,
 // lap("name") synchronises the device and prints the wall time since the previous lap.
 struct StageTrace {

@@ -79,6 +79,11 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
                int *__restrict__ partials, const void *__restrict__ list_grad) {
   extern __shared__ __align__(16) int smem[];
+  // the histogram of the CTA's first item is cleared while the kernel before this one drains
+  overlap_release();
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+  overlap_wait();
+  bool cleared = true;
   int *G = smem;
   constexpr int kWarps = kHistThreads / 32;
   unsigned char *stage0 = reinterpret_cast<unsigned char *>(smem + 2 * kHistWords);
@@ -99,7 +104,9 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
 
   for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
     const WorkItem item = items[it];
-    for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+    if (!cleared)
+      for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+    cleared = false;
     __syncthreads();
     const unsigned len = item.len;
     const int nb = int((len + 31) / 32);  // batches of 32 rows, dealt round-robin to warps
@@ -244,6 +251,8 @@ __global__ void reduce_kernel(const int *__restrict__ partials, const int *__res
                               const int *__restrict__ build_node, long long *__restrict__ level_hist,
                               const long long *__restrict__ parent_hist, const int NT,
                               const int slices, const bool atomic) {
+  overlap_release();
+  overlap_wait();
   const int b = blockIdx.z / slices, slice = blockIdx.z - b * slices, tile = blockIdx.y;
   const int w = blockIdx.x * blockDim.x + threadIdx.x;
   const int first = item_first[b], last = item_first[b + 1];
@@ -274,6 +283,8 @@ __global__ void subtract_kernel(long long *__restrict__ level_hist,
                                 const long long *__restrict__ parent_hist,
                                 const int *__restrict__ built_child, const size_t words_per_node,
                                 const size_t total) {
+  overlap_release();
+  overlap_wait();
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += size_t(gridDim.x) * blockDim.x) {
     const size_t p = i / words_per_node;
@@ -346,9 +357,8 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
 #define ARB_LAUNCH(P, I)                                                                      \
   do {                                                                                        \
     ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                               \
-    hist_u8_kernel<P, I><<<grid, kHistThreads, smem, s>>>(g.bins, g.pitch, g.NT, a.rowid,     \
-                                                          a.grad, a.items, a.n_items,         \
-                                                          a.partials, a.list_grad);           \
+    launch_overlapped(hist_u8_kernel<P, I>, grid, kHistThreads, smem, s, g.bins, g.pitch,     \
+                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.partials, a.list_grad);    \
   } while (0)
     if (a.pair) {
       if (ident) ARB_LAUNCH(true, true); else ARB_LAUNCH(true, false);
@@ -443,20 +453,18 @@ void launch_reduce(const ReduceLaunch &a, cudaStream_t s) {
   if (slices > 1 || a.accumulate) {
     const size_t bytes = size_t(a.level_nodes) * a.NT * kHistWords * 2 * sizeof(long long);
     if (!a.accumulate) ARB_CUDA(cudaMemsetAsync(a.level_hist, 0, bytes, s));
-    reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, slices, true);
-    ARB_CUDA(cudaGetLastError());
+    launch_overlapped(reduce_kernel<false>, grid, threads, 0, s, a.partials, a.item_first, a.build_node,
+                      a.level_hist, nullptr, a.NT, slices, true);
     count_launch();
     if (a.subtract) launch_subtract(a.level_hist, a.parent_hist, a.built_child, a.level_nodes / 2, a.NT, s);
     return;
   }
   if (a.subtract)
-    reduce_kernel<true><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node, a.level_hist,
-                                                 a.parent_hist, a.NT, 1, false);
+    launch_overlapped(reduce_kernel<true>, grid, threads, 0, s, a.partials, a.item_first, a.build_node,
+                      a.level_hist, a.parent_hist, a.NT, 1, false);
   else
-    reduce_kernel<false><<<grid, threads, 0, s>>>(a.partials, a.item_first, a.build_node,
-                                                  a.level_hist, nullptr, a.NT, 1, false);
-  ARB_CUDA(cudaGetLastError());
+    launch_overlapped(reduce_kernel<false>, grid, threads, 0, s, a.partials, a.item_first, a.build_node,
+                      a.level_hist, nullptr, a.NT, 1, false);
   count_launch();
 }
 
@@ -466,9 +474,8 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
   const size_t total = words_per_node * n_parents;
   const int threads = 256;
   const int blocks = int(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
-  subtract_kernel<<<blocks, threads, 0, s>>>(level_hist, parent_hist, built_child, words_per_node,
-                                             total);
-  ARB_CUDA(cudaGetLastError());
+  launch_overlapped(subtract_kernel, blocks, threads, 0, s, level_hist, parent_hist, built_child, words_per_node,
+                    total);
   count_launch();
 }
 

@@ -84,6 +84,8 @@ template <bool EMIT>
 __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
                                    int *__restrict__ grad, QuantScale *qs, size_t n,
                                    unsigned long long row0, unsigned round, int lim, size_t n4) {
+  overlap_release();
+  overlap_wait();
   float m = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f;
   const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
@@ -109,6 +111,8 @@ template <bool EMIT>
 __global__ void grad_logistic_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
                                      int2 *__restrict__ grad, QuantScale *qs, size_t n,
                                      unsigned long long row0, unsigned round, int lim, size_t n4) {
+  overlap_release();
+  overlap_wait();
   float mg = 0.0f, mh = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f, sh = EMIT ? qs->sh : 0.0f;
   const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
@@ -160,6 +164,8 @@ __global__ void grad_softmax_kernel(const unsigned char *__restrict__ label,
 }
 
 __global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) {
+  overlap_release();
+  overlap_wait();
   // largest |g| < 2^e  =>  |g * 2^(quant_bits - e)| < 2^quant_bits
   int eg = 0, eh = 0;
   const float mg = __uint_as_float(qs->max_g_bits), mh = __uint_as_float(qs->max_h_bits);
@@ -201,6 +207,8 @@ __global__ void quantize_single_kernel(float *grad, size_t n, const QuantScale *
 
 template <bool PAIR>
 __global__ void leaf_weights_kernel(LeafLaunch a) {
+  overlap_release();
+  overlap_wait();
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= a.L) return;
   const NodeRec r = a.last_rec[n];
@@ -277,11 +285,11 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
   const size_t n4 = aligned ? n / 4 * 4 : 0;
   const int grid4 = grid_for(n4 / 4 + (n - n4), threads);
   if (objective == 0) {
-    if (emit) grad_linear_kernel<true><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
-    else grad_linear_kernel<false><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
+    if (emit) launch_overlapped(grad_linear_kernel<true>, grid4, threads, 0, s, y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
+    else launch_overlapped(grad_linear_kernel<false>, grid4, threads, 0, s, y, yhat, static_cast<int *>(grad), qs, n, row0, round, lim, n4);
   } else if (objective == 1) {
-    if (emit) grad_logistic_kernel<true><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
-    else grad_logistic_kernel<false><<<grid4, threads, 0, s>>>(y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
+    if (emit) launch_overlapped(grad_logistic_kernel<true>, grid4, threads, 0, s, y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
+    else launch_overlapped(grad_logistic_kernel<false>, grid4, threads, 0, s, y, yhat, static_cast<int2 *>(grad), qs, n, row0, round, lim, n4);
   } else if (!emit) {  // the K double-precision exponentials per row are not computed twice:
     grad_softmax_kernel<<<grid, threads, 0, s>>>(label, yhat, static_cast<float2 *>(grad), qs, n, K);
   } else {             // the floats are stored by the first pass and turned into integers in place
@@ -294,8 +302,7 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
 
 void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s) {
   (void)K;
-  finish_scales_kernel<<<1, 1, 0, s>>>(qs, quant_bits, pair);
-  ARB_CUDA(cudaGetLastError());
+  launch_overlapped(finish_scales_kernel, 1, 1, 0, s, qs, quant_bits, pair);
   count_launch();
 }
 
@@ -315,10 +322,9 @@ void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs
 void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s) {
   const int threads = 128;
   if (a.pair)
-    leaf_weights_kernel<true><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
+    launch_overlapped(leaf_weights_kernel<true>, ceil_div(a.L, threads), threads, 0, s, a);
   else
-    leaf_weights_kernel<false><<<ceil_div(a.L, threads), threads, 0, s>>>(a);
-  ARB_CUDA(cudaGetLastError());
+    launch_overlapped(leaf_weights_kernel<false>, ceil_div(a.L, threads), threads, 0, s, a);
   count_launch();
 }
 

@@ -108,6 +108,8 @@ __global__ void plan_level_kernel(const unsigned *__restrict__ child_count,
                                   unsigned *__restrict__ node_begin, NodeRec *__restrict__ parent_rec,
                                   int L, int item_rows, bool use_trick, bool by_hessian,
                                   PlanBuffers pb, int max_items) {
+  overlap_release();
+  overlap_wait();
   unsigned *sb = pb.scratch_begin, *sl = pb.scratch_len;
   int *sn = pb.scratch_node;
   if (child_count) {  // rows that went right, per parent; the others of the parent went left
@@ -182,6 +184,8 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
                const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
                unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
                float *__restrict__ yhat, const size_t n) {
+  overlap_release();
+  overlap_wait();
   __shared__ unsigned table[kSmemNodes];  // feature << 16 | split bin; feature 0xffff: no split
   __shared__ unsigned cnt[kSmemNodes];    // rows of this CTA that went right, per node
   const bool cached = L <= kSmemNodes;
@@ -269,6 +273,8 @@ descend_wide_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_r
                     const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
                     unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
                     float *__restrict__ yhat, const size_t n) {
+  overlap_release();
+  overlap_wait();
   __shared__ unsigned table[kSmemNodes];             // feature << 16 | split bin; feature 0xffff: no split
   __shared__ unsigned cnt[FINAL ? 1 : kSmemNodes];   // rows of this CTA that went right, per node
   for (int i = threadIdx.x; i < L; i += blockDim.x) {
@@ -374,6 +380,8 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
                     const unsigned *__restrict__ list_base, unsigned *__restrict__ cursor,
                     unsigned *__restrict__ list, const GRAD_T *__restrict__ grad,
                     GRAD_T *__restrict__ list_grad) {
+  overlap_release();
+  overlap_wait();
   // per node: first the CTA's row count, then where the CTA's rows of the node go (kNoList:
   // the node has no list)
   __shared__ unsigned s_at[kSmemNodes];
@@ -459,9 +467,8 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
 }  // namespace
 
 void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
-  plan_level_kernel<<<1, 256, 0, s>>>(a.child_count, a.parent_begin, a.node_begin, a.parent_rec, a.L, a.item_rows,
-                                      a.use_trick, a.by_hessian, a.pb, a.max_items);
-  ARB_CUDA(cudaGetLastError());
+  launch_overlapped(plan_level_kernel, 1, 256, 0, s, a.child_count, a.parent_begin, a.node_begin, a.parent_rec,
+                    a.L, a.item_rows, a.use_trick, a.by_hessian, a.pb, a.max_items);
   count_launch();
 }
 
@@ -494,8 +501,8 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
     static int resident = 0;                                                                        \
     if (!resident) resident = resident_ctas(descend_wide_kernel<T, FIN>, 256);                      \
     const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
-    descend_wide_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins_cm, g.cm_rows, a.rec, a.L, a.node_of,   \
-                                                     a.child_count, a.leaf_w, a.yhat, a.n);         \
+    launch_overlapped(descend_wide_kernel<T, FIN>, grid, 256, 0, s, g.bins_cm, g.cm_rows, a.rec,    \
+                      a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);                        \
   } while (0)
     if (g.bin_bytes == 1) {
       if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
@@ -513,8 +520,8 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
     static int resident = 0;                                                                        \
     if (!resident) resident = resident_ctas(descend_kernel<T, FIN>, 256);                           \
     const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
-    descend_kernel<T, FIN><<<grid, 256, 0, s>>>(g.bins, g.pitch, g.bins_cm, g.cm_rows, a.rec, a.L,  \
-                                                a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);   \
+    launch_overlapped(descend_kernel<T, FIN>, grid, 256, 0, s, g.bins, g.pitch, g.bins_cm,          \
+                      g.cm_rows, a.rec, a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);      \
   } while (0)
   if (g.bin_bytes == 1) {
     if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
@@ -532,17 +539,14 @@ void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const P
   if (n == 0) return;
   const unsigned grid = unsigned((n + kListRows - 1) / kListRows);
   if (!list_grad)
-    gather_lists_kernel<char><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
-                                                            nullptr, nullptr);
+    launch_overlapped(gather_lists_kernel<char>, grid, kListThreads, 0, s, node_of, n, L, pb.list_base, pb.cursor,
+                      list, nullptr, nullptr);
   else if (pair)
-    gather_lists_kernel<int2><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
-                                                            static_cast<const int2 *>(grad),
-                                                            static_cast<int2 *>(list_grad));
+    launch_overlapped(gather_lists_kernel<int2>, grid, kListThreads, 0, s, node_of, n, L, pb.list_base, pb.cursor,
+                      list, static_cast<const int2 *>(grad), static_cast<int2 *>(list_grad));
   else
-    gather_lists_kernel<int><<<grid, kListThreads, 0, s>>>(node_of, n, L, pb.list_base, pb.cursor, list,
-                                                           static_cast<const int *>(grad),
-                                                           static_cast<int *>(list_grad));
-  ARB_CUDA(cudaGetLastError());
+    launch_overlapped(gather_lists_kernel<int>, grid, kListThreads, 0, s, node_of, n, L, pb.list_base, pb.cursor,
+                      list, static_cast<const int *>(grad), static_cast<int *>(list_grad));
   count_launch();
 }
 

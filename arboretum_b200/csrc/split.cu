@@ -61,6 +61,8 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
              unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
              NodeRec *__restrict__ rec, const QuantScale *__restrict__ qs, const GainParams gp,
              const int TW, const int NT, const int F, const int hist_size, const int parts) {
+  overlap_release();
+  overlap_wait();
   __shared__ long long part_g[kSplitThreads], part_h[kSplitThreads];
   __shared__ float best_gain[kSplitThreads];
   __shared__ int best_bin[kSplitThreads];
@@ -168,14 +170,11 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   while (parts > 1 && a.L * a.geo.NT * parts > 2 * 148) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair)
-    split_kernel<true><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
-                                                      a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
-                                                      a.geo.hist_size, parts);
+    launch_overlapped(split_kernel<true>, grid, kSplitThreads, 0, s, a.hist, a.feature_active, a.keys, done,
+                      a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   else
-    split_kernel<false><<<grid, kSplitThreads, 0, s>>>(a.hist, a.feature_active, a.keys, done, a.rec,
-                                                       a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F,
-                                                       a.geo.hist_size, parts);
-  ARB_CUDA(cudaGetLastError());
+    launch_overlapped(split_kernel<false>, grid, kSplitThreads, 0, s, a.hist, a.feature_active, a.keys, done,
+                      a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   count_launch();
 }
 

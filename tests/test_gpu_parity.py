@@ -519,6 +519,49 @@ def test_freed_memory_is_kept_and_can_be_released():
     assert free0 - torch.cuda.mem_get_info()[0] < kept / 4  # ... and the driver gets them back on request
 
 
+_OVERLAP_JOB = """
+import hashlib, json, sys
+import numpy as np
+import arboretum_b200 as arboretum
+rng = np.random.default_rng(77)
+n, F = 1500000, 28
+X = rng.standard_normal((n, F)).astype(np.float32)
+w = rng.standard_normal(F)
+y = (X @ w + rng.standard_normal(n) > 0).astype(np.float32)
+cfg = {"objective": 1, "method": 1,
+       "internals": {"double_precision": True, "compute_overlap": 2, "seed": 0,
+                     "use_hist_subtraction_trick": True, "upload_features": True, "hist_size": 255},
+       "verbose": {"gpu": False, "booster": False, "data": False},
+       "tree": {"eta": 0.3, "max_depth": 8, "lambda": 1.0, "alpha": 0.0, "min_child_weight": 1.0,
+                "min_leaf_size": 1, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}}
+model = arboretum.train(cfg, arboretum.DMatrix(X, y=y), 12)
+h = hashlib.sha256(model.dump().encode())
+h.update(np.ascontiguousarray(model.predict(arboretum.DMatrix(X[:100000]))).tobytes())
+print("digest", h.hexdigest())
+"""
+
+
+def test_overlapped_launches_give_the_same_model():
+    """The level kernels are launched so that each may start while the one before it drains
+    and waits for it before touching global memory.  A kernel that read too early would
+    change a sum somewhere in 12 rounds over 1.5 M rows: the model must be identical, byte
+    for byte, to the one built with plain stream-ordered launches."""
+    import subprocess
+    import sys
+    arb()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    digests = []
+    for plain in (False, True, False):
+        env = dict(os.environ)
+        env.pop("ARBORETUM_NO_LAUNCH_OVERLAP", None)
+        if plain:
+            env["ARBORETUM_NO_LAUNCH_OVERLAP"] = "1"
+        out = subprocess.run([sys.executable, "-c", _OVERLAP_JOB], cwd=root, env=env, check=True,
+                             capture_output=True, text=True, timeout=600).stdout
+        digests.append([l for l in out.splitlines() if l.startswith("digest")][0])
+    assert digests[0] == digests[1] == digests[2]
+
+
 def test_bad_calls_return_errors():
     arboretum = arb()
     X, y = synth("linear", 100, 4, seed=1)
