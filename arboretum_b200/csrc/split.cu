@@ -40,6 +40,7 @@ __device__ void finalize_node(const long long *__restrict__ hist, unsigned long 
     const int tile = r.fid / TW, fl = r.fid % TW;
     const long long *base = hist + (size_t(node) * NT + tile) * kHistWords * 2;
     long long g = 0, h = 0;
+#pragma unroll 8  // the loads of eight turns are in flight together: one latency, not eight
     for (int b = lane; b <= r.bin; b += 32) {
       g += base[(size_t(b) * TW + fl) * 2];
       h += base[(size_t(b) * TW + fl) * 2 + 1];
@@ -83,18 +84,55 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
     sg += v[k].x;
     sh += v[k].y;
   }
-  part_g[threadIdx.x] = sg;
-  part_h[threadIdx.x] = sh;
-  __syncthreads();
   long long og = 0, oh = 0, tg = 0, th = 0;
-  for (int c = 0; c < nchunks; ++c) {
-    const long long g = part_g[c * TW + lane], h = part_h[c * TW + lane];
-    if (c < chunk) {
-      og += g;
-      oh += h;
+  if (TW == 32) {
+    // A warp is one chunk of all 32 features.  The sums change places through shared memory
+    // (slot feature * 32 + (chunk ^ feature): no bank conflict on the feature-major side), so
+    // that warp f holds the 32 chunk sums of feature f and scans them with shuffles; the
+    // offsets travel back through the same slots.
+    __shared__ long long tot_g[32], tot_h[32];
+    const int slot = lane * 32 + (chunk ^ lane);
+    part_g[slot] = sg;
+    part_h[slot] = sh;
+    __syncthreads();
+    {
+      const int f_w = chunk, c_l = lane;  // this thread now stands for (chunk c_l, feature f_w)
+      const int at = f_w * 32 + (c_l ^ f_w);
+      const long long vg = part_g[at], vh = part_h[at];
+      long long xg = vg, xh = vh;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long ug = __shfl_up_sync(0xffffffffu, xg, o), uh = __shfl_up_sync(0xffffffffu, xh, o);
+        if (c_l >= o) {
+          xg += ug;
+          xh += uh;
+        }
+      }
+      part_g[at] = xg - vg;
+      part_h[at] = xh - vh;
+      if (c_l == 31) {
+        tot_g[f_w] = xg;
+        tot_h[f_w] = xh;
+      }
     }
-    tg += g;
-    th += h;
+    __syncthreads();
+    og = part_g[slot];
+    oh = part_h[slot];
+    tg = tot_g[lane];
+    th = tot_h[lane];
+  } else {
+    part_g[threadIdx.x] = sg;
+    part_h[threadIdx.x] = sh;
+    __syncthreads();
+    for (int c = 0; c < nchunks; ++c) {
+      const long long g = part_g[c * TW + lane], h = part_h[c * TW + lane];
+      if (c < chunk) {
+        og += g;
+        oh += h;
+      }
+      tg += g;
+      th += h;
+    }
   }
   if (tile == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     rec[node].tg = tg;
