@@ -202,10 +202,17 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   // the level's plan kernel
   unsigned *done = reinterpret_cast<unsigned *>(a.keys + a.max_nodes);
   // Small levels: the double-precision gain arithmetic of a (node, tile) is spread over up
-  // to 8 CTAs, which all re-read the tile.  Large levels have enough (node, tile) pairs to
-  // fill the GPU, and the re-reads would only multiply the traffic.
+  // to 8 CTAs, which all re-read the tile.  A CTA of 1024 threads with 64 registers each
+  // has an SM to itself, so more CTAs than SMs would only run as a second wave: the gains
+  // they share out would wait in line all the same, after re-reading the tile.
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    ARB_CUDA(cudaGetDevice(&dev));
+    ARB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
   int parts = kBinsPerThread;
-  while (parts > 1 && a.L * a.geo.NT * parts > 2 * 148) parts >>= 1;
+  while (parts > 1 && a.L * a.geo.NT * parts > sms) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair)
     launch_overlapped(split_kernel<true>, grid, kSplitThreads, 0, s, a.hist, a.feature_active, a.keys, done,
