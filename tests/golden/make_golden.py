@@ -43,7 +43,9 @@ def extract_sklearn(path):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REF", "")
+    if not os.path.isdir(os.path.join(ref, "tests", "py")):
+        raise SystemExit("usage: make_golden.py /path/to/the/reference/tree  (or REF=...)")
     out = {"hist_logregression": extract_logreg(os.path.join(ref, "tests/py/test_hist_logregression.py")),
            "sklearn_classification": extract_sklearn(os.path.join(ref, "tests/py/test_sklearn_classification.py")),
            "config": {"objective": 1, "method": 1,
