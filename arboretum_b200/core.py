@@ -33,8 +33,8 @@ def _load_lib():
                  "ASetLabel", "ASetWeights", "ADumpModel", "ALoadModel",
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
-                 "AGetLevelStats", "ASetProfile", "AGetTimings", "ABuildHistogram",
-                 "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak",
+                 "AGetLevelStats", "AGetLevelStatsOf", "ASetProfile", "AGetTimings", "ABuildHistogram",
+                 "ABuildHistogramFromParents", "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak",
                  "AReleaseCachedMemory"):
         getattr(lib, name).restype = ctypes.c_char_p
     lib.ADumpModel.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.c_void_p]
@@ -59,12 +59,16 @@ def _load_lib():
                               ctypes.c_void_p, ctypes.c_void_p]
     lib.AGetTrainY.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.AGetLevelStats.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 9
+    lib.AGetLevelStatsOf.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 9
     lib.ASetProfile.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.AGetTimings.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p)]
     lib.ABuildHistogram.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    lib.ABuildHistogramFromParents.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
+                                               ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 4
     lib.ASharedAtomicPeak.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     lib.AThresholdsNoAlloc.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
                                        ctypes.c_void_p, ctypes.c_void_p]
@@ -270,15 +274,16 @@ class Garden(object):
         _call_and_throw_if_error(_LIB.AGetTrainY(self.handle, _ptr(out)))
         return out
 
-    def level_stats(self, level):
-        """Split records of one level of the last grown tree."""
+    def level_stats(self, level, tree_in_round=-1):
+        """Split records of one level of a tree of the last round (-1: the last tree grown;
+        multi:softmax grows ``labels_count`` trees per round, numbered from 0)."""
         L = 1 << level
         out = {"node_begin": np.empty(L + 1, dtype=np.uint32), "gain": np.empty(L, dtype=np.float32),
                "fid": np.empty(L, dtype=np.int32), "bin": np.empty(L, dtype=np.int32),
                "left_g": np.empty(L), "left_h": np.empty(L), "tot_g": np.empty(L),
                "tot_h": np.empty(L), "left_count": np.empty(L, dtype=np.uint32)}
-        _call_and_throw_if_error(_LIB.AGetLevelStats(
-            self.handle, level, *[_ptr(out[k]) for k in ("node_begin", "gain", "fid", "bin", "left_g",
+        _call_and_throw_if_error(_LIB.AGetLevelStatsOf(
+            self.handle, int(tree_in_round), level, *[_ptr(out[k]) for k in ("node_begin", "gain", "fid", "bin", "left_g",
                                                          "left_h", "tot_g", "tot_h", "left_count")]))
         return out
 
@@ -324,12 +329,15 @@ def shared_atomic_peak(steps=2000):
     return out.value
 
 
-def build_histogram(bins, grad, hist_size, rowid=None, node_begin=None, quant_bits=17, reps=0):
+def build_histogram(bins, grad, hist_size, rowid=None, node_begin=None, quant_bits=17, reps=0,
+                    parents=None):
     """One histogram launch (kernel-level entry point ``ABuildHistogram``).
 
     bins: [rows][columns] uint8/uint16; grad: [rows] or [rows][2] float32.
     Returns (sum_g, sum_h) as [nodes][columns][hist_size + 1] doubles and, when
     ``reps`` > 0, the mean device time of one launch in milliseconds.
+    ``parents`` = (sum_g, sum_h) of the nodes' parents switches the subtraction trick on
+    (``ABuildHistogramFromParents``): only the smaller child of every pair is scanned.
     """
     bins = np.ascontiguousarray(bins)
     assert bins.dtype in (np.uint8, np.uint16)
@@ -345,6 +353,14 @@ def build_histogram(bins, grad, hist_size, rowid=None, node_begin=None, quant_bi
     og = np.zeros((nn, F, hist_size + 1))
     oh = np.zeros((nn, F, hist_size + 1))
     ms = ctypes.c_float(0)
+    if parents is not None:
+        pg = np.ascontiguousarray(parents[0], dtype=np.float64)
+        ph = np.ascontiguousarray(parents[1], dtype=np.float64)
+        assert pg.shape == (nn // 2, F, hist_size + 1) and ph.shape == pg.shape
+        _call_and_throw_if_error(_LIB.ABuildHistogramFromParents(
+            _ptr(bins), bins.dtype.itemsize, n, F, hist_size, _ptr(grad), pair, _ptr(rowid),
+            _ptr(node_begin), nn, quant_bits, _ptr(pg), _ptr(ph), _ptr(og), _ptr(oh)))
+        return og, oh
     _call_and_throw_if_error(_LIB.ABuildHistogram(
         _ptr(bins), bins.dtype.itemsize, n, F, hist_size, _ptr(grad), pair, _ptr(rowid),
         _ptr(node_begin), nn, quant_bits, _ptr(og), _ptr(oh), reps, ctypes.byref(ms)))

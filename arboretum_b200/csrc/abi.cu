@@ -137,12 +137,14 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
                                    int ncol, int ccol, float missing, VoidPointer *out) {
   ARB_TRY
   (void)missing;     // never read by the reference either (arboretum_wrapper.cu:16-39)
-  (void)categories;  // categorical training is a stub in the reference (hist_tree_grower.h:55-63)
   ARB_CHECK(out != nullptr, "out is NULL");
   ARB_CHECK(nrow > 0 && ncol > 0 && ccol >= 0, "bad matrix shape");
   ARB_CHECK(data != nullptr, "data is NULL");
-  ARB_CHECK(ccol == 0, "categorical columns are not supported by this build");
+  ARB_CHECK(ccol == 0 || categories != nullptr, "categories is NULL");
   std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, ccol));
+  if (ccol > 0) {  // arboretum_wrapper.cu:30-33; kept on the host for the quantiser
+    m->cat.assign(categories, categories + size_t(nrow) * ccol);
+  }
   StageTrace trace("ACreateFromDenseMatrix");
   // The matrix goes straight into HBM (one host->device copy from the caller's buffer,
   // no staging copy on the host); quantisation and inference read it there.  Without a
@@ -165,6 +167,11 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
     m->x.assign(data, data + size_t(nrow) * ncol);
   }
   trace.lap("matrix to HBM");
+  if (ccol > 0 && on_device) {  // inference reads the category codes beside the matrix
+    m->d_cat.alloc(m->cat.size() * sizeof(unsigned));
+    ARB_CUDA(cudaMemcpy(m->d_cat.p, m->cat.data(), m->d_cat.bytes, cudaMemcpyHostToDevice));
+  }
+  ARB_CHECK(ccol == 0 || on_device, "categorical columns need the matrix in device memory");
   *out = m.release();
   ARB_CATCH
 }
@@ -232,6 +239,11 @@ const char *ASetThresholds(VoidPointer data, const float *thr, const int *size, 
   ARB_CHECK(data && thr && size, "NULL argument");
   DataMatrix *d = static_cast<DataMatrix *>(data);
   ARB_CHECK(!d->binned, "the matrix is already quantised");
+  ARB_CHECK(hist_size > 0 && hist_size < 2048, "hist_size must be in [1, 2047]");
+  // bin ids index the threshold table and the shared-memory histograms: a size outside
+  // [1, hist_size] would send both out of range
+  for (int f = 0; f < d->cols_dense; ++f)
+    ARB_CHECK(size[f] >= 1 && size[f] <= hist_size, "size[f] must be in [1, hist_size]");
   d->thr.assign(thr, thr + size_t(d->cols_dense) * hist_size);
   d->fsize.assign(size, size + d->cols_dense);
   d->thresholds_given = true;
@@ -362,12 +374,19 @@ const char *AGetTrainY(VoidPointer garden, float *out) {
 const char *AGetLevelStats(VoidPointer garden, int level, unsigned *node_begin, float *gain, int *fid,
                            int *bin, double *left_g, double *left_h, double *tot_g, double *tot_h,
                            unsigned *left_count) {
+  return AGetLevelStatsOf(garden, -1, level, node_begin, gain, fid, bin, left_g, left_h, tot_g, tot_h,
+                          left_count);
+}
+
+const char *AGetLevelStatsOf(VoidPointer garden, int tree_in_round, int level, unsigned *node_begin,
+                             float *gain, int *fid, int *bin, double *left_g, double *left_h,
+                             double *tot_g, double *tot_h, unsigned *left_count) {
   ARB_TRY
   ARB_CHECK(garden, "NULL argument");
   Garden *g = static_cast<Garden *>(garden);
   int max_nodes = 0, levels = 0, stride = 0;
-  const NodeRec *rec = BuilderView::host_rec(g, &max_nodes, &levels);
-  const unsigned *nb = BuilderView::host_node_begin(g, &stride);
+  const NodeRec *rec = BuilderView::host_rec(g, tree_in_round, &max_nodes, &levels);
+  const unsigned *nb = BuilderView::host_node_begin(g, tree_in_round, &stride);
   ARB_CHECK(level >= 0 && level < levels, "level out of range");
   QuantScale q;
   BuilderView::scales(g, &q);
@@ -439,29 +458,59 @@ const char *ASharedAtomicPeak(int steps, double *pair_updates_per_s) {
   ARB_CATCH
 }
 
-const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
-                            const float *grad, int pair, const unsigned *rowid,
-                            const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
-                            double *out_h, int reps, float *ms) {
+static const char *build_histogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                                   const float *grad, int pair, const unsigned *rowid,
+                                   const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
+                                   double *out_h, int reps, float *ms, const double *parent_g,
+                                   const double *parent_h) {
   ARB_TRY
+  const bool trick = parent_g != nullptr;
+  ARB_CHECK(!trick || (parent_h != nullptr && n_nodes % 2 == 0), "the subtraction needs both parent arrays and an even node count");
   ARB_CHECK(bins && grad && node_begin && out_g && out_h, "NULL argument");
   ARB_CHECK(bin_bytes == 1 || bin_bytes == 2, "bin_bytes must be 1 or 2");
   ARB_CHECK(nrow > 0 && ncol > 0 && n_nodes > 0, "bad shape");
   ARB_CHECK(hist_size > 0 && hist_size < 2048 && (bin_bytes == 2 || hist_size < 256), "bad hist_size");
   ARB_CHECK(quant_bits >= 10 && quant_bits <= 20, "quant_bits must be in [10, 20]");
+  ARB_CHECK(nrow < (int64_t(1) << 31), "row count must be below 2^31");
   const size_t n = size_t(nrow);
+  // The arrays below drive gathers and shared-memory updates on the device; anything out of
+  // range is refused here, where it is an error string and not a memory fault.
+  for (int i = 0; i < n_nodes; ++i)
+    ARB_CHECK(node_begin[i] <= node_begin[i + 1], "node_begin must be non-decreasing");
+  ARB_CHECK(node_begin[n_nodes] <= n, "node_begin exceeds the row count");
+  if (rowid)
+    for (size_t i = 0; i < n; ++i) ARB_CHECK(rowid[i] < n, "rowid out of range");
+  {
+    const size_t cells = n * size_t(ncol);
+    bool ok = true;
+    if (bin_bytes == 1) {
+      const unsigned char *b = static_cast<const unsigned char *>(bins);
+      for (size_t i = 0; i < cells; ++i) ok = ok && b[i] <= hist_size;
+    } else {
+      const unsigned short *b = static_cast<const unsigned short *>(bins);
+      for (size_t i = 0; i < cells; ++i) ok = ok && b[i] <= hist_size;
+    }
+    ARB_CHECK(ok, "bin id above hist_size (ids 0..hist_size-1 are bins, hist_size is the missing-value bin)");
+  }
   Geometry geo;
   geo.pitch = DataMatrix::PitchFor(ncol, bin_bytes);
   geo.bin_bytes = bin_bytes;
   geo.F = ncol;
+  geo.n_dense = ncol;
   geo.hist_size = hist_size;
   int bins_pad = 256;
   while (bins_pad < hist_size + 1) bins_pad <<= 1;
   geo.BINS = bins_pad;
   geo.TW = kHistWords / bins_pad;
   geo.NT = (ncol + geo.TW - 1) / geo.TW;
-  cudaStream_t s;
-  ARB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  struct StreamGuard {  // destroyed on every way out, also when something below throws
+    cudaStream_t s = nullptr;
+    ~StreamGuard() {
+      if (s) cudaStreamDestroy(s);
+    }
+  } stream_guard;
+  ARB_CUDA(cudaStreamCreateWithFlags(&stream_guard.s, cudaStreamNonBlocking));
+  cudaStream_t s = stream_guard.s;
   DevBuf d_bins, d_grad, d_rowid, d_items, d_nitems, d_hist, d_qs;
   d_bins.alloc(n * geo.pitch);
   ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, d_bins.bytes, s));
@@ -487,14 +536,23 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   launch_quantize_grads(d_grad.p, n, pair != 0, d_qs.as<QuantScale>(), quant_bits, s);
   const unsigned cap = 1u << (31 - quant_bits);
   std::vector<WorkItem> items;
-  std::vector<int> first(n_nodes + 1, 0), ids(n_nodes);
-  for (int node = 0; node < n_nodes; ++node) {
-    first[node] = int(items.size());
-    ids[node] = node;
-    for (unsigned b = node_begin[node]; b < node_begin[node + 1]; b += cap)
-      items.push_back(WorkItem{b, std::min(cap, node_begin[node + 1] - b), node, 0});
+  // with parents: one child per pair is built, the smaller one, ties the left
+  // (hist_grad_sum.cu:288-290 of the reference); the other is parent - built
+  const int n_build = trick ? n_nodes / 2 : n_nodes;
+  std::vector<int> first(n_build + 1, 0), ids(n_build), built(std::max(1, n_nodes / 2), 0);
+  for (int b = 0; b < n_build; ++b) {
+    int node = b;
+    if (trick) {
+      const unsigned ls = node_begin[2 * b + 1] - node_begin[2 * b], rs = node_begin[2 * b + 2] - node_begin[2 * b + 1];
+      built[b] = ls <= rs ? 0 : 1;
+      node = 2 * b + built[b];
+    }
+    first[b] = int(items.size());
+    ids[b] = node;
+    for (unsigned at = node_begin[node]; at < node_begin[node + 1]; at += cap)
+      items.push_back(WorkItem{at, std::min(cap, node_begin[node + 1] - at), node, 0});
   }
-  first[n_nodes] = int(items.size());
+  first[n_build] = int(items.size());
   ARB_CHECK(!items.empty(), "no rows");
   const int n_items = int(items.size());
   DevBuf d_first, d_ids, d_partials;
@@ -509,6 +567,25 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   ARB_CUDA(cudaMemcpyAsync(d_ids.p, ids.data(), d_ids.bytes, cudaMemcpyHostToDevice, s));
   const size_t words = size_t(n_nodes) * geo.NT * kHistWords * 2;
   d_hist.alloc(words * sizeof(long long));
+  ARB_CUDA(cudaMemsetAsync(d_hist.p, 0, d_hist.bytes, s));
+  DevBuf d_parent, d_built;
+  if (trick) {  // the parents' sums as the fixed-point integers the kernels subtract from
+    const int HWp = hist_size + 1;
+    std::vector<long long> parent(words / 2, 0);
+    for (int p = 0; p < n_nodes / 2; ++p)
+      for (int f = 0; f < ncol; ++f)
+        for (int b = 0; b < HWp; ++b) {
+          const size_t src = (size_t(p) * ncol + f) * HWp + b;
+          const size_t dst = (((size_t(p) * geo.NT + f / geo.TW) * geo.BINS + b) * geo.TW + f % geo.TW) * 2;
+          parent[dst] = std::llrint(parent_g[src] * double(q.sg));
+          parent[dst + 1] = std::llrint(parent_h[src] * double(q.sh));
+        }
+    d_parent.alloc(parent.size() * sizeof(long long));
+    d_built.alloc(built.size() * sizeof(int));
+    ARB_CUDA(cudaMemcpyAsync(d_parent.p, parent.data(), d_parent.bytes, cudaMemcpyHostToDevice, s));
+    ARB_CUDA(cudaMemcpyAsync(d_built.p, built.data(), d_built.bytes, cudaMemcpyHostToDevice, s));
+    ARB_CUDA(cudaStreamSynchronize(s));  // `parent` and `built` leave scope below
+  }
   HistLaunch h;
   h.geo = geo;
   h.rowid = rowid ? d_rowid.as<unsigned>() : nullptr;
@@ -522,34 +599,37 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
   rd.partials = d_partials.as<int>();
   rd.item_first = d_first.as<int>();
   rd.build_node = d_ids.as<int>();
-  rd.n_build = n_nodes;
+  rd.n_build = n_build;
   rd.NT = geo.NT;
   rd.level_hist = d_hist.as<long long>();
-  rd.parent_hist = nullptr;
-  rd.subtract = false;
+  rd.parent_hist = trick ? d_parent.as<long long>() : nullptr;
+  rd.subtract = trick;
   rd.level_nodes = n_nodes;
-  rd.built_child = nullptr;
+  rd.built_child = trick ? d_built.as<int>() : nullptr;
   if (reps > 0) {
-    cudaEvent_t e0, e1;
-    ARB_CUDA(cudaEventCreate(&e0));
-    ARB_CUDA(cudaEventCreate(&e1));
+    struct EventPair {
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      ~EventPair() {
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+      }
+    } ev;
+    ARB_CUDA(cudaEventCreate(&ev.e0));
+    ARB_CUDA(cudaEventCreate(&ev.e1));
     for (int i = 0; i < 3; ++i) launch_hist(h, s);
-    ARB_CUDA(cudaEventRecord(e0, s));
+    ARB_CUDA(cudaEventRecord(ev.e0, s));
     for (int i = 0; i < reps; ++i) launch_hist(h, s);
-    ARB_CUDA(cudaEventRecord(e1, s));
-    ARB_CUDA(cudaEventSynchronize(e1));
+    ARB_CUDA(cudaEventRecord(ev.e1, s));
+    ARB_CUDA(cudaEventSynchronize(ev.e1));
     float t = 0;
-    ARB_CUDA(cudaEventElapsedTime(&t, e0, e1));
+    ARB_CUDA(cudaEventElapsedTime(&t, ev.e0, ev.e1));
     if (ms) *ms = t / reps;
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
   }
   launch_hist(h, s);
   launch_reduce(rd, s);
   std::vector<long long> host(words);
   ARB_CUDA(cudaMemcpyAsync(host.data(), d_hist.p, d_hist.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaStreamSynchronize(s));
-  cudaStreamDestroy(s);
   const int HW = hist_size + 1;
   for (int node = 0; node < n_nodes; ++node)
     for (int f = 0; f < ncol; ++f) {
@@ -562,6 +642,24 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
       }
     }
   ARB_CATCH
+}
+
+const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                            const float *grad, int pair, const unsigned *rowid,
+                            const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
+                            double *out_h, int reps, float *ms) {
+  return build_histogram(bins, bin_bytes, nrow, ncol, hist_size, grad, pair, rowid, node_begin, n_nodes,
+                         quant_bits, out_g, out_h, reps, ms, nullptr, nullptr);
+}
+
+const char *ABuildHistogramFromParents(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                                       const float *grad, int pair, const unsigned *rowid,
+                                       const unsigned *node_begin, int n_nodes, int quant_bits,
+                                       const double *parent_g, const double *parent_h, double *out_g,
+                                       double *out_h) {
+  if (!parent_g || !parent_h) return fail("NULL argument");
+  return build_histogram(bins, bin_bytes, nrow, ncol, hist_size, grad, pair, rowid, node_begin, n_nodes,
+                         quant_bits, out_g, out_h, 0, nullptr, parent_g, parent_h);
 }
 
 const char *ANcclUniqueId(char *id128) {

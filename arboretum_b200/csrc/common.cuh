@@ -184,6 +184,8 @@ struct NodeRec {
                         // descend step's counts)
   long long lg, lh;     // left child sums
   long long tg, th;     // node totals
+  unsigned lcnt, tcnt;  // rows left of the split / in the node, from the count histogram that
+                        // (gradient, hessian) objectives keep when min_leaf_size > 1; else 0
 };
 
 // A contiguous piece of one node's row list, the unit of work of the histogram

@@ -185,6 +185,62 @@ void DataMatrix::ShardedThresholds(const float *d_x_local, int hs, const ShardIn
   }
 }
 
+// Bins of the categorical columns (this build's completion of the reference's stub,
+// hist_tree_grower.h:55-63; the intended split is one category against the rest,
+// builder.h:75-105, garden.h:79-84).  A category's bin id is its rank by frequency (most
+// frequent first, ties: smaller code first).  A column with more than hist_size categories
+// keeps the hist_size - 1 most frequent ones; the others share bin hist_size - 1, which no
+// split may name.  Appends the columns' entries to fsize and fills cat_codes /
+// cat_candidates; the bin ids go into columns cols_dense.. of d_bins.
+void DataMatrix::BinCategories(cudaStream_t s) {
+  const size_t n = size_t(rows);
+  const int C = cols_cat, hs = hist_size;
+  ARB_CHECK(cat.size() == n * size_t(C), "categories are missing");
+  fsize.resize(size_t(cols_dense));
+  cat_codes.assign(size_t(C), std::vector<unsigned>());
+  std::vector<unsigned char> ids8;
+  std::vector<unsigned short> ids16;
+  if (bin_bytes == 1) ids8.resize(n * C); else ids16.resize(n * C);
+  std::vector<unsigned> col(n);
+  for (int c = 0; c < C; ++c) {
+    for (size_t r = 0; r < n; ++r) col[r] = cat[r * C + c];
+    std::sort(col.begin(), col.end());
+    std::vector<std::pair<unsigned, size_t>> freq;  // (code, rows)
+    for (size_t i = 0; i < n;) {
+      size_t j = i;
+      while (j < n && col[j] == col[i]) ++j;
+      freq.emplace_back(col[i], j - i);
+      i = j;
+    }
+    std::stable_sort(freq.begin(), freq.end(),
+                     [](const std::pair<unsigned, size_t> &a, const std::pair<unsigned, size_t> &b) {
+                       return a.second > b.second;  // codes ascend within equal counts (stable)
+                     });
+    const bool overflow = freq.size() > size_t(hs);
+    const size_t kept = overflow ? size_t(hs - 1) : freq.size();
+    std::vector<std::pair<unsigned, unsigned>> by_code;  // (code, bin)
+    for (size_t b = 0; b < kept; ++b) {
+      cat_codes[c].push_back(freq[b].first);
+      by_code.emplace_back(freq[b].first, unsigned(b));
+    }
+    std::sort(by_code.begin(), by_code.end());
+    fsize.push_back(int(kept + (overflow ? 1 : 0)));
+    cat_candidates[size_t(cols_dense + c)] = int(kept);
+    for (size_t r = 0; r < n; ++r) {
+      const unsigned code = cat[r * C + c];
+      auto it = std::lower_bound(by_code.begin(), by_code.end(), std::make_pair(code, 0u));
+      const unsigned b = (it != by_code.end() && it->first == code) ? it->second : unsigned(kept);
+      if (bin_bytes == 1) ids8[r * C + c] = (unsigned char)b; else ids16[r * C + c] = (unsigned short)b;
+    }
+  }
+  DevBuf d_ids;
+  d_ids.alloc(n * C * size_t(bin_bytes));
+  const void *src = bin_bytes == 1 ? static_cast<const void *>(ids8.data()) : static_cast<const void *>(ids16.data());
+  ARB_CUDA(cudaMemcpyAsync(d_ids.p, src, d_ids.bytes, cudaMemcpyHostToDevice, s));
+  launch_place_columns(d_ids.p, n, C, cols_dense, d_bins.as<unsigned char>(), pitch, bin_bytes, s);
+  ARB_CUDA(cudaStreamSynchronize(s));
+}
+
 void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s, long long chunk_rows,
                           const ShardInfo *shards) {
   if (binned) return;
@@ -195,9 +251,12 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
   hist_size = hs;
   // io.cu:342-347: hist_size < 256 -> uint8 bins, else uint16
   bin_bytes = hs < 256 ? 1 : 2;
-  pitch = PitchFor(F, bin_bytes);
+  pitch = PitchFor(cols(), bin_bytes);
   const size_t n = size_t(rows);
   StageTrace trace("InitHist");
+  ARB_CHECK(cols_cat == 0 || !(shards && shards->world > 1),
+            "categorical columns are not supported with row shards (their bins follow the category "
+            "frequencies of the whole data set)");
   if (!prebinned) {
     DevBuf d_quant_arena, d_x_tmp, d_col, d_sorted, d_tmp, d_scratch, d_thr_f;
     if (!d_x.p) {
@@ -269,6 +328,8 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     ARB_CUDA(cudaMemsetAsync(d_bins.p, 0, n * pitch, s));
     launch_binning(d_x.as<float>(), n, F, d_thr.as<float>(), d_fsize.as<int>(), hs, missing_bin,
                    d_bins.as<unsigned char>(), pitch, bin_bytes, s);
+    cat_candidates.assign(size_t(cols()), 0);
+    if (cols_cat > 0) BinCategories(s);
     if (out_of_core) {  // the bins live in pinned host memory and are streamed per level
       h_bins.alloc(n * pitch);
       ARB_CUDA(cudaMemcpyAsync(h_bins.p, d_bins.p, n * pitch, cudaMemcpyDeviceToHost, s));
@@ -319,12 +380,13 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     ARB_CUDA(cudaStreamSynchronize(s));
   }
   if (!out_of_core) {  // feature-major copy: F x N bins more, cheap next to the row-major matrix
-    d_bins_cm.alloc(size_t(F) * n * bin_bytes);
-    launch_transpose_bins(d_bins.as<unsigned char>(), pitch, bin_bytes, n, F,
+    d_bins_cm.alloc(size_t(cols()) * n * bin_bytes);
+    launch_transpose_bins(d_bins.as<unsigned char>(), pitch, bin_bytes, n, cols(),
                           d_bins_cm.as<unsigned char>(), s);
     ARB_CUDA(cudaStreamSynchronize(s));
   }
   trace.lap("feature-major copy (and temporaries freed)");
+  if (cat_candidates.empty()) cat_candidates.assign(size_t(cols()), 0);
   max_reduced_bits = 0;
   for (int f = 0; f < F; ++f) {
     int bits = 0;
@@ -335,6 +397,40 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
   if (verbose) printf("max feature size %d \n", max_reduced_bits);
   binned = true;
 }
+
+namespace {
+// rows of `data` as fp32 on the device, `chunk` rows at a time
+struct RowFeeder {
+  DataMatrix *d;
+  DevBuf buf;
+  std::vector<float> staged;
+  size_t chunk;
+  explicit RowFeeder(DataMatrix *dm) : d(dm) {
+    const size_t row_bytes = size_t(d->cols_dense) * sizeof(float);
+    chunk = std::max<size_t>(1, std::min<size_t>(size_t(d->rows), (size_t(1) << 30) / row_bytes));
+    if (!d->d_x.p) buf.alloc(chunk * row_bytes);
+  }
+  // category codes of the rows from `first` on (device), or nullptr
+  const unsigned *categories(size_t first) const {
+    return d->d_cat.p ? d->d_cat.as<unsigned>() + first * size_t(d->cols_cat) : nullptr;
+  }
+  const float *load(size_t first, size_t count, cudaStream_t s) {
+    const int F = d->cols_dense;
+    if (d->d_x.p) return d->d_x.as<float>() + first * F;  // already in HBM
+    if (d->prebinned && d->d_raw.p) {  // pre-binned rows predict on their bin ids as values
+      launch_u8_to_f32(d->d_raw.as<unsigned char>() + first * F, buf.as<float>(), count * F, s);
+    } else if (d->prebinned) {
+      staged.resize(count * F);
+      for (size_t i = 0; i < count * F; ++i) staged[i] = float(d->host_bins[first * F + i]);
+      ARB_CUDA(cudaMemcpyAsync(buf.p, staged.data(), count * F * sizeof(float), cudaMemcpyHostToDevice, s));
+    } else {
+      ARB_CUDA(cudaMemcpyAsync(buf.p, d->x.data() + first * F, count * F * sizeof(float),
+                               cudaMemcpyHostToDevice, s));
+    }
+    return buf.as<float>();
+  }
+};
+}  // namespace
 
 // ---------------------------------------------------------------------------
 // Builder: device state of one (Garden, DataMatrix) pair
@@ -347,6 +443,7 @@ class Builder {
   Builder &operator=(const Builder &) = delete;
   void UpdateGrad();
   void GrowTree(int label, Tree *tree);
+  void Resume();
   DataMatrix *data;
 
  private:
@@ -363,8 +460,17 @@ class Builder {
   GainParams gp_;
 
   DevBuf d_y_, d_label_, d_yhat_, d_grad_, d_node_begin_, d_rec_, d_hist_[2], d_keys_, d_qs_,
-    d_leaf_w_, d_active_, d_fsize_;
+    d_leaf_w_, d_active_, d_fsize_, d_cat_candidates_;
   DevBuf d_compact_;  // row shards: the built nodes' histograms of a level, the part the ranks sum
+  // (gradient, hessian) objectives with min_leaf_size > 1 keep a second histogram that counts
+  // rows (the reference's count histogram, gain.cu:125-134): the reg:linear kernel run on a
+  // "gradient" array of ones; same level buffers, same subtraction, same exchange
+  bool count_plane_ = false;
+  DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
+  // records of every tree of the last round (multi:softmax grows labels_count of them)
+  std::vector<std::vector<NodeRec>> round_rec_;
+  std::vector<std::vector<unsigned>> round_nb_;
+  void SampleFeatures();
   DevBuf d_node_of_;  // per row: the node (inside the current level) it stands on
   DevBuf d_list_;     // row lists of the built nodes of the current level, back to back
   DevBuf d_list_grad_;  // their gradient records in the same order (uint8 data)
@@ -414,7 +520,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   cudaStream_t s = g->stream;
   StageTrace trace("Builder");
   n_ = size_t(d->rows);
-  F_ = d->cols_dense;
+  F_ = d->cols();
   K_ = int(tp.labels_count);
   ARB_CHECK(tp.depth >= 2 && tp.depth <= kMaxLevels, "max_depth must be in [1, 15]");
   ARB_CHECK(n_ < (size_t(1) << 31), "row count must be below 2^31");
@@ -428,8 +534,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   max_nodes_ = 1 << (levels_ - 1);
   nb_stride_ = 2 * max_nodes_ + 1;
   pair_ = cfg.objective != kLinearRegression;
-  ARB_CHECK(!(pair_ && tp.min_leaf_size > 1),
-            "min_leaf_size > 1 with a (gradient, hessian) objective is not supported by this build");
+  count_plane_ = pair_ && tp.min_leaf_size > 1;
   if (cfg.objective == kSoftMaxOneVsAll)
     ARB_CHECK(d->has_labels(), "multi:softmax needs labels (ASetLabel)");
   else
@@ -439,6 +544,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   geo_.pitch = d->pitch;
   geo_.bin_bytes = d->bin_bytes;
   geo_.F = F_;
+  geo_.n_dense = d->cols_dense;
   geo_.hist_size = d->hist_size;
   int bins_pad = 256;
   while (bins_pad < d->hist_size + 1) bins_pad <<= 1;
@@ -531,6 +637,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
       {&d_leaf_w_, 2 * max_nodes_ * sizeof(float)},
       {&d_active_, size_t(levels_) * F_},
       {&d_fsize_, F_ * sizeof(int)},
+      {&d_cat_candidates_, F_ * sizeof(int)},
       {&d_hist_items_, max_hist_items_ * sizeof(WorkItem)},
       {&d_counters_, sizeof(int)},
       {&d_first_, (max_nodes_ + 2) * sizeof(int)},
@@ -554,11 +661,27 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     const unsigned root[2] = {0u, unsigned(chunks_[c].rows)};
     ARB_CUDA(cudaMemcpyAsync(node_begin(int(c), 0), root, sizeof root, cudaMemcpyHostToDevice, s));
   }
+  ARB_CHECK(int(d->fsize.size()) == F_ && int(d->cat_candidates.size()) == F_, "feature tables have the wrong size");
   ARB_CUDA(cudaMemcpyAsync(d_fsize_.p, d->fsize.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
+  ARB_CUDA(cudaMemcpyAsync(d_cat_candidates_.p, d->cat_candidates.data(), F_ * sizeof(int), cudaMemcpyHostToDevice, s));
   const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
   d_hist_[0].alloc(level_hist_bytes);
   d_hist_[1].alloc(level_hist_bytes);
   d_partials_.alloc(size_t(max_hist_items_) * geo_.NT * 2 * kHistWords * sizeof(int));
+  const bool sharded = g->allreduce != nullptr;
+  const size_t compact_bytes = size_t(std::max(1, max_nodes_ / 2)) * geo_.NT * kHistWords * 2 * sizeof(long long);
+  // made here, not inside a round: an allocation that fails between two collectives would
+  // leave the other ranks waiting inside theirs
+  if (sharded && cfg.internal.use_hist_subtraction_trick) d_compact_.alloc(compact_bytes);
+  if (count_plane_) {
+    d_ones_.alloc(n_ * sizeof(int));
+    launch_fill_u32(d_ones_.as<unsigned>(), n_, 1u, s);
+    d_cnt_hist_[0].alloc(level_hist_bytes);
+    d_cnt_hist_[1].alloc(level_hist_bytes);
+    if (sharded && cfg.internal.use_hist_subtraction_trick) d_compact_cnt_.alloc(compact_bytes);
+  }
+  round_rec_.resize(K_);
+  round_nb_.resize(K_);
   pb_.hist_items = d_hist_items_.as<WorkItem>();
   pb_.n_hist_items = d_counters_.as<int>();
   pb_.hist_item_first = d_first_.as<int>();
@@ -701,17 +824,34 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   }
 }
 
-void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
-  const Configuration &cfg = g_->cfg;
-  const TreeParam &tp = cfg.tree;
-  cudaStream_t s = g_->stream;
-  const bool prof = g_->profile;
-  if (prof) EnsureEvents();
-  QuantScale *qs = d_qs_.as<QuantScale>();
-  const void *grad = static_cast<const char *>(d_grad_.p) +
-                     size_t(label) * n_ * (pair_ ? sizeof(float2) : sizeof(float));
+// Training continues a model that was loaded (ALoadModel) or grown on another matrix: the
+// predictions start from what the existing trees give on this matrix's raw values, and the
+// feature-sampling engine and the round counter stand where they would after growing those
+// trees here.  (The reference restores the trees only: a builder made after `load` starts
+// from initial_y, garden.cu:585-606,659-677.)
+void Builder::Resume() {
+  Garden *g = g_;
+  cudaStream_t s = g->stream;
+  ARB_CHECK(g->max_fid < data->cols(), "the model tests a feature the matrix does not have");
+  g->SyncForest();
+  const PackedTree pt{g->d_fid.as<int>(), g->d_thr.as<float>(), g->d_w.as<float>(), g->d_label.as<int>(),
+                      g->d_category.as<unsigned>()};
+  RowFeeder feed(data);
+  for (size_t first = 0; first < n_; first += feed.chunk) {
+    const size_t count = std::min(feed.chunk, n_ - first);
+    const float *X = feed.load(first, count, s);
+    launch_predict(X, count, data->cols_dense, pt, 0, int(g->trees.size()), int(g->cfg.tree.depth),
+                   d_yhat_.as<float>() + first, s, n_, feed.categories(first), data->cols_cat);
+    ARB_CUDA(cudaStreamSynchronize(s));
+  }
+  for (size_t t = 0; t < g->trees.size(); ++t) SampleFeatures();
+  round_ = unsigned(g->trees.size() / size_t(K_));
+}
 
-  // ---- feature sampling: garden.cu:126-165,252-253 ---------------------------
+// Feature sampling of one tree (garden.cu:126-165,252-253 of the reference): the same
+// shuffles of the same engine in the same order, also when both ratios are 1.
+void Builder::SampleFeatures() {
+  const TreeParam &tp = g_->cfg.tree;
   int take = int(tp.colsample_bytree * F_);
   if (take == 0) throw std::runtime_error("colsample_bytree is too small");
   take = int(tp.colsample_bytree * tp.colsample_bylevel * F_);
@@ -725,15 +865,36 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     for (unsigned j = 0; j < take_l && j < unsigned(F_); ++j)
       active_host_[size_t(l) * F_ + active_fids_[j]] = 1;
   }
+}
+
+void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
+  const Configuration &cfg = g_->cfg;
+  const TreeParam &tp = cfg.tree;
+  cudaStream_t s = g_->stream;
+  const bool prof = g_->profile;
+  if (prof) EnsureEvents();
+  QuantScale *qs = d_qs_.as<QuantScale>();
+  const void *grad = static_cast<const char *>(d_grad_.p) +
+                     size_t(label) * n_ * (pair_ ? sizeof(float2) : sizeof(float));
+
+  SampleFeatures();
   ARB_CUDA(cudaMemcpyAsync(d_active_.p, active_host_.data(), active_host_.size(),
                            cudaMemcpyHostToDevice, s));
   if (prof) ARB_CUDA(cudaEventRecord(ev_tree_[0], s));
+  // a tree that threw half way (an exchange that failed) leaves the cyclic visiting order of
+  // the streamed chunks out of step: start over from the first one
+  if (!streamed_.empty() && consumed_ % streamed_.size() != 0) {
+    ARB_CUDA(cudaStreamSynchronize(copy_stream_));
+    ARB_CUDA(cudaStreamSynchronize(s));
+    issued_ = consumed_ = 0;
+  }
 
   const bool use_trick = cfg.internal.use_hist_subtraction_trick;
   const int n_chunks = int(chunks_.size());
   const bool multi = n_chunks > 1;  // row chunks add their histograms like GPUs do
   const bool by_hessian = g_->allreduce != nullptr || multi;
   const size_t gsz = pair_ ? sizeof(float2) : sizeof(float);
+  const int n_sets = count_plane_ ? 2 : 1;  // histogram sets: (g, h) sums, then row counts
   int ev = 0;
   auto mark = [&]() {
     if (prof && !multi) ARB_CUDA(cudaEventRecord(ev_[ev], s));
@@ -745,16 +906,20 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     const int L = 1 << l;
     const bool trick_level = use_trick && l > 0;
     const int n_build = trick_level ? L / 2 : L;
-    long long *hist = d_hist_[l & 1].as<long long>();
     // Row shards sum only what they built: below the root that is one child per parent, so
     // the exchanged buffer holds those alone and the siblings follow from the parents after
     // the exchange.
     const bool compact = trick_level && g_->allreduce != nullptr;
-    if (compact && !d_compact_.p)
-      d_compact_.alloc(size_t(std::max(1, max_nodes_ / 2)) * geo_.NT * kHistWords * 2 * sizeof(long long));
-    long long *reduce_to = compact ? d_compact_.as<long long>() : hist;
-    if (multi)
-      ARB_CUDA(cudaMemsetAsync(reduce_to, 0, size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+    long long *hist[2], *reduce_to[2];
+    const long long *parent_hist[2];
+    for (int k = 0; k < n_sets; ++k) {
+      DevBuf *levels = k == 0 ? d_hist_ : d_cnt_hist_;
+      hist[k] = levels[l & 1].as<long long>();
+      parent_hist[k] = l > 0 ? levels[(l - 1) & 1].as<long long>() : nullptr;
+      reduce_to[k] = compact ? (k == 0 ? d_compact_ : d_compact_cnt_).as<long long>() : hist[k];
+      if (multi)
+        ARB_CUDA(cudaMemsetAsync(reduce_to[k], 0, size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+    }
     for (int c = 0; c < n_chunks; ++c) {
       const Chunk &ch = chunks_[c];
       const bool last = c + 1 == n_chunks;
@@ -799,51 +964,59 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       void *list_grad = d_list_grad_.p ? static_cast<char *>(d_list_grad_.p) + ch.begin * gsz : nullptr;
       if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
       if (last) mark();
-      HistLaunch h;
-      h.geo = geo;
-      h.rowid = l == 0 ? nullptr : list;
-      h.grad = grad_c;
-      h.pair = pair_;
-      h.items = pb_.hist_items;
-      h.n_items = pb_.n_hist_items;
-      h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
-      h.partials = d_partials_.as<int>();
-      h.list_grad = l == 0 ? nullptr : list_grad;
-      launch_hist(h, s);
-      ReduceLaunch rd;
-      rd.partials = d_partials_.as<int>();
-      rd.item_first = pb_.hist_item_first;
-      rd.build_node = compact ? nullptr : pb_.scratch_node;
-      rd.n_build = n_build;
-      rd.NT = geo.NT;
-      rd.level_hist = reduce_to;
-      rd.parent_hist = l > 0 ? d_hist_[(l - 1) & 1].as<long long>() : nullptr;
-      rd.subtract = trick_level && !g_->allreduce && !multi;
-      rd.level_nodes = compact ? n_build : L;
-      rd.built_child = pb_.built_child;
-      rd.accumulate = multi;
-      launch_reduce(rd, s);
+      for (int k = 0; k < n_sets; ++k) {
+        HistLaunch h;
+        h.geo = geo;
+        h.rowid = l == 0 ? nullptr : list;
+        // the count set: every row's "gradient" is 1 and the hessian plane of the
+        // reg:linear kernel counts the rows
+        h.grad = k == 0 ? grad_c : static_cast<const void *>(d_ones_.as<int>() + ch.begin);
+        h.pair = k == 0 ? pair_ : false;
+        h.items = pb_.hist_items;
+        h.n_items = pb_.n_hist_items;
+        h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
+        h.partials = d_partials_.as<int>();
+        h.list_grad = (l == 0 || k > 0) ? nullptr : list_grad;
+        launch_hist(h, s);
+        ReduceLaunch rd;
+        rd.partials = d_partials_.as<int>();
+        rd.item_first = pb_.hist_item_first;
+        rd.build_node = compact ? nullptr : pb_.scratch_node;
+        rd.n_build = n_build;
+        rd.NT = geo.NT;
+        rd.level_hist = reduce_to[k];
+        rd.parent_hist = parent_hist[k];
+        rd.subtract = trick_level && !g_->allreduce && !multi;
+        rd.level_nodes = compact ? n_build : L;
+        rd.built_child = pb_.built_child;
+        rd.accumulate = multi;
+        launch_reduce(rd, s);
+      }
       Release(c);
     }
     mark();
     if (g_->allreduce) {
       const size_t count = size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2;
-      if (g_->allreduce(g_->allreduce_ctx, reduce_to, count, s) != 0)
-        throw std::runtime_error("histogram allreduce failed");
+      for (int k = 0; k < n_sets; ++k)
+        if (g_->allreduce(g_->allreduce_ctx, reduce_to[k], count, s) != 0)
+          throw std::runtime_error("histogram allreduce failed");
     }
     mark();
-    if (compact)
-      launch_expand(d_compact_.as<long long>(), d_hist_[(l - 1) & 1].as<long long>(), hist, pb_.built_child,
-                    L / 2, geo_.NT, s);
-    else if (trick_level && multi)
-      launch_subtract(hist, d_hist_[(l - 1) & 1].as<long long>(), pb_.built_child, L / 2, geo_.NT, s);
+    for (int k = 0; k < n_sets; ++k) {
+      if (compact)
+        launch_expand(reduce_to[k], parent_hist[k], hist[k], pb_.built_child, L / 2, geo_.NT, s);
+      else if (trick_level && multi)
+        launch_subtract(hist[k], parent_hist[k], pb_.built_child, L / 2, geo_.NT, s);
+    }
     mark();
     SplitLaunch sp;
     sp.geo = geo_;
-    sp.hist = hist;
+    sp.hist = hist[0];
+    sp.count_hist = count_plane_ ? hist[1] : nullptr;
     sp.node_begin = node_begin(0, l);
     sp.feature_active = d_active_.as<unsigned char>() + size_t(l) * F_;
     sp.feature_size = d_fsize_.as<int>();
+    sp.cat_candidates = data->cols_cat > 0 ? d_cat_candidates_.as<int>() : nullptr;
     sp.keys = d_keys_.as<unsigned long long>();
     sp.max_nodes = max_nodes_;
     sp.rec = rec(l);
@@ -868,6 +1041,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   lf.mlw = tp.max_leaf_weight;
   lf.eta = tp.eta;
   lf.pair = pair_;
+  lf.counts = count_plane_;
   launch_leaf_weights(lf, s);
   for (int c = 0; c < n_chunks; ++c) {  // the tree walk needs the bins once more
     Geometry geo = geo_;
@@ -900,6 +1074,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     for (int c = 0; c < n_chunks; ++c)
       for (size_t i = 0; i < per_chunk; ++i) h_nb_total_[i] += all[size_t(c) * per_chunk + i];
   }
+  round_rec_[label].assign(h_rec_.as<NodeRec>(), h_rec_.as<NodeRec>() + size_t(levels_) * max_nodes_);
+  round_nb_[label] = h_nb_total_;
 
   // ---- UpdateTree garden.cu:447-485 -----------------------------------------------
   const int depth = int(tp.depth);
@@ -916,7 +1092,14 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       TreeNode &nd = tree->nodes[i + offset];
       if (r.fid >= 0) {
         nd.fid = r.fid;
+        g_->max_fid = std::max(g_->max_fid, r.fid);
         nd.quantized = unsigned(r.bin);
+        if (r.fid >= data->cols_dense) {  // one category against the rest
+          nd.categorical = true;
+          nd.category = data->cat_codes[size_t(r.fid - data->cols_dense)][size_t(r.bin)];
+          nd.threshold = std::numeric_limits<float>::infinity();
+          continue;
+        }
         // a split on the last bin in use separates present from missing values
         const bool last_real = r.bin >= data->fsize[r.fid] - 1;
         nd.threshold = (r.bin >= H || last_real) ? std::numeric_limits<float>::infinity()
@@ -981,16 +1164,20 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   }
 }
 
-const NodeRec *BuilderView::host_rec(const Garden *g, int *max_nodes, int *levels) {
-  ARB_CHECK(g->builder && !g->trees.empty(), "no tree has been grown yet");
+const NodeRec *BuilderView::host_rec(const Garden *g, int tree_in_round, int *max_nodes, int *levels) {
+  ARB_CHECK(g->builder && !g->builder->round_rec_.back().empty(), "no tree has been grown yet");
+  const int K = int(g->builder->round_rec_.size());
+  ARB_CHECK(tree_in_round >= -1 && tree_in_round < K, "tree index out of range");
   *max_nodes = g->builder->max_nodes_;
   *levels = g->builder->levels_;
-  return g->builder->h_rec_.as<NodeRec>();
+  return g->builder->round_rec_[tree_in_round < 0 ? K - 1 : tree_in_round].data();
 }
-const unsigned *BuilderView::host_node_begin(const Garden *g, int *stride) {
-  ARB_CHECK(g->builder && !g->trees.empty(), "no tree has been grown yet");
+const unsigned *BuilderView::host_node_begin(const Garden *g, int tree_in_round, int *stride) {
+  ARB_CHECK(g->builder && !g->builder->round_nb_.back().empty(), "no tree has been grown yet");
+  const int K = int(g->builder->round_nb_.size());
+  ARB_CHECK(tree_in_round >= -1 && tree_in_round < K, "tree index out of range");
   *stride = g->builder->nb_stride_;
-  return g->builder->h_nb_total_.data();
+  return g->builder->round_nb_[tree_in_round < 0 ? K - 1 : tree_in_round].data();
 }
 void BuilderView::scales(Garden *g, QuantScale *out) {
   ARB_CHECK(g->builder, "no tree has been grown yet");
@@ -1058,6 +1245,12 @@ Garden::Garden(const Configuration &c) : cfg(c) {
     throw std::runtime_error("method 0 (exact) is not part of this build; use method 1 (hist)");
   if (cfg.objective == kSoftMaxOneVsAll && cfg.tree.labels_count < 2)
     throw std::runtime_error("multi:softmax needs tree.labels_count >= 2");
+}
+
+// The stream is made by the first call that needs the device, so that a Garden can be made,
+// loaded and dumped on a host without one.
+void Garden::EnsureStream() {
+  if (stream) return;
   if (cfg.internal.device >= 0) ARB_CUDA(cudaSetDevice(cfg.internal.device));
   ARB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
 }
@@ -1075,10 +1268,12 @@ float Garden::InternalInitialY() const {  // objective.h:19,55-57
 
 void Garden::GrowTree(DataMatrix *data, const float *grad) {
   (void)grad;  // custom gradients are ignored by the reference as well (garden.cu:609-614)
+  EnsureStream();
   data->InitHist(cfg.internal.hist_size, cfg.internal.missing_bin, cfg.verbose.data, stream,
                  cfg.internal.chunk_rows, &shards);
   if (!builder) {
     builder = new Builder(this, data);
+    if (!trees.empty()) builder->Resume();
   } else if (builder->data != data) {
     throw std::runtime_error("this Garden is already bound to another DMatrix");
   }
@@ -1091,16 +1286,19 @@ void Garden::GrowTree(DataMatrix *data, const float *grad) {
 }
 
 void Garden::SyncForest() {
+  EnsureStream();
   if (forest_trees_on_device == trees.size()) return;
   const int depth = int(cfg.tree.depth);
   const size_t nodes = (size_t(1) << depth) - 1, leaves = size_t(1) << (depth - 1);
   std::vector<int> fid(trees.size() * nodes), label(trees.size());
+  std::vector<unsigned> category(trees.size() * nodes);
   std::vector<float> thr(trees.size() * nodes), w(trees.size() * leaves);
   for (size_t t = 0; t < trees.size(); ++t) {
     ARB_CHECK(trees[t].depth == depth, "tree depth differs from the configuration");
     for (size_t i = 0; i < nodes; ++i) {
       fid[t * nodes + i] = trees[t].nodes[i].fid;
       thr[t * nodes + i] = trees[t].nodes[i].threshold;
+      category[t * nodes + i] = trees[t].nodes[i].category;
     }
     std::copy(trees[t].weights.begin(), trees[t].weights.end(), w.begin() + t * leaves);
     label[t] = trees[t].label;
@@ -1109,6 +1307,8 @@ void Garden::SyncForest() {
   d_thr.alloc(thr.size() * sizeof(float));
   d_w.alloc(w.size() * sizeof(float));
   d_label.alloc(label.size() * sizeof(int));
+  d_category.alloc(category.size() * sizeof(unsigned));
+  ARB_CUDA(cudaMemcpyAsync(d_category.p, category.data(), d_category.bytes, cudaMemcpyHostToDevice, stream));
   ARB_CUDA(cudaMemcpyAsync(d_fid.p, fid.data(), d_fid.bytes, cudaMemcpyHostToDevice, stream));
   ARB_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), d_thr.bytes, cudaMemcpyHostToDevice, stream));
   ARB_CUDA(cudaMemcpyAsync(d_w.p, w.data(), d_w.bytes, cudaMemcpyHostToDevice, stream));
@@ -1117,40 +1317,12 @@ void Garden::SyncForest() {
   forest_trees_on_device = trees.size();
 }
 
-namespace {
-// rows of `data` as fp32 on the device, `chunk` rows at a time
-struct RowFeeder {
-  DataMatrix *d;
-  DevBuf buf;
-  std::vector<float> staged;
-  size_t chunk;
-  explicit RowFeeder(DataMatrix *dm) : d(dm) {
-    const size_t row_bytes = size_t(d->cols_dense) * sizeof(float);
-    chunk = std::max<size_t>(1, std::min<size_t>(size_t(d->rows), (size_t(1) << 30) / row_bytes));
-    if (!d->d_x.p) buf.alloc(chunk * row_bytes);
-  }
-  const float *load(size_t first, size_t count, cudaStream_t s) {
-    const int F = d->cols_dense;
-    if (d->d_x.p) return d->d_x.as<float>() + first * F;  // already in HBM
-    if (d->prebinned && d->d_raw.p) {  // pre-binned rows predict on their bin ids as values
-      launch_u8_to_f32(d->d_raw.as<unsigned char>() + first * F, buf.as<float>(), count * F, s);
-    } else if (d->prebinned) {
-      staged.resize(count * F);
-      for (size_t i = 0; i < count * F; ++i) staged[i] = float(d->host_bins[first * F + i]);
-      ARB_CUDA(cudaMemcpyAsync(buf.p, staged.data(), count * F * sizeof(float), cudaMemcpyHostToDevice, s));
-    } else {
-      ARB_CUDA(cudaMemcpyAsync(buf.p, d->x.data() + first * F, count * F * sizeof(float),
-                               cudaMemcpyHostToDevice, s));
-    }
-    return buf.as<float>();
-  }
-};
-}  // namespace
 
 // Garden::Predict garden.cu:643-657; n_rounds counts trees, like the reference
 void Garden::Predict(DataMatrix *data, std::vector<float> &out, int n_rounds) {
   const int K = int(cfg.tree.labels_count);
   const size_t n = size_t(data->rows);
+  ARB_CHECK(max_fid < data->cols(), "the model tests a feature the matrix does not have");
   out.resize(n * K);
   SyncForest();
   const int use = int(std::min<long long>(n_rounds, (long long)trees.size()));
@@ -1158,12 +1330,14 @@ void Garden::Predict(DataMatrix *data, std::vector<float> &out, int n_rounds) {
   DevBuf d_int, d_out;
   d_int.alloc(feed.chunk * K * sizeof(float));
   d_out.alloc(feed.chunk * K * sizeof(float));
-  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>()};
+  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>(),
+                      d_category.as<unsigned>()};
   for (size_t first = 0; first < n; first += feed.chunk) {
     const size_t count = std::min(feed.chunk, n - first);
     const float *X = feed.load(first, count, stream);
     launch_fill(d_int.as<float>(), count * K, InternalInitialY(), stream);
-    launch_predict(X, count, data->cols_dense, pt, 0, use, int(cfg.tree.depth), d_int.as<float>(), stream);
+    launch_predict(X, count, data->cols_dense, pt, 0, use, int(cfg.tree.depth), d_int.as<float>(), stream, 0,
+                   feed.categories(first), data->cols_cat);
     launch_link(cfg.objective, K, count, d_int.as<float>(), d_out.as<float>(), stream);
     ARB_CUDA(cudaMemcpyAsync(out.data() + first * K, d_out.p, count * K * sizeof(float),
                              cudaMemcpyDeviceToHost, stream));
@@ -1177,6 +1351,8 @@ void Garden::UpdateByLastTree(DataMatrix *data) {
   const int K = int(cfg.tree.labels_count);
   const size_t n = size_t(data->rows);
   ARB_CHECK(trees.size() >= size_t(K), "no tree has been grown yet");
+  ARB_CHECK(max_fid < data->cols(), "the model tests a feature the matrix does not have");
+  EnsureStream();
   if (!data->d_yhat.p || data->yhat_planes != K) {
     data->d_yhat.alloc(n * K * sizeof(float));
     data->yhat_planes = K;
@@ -1184,7 +1360,8 @@ void Garden::UpdateByLastTree(DataMatrix *data) {
   }
   SyncForest();
   RowFeeder feed(data);
-  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>()};
+  const PackedTree pt{d_fid.as<int>(), d_thr.as<float>(), d_w.as<float>(), d_label.as<int>(),
+                      d_category.as<unsigned>()};
   DevBuf d_tmp;
   d_tmp.alloc(feed.chunk * K * sizeof(float));
   for (size_t first = 0; first < n; first += feed.chunk) {
@@ -1196,7 +1373,7 @@ void Garden::UpdateByLastTree(DataMatrix *data) {
                                data->d_yhat.as<float>() + size_t(k) * n + first, count * sizeof(float),
                                cudaMemcpyDeviceToDevice, stream));
     launch_predict(X, count, data->cols_dense, pt, int(trees.size()) - K, K, int(cfg.tree.depth),
-                   d_tmp.as<float>(), stream);
+                   d_tmp.as<float>(), stream, 0, feed.categories(first), data->cols_cat);
     for (int k = 0; k < K; ++k)
       ARB_CUDA(cudaMemcpyAsync(data->d_yhat.as<float>() + size_t(k) * n + first,
                                d_tmp.as<float>() + size_t(k) * count, count * sizeof(float),
@@ -1213,6 +1390,7 @@ void Garden::GetY(DataMatrix *data, std::vector<float> &out) {
     out.clear();
     return;
   }
+  EnsureStream();
   out.resize(n * K);
   DevBuf d_out;
   d_out.alloc(n * K * sizeof(float));
@@ -1241,6 +1419,8 @@ std::string Garden::GetModel() const {
         jn["right"] = Json::integer(2 * i + 2);
         jn["threshold"] = Json::number(double(t.nodes[i].threshold));  // +inf -> null
         jn["fid"] = Json::integer(t.nodes[i].fid);
+        // additive key (the reference does not serialise categories, json_conversion.h:13-35)
+        if (t.nodes[i].categorical) jn["category"] = Json::integer(t.nodes[i].category);
       } else {
         jn["idx"] = Json::integer(i - first_leaf);
       }
@@ -1263,10 +1443,16 @@ void Garden::Restore(const char *json_model) {
   const Json j = JsonParser(json_model).parse();
   const Json &model = j.at("model");
   ARB_CHECK(model.type == Json::Arr, "model must be an array of trees");
+  const int K = std::max(1, int(cfg.tree.labels_count));
   for (const Json &jt : model.arr) {
     Tree t;
-    t.depth = int(jt.at("depth").as_num());
-    t.label = 0;
+    const double depth_num = jt.at("depth").as_num();
+    ARB_CHECK(depth_num >= 1 && depth_num <= kMaxLevels, "tree depth out of range");
+    t.depth = int(depth_num);
+    // the reference gives every restored tree label 0 (garden.cu:659-677), which is right for
+    // its single-output objectives; the trees of a multi:softmax model were dumped class after
+    // class, round after round
+    t.label = int(trees.size() % size_t(K));
     const Json &nodes = jt.at("nodes");
     t.nodes.assign(nodes.arr.size(), TreeNode());
     for (const Json &jn : nodes.arr) {
@@ -1277,7 +1463,17 @@ void Garden::Restore(const char *json_model) {
         t.nodes[id].threshold = th.type == Json::Null ? std::numeric_limits<float>::infinity()
                                                       : float(th.as_num());
       }
-      if (jn.has("fid")) t.nodes[id].fid = int(jn.at("fid").as_num());
+      if (jn.has("category")) {
+        t.nodes[id].categorical = true;
+        t.nodes[id].category = unsigned(jn.at("category").as_num());
+      }
+      if (jn.has("fid")) {
+        // inference indexes a row of the matrix with it, on the device
+        const double fid = jn.at("fid").as_num();
+        ARB_CHECK(fid >= 0 && fid < 65535, "feature id out of range");
+        t.nodes[id].fid = int(fid);
+        max_fid = std::max(max_fid, int(fid));
+      }
     }
     for (const Json &w : jt.at("weights").arr) t.weights.push_back(float(w.as_num()));
     ARB_CHECK(t.depth >= 1 && t.nodes.size() == (size_t(1) << t.depth) - 1 &&

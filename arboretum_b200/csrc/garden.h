@@ -43,6 +43,19 @@ class DataMatrix {
   bool has_y() const { return d_y.p || y.size() == size_t(rows); }
   bool has_labels() const { return d_labels.p || labels.size() == size_t(rows); }
   std::vector<float> weights;
+  // categorical columns (arboretum_wrapper.cu:30-33): category codes, row-major [rows][cols_cat],
+  // on the host (for the quantiser) and on the device (for inference).  Feature ids
+  // cols_dense .. cols_dense + cols_cat - 1 denote them, as in the reference (garden.h:79-84).
+  std::vector<unsigned> cat;
+  DevBuf d_cat;
+  int cols() const { return cols_dense + cols_cat; }
+  // Quantised categorical column c: the categories that got a bin of their own, most
+  // frequent first (ties: smaller code first), bin id = position; when a column has more
+  // categories than bins, the rest share the bin after them, which no split can single out.
+  std::vector<std::vector<unsigned>> cat_codes;
+  std::vector<int> cat_candidates;  // per feature (dense and categorical): bins a one-vs-rest
+                                    // split may name; 0 for dense features
+  void BinCategories(cudaStream_t s);
 
   // quantised form (built by the first AGrowTree, like DataMatrix::InitHist)
   bool binned = false;
@@ -78,6 +91,8 @@ struct TreeNode {  // reg_tree.h:16-38
   int fid = 0;
   float threshold = 0.0f;
   unsigned quantized = 0;
+  bool categorical = false;  // the test is `value == category` (garden.h:79-84)
+  unsigned category = unsigned(-1);
 };
 struct Tree {  // reg_tree.h:40-45 + RegTree::label
   int depth = 0;
@@ -112,8 +127,9 @@ class Garden;
 // Read-only window on the builder's state of the last grown tree, for the
 // read-back entry points of the C ABI.
 struct BuilderView {
-  static const NodeRec *host_rec(const Garden *g, int *max_nodes, int *levels);
-  static const unsigned *host_node_begin(const Garden *g, int *stride);
+  // records of tree `tree_in_round` (0 .. labels_count - 1; -1 = the last one) of the last round
+  static const NodeRec *host_rec(const Garden *g, int tree_in_round, int *max_nodes, int *levels);
+  static const unsigned *host_node_begin(const Garden *g, int tree_in_round, int *stride);
   static void scales(Garden *g, QuantScale *out);
   static void train_yhat(Garden *g, float *out);
 };
@@ -132,6 +148,7 @@ class Garden {
   float InternalInitialY() const;
 
   std::vector<Tree> trees;
+  int max_fid = -1;  // largest feature id any tree tests: a matrix given to Predict must have it
   AllreduceFn allreduce = nullptr;
   AllreduceMaxFn allreduce_max = nullptr;
   ShardInfo shards;  // rank, world and the all-gather of the sharded quantizer
@@ -140,7 +157,8 @@ class Garden {
   PhaseTimes times;
   // device copies of the forest for inference
   void SyncForest();
-  DevBuf d_fid, d_thr, d_w, d_label;
+  void EnsureStream();
+  DevBuf d_fid, d_thr, d_w, d_label, d_category;
   size_t forest_trees_on_device = 0;
   cudaStream_t stream = nullptr;
   Builder *builder = nullptr;

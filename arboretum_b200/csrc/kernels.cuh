@@ -26,7 +26,8 @@ struct Geometry {
   const unsigned char *bins;
   size_t pitch;
   int bin_bytes;
-  int F;
+  int F;        // all features: dense ones first, then the categorical ones
+  int n_dense;  // features below this id split by `bin <= b`, the others by `bin == b`
   int TW, NT, BINS;
   int hist_size;  // bins a split may use (config value); id hist_size = missing
   // optional feature-major copy bins_cm[f * cm_rows + row] (nullptr: absent): the row
@@ -84,9 +85,13 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
 struct SplitLaunch {
   Geometry geo;
   const long long *hist;       // level buffer
+  const long long *count_hist = nullptr;  // same layout, second word of a pair = rows ((g, h)
+                                          // objectives with min_leaf_size > 1), or nullptr
   const unsigned *node_begin;  // L+1 prefix counts of this level
   const unsigned char *feature_active;  // F flags: evaluated at this level
   const int *feature_size;     // bins in use per feature
+  const int *cat_candidates = nullptr;  // per feature: bins a one-vs-rest split may name
+                                        // (categorical features), 0 for dense ones; or nullptr
   unsigned long long *keys;    // max_nodes packed (gain, feature, bin) maxima followed by
                                // max_nodes u32 arrival counters; zeroed by the plan kernel of the
                                // level (PlanBuffers::split_scratch)
@@ -179,6 +184,7 @@ struct LeafLaunch {
   unsigned mls;
   float lambda, alpha, mlw, eta;
   bool pair;
+  bool counts = false;  // last_rec carries true row counts (lcnt, tcnt)
 };
 void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s);
 
@@ -188,10 +194,15 @@ struct PackedTree {  // device arrays of one forest
   const float *thr;      // [trees][nodes]
   const float *weights;  // [trees][leaves]
   const int *label;      // [trees]
+  const unsigned *category = nullptr;  // [trees][nodes], read for nodes with fid >= F
 };
+// out[label * plane_stride + row] += leaf weight (plane_stride 0 = n).  A node with fid >= F
+// tests the categorical column fid - F of `cat` (row-major [n][ccol]) for equality.
 void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tree, int n_trees,
-                    int depth, float *out /*[K][n]*/, cudaStream_t s);
+                    int depth, float *out /*[K][plane_stride]*/, cudaStream_t s, size_t plane_stride = 0,
+                    const unsigned *cat = nullptr, int ccol = 0);
 void launch_fill(float *dst, size_t n, float value, cudaStream_t s);
+void launch_fill_u32(unsigned *dst, size_t n, unsigned value, cudaStream_t s);
 void launch_link(int objective, int K, size_t n, const float *internal /*[K][n]*/,
                  float *out /*[n][K]*/, cudaStream_t s);
 
@@ -204,6 +215,10 @@ size_t thresholds_scratch_words(size_t n);
 void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist_size]*/,
                     const int *fsize, int hist_size, bool missing_bin, unsigned char *bins,
                     size_t pitch, int bin_bytes, cudaStream_t s);
+// bin ids of the categorical columns ([n][ccol], BIN_T wide) into columns f0 .. f0 + ccol - 1
+// of the padded row-major bin matrix
+void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned char *bins, size_t pitch,
+                          int bin_bytes, cudaStream_t s);
 // row-major padded bins -> feature-major copy
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
                            unsigned char *bins_cm, cudaStream_t s);

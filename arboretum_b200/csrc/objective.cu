@@ -205,7 +205,7 @@ __global__ void quantize_single_kernel(float *grad, size_t n, const QuantScale *
     reinterpret_cast<int *>(grad)[i] = to_fixed(grad[i], sg, i, kNoDither, 0u, lim);
 }
 
-template <bool PAIR>
+template <bool PAIR, bool COUNTS>
 __global__ void leaf_weights_kernel(LeafLaunch a) {
   overlap_release();
   overlap_wait();
@@ -215,8 +215,8 @@ __global__ void leaf_weights_kernel(LeafLaunch a) {
   const double isg = a.qs->inv_sg, ish = a.qs->inv_sh;
   const long long rg = r.tg - r.lg, rh = r.th - r.lh;
   // counts only gate `c >= min_leaf_size`; see split.cu for the PAIR stand-in
-  const unsigned lc = PAIR ? unsigned(r.lh > 0) : unsigned(r.lh);
-  const unsigned rc = PAIR ? unsigned(rh > 0) : unsigned(rh);
+  const unsigned lc = COUNTS ? r.lcnt : PAIR ? unsigned(r.lh > 0) : unsigned(r.lh);
+  const unsigned rc = COUNTS ? r.tcnt - r.lcnt : PAIR ? unsigned(rh > 0) : unsigned(rh);
   // garden.cu:487-503, split.cu:25-35: eta is applied to the float weight
   a.leaf_w[2 * n] = leaf_weight<PAIR>(double(r.lg) * isg, double(r.lh) * ish, lc, a.mcw, a.mls,
                                       a.lambda, a.alpha, a.mlw) * a.eta;
@@ -228,7 +228,8 @@ __global__ void leaf_weights_kernel(LeafLaunch a) {
 // NaN goes right; trees are added in order, in float, like the reference's loop
 // in Garden::Predict garden.cu:643-657.
 __global__ void predict_kernel(const float *__restrict__ X, size_t n, int F, PackedTree t,
-                               int first_tree, int n_trees, int depth, float *__restrict__ out) {
+                               int first_tree, int n_trees, int depth, float *__restrict__ out,
+                               size_t plane_stride, const unsigned *__restrict__ cat, int ccol) {
   const int nodes = (1 << depth) - 1;
   const int leaves = 1 << (depth - 1);
   const int offset = leaves - 1;
@@ -239,8 +240,16 @@ __global__ void predict_kernel(const float *__restrict__ X, size_t n, int F, Pac
       const int *fid = t.fid + size_t(k) * nodes;
       const float *thr = t.thr + size_t(k) * nodes;
       int node = 0;
-      for (int j = 1; j < depth; ++j) node = row[fid[node]] < thr[node] ? 2 * node + 1 : 2 * node + 2;
-      out[size_t(t.label[k]) * n + i] += t.weights[size_t(k) * leaves + node - offset];
+      for (int j = 1; j < depth; ++j) {
+        const int f = fid[node];
+        // garden.h:79-84: dense features go left below the threshold, categorical ones when
+        // the value is the node's category
+        const bool left = f < F ? row[f] < thr[node]
+                                : (cat != nullptr && f - F < ccol &&
+                                   cat[i * size_t(ccol) + (f - F)] == t.category[size_t(k) * nodes + node]);
+        node = left ? 2 * node + 1 : 2 * node + 2;
+      }
+      out[size_t(t.label[k]) * plane_stride + i] += t.weights[size_t(k) * leaves + node - offset];
     }
   }
 }
@@ -261,7 +270,8 @@ __global__ void link_kernel(int objective, int K, size_t n, const float *__restr
   }
 }
 
-__global__ void fill_kernel(float *dst, size_t n, float v) {
+template <typename T>
+__global__ void fill_kernel(T *dst, size_t n, T v) {
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x)
     dst[i] = v;
@@ -321,25 +331,36 @@ void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs
 
 void launch_leaf_weights(const LeafLaunch &a, cudaStream_t s) {
   const int threads = 128;
-  if (a.pair)
-    launch_overlapped(leaf_weights_kernel<true>, ceil_div(a.L, threads), threads, 0, s, a);
+  if (a.pair && a.counts)
+    launch_overlapped(leaf_weights_kernel<true, true>, ceil_div(a.L, threads), threads, 0, s, a);
+  else if (a.pair)
+    launch_overlapped(leaf_weights_kernel<true, false>, ceil_div(a.L, threads), threads, 0, s, a);
   else
-    launch_overlapped(leaf_weights_kernel<false>, ceil_div(a.L, threads), threads, 0, s, a);
+    launch_overlapped(leaf_weights_kernel<false, false>, ceil_div(a.L, threads), threads, 0, s, a);
   count_launch();
 }
 
 void launch_predict(const float *X, size_t n, int F, PackedTree t, int first_tree, int n_trees,
-                    int depth, float *out, cudaStream_t s) {
+                    int depth, float *out, cudaStream_t s, size_t plane_stride, const unsigned *cat,
+                    int ccol) {
   if (n_trees <= 0 || n == 0) return;
   const int threads = 256;
-  predict_kernel<<<grid_for(n, threads), threads, 0, s>>>(X, n, F, t, first_tree, n_trees, depth, out);
+  predict_kernel<<<grid_for(n, threads), threads, 0, s>>>(X, n, F, t, first_tree, n_trees, depth, out,
+                                                          plane_stride ? plane_stride : n, cat, ccol);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
 
 void launch_fill(float *dst, size_t n, float value, cudaStream_t s) {
   if (n == 0) return;
-  fill_kernel<<<grid_for(n, 256), 256, 0, s>>>(dst, n, value);
+  fill_kernel<float><<<grid_for(n, 256), 256, 0, s>>>(dst, n, value);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_fill_u32(unsigned *dst, size_t n, unsigned value, cudaStream_t s) {
+  if (n == 0) return;
+  fill_kernel<unsigned><<<grid_for(n, 256), 256, 0, s>>>(dst, n, value);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

@@ -28,6 +28,7 @@ namespace arb {
 namespace {
 
 constexpr unsigned kNoList = 0xffffffffu;
+constexpr unsigned kCatFlag = 0x8000u;  // in a packed split: the feature is categorical
 constexpr int kDescendPasses = 8;   // a warp takes 32 * 8 consecutive rows per turn
 constexpr int kSmemNodes = 2048;    // nodes of a level whose tables fit in shared memory
 constexpr int kListRows = 2048;     // rows of one CTA of the list pass
@@ -183,15 +184,18 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
                const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
                const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
                unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
-               float *__restrict__ yhat, const size_t n) {
+               float *__restrict__ yhat, const size_t n, const int n_dense) {
   overlap_release();
   overlap_wait();
-  __shared__ unsigned table[kSmemNodes];  // feature << 16 | split bin; feature 0xffff: no split
+  // feature << 16 | split bin, bit 15 set for a categorical feature (left <=> bin == split
+  // bin; a dense feature goes left with bin <= split bin); feature 0xffff: no split
+  __shared__ unsigned table[kSmemNodes];
   __shared__ unsigned cnt[kSmemNodes];    // rows of this CTA that went right, per node
   const bool cached = L <= kSmemNodes;
   auto packed = [&](int i) {
     const int fid = rec[i].fid;
-    return fid < 0 ? 0xffff0000u : (unsigned(fid) << 16) | unsigned(rec[i].bin);
+    return fid < 0 ? 0xffff0000u
+                   : (unsigned(fid) << 16) | unsigned(rec[i].bin) | (fid >= n_dense ? kCatFlag : 0u);
   };
   if (cached) {
     for (int i = threadIdx.x; i < L; i += blockDim.x) {
@@ -219,7 +223,7 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
       const size_t r = base + size_t(k) * 32 + lane;
       const unsigned e = cached ? table[node[k]] : packed(node[k]);
       const int fid = int(e >> 16);
-      split_bin[k] = int(e & 0xffffu);
+      split_bin[k] = int(e & 0xffffu);  // with the categorical flag
       binv[k] = -1;  // no split, or past the end: left
       if (fid != 0xffff && r < n)
         binv[k] = bins_cm ? int(reinterpret_cast<const BIN_T *>(bins_cm)[size_t(fid) * cm_rows + r])
@@ -228,7 +232,8 @@ descend_kernel(const unsigned char *__restrict__ bins, const size_t pitch,
 #pragma unroll
     for (int k = 0; k < kDescendPasses; ++k) {
       const size_t r = base + size_t(k) * 32 + lane;
-      const bool right = binv[k] > split_bin[k];
+      const bool right = (split_bin[k] & int(kCatFlag)) ? (binv[k] >= 0 && binv[k] != (split_bin[k] & 0x7fff))
+                                                       : binv[k] > split_bin[k];
       const int child = 2 * node[k] + (right ? 1 : 0);
       if (FINAL) {
         if (r < n) yhat[r] += leaf_w[child];
@@ -272,14 +277,15 @@ __global__ void __launch_bounds__(256, FINAL ? 5 : kWideCtasPerSm)
 descend_wide_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
                     const NodeRec *__restrict__ rec, const int L, unsigned short *__restrict__ node_of,
                     unsigned *__restrict__ right_count, const float *__restrict__ leaf_w,
-                    float *__restrict__ yhat, const size_t n) {
+                    float *__restrict__ yhat, const size_t n, const int n_dense) {
   overlap_release();
   overlap_wait();
-  __shared__ unsigned table[kSmemNodes];             // feature << 16 | split bin; feature 0xffff: no split
+  __shared__ unsigned table[kSmemNodes];             // packed splits, as in descend_kernel
   __shared__ unsigned cnt[FINAL ? 1 : kSmemNodes];   // rows of this CTA that went right, per node
   for (int i = threadIdx.x; i < L; i += blockDim.x) {
     const int fid = rec[i].fid;
-    table[i] = fid < 0 ? 0xffff0000u : (unsigned(fid) << 16) | unsigned(rec[i].bin);
+    table[i] = fid < 0 ? 0xffff0000u
+                       : (unsigned(fid) << 16) | unsigned(rec[i].bin) | (fid >= n_dense ? kCatFlag : 0u);
     if (!FINAL) cnt[i] = 0;
   }
   __syncthreads();
@@ -324,7 +330,8 @@ descend_wide_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_r
 #pragma unroll
     for (int k = 0; k < kWideRows; ++k) {
       const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
-      const bool right = binv[k] > int((sb[k >> 1] >> (16 * (k & 1))) & 0xffffu);
+      const int sbin = int((sb[k >> 1] >> (16 * (k & 1))) & 0xffffu);
+      const bool right = (sbin & int(kCatFlag)) ? (binv[k] >= 0 && binv[k] != (sbin & 0x7fff)) : binv[k] > sbin;
       const unsigned child = 2u * node + (right ? 1u : 0u);
       if (FINAL) {
         y[k] += leaf_w[child];
@@ -502,7 +509,7 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
     if (!resident) resident = resident_ctas(descend_wide_kernel<T, FIN>, 256);                      \
     const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
     launch_overlapped(descend_wide_kernel<T, FIN>, grid, 256, 0, s, g.bins_cm, g.cm_rows, a.rec,    \
-                      a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);                        \
+                      a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n, g.n_dense);             \
   } while (0)
     if (g.bin_bytes == 1) {
       if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);
@@ -521,7 +528,8 @@ void launch_descend(const DescendLaunch &a, cudaStream_t s) {
     if (!resident) resident = resident_ctas(descend_kernel<T, FIN>, 256);                           \
     const int grid = int(std::min<size_t>((a.n + span - 1) / span, size_t(resident)));              \
     launch_overlapped(descend_kernel<T, FIN>, grid, 256, 0, s, g.bins, g.pitch, g.bins_cm,          \
-                      g.cm_rows, a.rec, a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n);      \
+                      g.cm_rows, a.rec, a.L, a.node_of, a.child_count, a.leaf_w, a.yhat, a.n,       \
+                      g.n_dense);                                                                   \
   } while (0)
   if (g.bin_bytes == 1) {
     if (fin) ARB_LAUNCH(unsigned char, true); else ARB_LAUNCH(unsigned char, false);

@@ -215,6 +215,18 @@ __global__ void pad_rows_kernel(const unsigned char *__restrict__ raw, int F, si
   }
 }
 
+template <typename BIN_T>
+__global__ void place_columns_kernel(const BIN_T *__restrict__ src, size_t n, int ccol, int f0,
+                                     unsigned char *__restrict__ bins, size_t pitch) {
+  const size_t total = n * size_t(ccol);
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = e / ccol;
+    const int c = int(e - r * ccol);
+    reinterpret_cast<BIN_T *>(bins + r * pitch)[f0 + c] = src[e];
+  }
+}
+
 __global__ void u8_to_f32_kernel(const unsigned char *__restrict__ src, float *__restrict__ dst,
                                  size_t count) {
   for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < count;
@@ -286,6 +298,21 @@ void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *b
   const size_t total = n * size_t(words);
   const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
   pad_rows_kernel<<<grid, 256, 0, s>>>(raw, F, n, reinterpret_cast<unsigned *>(bins), words);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned char *bins, size_t pitch,
+                          int bin_bytes, cudaStream_t s) {
+  if (n == 0 || ccol == 0) return;
+  const size_t total = n * size_t(ccol);
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
+  if (bin_bytes == 1)
+    place_columns_kernel<unsigned char><<<grid, 256, 0, s>>>(static_cast<const unsigned char *>(src), n, ccol, f0,
+                                                            bins, pitch);
+  else
+    place_columns_kernel<unsigned short><<<grid, 256, 0, s>>>(static_cast<const unsigned short *>(src), n, ccol,
+                                                             f0, bins, pitch);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }

@@ -24,24 +24,36 @@ __device__ __forceinline__ unsigned long long pack_key(float gain, int fid, int 
 }
 
 // Decode the winner of a node and sum its left side (one warp).
-__device__ void finalize_node(const long long *__restrict__ hist, unsigned long long key,
+__device__ void finalize_node(const long long *__restrict__ hist, const long long *__restrict__ count_hist,
+                              const int *__restrict__ cat_candidates, unsigned long long key,
                               NodeRec *__restrict__ rec, int node, int TW, int NT, int lane) {
   NodeRec r = rec[node];
+  r.lcnt = r.tcnt = 0;
+  if (count_hist) {  // rows of the node: all bins of its first feature
+    const long long *cb = count_hist + size_t(node) * NT * kHistWords * 2;
+    long long c = 0;
+    for (int b = lane; b < kHistWords / TW; b += 32) c += cb[size_t(b) * TW * 2 + 1];
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    r.tcnt = unsigned(c);
+  }
   if (key == 0ull) {  // no positive gain: all rows stay left (hist_tree_grower.cu:84-93)
     r.gain = 0.0f;
     r.fid = -1;
     r.bin = -1;
     r.lg = r.tg;
     r.lh = r.th;
+    r.lcnt = r.tcnt;
   } else {
     r.gain = __uint_as_float(unsigned(key >> 32));
     r.fid = int(0xFFFFFu - unsigned((key >> 12) & 0xFFFFFu));
     r.bin = int(key & 0xFFFu);
     const int tile = r.fid / TW, fl = r.fid % TW;
     const long long *base = hist + (size_t(node) * NT + tile) * kHistWords * 2;
+    // a categorical winner sends one bin left, a dense one every bin up to the winner
+    const int first_bin = (cat_candidates && cat_candidates[r.fid] > 0) ? r.bin : 0;
     long long g = 0, h = 0;
 #pragma unroll 8  // the loads of eight turns are in flight together: one latency, not eight
-    for (int b = lane; b <= r.bin; b += 32) {
+    for (int b = first_bin + lane; b <= r.bin; b += 32) {
       g += base[(size_t(b) * TW + fl) * 2];
       h += base[(size_t(b) * TW + fl) * 2 + 1];
     }
@@ -51,14 +63,22 @@ __device__ void finalize_node(const long long *__restrict__ hist, unsigned long 
     }
     r.lg = g;
     r.lh = h;
+    if (count_hist) {
+      const long long *cbase = count_hist + (size_t(node) * NT + tile) * kHistWords * 2;
+      long long c = 0;
+      for (int b = first_bin + lane; b <= r.bin; b += 32) c += cbase[(size_t(b) * TW + fl) * 2 + 1];
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+      r.lcnt = unsigned(c);
+    }
   }
   r.left_count = 0;
   if (lane == 0) rec[node] = r;
 }
 
-template <bool PAIR>
+template <bool PAIR, bool COUNTS>
 __global__ void __launch_bounds__(kSplitThreads)
-split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict__ feature_active,
+split_kernel(const long long *__restrict__ hist, const long long *__restrict__ count_hist,
+             const unsigned char *__restrict__ feature_active, const int *__restrict__ cat_candidates,
              unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
              NodeRec *__restrict__ rec, const QuantScale *__restrict__ qs, const GainParams gp,
              const int TW, const int NT, const int F, const int hist_size, const int parts) {
@@ -84,7 +104,18 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
     sg += v[k].x;
     sh += v[k].y;
   }
-  long long og = 0, oh = 0, tg = 0, th = 0;
+  // row counts of the thread's bins ((g, h) objectives with min_leaf_size > 1 only)
+  long long cv[COUNTS ? kBinsPerThread : 1];
+  long long sc = 0;
+  if (COUNTS) {
+    const long long *cbase = count_hist + (size_t(node) * NT + tile) * kHistWords * 2;
+#pragma unroll
+    for (int k = 0; k < kBinsPerThread; ++k) {
+      cv[k] = cbase[(size_t(bin0 + k) * TW + lane) * 2 + 1];
+      sc += cv[k];
+    }
+  }
+  long long og = 0, oh = 0, tg = 0, th = 0, oc = 0, tcn = 0;
   if (TW == 32) {
     // A warp is one chunk of all 32 features.  The sums change places through shared memory
     // (slot feature * 32 + (chunk ^ feature): no bank conflict on the feature-major side), so
@@ -120,6 +151,25 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
     oh = part_h[slot];
     tg = tot_g[lane];
     th = tot_h[lane];
+    if (COUNTS) {  // the same exchange once more for the counts
+      __syncthreads();
+      part_g[slot] = sc;
+      __syncthreads();
+      const int f_w = chunk, c_l = lane;
+      const int at = f_w * 32 + (c_l ^ f_w);
+      const long long vc = part_g[at];
+      long long xc = vc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long uc = __shfl_up_sync(0xffffffffu, xc, o);
+        if (c_l >= o) xc += uc;
+      }
+      part_g[at] = xc - vc;
+      if (c_l == 31) tot_g[f_w] = xc;
+      __syncthreads();
+      oc = part_g[slot];
+      tcn = tot_g[lane];
+    }
   } else {
     part_g[threadIdx.x] = sg;
     part_h[threadIdx.x] = sh;
@@ -133,6 +183,16 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
       tg += g;
       th += h;
     }
+    if (COUNTS) {
+      __syncthreads();
+      part_g[threadIdx.x] = sc;
+      __syncthreads();
+      for (int c = 0; c < nchunks; ++c) {
+        const long long v = part_g[c * TW + lane];
+        if (c < chunk) oc += v;
+        tcn += v;
+      }
+    }
   }
   if (tile == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     rec[node].tg = tg;
@@ -144,26 +204,34 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
   // every thread's 8 goes to CTA k % parts; all of them redo the cheap prefix sums above,
   // so the long double-precision chains run side by side instead of one after another
   const bool active = f < F && feature_active[f];
+  // > 0: a categorical feature; a candidate sends the rows of ONE bin left (builder.h:75-105)
+  const int ncand = (active && cat_candidates) ? cat_candidates[f] : 0;
   if (active && th != 0) {
     const double isg = qs->inv_sg, ish = qs->inv_sh;
     const double dtg = double(tg) * isg, dth = double(th) * ish;
-    long long rg = og, rh = oh;
+    long long rg = og, rh = oh, rc = oc;
 #pragma unroll
     for (int k = 0; k < kBinsPerThread; ++k) {
       const int bin = bin0 + k;
       rg += v[k].x;
       rh += v[k].y;
+      if (COUNTS) rc += cv[k];
       if (bin >= hist_size) continue;  // ids >= hist_size hold missing values: never a threshold
       if ((k & (parts - 1)) != int(blockIdx.z)) continue;  // another CTA's candidate
+      if (ncand > 0 && bin >= ncand) continue;  // the shared bin of the rare categories
+      const long long lg = ncand > 0 ? v[k].x : rg, lh = ncand > 0 ? v[k].y : rh;
       unsigned long long lc, tc;
-      if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
-        lc = rh > 0;
-        tc = lc + ((th - rh) > 0);
+      if (COUNTS) {  // true row counts (gain.cu:125-134 gates every candidate on them)
+        lc = (unsigned long long)(ncand > 0 ? cv[k] : rc);
+        tc = (unsigned long long)tcn;
+      } else if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
+        lc = lh > 0;
+        tc = lc + ((th - lh) > 0);
       } else {  // h_q == 1 for every row: the sum is the row count
-        lc = (unsigned long long)rh;
+        lc = (unsigned long long)lh;
         tc = (unsigned long long)th;
       }
-      const float gain = split_gain<PAIR>(double(rg) * isg, double(rh) * ish, dtg, dth, lc, tc, gp);
+      const float gain = split_gain<PAIR>(double(lg) * isg, double(lh) * ish, dtg, dth, lc, tc, gp);
       if (gain > 0.0f && gain >= bgain) {
         bgain = gain;
         bbin = bin;
@@ -191,7 +259,7 @@ split_kernel(const long long *__restrict__ hist, const unsigned char *__restrict
   if (is_last && threadIdx.x < 32) {
     __threadfence();
     const unsigned long long key = atomicMax(&keys[node], 0ull);
-    finalize_node(hist, key, rec, node, TW, NT, threadIdx.x);
+    finalize_node(hist, COUNTS ? count_hist : nullptr, cat_candidates, key, rec, node, TW, NT, threadIdx.x);
   }
 }
 
@@ -214,12 +282,15 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   int parts = kBinsPerThread;
   while (parts > 1 && a.L * a.geo.NT * parts > sms) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);
-  if (a.pair)
-    launch_overlapped(split_kernel<true>, grid, kSplitThreads, 0, s, a.hist, a.feature_active, a.keys, done,
-                      a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+  if (a.pair && a.count_hist)
+    launch_overlapped(split_kernel<true, true>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
+                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+  else if (a.pair)
+    launch_overlapped(split_kernel<true, false>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
+                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   else
-    launch_overlapped(split_kernel<false>, grid, kSplitThreads, 0, s, a.hist, a.feature_active, a.keys, done,
-                      a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+    launch_overlapped(split_kernel<false, false>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
+                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   count_launch();
 }
 

@@ -74,6 +74,11 @@ const char *AGetTrainY(VoidPointer garden, float *out);
 const char *AGetLevelStats(VoidPointer garden, int level, unsigned *node_begin, float *gain,
                            int *fid, int *bin, double *left_g, double *left_h, double *tot_g,
                            double *tot_h, unsigned *left_count);
+/* The same for tree `tree_in_round` (0 .. labels_count - 1, -1 = the last) of the last round:
+ * multi:softmax grows one tree per class in every round. */
+const char *AGetLevelStatsOf(VoidPointer garden, int tree_in_round, int level, unsigned *node_begin,
+                             float *gain, int *fid, int *bin, double *left_g, double *left_h,
+                             double *tot_g, double *tot_h, unsigned *left_count);
 /* CUDA-event timing of the kernel classes: switch on, then read a JSON summary. */
 const char *ASetProfile(VoidPointer garden, int on);
 const char *AGetTimings(VoidPointer garden, const char **json);
@@ -86,6 +91,16 @@ const char *ABuildHistogram(const void *bins, int bin_bytes, int64_t nrow, int n
                             const float *grad, int pair, const unsigned *rowid,
                             const unsigned *node_begin, int n_nodes, int quant_bits, double *out_g,
                             double *out_h, int reps, float *ms);
+/* The same launch with the subtraction trick (hist_grad_sum.cu:6-33,288-290 of the reference):
+ * nodes 2p and 2p + 1 are the children of parent p, whose sums parent_g / parent_h
+ * [n_nodes / 2][ncol][hist_size + 1] are given (multiples of the fixed-point step, e.g.
+ * integers); only the smaller child of every pair is scanned (ties: the left one), the other
+ * is parent - scanned. */
+const char *ABuildHistogramFromParents(const void *bins, int bin_bytes, int64_t nrow, int ncol, int hist_size,
+                                       const float *grad, int pair, const unsigned *rowid,
+                                       const unsigned *node_begin, int n_nodes, int quant_bits,
+                                       const double *parent_g, const double *parent_h, double *out_g,
+                                       double *out_h);
 /* Multi-GPU: rows are sharded over one process per GPU; every level's histogram
  * is summed over the ranks with ncclAllReduce, and the first AGrowTree finds the
  * thresholds of the whole data set with the other ranks (unless ASetThresholds gave

@@ -18,6 +18,7 @@
 #include <limits>
 #include <random>
 #include <string>
+#include <map>
 #include <vector>
 
 namespace orc {
@@ -283,6 +284,10 @@ struct Node {
   int fid;
   unsigned quantized;
   float threshold;
+  // extension (the reference's categorical training is a stub, hist_tree_grower.h:55-63):
+  // the node sends `value == category` left, like RegTree::Predict garden.h:79-84
+  bool categorical = false;
+  unsigned category = unsigned(-1);
 };
 struct Tree {  // reg_tree.h:16-45, garden.h:32-68
   int depth;
@@ -331,6 +336,12 @@ class TrainerBase {
   int keep_hist = 0;
   std::vector<std::vector<std::vector<double>>> hist_g, hist_h;
   std::vector<std::vector<std::vector<uint32_t>>> hist_c;
+  // categorical features (extension): ids n_dense .. F - 1; bin id = rank of the category
+  // by frequency; cat_candidates[f] = bins a one-vs-rest split may name (0 for dense
+  // features); cat_codes[f - n_dense][bin] = category code
+  int n_dense = 1 << 30;
+  std::vector<int> cat_candidates;
+  std::vector<std::vector<uint32_t>> cat_codes;
 };
 
 // One boosting state bound to one data set; mirrors ContinuousGardenBuilder
@@ -449,7 +460,7 @@ class Trainer : public TrainerBase {
     Tree tree;
     tree.depth = depth;
     tree.label = k;
-    tree.nodes.assign((1 << depth) - 1, Node{0, 0, 0.f});
+    tree.nodes.assign((1 << depth) - 1, Node{0, 0, 0.f, false, unsigned(-1)});
     tree.weights.assign(1 << (depth - 1), 0.f);
     std::vector<LevelStat> tstats;
     G *g = grad.data() + size_t(k) * n;
@@ -609,10 +620,14 @@ class Trainer : public TrainerBase {
         cd.t2.assign(L, 0.f);
         std::vector<float> &cgain = cd.cgain, &top1l = cd.t1, &top2l = cd.t2;
         std::vector<unsigned> &cidx = cd.cidx;
+        const int ncand = fid >= n_dense ? cat_candidates[fid] : 0;
         for (size_t i = 0; i < size_t(L) * HW; ++i) {
           const unsigned seg = unsigned(i / HW);
-          const S lsum = prefix[i] - psum[seg];
-          const uint32_t lcnt = cprefix[i] - pcount[seg];
+          // categorical feature (extension, builder.h:75-105): one bin against the rest; the
+          // bin shared by the rare categories is no candidate
+          if (fid >= n_dense && int(i % HW) >= ncand) continue;
+          const S lsum = fid >= n_dense ? sum[i] : prefix[i] - psum[seg];
+          const uint32_t lcnt = fid >= n_dense ? cnt[i] : cprefix[i] - pcount[seg];
           const S tsum = psum[seg + 1] - psum[seg];
           const uint32_t tcnt = pcount[seg + 1] - pcount[seg];
           const float gn = gain_func(lsum, tsum, lcnt, tcnt, gp);
@@ -632,8 +647,13 @@ class Trainer : public TrainerBase {
         cd.sum_at.resize(L);
         cd.cnt_at.resize(L);
         for (int node = 0; node < L; ++node) {
-          cd.sum_at[node] = prefix[cidx[node]];
-          cd.cnt_at[node] = cprefix[cidx[node]];
+          if (fid >= n_dense) {  // as if the winner's rows lay first in the node
+            cd.sum_at[node] = psum[node] + sum[cidx[node]];
+            cd.cnt_at[node] = pcount[node] + cnt[cidx[node]];
+          } else {
+            cd.sum_at[node] = prefix[cidx[node]];
+            cd.cnt_at[node] = cprefix[cidx[node]];
+          }
         }
         if (cfg.use_trick) {  // Histogram::Update histogram.cu:30-44
           saved_sum[fid] = sum;
@@ -674,7 +694,7 @@ class Trainer : public TrainerBase {
               best_split[node] = thr;
               // apply_split builder.h:107-123: right <=> bin >= thr + 1
               for (uint32_t i = nstart; i < nend; ++i)
-                go_right[i] = bins[fid][i] >= thr + 1;
+                go_right[i] = fid >= n_dense ? bins[fid][i] != thr : bins[fid][i] >= thr + 1;
               pcount_next[2 * node + 1] = cd.cnt_at[node];
               pcount_next[2 * node + 2] = nend;
               psum_next[2 * node + 1] = cd.sum_at[node];
@@ -715,6 +735,11 @@ class Trainer : public TrainerBase {
           nd.threshold = (q >= unsigned(H) || last_real)
                            ? INFINITY
                            : mapping[best_fid[i]][q];
+          if (best_fid[i] >= n_dense) {
+            nd.categorical = true;
+            nd.category = cat_codes[best_fid[i] - n_dense][q];
+            nd.threshold = INFINITY;
+          }
         } else {
           nd.fid = 0;
           nd.quantized = q;
@@ -769,16 +794,18 @@ class Trainer : public TrainerBase {
   }
 };
 
-// RegTree::Predict garden.h:70-90 (dense features only): out[row] += leaf weight
+// RegTree::Predict garden.h:70-90: out[row] += leaf weight; features >= F test the
+// categorical column fid - F of `cat` (row-major [n][C]) for equality
 static void tree_predict(const Tree &t, const float *X, int64_t n, int F,
-                         float *out) {
+                         float *out, const uint32_t *cat = nullptr, int C = 0) {
   const int offset = (1 << (t.depth - 1)) - 1;
 #pragma omp parallel for
   for (int64_t i = 0; i < n; ++i) {
     unsigned node = 0;
     for (int j = 1; j < t.depth; ++j) {
       const Node &nd = t.nodes[node];
-      const bool left = X[size_t(i) * F + nd.fid] < nd.threshold;
+      const bool left = nd.fid < F ? X[size_t(i) * F + nd.fid] < nd.threshold
+                                   : (cat && cat[size_t(i) * C + (nd.fid - F)] == nd.category);
       node = left ? 2 * node + 1 : 2 * node + 2;
     }
     out[i] += t.weights[node - offset];
@@ -795,6 +822,11 @@ struct Handle {
   std::vector<int> fsize;
   std::vector<float> y;
   std::vector<uint8_t> label;
+  // categorical columns (extension): codes row-major [n][C], set before the dense matrix
+  int C = 0;
+  std::vector<uint32_t> cat;
+  std::vector<int> cat_candidates;
+  std::vector<std::vector<uint32_t>> cat_codes;
   TrainerBase *trainer = nullptr;
   std::string error;
   ~Handle() { delete trainer; }
@@ -867,6 +899,48 @@ void *orc_create(const Config *cfg) {
 void orc_free(void *p) { delete static_cast<Handle *>(p); }
 const char *orc_error(void *p) { return static_cast<Handle *>(p)->error.c_str(); }
 
+// Categorical columns (extension), to be given BEFORE orc_set_dense: uint32 codes,
+// row-major [n][C].  orc_set_dense then appends them as features F .. F + C - 1.
+// Bins: a category's bin is its rank by frequency (most frequent first, ties: smaller code
+// first); a column with more than hist_size categories keeps the hist_size - 1 most frequent
+// ones and gives all others bin hist_size - 1, which no split may name.
+int orc_set_categories(void *p, const uint32_t *cat, int64_t n, int C) {
+  Handle *h = static_cast<Handle *>(p);
+  h->C = C;
+  h->cat.assign(cat, cat + size_t(n) * C);
+  return 0;
+}
+static void bin_categories(Handle *h) {
+  const int64_t n = h->n;
+  const int Fd = h->F, C = h->C, H = h->cfg.hist_size;
+  h->bins.resize(size_t(n) * (Fd + C));
+  h->mapping.resize(size_t(Fd + C) * H, INFINITY);
+  h->fsize.resize(Fd + C);
+  h->cat_candidates.assign(Fd + C, 0);
+  h->cat_codes.assign(C, std::vector<uint32_t>());
+  for (int c = 0; c < C; ++c) {
+    std::map<uint32_t, uint64_t> count;
+    for (int64_t i = 0; i < n; ++i) count[h->cat[size_t(i) * C + c]]++;
+    std::vector<std::pair<uint32_t, uint64_t>> freq(count.begin(), count.end());  // codes ascending
+    std::stable_sort(freq.begin(), freq.end(),
+                     [](const std::pair<uint32_t, uint64_t> &a, const std::pair<uint32_t, uint64_t> &b) {
+                       return a.second > b.second;
+                     });
+    const bool overflow = freq.size() > size_t(H);
+    const size_t kept = overflow ? size_t(H - 1) : freq.size();
+    std::map<uint32_t, uint16_t> bin_of_code;
+    for (size_t b = 0; b < kept; ++b) {
+      h->cat_codes[c].push_back(freq[b].first);
+      bin_of_code[freq[b].first] = uint16_t(b);
+    }
+    h->fsize[Fd + c] = int(kept + (overflow ? 1 : 0));
+    h->cat_candidates[Fd + c] = int(kept);
+    for (int64_t i = 0; i < n; ++i) {
+      auto it = bin_of_code.find(h->cat[size_t(i) * C + c]);
+      h->bins[size_t(Fd + c) * n + i] = it == bin_of_code.end() ? uint16_t(kept) : it->second;
+    }
+  }
+}
 // dense fp32 row-major input; quantised here (DataMatrix::InitHist io.cu:342-347)
 int orc_set_dense(void *p, const float *X, int64_t n, int F) {
   Handle *h = static_cast<Handle *>(p);
@@ -885,6 +959,7 @@ int orc_set_dense(void *p, const float *X, int64_t n, int F) {
                                       &h->mapping[size_t(f) * H],
                                       &h->bins[size_t(f) * n]);
   }
+  if (h->C > 0) bin_categories(h);
   return 0;
 }
 // pre-binned feature-major input with explicit thresholds (extension)
@@ -921,6 +996,20 @@ void orc_keep_hist(void *p, int on) {
 static void ensure_trainer(Handle *h) {
   if (h->trainer) return;
   const Config &c = h->cfg;
+  const int Fd = h->F;
+  struct Restore {  // the trainers take the feature count from h->F
+    Handle *h;
+    int Fd;
+    ~Restore() {
+      h->F = Fd;
+      if (h->trainer && h->C > 0) {
+        h->trainer->n_dense = Fd;
+        h->trainer->cat_candidates = h->cat_candidates;
+        h->trainer->cat_codes = h->cat_codes;
+      }
+    }
+  } restore{h, Fd};
+  h->F = Fd + h->C;
   const uint8_t *lab = h->label.empty() ? nullptr : h->label.data();
   const float *y = h->y.empty() ? nullptr : h->y.data();
   // chained() dispatch garden.cu:506-569
@@ -973,6 +1062,15 @@ void orc_get_tree(void *p, int t, int *fid, int *quantized, float *threshold,
   }
   std::copy(tr.weights.begin(), tr.weights.end(), weights);
 }
+// which nodes test a category, and which (extension)
+void orc_get_tree_categories(void *p, int t, int *categorical, uint32_t *category) {
+  Handle *h = static_cast<Handle *>(p);
+  const Tree &tr = h->trainer->trees[t];
+  for (size_t i = 0; i < tr.nodes.size(); ++i) {
+    categorical[i] = tr.nodes[i].categorical ? 1 : 0;
+    category[i] = tr.nodes[i].category;
+  }
+}
 // per-level stats of tree t, level l (L = 1<<l entries; node_begin L+1)
 void orc_get_level(void *p, int t, int l, uint32_t *node_begin, float *gain, float *gain2,
                    int *fid, int *bin, double *left_g, double *left_h, double *tot_g,
@@ -1011,7 +1109,12 @@ void orc_get_yhat(void *p, float *out) {
 }
 // Garden::Predict garden.cu:643-657 over the handle's own dense rows or X given
 // explicitly; out layout [row] or [row][K] (core.py:273-277)
+void orc_predict_cat(void *p, const float *X, const uint32_t *cat, int64_t n, int n_rounds, float *out);
 void orc_predict(void *p, const float *X, int64_t n, int n_rounds, float *out) {
+  orc_predict_cat(p, X, nullptr, n, n_rounds, out);
+}
+// the same with the rows' category codes (row-major [n][C]; extension)
+void orc_predict_cat(void *p, const float *X, const uint32_t *cat, int64_t n, int n_rounds, float *out) {
   Handle *h = static_cast<Handle *>(p);
   const Config &c = h->cfg;
   const int K = c.labels_count;
@@ -1021,7 +1124,7 @@ void orc_predict(void *p, const float *X, int64_t n, int n_rounds, float *out) {
   const auto &trees = h->trainer->trees;
   const int cnt = std::min<int>(n_rounds < 0 ? INT32_MAX : n_rounds, int(trees.size()));
   for (int i = 0; i < cnt; ++i)
-    tree_predict(trees[i], X, n, h->F, tmp.data() + size_t(trees[i].label) * n);
+    tree_predict(trees[i], X, n, h->F, tmp.data() + size_t(trees[i].label) * n, cat, h->C);
   if (c.objective == 1) {
     for (int64_t i = 0; i < n; ++i) out[i] = sigmoid(tmp[i]);  // objective.h:58-64
   } else if (c.objective == 3) {                               // objective.h:80-113

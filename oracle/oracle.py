@@ -82,6 +82,12 @@ def lib():
         L.orc_set_dense.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
         L.orc_set_binned.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                      ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        L.orc_set_categories.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+        L.orc_get_tree_categories.restype = None
+        L.orc_get_tree_categories.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        L.orc_predict_cat.restype = None
+        L.orc_predict_cat.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                      ctypes.c_int, ctypes.c_void_p]
         L.orc_set_y.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         L.orc_set_label.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         L.orc_get_bins.restype = None
@@ -183,9 +189,17 @@ class Oracle(object):
             lib().orc_free(self.h)
             self.h = None
 
-    def set_dense(self, X):
+    def set_dense(self, X, categories=None):
+        """Dense fp32 rows and, optionally, categorical columns (uint32 codes [rows][C]):
+        features ``F .. F + C - 1`` of the trees (extension of this build)."""
         X = np.ascontiguousarray(X, dtype=np.float32)
         self.n, self.F = X.shape
+        self.C = 0
+        if categories is not None:
+            categories = np.ascontiguousarray(categories, dtype=np.uint32)
+            assert categories.shape[0] == self.n
+            self.C = categories.shape[1]
+            lib().orc_set_categories(self.h, _p(categories), self.n, self.C)
         lib().orc_set_dense(self.h, _p(X), self.n, self.F)
         return self
 
@@ -212,9 +226,10 @@ class Oracle(object):
     def bins(self):
         """(bins [F][n] uint16, thresholds [F][H] float32, bins in use [F])."""
         H = self.cfg.hist_size
-        b = np.empty((self.F, self.n), dtype=np.uint16)
-        m = np.empty((self.F, H), dtype=np.float32)
-        s = np.empty(self.F, dtype=np.int32)
+        F = self.F + getattr(self, "C", 0)  # categorical columns follow the dense ones
+        b = np.empty((F, self.n), dtype=np.uint16)
+        m = np.empty((F, H), dtype=np.float32)
+        s = np.empty(F, dtype=np.int32)
         lib().orc_get_bins(self.h, _p(b), _p(m), _p(s))
         return b, m, s
 
@@ -239,7 +254,11 @@ class Oracle(object):
         thr = np.empty(nn, dtype=np.float32)
         w = np.empty(1 << (depth - 1), dtype=np.float32)
         lib().orc_get_tree(self.h, t, _p(fid), _p(q), _p(thr), _p(w))
-        return {"fid": fid, "quantized": q, "threshold": thr, "weights": w}
+        is_cat = np.empty(nn, dtype=np.int32)
+        category = np.empty(nn, dtype=np.uint32)
+        lib().orc_get_tree_categories(self.h, t, _p(is_cat), _p(category))
+        return {"fid": fid, "quantized": q, "threshold": thr, "weights": w,
+                "categorical": is_cat, "category": category}
 
     def level(self, t, l):
         L = 1 << l
@@ -270,11 +289,13 @@ class Oracle(object):
         lib().orc_get_yhat(self.h, _p(out))
         return out
 
-    def predict(self, X, n_rounds=-1):
+    def predict(self, X, n_rounds=-1, categories=None):
         X = np.ascontiguousarray(X, dtype=np.float32)
         K = self.cfg.labels_count
         out = np.empty(X.shape[0] * K, dtype=np.float32)
-        lib().orc_predict(self.h, _p(X), X.shape[0], n_rounds, _p(out))
+        if categories is not None:
+            categories = np.ascontiguousarray(categories, dtype=np.uint32)
+        lib().orc_predict_cat(self.h, _p(X), _p(categories), X.shape[0], n_rounds, _p(out))
         return out if K == 1 else out.reshape(X.shape[0], K)
 
     def model_dict(self):
@@ -291,6 +312,8 @@ class Oracle(object):
                     nodes.append({"fid": int(tr["fid"][i]), "id": i, "leaf": False,
                                   "left": 2 * i + 1, "right": 2 * i + 2,
                                   "threshold": None if np.isinf(thr) else thr})
+                    if tr["categorical"][i]:
+                        nodes[-1]["category"] = int(tr["category"][i])
                 else:
                     nodes.append({"id": i, "idx": i - first_leaf, "leaf": True})
             trees.append({"depth": depth, "nodes": nodes,

@@ -54,3 +54,53 @@ def test_python_surface_matches_reference():
         assert hasattr(arboretum, name)
     for name in ("grow_tree", "append_last_tree", "get_y", "predict", "dump", "load"):
         assert hasattr(arboretum.Garden, name)
+
+
+def _model_json(fid, depth=2):
+    nodes = [{"id": 0, "leaf": False, "left": 1, "right": 2, "threshold": 0.5, "fid": fid},
+             {"id": 1, "leaf": True, "idx": 0}, {"id": 2, "leaf": True, "idx": 1}]
+    cfg = {"objective": 0, "method": 1, "tree": {"max_depth": depth - 1}}
+    return cfg, json.dumps({"configuration": cfg, "model": [{"depth": depth, "nodes": nodes,
+                                                             "weights": [0.25, -0.25]}]})
+
+
+def test_loading_a_model_checks_what_inference_would_index():
+    """A dumped model is input like any other: a feature id or a depth that the device-side
+    tree walk would index out of range is refused when the model is loaded."""
+    import arboretum_b200
+    lib = arboretum_b200.lib()
+    cfg, good = _model_json(1)
+    h = ctypes.c_void_p()
+    assert lib.AInitGarden(json.dumps(cfg).encode(), ctypes.byref(h)) is None
+    assert lib.ALoadModel(good.encode(), h) is None
+    out = ctypes.c_char_p()
+    assert lib.ADumpModel(ctypes.byref(out), h) is None
+    assert json.loads(out.value.decode())["model"][0]["nodes"][0]["fid"] == 1
+    for bad in (_model_json(-3)[1], _model_json(70000)[1],
+                good.replace('"depth": 2', '"depth": 99'), good.replace('"depth": 2', '"depth": 0')):
+        msg = lib.ALoadModel(bad.encode(), h)
+        assert msg is not None and (b"range" in msg or b"depth" in msg)
+    assert lib.AFreeGarden(h) is None
+
+
+def test_thresholds_and_histogram_arguments_are_validated():
+    import numpy as np
+    import arboretum_b200
+    lib = arboretum_b200.lib()
+    bins = np.zeros((8, 2), dtype=np.uint8)
+    grad = np.ones(8, dtype=np.float32)
+    og = np.zeros((1, 2, 5))
+    oh = np.zeros((1, 2, 5))
+    ms = ctypes.c_float(0)
+
+    def call(b, rowid, node_begin, n_nodes=1):
+        p = lambda a: None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+        return lib.ABuildHistogram(p(b), 1, 8, 2, 4, p(grad), 0, p(rowid), p(node_begin), n_nodes, 17,
+                                   p(og), p(oh), 0, ctypes.byref(ms))
+    nb = np.array([0, 8], dtype=np.uint32)
+    assert b"exceeds" in call(bins, None, np.array([0, 9], dtype=np.uint32))
+    assert b"non-decreasing" in call(bins, None, np.array([5, 2, 8], dtype=np.uint32), 2)
+    assert b"rowid" in call(bins, np.array([0, 1, 2, 3, 4, 5, 6, 99], dtype=np.uint32), nb)
+    too_big = bins.copy()
+    too_big[3, 1] = 5
+    assert b"bin id" in call(too_big, None, nb)

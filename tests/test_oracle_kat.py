@@ -165,3 +165,73 @@ def test_iris_sklearn_golden(hist_size):  # tests/py/test_sklearn_classification
     X, y = _iris()
     o = orc.Oracle(cfg).set_dense(X).set_y(y).grow(1)
     assert np.allclose(o.predict(X), gold["sklearn_classification"]["predictions"][0])
+
+
+# --- multi-node histogram sums: tests/cpp/test_hist_sum.cu:383-640 ---------------------
+def multi_node_kats():
+    """(name, bins, grad, node_begin, with_parent, expected counts, expected sums); None = unchecked.
+    Inputs follow the reference tests' formulas (grad[i] = i, bin = i % 4 or 0, two nodes)."""
+    size = 1280
+    i = np.arange(size)
+    g = i.astype(np.float32)
+    b4 = (i % 4).astype(np.uint16)
+    whole = np.array([np.bincount(b4, weights=g, minlength=4)]), np.array([np.bincount(b4, minlength=4)])
+    return [
+        ("2_NodesNoTrick", b4, g, [0, size // 2, size], None,           # :383-424
+         [size // 8] * 8, None),
+        ("2_NodesAsymmetricNoTrick", b4, g, [0, 10, size], None,        # :426-477
+         [3, 3, 2, 2, 317, 317, 318, 318],
+         [12.0, 15.0, 8.0, 10.0, 204148.0, 204465.0, 204792.0, 205110.0]),
+        ("2_NodesAsymmetricWithTrick", b4, g, [0, 10, size], whole,     # :479-538
+         [3, 3, 2, 2, 317, 317, 318, 318],
+         [12.0, 15.0, 8.0, 10.0, 204148.0, 204465.0, 204792.0, 205110.0]),
+        ("2_NodesAsymmetricWithTrick2", b4, g, [0, size - 10, size], whole,  # :540-599
+         [318, 318, 317, 317, 2, 2, 3, 3],
+         [201612.0, 201930.0, 200978.0, 201295.0, 2548.0, 2550.0, 3822.0, 3825.0]),
+        ("SingleSegmentWithTrick", np.zeros(size, dtype=np.uint16), g, [0, size // 2, size],  # :601-650
+         (np.array([[g.sum(), 0, 0, 0]]), np.array([[size, 0, 0, 0]])),
+         [size // 2, 0, 0, 0, size // 2, 0, 0, 0],
+         [float(g[:size // 2].sum()), 0, 0, 0, float(g[size // 2:].sum()), 0, 0, 0]),
+    ]
+
+
+@pytest.mark.parametrize("case", range(5))
+def test_multi_node_hist_sum_kats(case):
+    name, bins, g, node_begin, parent, counts, sums = multi_node_kats()[case]
+    nb = np.array(node_begin, dtype=np.uint32)
+    if parent is None:
+        og, _, oc = orc.hist(bins, g, None, nb, 4)
+    else:  # the smaller child is scanned (ties: the left one), the other is parent - scanned
+        left_small = nb[1] - nb[0] <= nb[2] - nb[1]
+        seg = nb[:2] if left_small else nb[1:]
+        sg, _, sc = orc.hist(bins, g, None, np.array(seg, dtype=np.uint32), 4)
+        rest_g, rest_c = parent[0][0] - sg, parent[1][0] - sc
+        og = np.concatenate([sg, rest_g] if left_small else [rest_g, sg])
+        oc = np.concatenate([sc, rest_c] if left_small else [rest_c, sc])
+    assert oc.tolist() == counts
+    if sums is not None:
+        assert og.tolist() == sums
+    if name == "2_NodesNoTrick":
+        half = 1280 // 2
+        assert og[:4].sum() == half * (half - 1) / 2
+        assert og[4:].sum() == half * (half + 1280 - 1) / 2
+
+
+# --- categorical columns (extension: one category against the rest) --------------------
+def test_oracle_splits_on_a_category():
+    rng = np.random.default_rng(5)
+    n = 4000
+    X = rng.normal(size=(n, 3)).astype(np.float32)
+    cat = np.stack([rng.integers(0, 6, n), rng.integers(0, 400, n)], axis=1).astype(np.uint32)
+    y = (2.0 * (cat[:, 0] == 4) + 0.1 * X[:, 0] + rng.normal(0, 0.05, n)).astype(np.float32)
+    cfg = {"objective": 0, "method": 1, "internals": {"hist_size": 255, "seed": 0, "double_precision": True},
+           "tree": {"max_depth": 2, "eta": 1.0, "lambda": 0.0, "min_child_weight": 1.0, "min_leaf_size": 1,
+                    "initial_y": 0.0}}
+    o = orc.Oracle(cfg, missing_bin=True).set_dense(X, categories=cat).set_y(y).grow(1)
+    root = o.model_dict()[0]["nodes"][0]
+    assert root["fid"] == 3 and root["category"] == 4 and root["threshold"] is None
+    pred = o.predict(X, categories=cat)
+    assert np.abs(pred - y).mean() < 0.1
+    # 400 categories do not fit 255 bins: the 254 most frequent keep a bin, the rest share one
+    bins, _, sizes = o.bins()
+    assert sizes[4] == 255 and bins[4].max() == 254 and sizes[3] == 6
