@@ -33,7 +33,7 @@ def _load_lib():
                  "ASetLabel", "ASetWeights", "ADumpModel", "ALoadModel",
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
-                 "AGetLevelStats", "AGetLevelStatsOf", "ASetProfile", "AGetTimings", "ABuildHistogram",
+                 "AGetLevelStats", "AGetLevelStatsOf", "AGetGradientStep", "ASetProfile", "AGetTimings", "ABuildHistogram",
                  "ABuildHistogramFromParents", "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak",
                  "AReleaseCachedMemory"):
         getattr(lib, name).restype = ctypes.c_char_p
@@ -60,6 +60,8 @@ def _load_lib():
     lib.AGetTrainY.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.AGetLevelStats.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 9
     lib.AGetLevelStatsOf.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 9
+    lib.AGetGradientStep.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double),
+                                     ctypes.POINTER(ctypes.c_double)]
     lib.ASetProfile.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.AGetTimings.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p)]
     lib.ABuildHistogram.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
@@ -286,6 +288,12 @@ class Garden(object):
             self.handle, int(tree_in_round), level, *[_ptr(out[k]) for k in ("node_begin", "gain", "fid", "bin", "left_g",
                                                          "left_h", "tot_g", "tot_h", "left_count")]))
         return out
+
+    def gradient_step(self):
+        """(gradient step, hessian step) of the last round's fixed-point representation."""
+        g, h = ctypes.c_double(0), ctypes.c_double(0)
+        _call_and_throw_if_error(_LIB.AGetGradientStep(self.handle, ctypes.byref(g), ctypes.byref(h)))
+        return g.value, h.value
 
     def set_profile(self, on=True):
         self._ensure_init()

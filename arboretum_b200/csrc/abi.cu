@@ -406,6 +406,16 @@ const char *AGetLevelStatsOf(VoidPointer garden, int tree_in_round, int level, u
   ARB_CATCH
 }
 
+const char *AGetGradientStep(VoidPointer garden, double *g_step, double *h_step) {
+  ARB_TRY
+  ARB_CHECK(garden, "NULL argument");
+  QuantScale q;
+  BuilderView::scales(static_cast<Garden *>(garden), &q);
+  if (g_step) *g_step = q.inv_sg;
+  if (h_step) *h_step = q.inv_sh;
+  ARB_CATCH
+}
+
 const char *ASetProfile(VoidPointer garden, int on) {
   ARB_TRY
   ARB_CHECK(garden, "NULL argument");

@@ -113,6 +113,22 @@ struct PinnedBuf {
 
 static inline int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
 
+// Per-device facts are cached by device ordinal: one process may drive several devices, and
+// what was asked of the first says nothing about the second.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+  int dev = 0;
+  ARB_CUDA(cudaGetDevice(&dev));
+  ARB_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+  return dev;
+}
+inline int device_sm_count() {
+  static int sms[kMaxDevices] = {};
+  const int dev = current_device();
+  if (!sms[dev]) ARB_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+  return sms[dev];
+}
+
 // Kernels of this library launched so far in this process (reported by AGetTimings).
 extern long long g_kernel_launches;
 static inline void count_launch(int n = 1) { g_kernel_launches += n; }
@@ -204,6 +220,16 @@ struct QuantScale {
   float sg, sh;
   double inv_sg, inv_sh;
   unsigned max_g_bits, max_h_bits;  // float bit patterns, written by atomicMax
+  // reg:linear, whose targets may have outliers: tail[j] = rows with |g| >= max|g| / 2^(j + 1).
+  // From them follows a bound on the sum of the |g| of ANY 2^(31 - quant_bits) rows -- what an
+  // int32 sub-histogram must hold -- that is far below rows x max|g| when the largest
+  // gradients are few, and the scale is taken from that bound: up to `extra_bits` more bits
+  // for every gradient.  neg_s = 1024 - log2(sg): row shards agree on the coarsest scale with
+  // the element-wise maximum they already exchange.
+  unsigned neg_s;
+  int lim_g;  // |g_q| <= lim_g
+  unsigned tail[8];
 };
+constexpr int kTailLevels = 8;
 
 }  // namespace arb

@@ -465,6 +465,7 @@ class Builder {
   // (gradient, hessian) objectives with min_leaf_size > 1 keep a second histogram that counts
   // rows (the reference's count histogram, gain.cu:125-134): the reg:linear kernel run on a
   // "gradient" array of ones; same level buffers, same subtraction, same exchange
+  bool fused_steps_ = true;  // ARBORETUM_NO_FUSED_STEP in the environment: the three-pass level step
   bool count_plane_ = false;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
   // records of every tree of the last round (multi:softmax grows labels_count of them)
@@ -535,6 +536,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   nb_stride_ = 2 * max_nodes_ + 1;
   pair_ = cfg.objective != kLinearRegression;
   count_plane_ = pair_ && tp.min_leaf_size > 1;
+  fused_steps_ = std::getenv("ARBORETUM_NO_FUSED_STEP") == nullptr;
   if (cfg.objective == kSoftMaxOneVsAll)
     ARB_CHECK(d->has_labels(), "multi:softmax needs labels (ASetLabel)");
   else
@@ -810,7 +812,18 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   if (g_->allreduce_max &&
       g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
     throw std::runtime_error("gradient-scale allreduce failed");
-  launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s);
+  // reg:linear targets may have outliers: the scale also looks at how many gradients come
+  // near the largest one (see QuantScale); row shards agree on the coarsest scale
+  const bool tails = g_->cfg.objective == kLinearRegression;
+  if (tails) launch_gradient_tails(n_, y, d_yhat_.as<float>(), d_qs_.as<QuantScale>(), s);
+  if (tails && g_->allreduce_max) {
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, true, 1);
+    if (g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->neg_s, 1, s) != 0)
+      throw std::runtime_error("gradient-scale allreduce failed");
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, true, 2);
+  } else {
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, tails, 0);
+  }
   // pass 2: the gradients as fixed-point integers
   launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
                    d_qs_.as<QuantScale>(), true, s, row_offset_, round_, g_->cfg.internal.quant_bits);
@@ -892,7 +905,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   const bool use_trick = cfg.internal.use_hist_subtraction_trick;
   const int n_chunks = int(chunks_.size());
   const bool multi = n_chunks > 1;  // row chunks add their histograms like GPUs do
-  const bool by_hessian = g_->allreduce != nullptr || multi;
+  // the fused level step names the child to build by the hessian rule as well
+  const bool by_hessian = g_->allreduce != nullptr || multi || (fused_steps_ && geo_.bins_cm != nullptr);
   const size_t gsz = pair_ ? sizeof(float2) : sizeof(float);
   const int n_sets = count_plane_ ? 2 : 1;  // histogram sets: (g, h) sums, then row counts
   int ev = 0;
@@ -930,7 +944,25 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       unsigned short *node_of = d_node_of_.as<unsigned short>() + ch.begin;
       unsigned *list = d_list_.as<unsigned>() + ch.begin;
       if (c == 0) mark();
-      if (l > 0) {  // every row of the chunk steps from its node of level l - 1 to a child
+      void *list_grad = d_list_grad_.p ? static_cast<char *>(d_list_grad_.p) + ch.begin * gsz : nullptr;
+      // in-core levels of moderate width: the step to the children and their row lists in one pass
+      DescendListLaunch dl;
+      dl.geo = geo;
+      dl.rec = l > 0 ? rec(l - 1) : nullptr;
+      dl.parents = L / 2;
+      dl.node_of = node_of;
+      dl.parent_begin = l > 0 ? node_begin(c, l - 1) : nullptr;
+      dl.cursor = pb_.cursor;
+      dl.list = list;
+      dl.grad = list_grad ? grad_c : nullptr;
+      dl.list_grad = list_grad;
+      dl.pair = pair_;
+      dl.use_trick = use_trick;
+      dl.n = rows;
+      const bool fused = l > 0 && fused_steps_ && !multi && descend_lists_applies(dl);
+      if (fused) {
+        launch_descend_lists(dl, s);
+      } else if (l > 0) {  // every row of the chunk steps from its node of level l - 1 to a child
         DescendLaunch d;
         d.geo = geo;
         d.rec = rec(l - 1);
@@ -957,12 +989,18 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       pl.L = L;
       pl.item_rows = item_rows;
       pl.use_trick = use_trick;
-      pl.by_hessian = by_hessian;
+      pl.by_hessian = by_hessian || fused;
+      pl.fused = fused;
+      {  // the next level's fused step counts from cleared cursors
+        DescendListLaunch next = dl;
+        next.parents = L;
+        const bool next_fused = l + 1 < levels_ && fused_steps_ && !multi && descend_lists_applies(next);
+        pl.clear_cursors = next_fused ? std::min(2 * L, max_nodes_) : 0;
+      }
       pl.pb = pb_;
       pl.max_items = max_hist_items_;
       launch_plan_level(pl, s);
-      void *list_grad = d_list_grad_.p ? static_cast<char *>(d_list_grad_.p) + ch.begin * gsz : nullptr;
-      if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
+      if (l > 0 && !fused) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
       if (last) mark();
       for (int k = 0; k < n_sets; ++k) {
         HistLaunch h;

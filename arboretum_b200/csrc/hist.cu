@@ -314,14 +314,16 @@ __global__ void expand_kernel(const long long *__restrict__ compact,
   }
 }
 
-// opt in to more than 48 KB of dynamic shared memory, once per call site
+// opt in to more than 48 KB of dynamic shared memory, once per call site and device (the
+// attribute belongs to the kernel's image on the current device)
 #define ARB_SET_SMEM(kernel, bytes)                                                        \
   do {                                                                                     \
-    static bool done__ = false;                                                            \
-    if (!done__) {                                                                         \
+    static bool done__[kMaxDevices] = {};                                                  \
+    const int dev__ = current_device();                                                    \
+    if (!done__[dev__]) {                                                                  \
       ARB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                     int(bytes)));                                          \
-      done__ = true;                                                                       \
+      done__[dev__] = true;                                                                \
     }                                                                                      \
   } while (0)
 
@@ -332,7 +334,7 @@ void launch_expand(const long long *compact, const long long *parent_hist, long 
   const size_t words_per_node = size_t(NT) * kHistWords * 2;
   const size_t total = size_t(n_parents) * words_per_node;
   const int threads = 256;
-  const int blocks = int(std::min<size_t>((total + threads - 1) / threads, size_t(148) * 16));
+  const int blocks = int(std::min<size_t>((total + threads - 1) / threads, size_t(device_sm_count()) * 16));
   expand_kernel<<<blocks, threads, 0, s>>>(compact, parent_hist, level_hist, built_child, words_per_node,
                                            total);
   ARB_CUDA(cudaGetLastError());
@@ -344,7 +346,7 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
 
 int hist_grid_x(int max_items, int NT) {
   // persistent CTAs: kHistCtasPerSm per SM over all tiles
-  const int per_tile = std::max(8, (kHistCtasPerSm * 148 + NT - 1) / NT);
+  const int per_tile = std::max(8, (kHistCtasPerSm * device_sm_count() + NT - 1) / NT);
   return std::max(1, std::min(max_items, per_tile));
 }
 
@@ -424,7 +426,7 @@ double measure_shared_atomic_peak(int steps, cudaStream_t s) {
   ARB_SET_SMEM(shared_atomic_peak_kernel, smem);
   DevBuf sink;
   sink.alloc(sizeof(int));
-  const int grid = 2 * 148;
+  const int grid = 2 * device_sm_count();
   cudaEvent_t e0, e1;
   ARB_CUDA(cudaEventCreate(&e0));
   ARB_CUDA(cudaEventCreate(&e1));
@@ -473,7 +475,7 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
   const size_t words_per_node = size_t(NT) * kHistWords * 2;
   const size_t total = words_per_node * n_parents;
   const int threads = 256;
-  const int blocks = int(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+  const int blocks = int(std::min<size_t>((total + threads - 1) / threads, size_t(device_sm_count()) * 16));
   launch_overlapped(subtract_kernel, blocks, threads, 0, s, level_hist, parent_hist, built_child, words_per_node,
                     total);
   count_launch();

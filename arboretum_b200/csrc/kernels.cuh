@@ -138,6 +138,33 @@ struct DescendLaunch {
 };
 void launch_descend(const DescendLaunch &a, cudaStream_t s);
 
+// The fused level step: every row steps to a child AND, when the child gets a histogram of
+// its own, goes to the child's row list in the same pass.  Which child of a parent is built
+// is known before the pass from the parent's hessian sums (left sum <= right sum: the left
+// one), and the lists need no level-wide counts first: the left child's list grows upwards
+// from the start of the parent's range of the level above, the right child's downwards from
+// its end, so both end up exactly on the child's own range of the new level's prefix counts.
+// The children's row counts are what the list cursors hold afterwards (the plan kernel
+// reads them there).  For levels of at most kFusedParents parents with a feature-major copy
+// of the bins.
+constexpr int kFusedParents = 1024;
+struct DescendListLaunch {
+  Geometry geo;
+  const NodeRec *rec;            // split records of the parents
+  int parents;                   // nodes of the level above
+  unsigned short *node_of;
+  const unsigned *parent_begin;  // parents + 1 prefix counts of the level above
+  unsigned *cursor;              // per child (kCounterStride apart): rows listed so far; zero on entry
+  unsigned *list;
+  const void *grad;              // gradient records by row (nullptr: none copied)
+  void *list_grad;
+  bool pair;
+  bool use_trick;                // false: both children of every parent are listed
+  size_t n;
+};
+bool descend_lists_applies(const DescendListLaunch &a);
+void launch_descend_lists(const DescendListLaunch &a, cudaStream_t s);
+
 // Prefix counts of a level, the children to build, their lists and the histogram work items.
 struct LevelPlanLaunch {
   const unsigned *child_count;  // per parent (kCounterStride apart): rows that went right, from
@@ -149,6 +176,9 @@ struct LevelPlanLaunch {
   int item_rows;                // rows per work item
   bool use_trick;               // build one child per parent, the other is parent - built
   bool by_hessian;              // choose it by the hessian sums (row shards, row chunks)
+  bool fused = false;           // the level's rows were moved by launch_descend_lists: the children's
+                                // sizes are in pb.cursor, the lists are written already
+  int clear_cursors = 0;        // cursors to clear for the next level's fused step (after reading)
   PlanBuffers pb;
   int max_items;
 };
@@ -169,7 +199,14 @@ void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const P
 void launch_gradients(int objective, int K, size_t n, const float *y, const unsigned char *label,
                       const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s,
                       unsigned long long row0, unsigned round, int quant_bits);
-void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s);
+// reg:linear only, between the two passes of launch_gradients: the tail counts of |g| below
+// the round's maximum (QuantScale::tail)
+void launch_gradient_tails(size_t n, const float *y, const float *yhat, QuantScale *qs, cudaStream_t s);
+// stage 0: the scales from the maxima (and, `tails`, from the tail counts); stage 1: only this
+// rank's scale exponent into qs->neg_s (row shards then take the maximum over the ranks);
+// stage 2: the scales from qs->neg_s
+void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s, bool tails = false,
+                          int stage = 0);
 // float gradients -> fixed-point integers, in place, rounded to nearest
 // (g_q = rint(g * sg), h_q = max(1, rint(h * sh)))
 void launch_quantize_grads(void *grad, size_t n, bool pair, const QuantScale *qs, int quant_bits,

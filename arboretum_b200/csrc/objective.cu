@@ -3,6 +3,7 @@
 // src/core/objective.h:19-113, src/core/garden.cu:45-76,487-503,
 // src/core/garden.h:70-90).
 #include <cfloat>
+#include <cstddef>
 
 #include "kernels.cuh"
 
@@ -88,10 +89,11 @@ __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__r
   overlap_wait();
   float m = 0.0f;
   const float sg = EMIT ? qs->sg : 0.0f;
+  const int lim_g = EMIT ? qs->lim_g : lim;  // the scale may have taken extra bits from the tails
   const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
   auto row = [&](float yi, float yh, size_t i) -> int {
     const float g = yi - yh;
-    if (EMIT) return to_fixed(g, sg, row0 + i, round, 0u, lim);
+    if (EMIT) return to_fixed(g, sg, row0 + i, round, 0u, lim_g);
     m = fmaxf(m, fabsf(g));
     return 0;
   };
@@ -105,6 +107,42 @@ __global__ void grad_linear_kernel(const float *__restrict__ y, const float *__r
     if (EMIT) grad[i] = q;
   }
   if (!EMIT) block_max_to(qs, m, 0.0f);
+}
+
+// reg:linear between the two passes: rows with |g| >= max|g| / 2^(j + 1), j = 0 .. 7
+__global__ void grad_linear_tail_kernel(const float *__restrict__ y, const float *__restrict__ yhat,
+                                        QuantScale *qs, size_t n, size_t n4) {
+  overlap_release();
+  overlap_wait();
+  __shared__ unsigned block_cnt[kTailLevels];
+  if (threadIdx.x < kTailLevels) block_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  const float mx = __uint_as_float(qs->max_g_bits);
+  float t[kTailLevels];
+  unsigned c[kTailLevels];
+#pragma unroll
+  for (int j = 0; j < kTailLevels; ++j) {
+    t[j] = ldexpf(mx, -(j + 1));
+    c[j] = 0;
+  }
+  auto row = [&](float yi, float yh) {
+    const float a = fabsf(yi - yh);
+#pragma unroll
+    for (int j = 0; j < kTailLevels; ++j) c[j] += a >= t[j] ? 1u : 0u;
+  };
+  const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, total = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = tid * 4; i < n4; i += total * 4) {
+    const float4 a = *reinterpret_cast<const float4 *>(y + i), b = *reinterpret_cast<const float4 *>(yhat + i);
+    row(a.x, b.x), row(a.y, b.y), row(a.z, b.z), row(a.w, b.w);
+  }
+  for (size_t i = n4 + tid; i < n; i += total) row(y[i], yhat[i]);
+#pragma unroll
+  for (int j = 0; j < kTailLevels; ++j) {
+    const unsigned w = __reduce_add_sync(0xffffffffu, c[j]);
+    if ((threadIdx.x & 31) == 0 && w) atomicAdd(&block_cnt[j], w);
+  }
+  __syncthreads();
+  if (threadIdx.x < kTailLevels && block_cnt[threadIdx.x]) atomicAdd(&qs->tail[threadIdx.x], block_cnt[threadIdx.x]);
 }
 
 template <bool EMIT>
@@ -163,7 +201,7 @@ __global__ void grad_softmax_kernel(const unsigned char *__restrict__ label,
   block_max_to(qs, mg, mh);
 }
 
-__global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) {
+__global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair, bool tails, int stage) {
   overlap_release();
   overlap_wait();
   // largest |g| < 2^e  =>  |g * 2^(quant_bits - e)| < 2^quant_bits
@@ -171,8 +209,38 @@ __global__ void finish_scales_kernel(QuantScale *qs, int quant_bits, bool pair) 
   const float mg = __uint_as_float(qs->max_g_bits), mh = __uint_as_float(qs->max_h_bits);
   if (mg > 0.0f && mg <= FLT_MAX) frexpf(mg, &eg);
   if (mh > 0.0f && mh <= FLT_MAX) frexpf(mh, &eh);
-  qs->sg = ldexpf(1.0f, quant_bits - eg);
-  qs->inv_sg = ldexp(1.0, eg - quant_bits);
+  int s = quant_bits - eg;  // sg = 2^s
+  if (stage == 2) {
+    s = 1024 - int(qs->neg_s);
+  } else if (tails && mg > 0.0f && mg <= FLT_MAX) {
+    // An int32 sub-histogram takes at most cap = 2^(31 - quant_bits) rows.  Walking the tail
+    // counts from the top bounds the sum of the cap largest |g| by B x max|g|; every
+    // quantised value exceeds |g| sg by less than 1, so sg (B max|g|) + cap < 2^31 keeps the
+    // sums of any such rows inside an int32.  At most 24 - quant_bits bits are added, so that
+    // the largest value stays exactly representable in the float arithmetic of to_fixed.
+    const double cap = ldexp(1.0, 31 - quant_bits);
+    double remaining = cap, B = 0.0, prev = 0.0;
+    for (int j = 0; j < kTailLevels; ++j) {
+      const double cj = double(qs->tail[j]);
+      const double take = fmin(remaining, cj - prev);
+      B += take * ldexp(1.0, -j);
+      remaining -= take;
+      prev = cj;
+    }
+    B += remaining * ldexp(1.0, -kTailLevels);
+    const double room = (ldexp(1.0, 31) - 2.0 * cap) / (B * double(mg));
+    int s_tail = 0;
+    frexp(room, &s_tail);  // room in [2^(s_tail - 1), 2^s_tail)
+    s_tail -= 1;
+    const int most = s + max(0, 24 - quant_bits);
+    s = min(max(s, s_tail), most);
+  }
+  qs->neg_s = unsigned(1024 - s);
+  if (stage == 1) return;
+  qs->sg = ldexpf(1.0f, s);
+  qs->inv_sg = ldexp(1.0, -s);
+  // |g| sg < 2^(eg + s) <= 2^24
+  qs->lim_g = (1 << min(24, max(quant_bits, eg + s))) - 1;
   if (pair) {
     qs->sh = ldexpf(1.0f, quant_bits - eh);
     qs->inv_sh = ldexp(1.0, eh - quant_bits);
@@ -278,7 +346,7 @@ __global__ void fill_kernel(T *dst, size_t n, T v) {
 }
 
 inline int grid_for(size_t n, int threads) {
-  return int(std::min<size_t>((n + threads - 1) / threads, size_t(148) * 16));
+  return int(std::min<size_t>((n + threads - 1) / threads, size_t(device_sm_count()) * 16));
 }
 
 }  // namespace
@@ -287,7 +355,8 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
                       const float *yhat, void *grad, QuantScale *qs, bool emit, cudaStream_t s,
                       unsigned long long row0, unsigned round, int quant_bits) {
   const int lim = (1 << quant_bits) - 1;
-  if (!emit) ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, 2 * sizeof(unsigned), s));
+  if (!emit)  // the maxima, the scale exponent, the clamp and the tail counts
+    ARB_CUDA(cudaMemsetAsync(&qs->max_g_bits, 0, sizeof(QuantScale) - offsetof(QuantScale, max_g_bits), s));
   const int threads = 256;
   const int grid = grid_for(n, threads);
   const bool aligned = (reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(yhat) |
@@ -310,9 +379,18 @@ void launch_gradients(int objective, int K, size_t n, const float *y, const unsi
   count_launch();
 }
 
-void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s) {
+void launch_finish_scales(QuantScale *qs, int K, int quant_bits, bool pair, cudaStream_t s, bool tails,
+                          int stage) {
   (void)K;
-  launch_overlapped(finish_scales_kernel, 1, 1, 0, s, qs, quant_bits, pair);
+  launch_overlapped(finish_scales_kernel, 1, 1, 0, s, qs, quant_bits, pair, tails, stage);
+  count_launch();
+}
+
+void launch_gradient_tails(size_t n, const float *y, const float *yhat, QuantScale *qs, cudaStream_t s) {
+  const int threads = 256;
+  const bool aligned = (reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(yhat)) % 16 == 0;
+  const size_t n4 = aligned ? n / 4 * 4 : 0;
+  launch_overlapped(grad_linear_tail_kernel, grid_for(n4 / 4 + (n - n4), threads), threads, 0, s, y, yhat, qs, n, n4);
   count_launch();
 }
 

@@ -10,6 +10,8 @@
 //   min(thr[k], float((s[i] + s[i-1]) * 0.5)).
 // Binning then maps all features of all rows in one pass over the row-major fp32
 // matrix and writes the row-major bin matrix the histogram kernels read.
+#include <atomic>
+
 #include <cub/device/device_radix_sort.cuh>
 
 #include "kernels.cuh"
@@ -269,6 +271,8 @@ size_t thresholds_scratch_words(size_t n) { return (n + kScanTile - 1) / kScanTi
 void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
                        cudaStream_t s) {
   fill_inf_kernel<<<ceil_div(hist_size, 256), 256, 0, s>>>(thr, hist_size);  // io.cu:387
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
   if (n < 2) return;
   const int nblocks = int((n + kScanTile - 1) / kScanTile);
   const size_t seg = std::max<size_t>(1, n / size_t(hist_size));  // io.cu:376-377
@@ -276,7 +280,7 @@ void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr,
   border_scan_kernel<<<1, 1024, 0, s>>>(scratch, nblocks);
   border_apply_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, seg, hist_size, scratch, thr);
   ARB_CUDA(cudaGetLastError());
-  count_launch(4);
+  count_launch(3);
 }
 
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
@@ -296,7 +300,7 @@ void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *b
   if (n == 0) return;
   const int words = int(pitch / 4);
   const size_t total = n * size_t(words);
-  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
   pad_rows_kernel<<<grid, 256, 0, s>>>(raw, F, n, reinterpret_cast<unsigned *>(bins), words);
   ARB_CUDA(cudaGetLastError());
   count_launch();
@@ -306,7 +310,7 @@ void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned 
                           int bin_bytes, cudaStream_t s) {
   if (n == 0 || ccol == 0) return;
   const size_t total = n * size_t(ccol);
-  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
   if (bin_bytes == 1)
     place_columns_kernel<unsigned char><<<grid, 256, 0, s>>>(static_cast<const unsigned char *>(src), n, ccol, f0,
                                                             bins, pitch);
@@ -319,7 +323,7 @@ void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned 
 
 void launch_u8_to_f32(const unsigned char *src, float *dst, size_t count, cudaStream_t s) {
   if (count == 0) return;
-  const int grid = int(std::min<size_t>((count + 255) / 256, size_t(148) * 32));
+  const int grid = int(std::min<size_t>((count + 255) / 256, size_t(device_sm_count()) * 32));
   u8_to_f32_kernel<<<grid, 256, 0, s>>>(src, dst, count);
   ARB_CUDA(cudaGetLastError());
   count_launch();
@@ -353,7 +357,7 @@ void launch_binning(const float *X, size_t n, int F, const float *thr, const int
   if (n == 0) return;
   const int threads = 256;
   const size_t total = n * size_t(F);
-  const int grid = int(std::min<size_t>((total + threads - 1) / threads, size_t(148) * 32));
+  const int grid = int(std::min<size_t>((total + threads - 1) / threads, size_t(device_sm_count()) * 32));
   if (bin_bytes == 1)
     binning_kernel<unsigned char><<<grid, threads, 0, s>>>(X, n, F, thr, fsize, hist_size, missing_bin,
                                                            bins, pitch);
@@ -381,8 +385,9 @@ constexpr long long kStaticThresholdRows = 1ll << 26;  // 67,108,864 values per 
 constexpr size_t kStaticScratchWords = size_t(kStaticThresholdRows / kScanTile) + 1;
 // 128 KB of device memory per GPU that loads the library, held until exit
 static __device__ __align__(256) unsigned g_threshold_scratch[kStaticScratchWords];
-constexpr int kMaxDevices = 64;
-unsigned *g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+// device address of the array, per device; filled on a device's first call (two threads that
+// make it together store the same value)
+std::atomic<unsigned *> g_scratch_ptr[kMaxDevices];
 }  // namespace
 }  // namespace arb
 
@@ -401,16 +406,18 @@ extern "C" const char *AThresholdsNoAlloc(const float *sorted_device, long long 
     int dev = 0;
     ARB_CUDA(cudaGetDevice(&dev));
     ARB_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
-    if (!g_scratch_ptr[dev]) {
+    unsigned *scratch = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
       // In host code the array's name is only a handle: the kernels need the address
       // the symbol has on THIS device, which the runtime hands out here.
       void *p = nullptr;
       ARB_CUDA(cudaGetSymbolAddress(&p, g_threshold_scratch));
-      g_scratch_ptr[dev] = static_cast<unsigned *>(p);
+      scratch = static_cast<unsigned *>(p);
+      g_scratch_ptr[dev].store(scratch, std::memory_order_release);
     }
     // block counts are rewritten in full for the blocks of this call, so nothing of an
     // earlier call's contents is read: no clearing is needed
-    launch_thresholds(sorted_device, size_t(n), hist_size, thr_device, g_scratch_ptr[dev],
+    launch_thresholds(sorted_device, size_t(n), hist_size, thr_device, scratch,
                       static_cast<cudaStream_t>(stream));
     return nullptr;
   } catch (const std::exception &e) {

@@ -273,12 +273,7 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   // to 8 CTAs, which all re-read the tile.  A CTA of 1024 threads with 64 registers each
   // has an SM to itself, so more CTAs than SMs would only run as a second wave: the gains
   // they share out would wait in line all the same, after re-reading the tile.
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    ARB_CUDA(cudaGetDevice(&dev));
-    ARB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  }
+  const int sms = device_sm_count();
   int parts = kBinsPerThread;
   while (parts > 1 && a.L * a.geo.NT * parts > sms) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);

@@ -79,6 +79,10 @@ const char *AGetLevelStats(VoidPointer garden, int level, unsigned *node_begin, 
 const char *AGetLevelStatsOf(VoidPointer garden, int tree_in_round, int level, unsigned *node_begin,
                              float *gain, int *fid, int *bin, double *left_g, double *left_h,
                              double *tot_g, double *tot_h, unsigned *left_count);
+/* The fixed-point steps of the last round: every gradient (hessian) entered the histograms
+ * as an integer multiple of *g_step (*h_step), off from its float value by less than one
+ * step. */
+const char *AGetGradientStep(VoidPointer garden, double *g_step, double *h_step);
 /* CUDA-event timing of the kernel classes: switch on, then read a JSON summary. */
 const char *ASetProfile(VoidPointer garden, int on);
 const char *AGetTimings(VoidPointer garden, const char **json);
