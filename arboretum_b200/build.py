@@ -14,8 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "_build")
 LIB = os.path.join(HERE, "libarboretum.so")
-SOURCES = ["abi.cu", "garden.cu", "hist.cu", "split.cu", "partition.cu", "objective.cu", "quantize.cu"]
-HEADERS = ["common.cuh", "config.h", "gain.cuh", "garden.h", "json.h", "kernels.cuh"]
+SOURCES = ["abi.cu", "garden.cu", "hist.cu", "split.cu", "partition.cu", "objective.cu", "quantize.cu", "exchange.cu"]
+HEADERS = ["common.cuh", "config.h", "gain.cuh", "garden.h", "json.h", "kernels.cuh", "exchange.h"]
 NVCC = os.environ.get("NVCC", "nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "--fmad=false", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-ccbin", "/usr/bin/g++"]

@@ -480,7 +480,7 @@ static const char *build_histogram(const void *bins, int bin_bytes, int64_t nrow
   ARB_CHECK(bin_bytes == 1 || bin_bytes == 2, "bin_bytes must be 1 or 2");
   ARB_CHECK(nrow > 0 && ncol > 0 && n_nodes > 0, "bad shape");
   ARB_CHECK(hist_size > 0 && hist_size < 2048 && (bin_bytes == 2 || hist_size < 256), "bad hist_size");
-  ARB_CHECK(quant_bits >= 10 && quant_bits <= 20, "quant_bits must be in [10, 20]");
+  ARB_CHECK(quant_bits >= 10 && quant_bits <= 22, "quant_bits must be in [10, 22]");
   ARB_CHECK(nrow < (int64_t(1) << 31), "row count must be below 2^31");
   const size_t n = size_t(nrow);
   // The arrays below drive gathers and shared-memory updates on the device; anything out of

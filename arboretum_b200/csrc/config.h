@@ -45,7 +45,7 @@ struct Internals {  // param.h:52-62 (defaults :54-57)
   bool upload_features = true;
   int hist_size = 255;
   // additive keys of this build
-  int quant_bits = 18;   // fixed-point bits of a gradient (see hist.cu)
+  int quant_bits = 0;    // fixed-point bits of a gradient (see hist.cu); 0 = by the row count
   int device = -1;       // CUDA device ordinal, -1 = current device
   bool missing_bin = true;  // NaN -> dedicated bin id hist_size (always right)
   long long chunk_rows = 0;  // out-of-core: rows per streamed chunk, 0 = in-core

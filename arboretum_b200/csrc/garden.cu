@@ -4,6 +4,7 @@
 // synchronisation: node sizes, work lists and split records stay in device
 // memory, and the host reads the finished tree back once per tree.
 #include "garden.h"
+#include "exchange.h"
 
 #include <algorithm>
 #include <cmath>
@@ -452,6 +453,7 @@ class Builder {
   int F_, K_, levels_, max_nodes_, nb_stride_;
   bool pair_;
   Geometry geo_;
+  int qb_ = 18;        // fixed-point bits of a gradient
   int item_cap_;       // rows an int32 sub-histogram may take (2^(31 - quant_bits))
   int max_hist_items_;
   std::default_random_engine rnd_;  // garden.cu:87
@@ -465,6 +467,8 @@ class Builder {
   // (gradient, hessian) objectives with min_leaf_size > 1 keep a second histogram that counts
   // rows (the reference's count histogram, gain.cu:125-134): the reg:linear kernel run on a
   // "gradient" array of ones; same level buffers, same subtraction, same exchange
+  PeerExchange *xchg_ = nullptr;  // row shards of one box: the level exchange over peer memory
+  PinnedBuf h_xchg_status_;
   bool fused_steps_ = true;  // ARBORETUM_NO_FUSED_STEP in the environment: the three-pass level step
   bool count_plane_ = false;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
@@ -556,8 +560,37 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   geo_.bins_cm = d->d_bins_cm.as<unsigned char>();
   geo_.cm_rows = n_;
 
-  const int qb = cfg.internal.quant_bits;
-  ARB_CHECK(qb >= 10 && qb <= 20, "internals.quant_bits must be in [10, 20]");
+  size_t n_global = n_;
+  if (g->shards.world > 1 && g->shards.allgather) {
+    // where this shard's rows lie in the whole data set (shards are contiguous, in rank order)
+    const int world = g->shards.world;
+    DevBuf d_cnt;
+    d_cnt.alloc(sizeof(unsigned long long) * (world + 1));
+    const unsigned long long mine = n_;
+    ARB_CUDA(cudaMemcpyAsync(d_cnt.as<unsigned long long>() + world, &mine, sizeof mine, cudaMemcpyHostToDevice, s));
+    if (g->shards.allgather(g->shards.ctx, d_cnt.as<unsigned long long>() + world, d_cnt.p, sizeof mine, s) != 0)
+      throw std::runtime_error("row-count all-gather failed");
+    std::vector<unsigned long long> counts(world);
+    ARB_CUDA(cudaMemcpyAsync(counts.data(), d_cnt.p, sizeof(unsigned long long) * world, cudaMemcpyDeviceToHost, s));
+    ARB_CUDA(cudaStreamSynchronize(s));
+    for (int r = 0; r < g->shards.rank; ++r) row_offset_ += counts[r];
+    n_global = 0;
+    for (unsigned long long c : counts) n_global += size_t(c);
+  }
+  // Fixed-point bits of a gradient.  More bits mean smaller rounding errors in the sums (a
+  // node's gain is good to about 2 x 0.4 x step x sqrt(rows) / |sum g|) but fewer rows per
+  // int32 sub-histogram (2^(31 - bits)) and so more of them to store and add up.  Unless the
+  // configuration names a value, the whole data set's row count decides (so that shards and
+  // row chunks quantise like one GPU): about a thousand sub-histograms for the root level,
+  // between 18 bits (from 4 M rows) and 22 (up to half a million).
+  qb_ = cfg.internal.quant_bits;
+  if (qb_ == 0) {
+    int lg = 0;
+    while ((size_t(1) << lg) < std::max<size_t>(512, n_global / 1024)) ++lg;
+    qb_ = std::min(22, std::max(18, 31 - lg));
+  }
+  const int qb = qb_;
+  ARB_CHECK(qb >= 10 && qb <= 22, "internals.quant_bits must be 0 (chosen by the row count) or in [10, 22]");
   item_cap_ = 1 << (31 - qb);
   // items of one level: sum over nodes of ceil(len / item_rows) <= rows / item_rows + nodes, and
   // item_rows is ceil(rows / target) unless kMinItemRows (fewer items) or item_cap_ binds
@@ -604,20 +637,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   }
   // garden.cu:105: y_hat starts at IntoInternal(initial_y)
   launch_fill(d_yhat_.as<float>(), n_ * K_, g->InternalInitialY(), s);
-  if (g->shards.world > 1 && g->shards.allgather) {
-    // where this shard's rows lie in the whole data set (shards are contiguous, in rank order)
-    const int world = g->shards.world;
-    DevBuf d_cnt;
-    d_cnt.alloc(sizeof(unsigned long long) * (world + 1));
-    const unsigned long long mine = n_;
-    ARB_CUDA(cudaMemcpyAsync(d_cnt.as<unsigned long long>() + world, &mine, sizeof mine, cudaMemcpyHostToDevice, s));
-    if (g->shards.allgather(g->shards.ctx, d_cnt.as<unsigned long long>() + world, d_cnt.p, sizeof mine, s) != 0)
-      throw std::runtime_error("row-count all-gather failed");
-    std::vector<unsigned long long> counts(world);
-    ARB_CUDA(cudaMemcpyAsync(counts.data(), d_cnt.p, sizeof(unsigned long long) * world, cudaMemcpyDeviceToHost, s));
-    ARB_CUDA(cudaStreamSynchronize(s));
-    for (int r = 0; r < g->shards.rank; ++r) row_offset_ += counts[r];
-  }
   trace.lap("per-row state");
   // level state
   {
@@ -674,13 +693,21 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const size_t compact_bytes = size_t(std::max(1, max_nodes_ / 2)) * geo_.NT * kHistWords * 2 * sizeof(long long);
   // made here, not inside a round: an allocation that fails between two collectives would
   // leave the other ranks waiting inside theirs
-  if (sharded && cfg.internal.use_hist_subtraction_trick) d_compact_.alloc(compact_bytes);
+  if (sharded && std::getenv("ARBORETUM_NO_PEER_EXCHANGE") == nullptr) {
+    // what the ranks exchange per level: the built nodes' histograms (with the subtraction
+    // trick one child per parent below the root), for every histogram set
+    const size_t root_bytes = size_t(geo_.NT) * kHistWords * 2 * sizeof(long long);
+    const size_t most = cfg.internal.use_hist_subtraction_trick ? std::max(compact_bytes, root_bytes) : level_hist_bytes;
+    xchg_ = PeerExchange::Create((count_plane_ ? 2 : 1) * most, g->shards, s);
+    if (xchg_) h_xchg_status_.alloc(sizeof(int));
+  }
+  if (sharded && cfg.internal.use_hist_subtraction_trick && !xchg_) d_compact_.alloc(compact_bytes);
   if (count_plane_) {
     d_ones_.alloc(n_ * sizeof(int));
     launch_fill_u32(d_ones_.as<unsigned>(), n_, 1u, s);
     d_cnt_hist_[0].alloc(level_hist_bytes);
     d_cnt_hist_[1].alloc(level_hist_bytes);
-    if (sharded && cfg.internal.use_hist_subtraction_trick) d_compact_cnt_.alloc(compact_bytes);
+    if (sharded && cfg.internal.use_hist_subtraction_trick && !xchg_) d_compact_cnt_.alloc(compact_bytes);
   }
   round_rec_.resize(K_);
   round_nb_.resize(K_);
@@ -745,6 +772,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
 }
 
 Builder::~Builder() {
+  delete xchg_;
   if (events_made_) {
     for (auto &e : ev_) cudaEventDestroy(e);
     for (auto &e : ev_tree_) cudaEventDestroy(e);
@@ -807,26 +835,30 @@ void Builder::UpdateGrad() {  // objective.cu:28-56
   const unsigned char *labels = data->d_labels.p ? data->d_labels.as<unsigned char>() : d_label_.as<unsigned char>();
   // pass 1: the round's largest |gradient| and hessian (they fix the fixed-point scale)
   launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
-                   d_qs_.as<QuantScale>(), false, s, row_offset_, round_, g_->cfg.internal.quant_bits);
+                   d_qs_.as<QuantScale>(), false, s, row_offset_, round_, qb_);
   // row shards must share one fixed-point scale: take the maxima over all ranks
-  if (g_->allreduce_max &&
-      g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
+  if (xchg_)
+    xchg_->AllMax(&d_qs_.as<QuantScale>()->max_g_bits, 2, s);
+  else if (g_->allreduce_max &&
+           g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->max_g_bits, 2, s) != 0)
     throw std::runtime_error("gradient-scale allreduce failed");
   // reg:linear targets may have outliers: the scale also looks at how many gradients come
   // near the largest one (see QuantScale); row shards agree on the coarsest scale
   const bool tails = g_->cfg.objective == kLinearRegression;
   if (tails) launch_gradient_tails(n_, y, d_yhat_.as<float>(), d_qs_.as<QuantScale>(), s);
   if (tails && g_->allreduce_max) {
-    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, true, 1);
-    if (g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->neg_s, 1, s) != 0)
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, qb_, pair_, s, true, 1);
+    if (xchg_)
+      xchg_->AllMax(&d_qs_.as<QuantScale>()->neg_s, 1, s);
+    else if (g_->allreduce_max(g_->allreduce_ctx, &d_qs_.as<QuantScale>()->neg_s, 1, s) != 0)
       throw std::runtime_error("gradient-scale allreduce failed");
-    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, true, 2);
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, qb_, pair_, s, true, 2);
   } else {
-    launch_finish_scales(d_qs_.as<QuantScale>(), K_, g_->cfg.internal.quant_bits, pair_, s, tails, 0);
+    launch_finish_scales(d_qs_.as<QuantScale>(), K_, qb_, pair_, s, tails, 0);
   }
   // pass 2: the gradients as fixed-point integers
   launch_gradients(g_->cfg.objective, K_, n_, y, labels, d_yhat_.as<float>(), d_grad_.p,
-                   d_qs_.as<QuantScale>(), true, s, row_offset_, round_, g_->cfg.internal.quant_bits);
+                   d_qs_.as<QuantScale>(), true, s, row_offset_, round_, qb_);
   ++round_;
   if (g_->profile) {
     ARB_CUDA(cudaEventRecord(ev_[1], s));
@@ -924,13 +956,18 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     // the exchanged buffer holds those alone and the siblings follow from the parents after
     // the exchange.
     const bool compact = trick_level && g_->allreduce != nullptr;
+    // words of one histogram set that the ranks exchange at this level
+    const size_t xwords = size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2;
     long long *hist[2], *reduce_to[2];
     const long long *parent_hist[2];
     for (int k = 0; k < n_sets; ++k) {
       DevBuf *levels = k == 0 ? d_hist_ : d_cnt_hist_;
       hist[k] = levels[l & 1].as<long long>();
       parent_hist[k] = l > 0 ? levels[(l - 1) & 1].as<long long>() : nullptr;
-      reduce_to[k] = compact ? (k == 0 ? d_compact_ : d_compact_cnt_).as<long long>() : hist[k];
+      if (xchg_)  // summed where the peers will read it; the sets lie back to back
+        reduce_to[k] = xchg_->send_buffer() + size_t(k) * xwords;
+      else
+        reduce_to[k] = compact ? (k == 0 ? d_compact_ : d_compact_cnt_).as<long long>() : hist[k];
       if (multi)
         ARB_CUDA(cudaMemsetAsync(reduce_to[k], 0, size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
     }
@@ -1033,16 +1070,20 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       Release(c);
     }
     mark();
-    if (g_->allreduce) {
-      const size_t count = size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2;
+    if (xchg_) {
+      xchg_->AllReduce(size_t(n_sets) * xwords, s);
+    } else if (g_->allreduce) {
       for (int k = 0; k < n_sets; ++k)
-        if (g_->allreduce(g_->allreduce_ctx, reduce_to[k], count, s) != 0)
+        if (g_->allreduce(g_->allreduce_ctx, reduce_to[k], xwords, s) != 0)
           throw std::runtime_error("histogram allreduce failed");
     }
     mark();
     for (int k = 0; k < n_sets; ++k) {
+      const long long *summed = xchg_ ? xchg_->result_buffer() + size_t(k) * xwords : reduce_to[k];
+      if (xchg_ && !compact)  // a whole level (the root, or no subtraction): straight to its buffer
+        ARB_CUDA(cudaMemcpyAsync(hist[k], summed, xwords * sizeof(long long), cudaMemcpyDeviceToDevice, s));
       if (compact)
-        launch_expand(reduce_to[k], parent_hist[k], hist[k], pb_.built_child, L / 2, geo_.NT, s);
+        launch_expand(summed, parent_hist[k], hist[k], pb_.built_child, L / 2, geo_.NT, s);
       else if (trick_level && multi)
         launch_subtract(hist[k], parent_hist[k], pb_.built_child, L / 2, geo_.NT, s);
     }
@@ -1104,7 +1145,11 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   ARB_CUDA(cudaMemcpyAsync(h_leaf_w_.p, d_leaf_w_.p, d_leaf_w_.bytes, cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
                            cudaMemcpyDeviceToHost, s));
+  if (xchg_) ARB_CUDA(cudaMemcpyAsync(h_xchg_status_.p, xchg_->device_status(), sizeof(int), cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaStreamSynchronize(s));
+  if (xchg_ && *h_xchg_status_.as<int>() != 0)
+    throw std::runtime_error("a peer GPU did not answer within the time limit (exchange step " +
+                             std::to_string(*h_xchg_status_.as<int>()) + "): the tree is incomplete");
   {  // per-level prefix counts of the whole data set = sums over the row chunks
     const size_t per_chunk = size_t(levels_ + 1) * nb_stride_;
     h_nb_total_.assign(per_chunk, 0u);

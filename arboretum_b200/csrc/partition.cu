@@ -502,13 +502,15 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
 // list with one global atomicAdd per child it has rows for, and the rows (and their gradient
 // records) are written at the reserved positions: upwards from the start of the parent's
 // range for a left child, downwards from its end for a right child.
-constexpr int kFusedRows = 256 * kWideRows;
+constexpr int kFusedSteps = 4;      // a lane takes kFusedSteps x kWideRows rows per turn
+constexpr int kFusedRows = 256 * kWideRows * kFusedSteps;
 constexpr int kBallotParents = 2;   // up to here ranks come from ballots
 constexpr int kMatchParents = 8;    // up to here from __match_any_sync; beyond, one atomic per row
 constexpr unsigned kListLeft = 1u << 13, kListRight = 1u << 14;  // in a packed split: which children are listed
+constexpr unsigned kNotListed = 0xffffffffu;
 
 template <typename BIN_T, typename GRAD_T>  // GRAD_T: int2 / int copied along; char: none
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256, 3)
 descend_list_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
                     const NodeRec *__restrict__ rec, const int P, unsigned short *__restrict__ node_of,
                     const unsigned *__restrict__ parent_begin, unsigned *__restrict__ cursor,
@@ -537,67 +539,72 @@ descend_list_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_r
   int parity = 0;
   for (size_t base = size_t(blockIdx.x) * kFusedRows; base < n; base += size_t(gridDim.x) * kFusedRows, parity ^= 1) {
     unsigned *rank_of = s_rank[parity];
-    const size_t r0 = base + size_t(threadIdx.x) * kWideRows;
-    const bool whole = r0 + kWideRows <= n;
-    uint4 nodes = make_uint4(0u, 0u, 0u, 0u);  // eight nodes, two to a word (low half first)
-    if (P > 1 && r0 < n) nodes = *reinterpret_cast<const uint4 *>(node_of + r0);  // rows are padded to 8
-    unsigned nw[4] = {nodes.x, nodes.y, nodes.z, nodes.w};
-    unsigned ent[kWideRows];
-    int binv[kWideRows];
+    // per row of the lane: child << 16 | rank among the CTA's rows of that child this turn
+    // (a turn has 8192 rows, a level at most 2048 children), or kNotListed
+    unsigned slot[kFusedSteps * kWideRows];
 #pragma unroll
-    for (int k = 0; k < kWideRows; ++k) {
-      const bool valid = r0 + k < n;
-      const unsigned node = valid ? (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu : 0u;
-      if (!valid) nw[k >> 1] &= ~(0xffffu << (16 * (k & 1)));
-      ent[k] = table[node];
-      const unsigned fid = ent[k] >> 16;
-      binv[k] = -1;  // no split, or past the end: left
-      if (fid != 0xffffu && valid) binv[k] = int(cm[size_t(fid) * cm_rows + r0 + k]);
-    }
-    unsigned out[4] = {0u, 0u, 0u, 0u};
-    unsigned key[kWideRows];   // 2 * parent + side of a listed row, 0xffffffff: not listed
-    unsigned rank[kWideRows];
-    GRAD_T gv[kWideRows];
+    for (int step = 0; step < kFusedSteps; ++step) {
+      // step by step a warp covers 256 consecutive rows, a lane 8 of them
+      const size_t r0 = base + (size_t(step) * 256 + threadIdx.x) * kWideRows;
+      const bool whole = r0 + kWideRows <= n;
+      uint4 nodes = make_uint4(0u, 0u, 0u, 0u);  // eight nodes, two to a word (low half first)
+      if (P > 1 && r0 < n) nodes = *reinterpret_cast<const uint4 *>(node_of + r0);
+      unsigned nw[4] = {nodes.x, nodes.y, nodes.z, nodes.w};
+      unsigned ent[kWideRows];
+      int binv[kWideRows];
 #pragma unroll
-    for (int k = 0; k < kWideRows; ++k) {
-      const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
-      const int sbin = int(ent[k] & 0x7ffu);
-      const bool right = (ent[k] & kCatFlag) ? (binv[k] >= 0 && binv[k] != sbin) : binv[k] > sbin;
-      const unsigned child = 2u * node + (right ? 1u : 0u);
-      out[k >> 1] |= child << (16 * (k & 1));
-      const bool listed = r0 + k < n && (ent[k] & (right ? kListRight : kListLeft));
-      key[k] = listed ? child : 0xffffffffu;
-      if (sizeof(GRAD_T) > 1 && listed) gv[k] = grad[r0 + k];  // in flight while the ranks are taken
-    }
-    if (whole) {
-      *reinterpret_cast<uint4 *>(node_of + r0) = make_uint4(out[0], out[1], out[2], out[3]);
-    } else {
-      for (int k = 0; r0 + k < n; ++k) node_of[r0 + k] = (unsigned short)((out[k >> 1] >> (16 * (k & 1))) & 0xffffu);
-    }
+      for (int k = 0; k < kWideRows; ++k) {
+        const bool valid = r0 + k < n;
+        if (!valid) nw[k >> 1] &= ~(0xffffu << (16 * (k & 1)));  // what lies past the last row is no node
+        const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+        ent[k] = table[node];
+        const unsigned fid = ent[k] >> 16;
+        binv[k] = -1;  // no split, or past the end: left
+        if (fid != 0xffffu && valid) binv[k] = int(cm[size_t(fid) * cm_rows + r0 + k]);
+      }
+      unsigned out[4] = {0u, 0u, 0u, 0u};
+      unsigned key[kWideRows];
 #pragma unroll
-    for (int k = 0; k < kWideRows; ++k) {
-      rank[k] = 0;
-      if (P <= kBallotParents) {  // the few children of the level, one ballot each
-        for (unsigned c = 0; c < unsigned(2 * P); ++c) {
-          const unsigned m = __ballot_sync(0xffffffffu, key[k] == c);
-          if (m == 0) continue;
-          const int leader = __ffs(m) - 1;
-          unsigned first = 0;
-          if (lane == leader) first = atomicAdd(&rank_of[c], unsigned(__popc(m)));
-          first = __shfl_sync(0xffffffffu, first, leader);
-          if (key[k] == c) rank[k] = first + unsigned(__popc(m & lt));
+      for (int k = 0; k < kWideRows; ++k) {
+        const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+        const int sbin = int(ent[k] & 0x7ffu);
+        const bool right = (ent[k] & kCatFlag) ? (binv[k] >= 0 && binv[k] != sbin) : binv[k] > sbin;
+        const unsigned child = 2u * node + (right ? 1u : 0u);
+        out[k >> 1] |= child << (16 * (k & 1));
+        const bool listed = r0 + k < n && (ent[k] & (right ? kListRight : kListLeft));
+        key[k] = listed ? child : kNotListed;
+      }
+      if (whole) {
+        *reinterpret_cast<uint4 *>(node_of + r0) = make_uint4(out[0], out[1], out[2], out[3]);
+      } else {
+        for (int k = 0; r0 + k < n; ++k) node_of[r0 + k] = (unsigned short)((out[k >> 1] >> (16 * (k & 1))) & 0xffffu);
+      }
+#pragma unroll
+      for (int k = 0; k < kWideRows; ++k) {
+        unsigned rank = 0;
+        if (P <= kBallotParents) {  // the few children of the level, one ballot each
+          for (unsigned c = 0; c < unsigned(2 * P); ++c) {
+            const unsigned m = __ballot_sync(0xffffffffu, key[k] == c);
+            if (m == 0) continue;
+            const int leader = __ffs(m) - 1;
+            unsigned first = 0;
+            if (lane == leader) first = atomicAdd(&rank_of[c], unsigned(__popc(m)));
+            first = __shfl_sync(0xffffffffu, first, leader);
+            if (key[k] == c) rank = first + unsigned(__popc(m & lt));
+          }
+        } else if (P <= kMatchParents) {
+          const unsigned peers = __match_any_sync(0xffffffffu, key[k]);
+          if (key[k] != kNotListed) {
+            const int leader = __ffs(peers) - 1;
+            unsigned first = 0;
+            if (lane == leader) first = atomicAdd(&rank_of[key[k]], unsigned(__popc(peers)));
+            first = __shfl_sync(peers, first, leader);
+            rank = first + unsigned(__popc(peers & lt));
+          }
+        } else if (key[k] != kNotListed) {
+          rank = atomicAdd(&rank_of[key[k]], 1u);
         }
-      } else if (P <= kMatchParents) {
-        const unsigned peers = __match_any_sync(0xffffffffu, key[k]);
-        if (key[k] != 0xffffffffu) {
-          const int leader = __ffs(peers) - 1;
-          unsigned first = 0;
-          if (lane == leader) first = atomicAdd(&rank_of[key[k]], unsigned(__popc(peers)));
-          first = __shfl_sync(peers, first, leader);
-          rank[k] = first + unsigned(__popc(peers & lt));
-        }
-      } else if (key[k] != 0xffffffffu) {
-        rank[k] = atomicAdd(&rank_of[key[k]], 1u);
+        slot[step * kWideRows + k] = key[k] == kNotListed ? kNotListed : (key[k] << 16) | rank;
       }
     }
     __syncthreads();
@@ -610,12 +617,17 @@ descend_list_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_r
     }
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < kWideRows; ++k) {
-      if (key[k] == 0xffffffffu) continue;
-      const unsigned parent = key[k] >> 1, at = s_base[key[k]] + rank[k];
-      const unsigned pos = (key[k] & 1u) ? pbeg[parent + 1] - 1u - at : pbeg[parent] + at;
-      list[pos] = unsigned(r0 + k);
-      if (sizeof(GRAD_T) > 1) list_grad[pos] = gv[k];
+    for (int step = 0; step < kFusedSteps; ++step) {
+      const size_t r0 = base + (size_t(step) * 256 + threadIdx.x) * kWideRows;
+#pragma unroll
+      for (int k = 0; k < kWideRows; ++k) {
+        const unsigned sl = slot[step * kWideRows + k];
+        if (sl == kNotListed) continue;
+        const unsigned child = sl >> 16, parent = child >> 1, at = s_base[child] + (sl & 0xffffu);
+        const unsigned pos = (child & 1u) ? pbeg[parent + 1] - 1u - at : pbeg[parent] + at;
+        list[pos] = unsigned(r0 + k);
+        if (sizeof(GRAD_T) > 1) list_grad[pos] = grad[r0 + k];
+      }
     }
   }
 }

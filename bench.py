@@ -81,26 +81,56 @@ def make_c1(n, seed):  # small regression: y = w.x + 0.5 x0 x1 + N(0, 0.1)
     return X, y.astype(np.float32), None
 
 
-def make_c3(n, seed):  # wide table, 20 % missing; the 10 categorical columns enter as numbers
+_C3_CACHE = {}
+
+
+def _c3(n, seed):
+    """Wide table: 1990 log-normal columns with 20 % of the cells missing and 10 categorical
+    columns (cardinality 50 .. 1000, Zipf-distributed codes); the target is the sum of 30
+    column effects plus noise."""
+    key = (n, seed)
+    if key in _C3_CACHE:
+        return _C3_CACHE[key]
     rng = np.random.default_rng([3, seed])
-    F = 2000
+    F, n_cat = 2000, 10
+    Fd = F - n_cat
     prm = np.random.default_rng(3)
     cols = prm.choice(F, 30, replace=False)
     coef = prm.normal(size=30).astype(np.float32)
-    cards = prm.integers(50, 1001, size=10)
-    X = np.empty((n, F), dtype=np.float32)
+    cards = prm.integers(50, 1001, size=n_cat)
+    offsets = [prm.normal(size=int(c)).astype(np.float32) for c in cards]
+    X = np.empty((n, Fd), dtype=np.float32)
     y = rng.normal(0, 0.5, n).astype(np.float32)
-    for lo in range(0, F, 100):  # column blocks keep the temporaries small
-        blk = np.exp(rng.standard_normal((n, 100), dtype=np.float32))
-        if lo == F - 100:
-            for j in range(10):
-                blk[:, 90 + j] = np.minimum(rng.zipf(1.2, n), cards[j]).astype(np.float32)
+    for lo in range(0, Fd, 100):  # column blocks keep the temporaries small
+        w = min(100, Fd - lo)
+        blk = np.exp(rng.standard_normal((n, w), dtype=np.float32))
         for k, c in enumerate(cols):
-            if lo <= c < lo + 100:
+            if lo <= c < lo + w:
                 y += coef[k] * np.log1p(blk[:, c - lo])
-        blk[rng.random((n, 100), dtype=np.float32) < 0.2] = np.nan
-        X[:, lo:lo + 100] = blk
-    return X, y.astype(np.float32), None
+        blk[rng.random((n, w), dtype=np.float32) < 0.2] = np.nan
+        X[:, lo:lo + w] = blk
+    cat = np.empty((n, n_cat), dtype=np.uint32)
+    for j in range(n_cat):
+        cat[:, j] = np.minimum(rng.zipf(1.2, n), cards[j]) - 1
+        for k, c in enumerate(cols):
+            if c == Fd + j:
+                y += offsets[j][cat[:, j]]
+    _C3_CACHE.clear()
+    _C3_CACHE[key] = (X, cat, y.astype(np.float32))
+    return _C3_CACHE[key]
+
+
+def make_c3(n, seed):
+    X, _, y = _c3(n, seed)
+    return X, y, None
+
+
+def make_c3_categories(n, seed):
+    return _c3(n, seed)[1]
+
+
+# workloads whose rows come with categorical columns: name -> generator of the codes
+CATEGORIES = {"c3": make_c3_categories}
 
 
 def make_c4(n, seed):  # 10 classes by argmax of random projections plus Gumbel noise
@@ -136,8 +166,8 @@ WORKLOADS = {
            "binary classification %d x 28 fp32, hist_size 255, reg:logistic, max_depth 8, eta 0.1 "
            "(configs[1])"),
     "c3": (1_000_000, 2000, make_c3, _cfg(0, 6, 0.1, colsample_bytree=0.5),
-           "wide table %d x 2000 fp32, 20%% NaN, colsample_bytree 0.5, max_depth 6 (configs[2], "
-           "categorical columns as numbers)"),
+           "wide table %d x (1990 fp32 with 20%% NaN + 10 categorical), colsample_bytree 0.5, "
+           "max_depth 6 (configs[2])"),
     "c4": (5_000_000, 50, make_c4, _cfg(3, 6, 0.2, labels_count=10),
            "multi:softmax %d x 50 fp32, 10 classes, max_depth 6, eta 0.2 (configs[3])"),
     "c5": (50_000_000, 100, make_c5, _cfg(1, 8, 0.1),
@@ -211,17 +241,27 @@ def measured_peak():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def _pin_host_threads():
+    """All host cores for the CPU port, whatever the launcher put in the environment
+    (torchrun sets OMP_NUM_THREADS=1 for its workers); to be called before the oracle's
+    library is loaded."""
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    return cores
+
+
 def oracle_rounds_per_s(rows, rounds, warmup, workload="c2"):
-    """The CPU port of the path on a bounded sample: rounds/s at `rows` rows."""
+    """The CPU port of the path on `rows` rows of the workload: rounds/s."""
     from oracle import oracle as orc
     _, features, gen, cfg, _ = WORKLOADS[workload]
     X, y, labels = gen(rows, 1000)
+    cat = CATEGORIES[workload](rows, 1000) if workload in CATEGORIES else None
     o = orc.Oracle(cfg, missing_bin=True)
     if X.dtype == np.uint8:
         thr = np.tile(np.arange(255, dtype=np.float32) + 0.5, (features, 1))
         o.set_binned(np.ascontiguousarray(X.T).astype(np.uint16), thr, np.full(features, 255, dtype=np.int32))
     else:
-        o.set_dense(X)
+        o.set_dense(X, categories=cat)
     if labels is not None:
         o.set_label(labels)
     else:
@@ -232,26 +272,57 @@ def oracle_rounds_per_s(rows, rounds, warmup, workload="c2"):
     return rounds / (time.perf_counter() - t0)
 
 
+# rows the CPU port is timed on in the reference arm, per workload: everything for the
+# headline configuration; the wider or longer ones are cut so that the arm ends in minutes
+REFERENCE_ARM_ROWS = {"c1": 100_000, "c2": FULL_ROWS, "c3": 100_000, "c4": 1_000_000, "c5": 5_000_000,
+                      "c5a": 5_000_000}
+
+
 def run_reference(args, rank, world):
-    """Reference arm: arboretum has no CPU training path, so this times the CPU port
-    of its algorithm (oracle/) with all host threads on a bounded row sample."""
+    """Reference arm.  arboretum has no CPU training path, so this times the CPU port of its
+    algorithm (oracle/) with all host threads -- on all rows of the headline workload; the
+    reference's own CUDA build is timed by the other arm's `ref_cuda` record."""
     if rank != 0:
         return
-    sample = min(args.rows, 1_000_000)
-    cores = os.cpu_count() or 1
-    rps_sample = oracle_rounds_per_s(sample, max(1, args.steps), max(0, args.warmup), args.workload)
-    value = rps_sample * sample / args.rows  # cost is linear in rows
+    cores = _pin_host_threads()
+    rows = min(args.rows, REFERENCE_ARM_ROWS[args.workload])
+    value = oracle_rounds_per_s(rows, max(1, args.steps), max(0, args.warmup), args.workload)
+    cfg = workload_config(args, world)
+    cfg["rows"] = rows  # what was timed, nothing scaled
+    cfg["rows_per_gpu"] = None
+    cfg["parallelism"] = "host threads x%d" % cores
+    cfg["workload"] = WORKLOADS[args.workload][4] % rows
     line = {"impl": "reference", "metric": "boosting_rounds_per_sec", "value": value,
             "unit": "rounds/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": workload_config(args, world),
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": value, "unit": "rounds/s", "cores": cores, "kind": "port",
-                             "sample": "%d of %d rows, %d rounds timed, rounds/s scaled by rows"
-                                       % (sample, args.rows, args.steps)},
+                             "sample": "all %d rows, %d rounds timed after %d (nothing scaled)"
+                                       % (rows, args.steps, args.warmup)},
             "e2e": {"value": value, "unit": "rounds/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_record(workload, rows):
+    """The reference's own CUDA build (oracle/_ref, compiled from its sources by
+    oracle/build_ref_cuda.py) on the same seeded rows, in a child process: rounds/s of
+    `for round: AGrowTree` on this GPU."""
+    from oracle import ref_cuda
+    if not ref_cuda.available():
+        return {"unavailable": "oracle/_ref/libarboretum_ref.so is not built"}
+    if workload not in ("c1", "c2"):
+        return {"unavailable": "the reference trains dense fp32 with reg:linear / reg:logistic only"}
+    cmd = [sys.executable, os.path.join(ROOT, "oracle", "ref_cuda.py"), "time", "--workload", workload,
+           "--rows", str(rows), "--rounds", "10", "--warmup", "2", "--double", "0"]
+    try:
+        out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+        rec = json.loads(out.stdout.strip().splitlines()[-1])
+    except Exception as e:  # a reference that misbehaves must not take the bench line with it
+        return {"unavailable": "the reference run failed: %r" % (e,)}
+    return {"value": rec["value"], "unit": rec["unit"], "config": rec["workload"],
+            "ms_per_round": rec["ms_per_round"], "double_precision": rec["double_precision"],
+            "first_round_with_quantisation_s": rec["first_round_with_quantisation_s"], "how": rec["how"]}
 
 
 def shared_atomics(t, features):
@@ -285,6 +356,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-cuda", action="store_true",
+                    help="skip the run of the reference's own CUDA build (the `ref_cuda` record)")
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the end-to-end jobs (profiling runs: fewer launches before the timed rounds)")
     ap.add_argument("--internals", default="", help='JSON merged into the "internals" configuration')
@@ -312,6 +385,7 @@ def main():
     n_local = args.rows // world
     _, features, gen, base_cfg, _ = WORKLOADS[args.workload]
     X, y, labels = gen(n_local, rank)
+    cat = CATEGORIES[args.workload](n_local, rank) if args.workload in CATEGORIES else None
     binned = X.dtype == np.uint8
     xp = torch.from_numpy(X).pin_memory()  # the job's host buffers are pinned
     Xh = xp.numpy()
@@ -330,6 +404,8 @@ def main():
 
     def new_model():
         kw = {"binned_hist_size": 255} if binned else {}
+        if cat is not None:
+            kw["data_category"] = cat
         if labels is not None:
             data = arboretum.DMatrix(Xh, labels=yh, **kw)
         else:
@@ -354,6 +430,8 @@ def main():
     warm_rows = min(n_local, 200_000)
     Xw, yw, lw = gen(warm_rows, 10_000 + rank)
     kw = {"binned_hist_size": 255} if binned else {}
+    if cat is not None:
+        kw["data_category"] = CATEGORIES[args.workload](warm_rows, 10_000 + rank)
     wd = arboretum.DMatrix(Xw, labels=lw, **kw) if lw is not None else arboretum.DMatrix(Xw, y=yw, **kw)
     wm = arboretum.Garden(cfg)
     wm.data = wd
@@ -394,7 +472,8 @@ def main():
         e2e_runs = [float("nan")]
     e2e_s = sorted(e2e_runs)[len(e2e_runs) // 2]
     e2e = {"value": None if args.no_e2e else args.steps / e2e_s, "unit": "rounds/s",
-           "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) * world / args.steps),
+           "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes + (cat.nbytes if cat is not None else 0))
+                                     * world / args.steps),
            "d2h_bytes_per_step": int(yhat.nbytes * world / args.steps),
            "runs_s": [] if args.no_e2e else [round(t, 4) for t in e2e_runs],
            "parts_s": {"order": ["DMatrix (host to device)", "quantise + first round", "other rounds",
@@ -464,6 +543,8 @@ def main():
                 "data": "synthetic", "config": workload_config(args, world), "clocks": clocks,
                 "e2e": e2e, "gpu_launches": int(launches), "wall_ms_per_step": 1000.0 * wall_s / args.steps,
                 "roofline": roofline}
+        if world == 1 and not args.no_ref_cuda:
+            line["ref_cuda"] = reference_cuda_record(args.workload, args.rows)
         if world == 1 and not args.no_cpu_baseline:
             sample = min(args.rows, max(20_000, 14_000_000 // features))
             cores = os.cpu_count() or 1

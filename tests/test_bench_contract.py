@@ -18,7 +18,8 @@ def test_generators_are_seeded_and_shaped():
     for name, (rows, features, gen, cfg, desc) in bench.WORKLOADS.items():
         a = gen(500, 3)
         b = gen(500, 3)
-        assert a[0].shape == (500, features), name
+        n_cat = bench.CATEGORIES[name](500, 3).shape[1] if name in bench.CATEGORIES else 0
+        assert a[0].shape == (500, features - n_cat), name
         assert np.array_equal(a[0], b[0], equal_nan=True), name
         target = a[2] if a[2] is not None else a[1]
         assert len(target) == 500, name
@@ -32,7 +33,7 @@ def test_generators_are_seeded_and_shaped():
     assert set(np.unique(labels)) <= set(range(10))
 
 
-@pytest.mark.parametrize("workload", ["c1", "c2", "c4", "c5"])
+@pytest.mark.parametrize("workload", ["c1", "c2", "c3", "c4", "c5"])
 def test_reference_arm_prints_one_json_line(workload):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
                         "--workload", workload, "--rows", "3000", "--steps", "1", "--warmup", "0"],
