@@ -455,7 +455,7 @@ class Builder {
   Geometry geo_;
   int qb_ = 18;        // fixed-point bits of a gradient
   int item_cap_;       // rows an int32 sub-histogram may take (2^(31 - quant_bits))
-  int max_hist_items_;
+  int max_hist_items_, max_hist_runs_;
   std::default_random_engine rnd_;  // garden.cu:87
   std::vector<unsigned> active_fids_;
   std::vector<unsigned char> active_host_;
@@ -469,7 +469,6 @@ class Builder {
   // "gradient" array of ones; same level buffers, same subtraction, same exchange
   PeerExchange *xchg_ = nullptr;  // row shards of one box: the level exchange over peer memory
   PinnedBuf h_xchg_status_;
-  bool fused_steps_ = true;  // ARBORETUM_NO_FUSED_STEP in the environment: the three-pass level step
   bool count_plane_ = false;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
   // records of every tree of the last round (multi:softmax grows labels_count of them)
@@ -479,7 +478,7 @@ class Builder {
   DevBuf d_node_of_;  // per row: the node (inside the current level) it stands on
   DevBuf d_list_;     // row lists of the built nodes of the current level, back to back
   DevBuf d_list_grad_;  // their gradient records in the same order (uint8 data)
-  DevBuf d_partials_, d_hist_items_, d_counters_, d_first_, d_built_, d_scratch_, d_list_base_,
+  DevBuf d_partials_, d_hist_items_, d_counters_, d_first_, d_slot_first_, d_item_slot_, d_built_, d_scratch_, d_list_base_,
     d_cursor_, d_child_count_;
   DevBuf d_arena_;      // backs the small per-level arrays below
   DevBuf d_rows_arena_; // backs the per-row arrays
@@ -540,7 +539,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   nb_stride_ = 2 * max_nodes_ + 1;
   pair_ = cfg.objective != kLinearRegression;
   count_plane_ = pair_ && tp.min_leaf_size > 1;
-  fused_steps_ = std::getenv("ARBORETUM_NO_FUSED_STEP") == nullptr;
   if (cfg.objective == kSoftMaxOneVsAll)
     ARB_CHECK(d->has_labels(), "multi:softmax needs labels (ASetLabel)");
   else
@@ -592,10 +590,15 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const int qb = qb_;
   ARB_CHECK(qb >= 10 && qb <= 22, "internals.quant_bits must be 0 (chosen by the row count) or in [10, 22]");
   item_cap_ = 1 << (31 - qb);
-  // items of one level: sum over nodes of ceil(len / item_rows) <= rows / item_rows + nodes, and
-  // item_rows is ceil(rows / target) unless kMinItemRows (fewer items) or item_cap_ binds
-  max_hist_items_ = std::max(std::max(max_nodes_, 3 * hist_grid_x(1 << 30, geo_.NT)), int(n_ / item_cap_) + 1) +
-                    max_nodes_ + 2;
+  // A level's rows are cut into items of item_cap_ >> j rows (a power-of-two share of what an
+  // int32 plane holds), about kItemsPerCta for every histogram CTA of a feature tile so that
+  // contiguous shares of items come out even; neighbouring items of a node that one CTA takes
+  // are accumulated as one run (see make_items in partition.cu).
+  //   items <= rows / item_rows + nodes <= 2 x (kItemsPerCta x CTAs) + rows / item_cap_ + nodes
+  //   runs  <= CTAs + nodes + rows / item_cap_ (+ nodes: the short last item of a node)
+  const int hist_ctas = hist_grid_x(1 << 30, geo_.NT);
+  max_hist_items_ = 2 * kItemsPerCta * hist_ctas + int(n_ / item_cap_) + 2 * max_nodes_ + 8;
+  max_hist_runs_ = hist_ctas + int(n_ / item_cap_) + 2 * max_nodes_ + 8;
 
   gp_ = GainParams{tp.min_leaf_size, tp.min_child_weight, tp.gamma_absolute, tp.gamma_relative,
                    tp.lambda,        tp.alpha,            tp.max_leaf_weight};
@@ -662,6 +665,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
       {&d_hist_items_, max_hist_items_ * sizeof(WorkItem)},
       {&d_counters_, sizeof(int)},
       {&d_first_, (max_nodes_ + 2) * sizeof(int)},
+      {&d_slot_first_, (max_nodes_ + 2) * sizeof(int)},
+      {&d_item_slot_, (2 * size_t(max_hist_items_) + 2) * sizeof(int)},
       {&d_built_, max_nodes_ * sizeof(int)},
       {&d_scratch_, 3 * size_t(max_nodes_ + 1) * sizeof(unsigned)},
       {&d_list_base_, max_nodes_ * sizeof(unsigned)},
@@ -688,7 +693,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   const size_t level_hist_bytes = size_t(max_nodes_) * geo_.NT * kHistWords * 2 * sizeof(long long);
   d_hist_[0].alloc(level_hist_bytes);
   d_hist_[1].alloc(level_hist_bytes);
-  d_partials_.alloc(size_t(max_hist_items_) * geo_.NT * 2 * kHistWords * sizeof(int));
+  d_partials_.alloc(size_t(max_hist_runs_) * geo_.NT * 2 * kHistWords * sizeof(int));
   const bool sharded = g->allreduce != nullptr;
   const size_t compact_bytes = size_t(std::max(1, max_nodes_ / 2)) * geo_.NT * kHistWords * 2 * sizeof(long long);
   // made here, not inside a round: an allocation that fails between two collectives would
@@ -714,6 +719,8 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   pb_.hist_items = d_hist_items_.as<WorkItem>();
   pb_.n_hist_items = d_counters_.as<int>();
   pb_.hist_item_first = d_first_.as<int>();
+  pb_.item_slot = d_item_slot_.as<int>();
+  pb_.slot_first = d_slot_first_.as<int>();
   pb_.built_child = d_built_.as<int>();
   pb_.list_base = d_list_base_.as<unsigned>();
   pb_.cursor = d_cursor_.as<unsigned>();
@@ -937,8 +944,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   const bool use_trick = cfg.internal.use_hist_subtraction_trick;
   const int n_chunks = int(chunks_.size());
   const bool multi = n_chunks > 1;  // row chunks add their histograms like GPUs do
-  // the fused level step names the child to build by the hessian rule as well
-  const bool by_hessian = g_->allreduce != nullptr || multi || (fused_steps_ && geo_.bins_cm != nullptr);
+  const bool by_hessian = g_->allreduce != nullptr || multi;
   const size_t gsz = pair_ ? sizeof(float2) : sizeof(float);
   const int n_sets = count_plane_ ? 2 : 1;  // histogram sets: (g, h) sums, then row counts
   int ev = 0;
@@ -982,24 +988,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       unsigned *list = d_list_.as<unsigned>() + ch.begin;
       if (c == 0) mark();
       void *list_grad = d_list_grad_.p ? static_cast<char *>(d_list_grad_.p) + ch.begin * gsz : nullptr;
-      // in-core levels of moderate width: the step to the children and their row lists in one pass
-      DescendListLaunch dl;
-      dl.geo = geo;
-      dl.rec = l > 0 ? rec(l - 1) : nullptr;
-      dl.parents = L / 2;
-      dl.node_of = node_of;
-      dl.parent_begin = l > 0 ? node_begin(c, l - 1) : nullptr;
-      dl.cursor = pb_.cursor;
-      dl.list = list;
-      dl.grad = list_grad ? grad_c : nullptr;
-      dl.list_grad = list_grad;
-      dl.pair = pair_;
-      dl.use_trick = use_trick;
-      dl.n = rows;
-      const bool fused = l > 0 && fused_steps_ && !multi && descend_lists_applies(dl);
-      if (fused) {
-        launch_descend_lists(dl, s);
-      } else if (l > 0) {  // every row of the chunk steps from its node of level l - 1 to a child
+      if (l > 0) {  // every row of the chunk steps from its node of level l - 1 to a child
         DescendLaunch d;
         d.geo = geo;
         d.rec = rec(l - 1);
@@ -1016,8 +1005,10 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       // rule of multi-GPU / multi-chunk runs has no such bound)
       const bool half = trick_level && !by_hessian;
       const size_t level_rows = half ? rows / 2 + 1 : rows;
-      const int target_items = std::max(n_build, 3 * hist_grid_x(1 << 30, geo.NT));
-      const int item_rows = int(std::min<size_t>(size_t(item_cap_), std::max<size_t>(kMinItemRows, (level_rows + target_items - 1) / target_items)));
+      const int hist_ctas = hist_grid_x(1 << 30, geo.NT);
+      int item_rows = item_cap_;  // the largest power-of-two share of a plane's rows that gives
+                                  // every CTA about kItemsPerCta items
+      while (item_rows > kMinItemRows && level_rows / size_t(item_rows) < size_t(kItemsPerCta) * hist_ctas) item_rows >>= 1;
       LevelPlanLaunch pl;
       pl.child_count = l > 0 ? d_child_count_.as<unsigned>() : nullptr;
       pl.parent_begin = l > 0 ? node_begin(c, l - 1) : nullptr;
@@ -1025,19 +1016,14 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       pl.parent_rec = l > 0 ? rec(l - 1) : nullptr;
       pl.L = L;
       pl.item_rows = item_rows;
+      pl.hist_grid_x = hist_ctas;
+      pl.items_per_run = item_cap_ / item_rows;
       pl.use_trick = use_trick;
-      pl.by_hessian = by_hessian || fused;
-      pl.fused = fused;
-      {  // the next level's fused step counts from cleared cursors
-        DescendListLaunch next = dl;
-        next.parents = L;
-        const bool next_fused = l + 1 < levels_ && fused_steps_ && !multi && descend_lists_applies(next);
-        pl.clear_cursors = next_fused ? std::min(2 * L, max_nodes_) : 0;
-      }
+      pl.by_hessian = by_hessian;
       pl.pb = pb_;
       pl.max_items = max_hist_items_;
       launch_plan_level(pl, s);
-      if (l > 0 && !fused) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
+      if (l > 0) launch_gather_lists(node_of, rows, L, pb_, list, grad_c, list_grad, pair_, s);
       if (last) mark();
       for (int k = 0; k < n_sets; ++k) {
         HistLaunch h;
@@ -1049,13 +1035,15 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         h.pair = k == 0 ? pair_ : false;
         h.items = pb_.hist_items;
         h.n_items = pb_.n_hist_items;
+        h.item_slot = pb_.item_slot;
+        h.grid_x = hist_ctas;
         h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
         h.partials = d_partials_.as<int>();
         h.list_grad = (l == 0 || k > 0) ? nullptr : list_grad;
         launch_hist(h, s);
         ReduceLaunch rd;
         rd.partials = d_partials_.as<int>();
-        rd.item_first = pb_.hist_item_first;
+        rd.item_first = pb_.slot_first;  // the planes of a node's runs
         rd.build_node = compact ? nullptr : pb_.scratch_node;
         rd.n_build = n_build;
         rd.NT = geo.NT;

@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
 hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
-               int *__restrict__ partials, const void *__restrict__ list_grad) {
+               const int *__restrict__ item_slot, int *__restrict__ partials,
+               const void *__restrict__ list_grad) {
   extern __shared__ __align__(16) int smem[];
   // the histogram of the CTA's first item is cleared while the kernel before this one drains
   overlap_release();
@@ -101,9 +102,16 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
   }
   constexpr int GSZ = PAIR ? 8 : 4;  // bytes of one quantised gradient record
   const int total_items = *n_items;
-
-  for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
-    const WorkItem item = items[it];
+  // A CTA takes a contiguous share of the items.  Neighbouring items of one node are one run
+  // (the plan kernel gave them the same slot: together they stay within what an int32 plane
+  // holds): their rows lie back to back in the node's list and go through the pipeline as one
+  // piece, and the planes are stored once per run.
+  const int per = (total_items + int(gridDim.x) - 1) / int(gridDim.x);
+  const int it_end = min(total_items, (int(blockIdx.x) + 1) * per);
+  for (int it = int(blockIdx.x) * per; it < it_end;) {
+    WorkItem item = items[it];
+    const int slot = item_slot ? item_slot[it] : it;
+    for (++it; it < it_end && item_slot && item_slot[it] == slot; ++it) item.len += items[it].len;
     if (!cleared)
       for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
     cleared = false;
@@ -192,7 +200,7 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
     }
     cp_async_wait<0>();
     __syncthreads();
-    store_planes(smem, partials + (size_t(it) * NT + tile) * 2 * kHistWords);
+    store_planes(smem, partials + (size_t(slot) * NT + tile) * 2 * kHistWords);
     __syncthreads();
   }
 }
@@ -203,7 +211,8 @@ __global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
 hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                     const int TW, const int F, const unsigned *__restrict__ rowid,
                     const void *__restrict__ grad, const WorkItem *__restrict__ items,
-                    const int *__restrict__ n_items, int *__restrict__ partials) {
+                    const int *__restrict__ n_items, const int *__restrict__ item_slot,
+                    int *__restrict__ partials) {
   extern __shared__ __align__(16) int smem[];
   int *G = smem;
   int *H = smem + kHistWords;
@@ -213,8 +222,12 @@ hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, 
   const int rsub = threadIdx.x / TW;
   const int f = tile * TW + f_in_tile;
   const int total_items = *n_items;
-  for (int it = blockIdx.x; it < total_items; it += gridDim.x) {
-    const WorkItem item = items[it];
+  const int per = (total_items + int(gridDim.x) - 1) / int(gridDim.x);  // runs of items: see hist_u8_kernel
+  const int it_end = min(total_items, (int(blockIdx.x) + 1) * per);
+  for (int it = int(blockIdx.x) * per; it < it_end;) {
+    WorkItem item = items[it];
+    const int slot = item_slot ? item_slot[it] : it;
+    for (++it; it < it_end && item_slot && item_slot[it] == slot; ++it) item.len += items[it].len;
     for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
     __syncthreads();
     if (f < F) {
@@ -235,7 +248,7 @@ hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, 
       }
     }
     __syncthreads();
-    store_planes(smem, partials + (size_t(it) * NT + tile) * 2 * kHistWords);
+    store_planes(smem, partials + (size_t(slot) * NT + tile) * 2 * kHistWords);
     __syncthreads();
   }
 }
@@ -352,7 +365,7 @@ int hist_grid_x(int max_items, int NT) {
 
 void launch_hist(const HistLaunch &a, cudaStream_t s) {
   const Geometry &g = a.geo;
-  const dim3 grid(hist_grid_x(a.max_items, g.NT), g.NT);
+  const dim3 grid(a.grid_x > 0 ? a.grid_x : hist_grid_x(a.max_items, g.NT), g.NT);
   const bool ident = a.rowid == nullptr;
   if (g.bin_bytes == 1 && g.TW == 32) {
     const size_t smem = 2 * kHistWords * 4 + (kHistThreads / 32) * kStages * kStageBytes;
@@ -360,7 +373,7 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
   do {                                                                                        \
     ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                               \
     launch_overlapped(hist_u8_kernel<P, I>, grid, kHistThreads, smem, s, g.bins, g.pitch,     \
-                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.partials, a.list_grad);    \
+                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.item_slot, a.partials, a.list_grad); \
   } while (0)
     if (a.pair) {
       if (ident) ARB_LAUNCH(true, true); else ARB_LAUNCH(true, false);
@@ -374,7 +387,8 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
   do {                                                                                        \
     ARB_SET_SMEM((hist_generic_kernel<P, I, T>), smem);                                       \
     hist_generic_kernel<P, I, T><<<grid, kHistThreads, smem, s>>>(                            \
-      g.bins, g.pitch, g.NT, g.TW, g.F, a.rowid, a.grad, a.items, a.n_items, a.partials);     \
+      g.bins, g.pitch, g.NT, g.TW, g.F, a.rowid, a.grad, a.items, a.n_items, a.item_slot,     \
+      a.partials);                                                                            \
   } while (0)
 #define ARB_LAUNCH_T(T)                                                        \
   do {                                                                         \

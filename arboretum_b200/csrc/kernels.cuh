@@ -15,7 +15,8 @@ constexpr int kHistCtasPerSm = 2;     // resident histogram CTAs per SM (32 warp
                                       // of the levels below the root needs them to hide its latency)
 constexpr int kMaxLevels = 16;
 constexpr int kCounterStride = 32;    // words between two counters that many CTAs add to
-constexpr int kMinItemRows = 2048;    // smallest piece a node's row list is cut into
+constexpr int kMinItemRows = 256;     // smallest piece a node's row list is cut into
+constexpr int kItemsPerCta = 6;       // items a histogram CTA gets at least (evens out the shares)
 
 // Geometry of the binned matrix and of the histograms built from it.
 //   bins : row-major, `pitch` bytes per row, feature f of row r at
@@ -43,8 +44,13 @@ struct HistLaunch {
   bool pair;
   const WorkItem *items;  // every item has at most 2^(31 - quant_bits) rows
   const int *n_items;
+  const int *item_slot = nullptr;  // per item: the run it belongs to (neighbouring items of one node
+                                   // that one CTA takes and whose rows together fit an int32 plane);
+                                   // nullptr: every item is a run of its own
   int max_items;
-  int *partials;  // [item][tile][2][kHistWords] int32 planes, written here
+  int grid_x = 0;  // CTAs per feature tile; must be what the plan kernel cut the runs for when
+                   // item_slot is given (0: from max_items)
+  int *partials;  // [run][tile][2][kHistWords] int32 planes, written here
   const void *list_grad = nullptr;  // gradient records in list order (position p of `rowid` <->
                                     // record p), or nullptr: gathered from `grad` by row id.
                                     // Read by the uint8 kernel only.
@@ -59,7 +65,7 @@ double measure_shared_atomic_peak(int steps, cudaStream_t s);
 // planes of the items of every built node -> the level's int64 histogram
 struct ReduceLaunch {
   const int *partials;
-  const int *item_first;  // n_build + 1: items of built node b are [first[b], first[b+1])
+  const int *item_first;  // n_build + 1: the planes of built node b are [first[b], first[b+1])
   const int *build_node;  // node index (inside the level) of built node b; nullptr: level_hist
                           // holds the built nodes only, in build order
   int n_build;
@@ -110,6 +116,8 @@ struct PlanBuffers {
   WorkItem *hist_items;
   int *n_hist_items;
   int *hist_item_first;   // per built node: its first item; max_nodes + 1 entries
+  int *item_slot;         // per item: its run (see HistLaunch); max_items entries
+  int *slot_first;        // per built node: its first run; max_nodes + 1 entries
   int *built_child;       // per parent: 0 = left child built, 1 = right child
   unsigned *list_base;    // per node of the level: where its row list starts (0xffffffff: none)
   unsigned *cursor;       // per node of the level, kCounterStride words apart: rows written to
@@ -138,33 +146,6 @@ struct DescendLaunch {
 };
 void launch_descend(const DescendLaunch &a, cudaStream_t s);
 
-// The fused level step: every row steps to a child AND, when the child gets a histogram of
-// its own, goes to the child's row list in the same pass.  Which child of a parent is built
-// is known before the pass from the parent's hessian sums (left sum <= right sum: the left
-// one), and the lists need no level-wide counts first: the left child's list grows upwards
-// from the start of the parent's range of the level above, the right child's downwards from
-// its end, so both end up exactly on the child's own range of the new level's prefix counts.
-// The children's row counts are what the list cursors hold afterwards (the plan kernel
-// reads them there).  For levels of at most kFusedParents parents with a feature-major copy
-// of the bins.
-constexpr int kFusedParents = 1024;
-struct DescendListLaunch {
-  Geometry geo;
-  const NodeRec *rec;            // split records of the parents
-  int parents;                   // nodes of the level above
-  unsigned short *node_of;
-  const unsigned *parent_begin;  // parents + 1 prefix counts of the level above
-  unsigned *cursor;              // per child (kCounterStride apart): rows listed so far; zero on entry
-  unsigned *list;
-  const void *grad;              // gradient records by row (nullptr: none copied)
-  void *list_grad;
-  bool pair;
-  bool use_trick;                // false: both children of every parent are listed
-  size_t n;
-};
-bool descend_lists_applies(const DescendListLaunch &a);
-void launch_descend_lists(const DescendListLaunch &a, cudaStream_t s);
-
 // Prefix counts of a level, the children to build, their lists and the histogram work items.
 struct LevelPlanLaunch {
   const unsigned *child_count;  // per parent (kCounterStride apart): rows that went right, from
@@ -174,11 +155,11 @@ struct LevelPlanLaunch {
   NodeRec *parent_rec;          // L / 2 records of the level above: left_count += lefts
   int L;
   int item_rows;                // rows per work item
+  int hist_grid_x;              // CTAs per feature tile of the histogram launch: each takes a
+                                // contiguous share of the items
+  int items_per_run;            // items of `item_rows` rows that fit an int32 plane together
   bool use_trick;               // build one child per parent, the other is parent - built
   bool by_hessian;              // choose it by the hessian sums (row shards, row chunks)
-  bool fused = false;           // the level's rows were moved by launch_descend_lists: the children's
-                                // sizes are in pb.cursor, the lists are written already
-  int clear_cursors = 0;        // cursors to clear for the next level's fused step (after reading)
   PlanBuffers pb;
   int max_items;
 };

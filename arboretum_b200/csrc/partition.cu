@@ -67,9 +67,15 @@ __device__ void block_exclusive_scan(const unsigned *in, unsigned *out, int n) {
 }
 
 // first[b] = first item of list b, items of `rows_per_item` rows; one CTA.
+// Runs: the histogram launch gives each of its `grid_x` CTAs (per feature tile) a contiguous
+// share of ceil(items / grid_x) items; inside a share, neighbouring items of one list are
+// one run while their rows fit an int32 plane together (`items_per_run` of them).  slot[it] =
+// the run of item it (runs numbered in item order), slot_first[b] = first run of list b:
+// the reduction adds up the planes of the runs [slot_first[b], slot_first[b + 1]).
 __device__ void make_items(const unsigned *begin, const unsigned *len, const int *node_id,
                            int n_lists, int rows_per_item, int *first, WorkItem *items,
-                           int *n_items, int max_items) {
+                           int *n_items, int max_items, int grid_x, int items_per_run, int *slot,
+                           int *slot_first) {
   __shared__ int total;
   unsigned *ufirst = reinterpret_cast<unsigned *>(first);
   for (int i = threadIdx.x; i < n_lists; i += blockDim.x)
@@ -81,6 +87,8 @@ __device__ void make_items(const unsigned *begin, const unsigned *len, const int
     *n_items = total;
   }
   __syncthreads();
+  const int per = (total + grid_x - 1) / max(1, grid_x);
+  unsigned *starts = reinterpret_cast<unsigned *>(slot) + max_items;  // scratch: max_items + 1 words
   for (int it = threadIdx.x; it < total; it += blockDim.x) {
     int lo = 0, hi = n_lists;  // last list with first[list] <= it
     while (hi - lo > 1) {
@@ -94,7 +102,17 @@ __device__ void make_items(const unsigned *begin, const unsigned *len, const int
     w.node = node_id[lo];
     w.pad = 0;
     items[it] = w;
+    // a run starts where a CTA's share or a list starts, and every items_per_run items from there
+    const int seg = max(first[lo], per > 0 ? (it / per) * per : 0);
+    starts[it] = ((it - seg) % items_per_run == 0) ? 1u : 0u;
   }
+  __syncthreads();
+  block_exclusive_scan(starts, starts, total);  // starts[it] = runs that begin before item it
+  for (int it = threadIdx.x; it < total; it += blockDim.x)
+    slot[it] = int(starts[it + 1]) - 1;  // the last run that begins at or before item it
+  for (int b = threadIdx.x; b <= n_lists; b += blockDim.x)
+    slot_first[b] = int(starts[b < n_lists ? min(first[b], total) : total]);
+  __syncthreads();
 }
 
 // One CTA per level: prefix counts, the children that get a histogram of their own, their
@@ -107,31 +125,13 @@ __device__ void make_items(const unsigned *begin, const unsigned *len, const int
 __global__ void plan_level_kernel(const unsigned *__restrict__ child_count,
                                   const unsigned *__restrict__ parent_begin,
                                   unsigned *__restrict__ node_begin, NodeRec *__restrict__ parent_rec,
-                                  int L, int item_rows, bool use_trick, bool by_hessian, bool fused,
-                                  int clear_cursors, PlanBuffers pb, int max_items) {
+                                  int L, int item_rows, bool use_trick, bool by_hessian,
+                                  PlanBuffers pb, int max_items, int hist_grid, int items_per_run) {
   overlap_release();
   overlap_wait();
   unsigned *sb = pb.scratch_begin, *sl = pb.scratch_len;
   int *sn = pb.scratch_node;
-  if (fused) {  // the fused step listed the children: their sizes are the cursors
-    for (int p = threadIdx.x; p < L / 2; p += blockDim.x) {
-      const unsigned size = parent_begin[p + 1] - parent_begin[p];
-      unsigned lefts;
-      if (use_trick) {  // one child listed: the one the hessian rule names (as in the fused step)
-        const long long lh = parent_rec[p].lh, rh = parent_rec[p].th - parent_rec[p].lh;
-        const int built = lh <= rh ? 0 : 1;
-        const unsigned c = pb.cursor[size_t(2 * p + built) * kPad];
-        lefts = built ? size - c : c;
-      } else {
-        lefts = pb.cursor[size_t(2 * p) * kPad];
-      }
-      sl[2 * p] = lefts;
-      sl[2 * p + 1] = size - lefts;
-    }
-    __syncthreads();
-    block_exclusive_scan(sl, node_begin, L);
-    for (int p = threadIdx.x; p < L / 2; p += blockDim.x) parent_rec[p].left_count += sl[2 * p];
-  } else if (child_count) {  // rows that went right, per parent; the others of the parent went left
+  if (child_count) {  // rows that went right, per parent; the others of the parent went left
     for (int p = threadIdx.x; p < L / 2; p += blockDim.x) {
       const unsigned size = parent_begin[p + 1] - parent_begin[p], rights = child_count[size_t(p) * kPad];
       sl[2 * p] = size - rights;
@@ -176,13 +176,11 @@ __global__ void plan_level_kernel(const unsigned *__restrict__ child_count,
   for (int b = threadIdx.x; b < n_build; b += blockDim.x) {
     sb[b] = node_begin[sn[b]];
     pb.list_base[sn[b]] = sb[b];
-    if (!fused) pb.cursor[size_t(sn[b]) * kPad] = 0;
+    pb.cursor[size_t(sn[b]) * kPad] = 0;
   }
-  // the next level's fused step starts from cleared cursors (this level's have been read)
-  for (int i = threadIdx.x; i < clear_cursors; i += blockDim.x) pb.cursor[size_t(i) * kPad] = 0;
   __syncthreads();
   make_items(sb, sl, sn, n_build, item_rows, pb.hist_item_first, pb.hist_items, pb.n_hist_items,
-             max_items);
+             max_items, hist_grid, items_per_run, pb.item_slot, pb.slot_first);
 }
 
 __device__ __forceinline__ void red_shared_u32(unsigned *p, unsigned v) {
@@ -493,150 +491,12 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
 }
 
 
-// The fused level step (see DescendListLaunch).  A CTA takes kFusedRows consecutive rows per
-// turn, a lane kWideRows consecutive ones: their nodes with one 16-byte load, their bins from
-// the feature-major copy, the children back with one 16-byte store.  A row whose child is
-// listed takes a rank among the CTA's rows of that child from a shared-memory counter -- one
-// atomic per group of lanes with the same child while the level has few parents, where all
-// lanes of a warp would meet on the same counters -- the CTA reserves room in the child's
-// list with one global atomicAdd per child it has rows for, and the rows (and their gradient
-// records) are written at the reserved positions: upwards from the start of the parent's
-// range for a left child, downwards from its end for a right child.
-constexpr int kFusedSteps = 4;      // a lane takes kFusedSteps x kWideRows rows per turn
-constexpr int kFusedRows = 256 * kWideRows * kFusedSteps;
-constexpr int kBallotParents = 2;   // up to here ranks come from ballots
-constexpr int kMatchParents = 8;    // up to here from __match_any_sync; beyond, one atomic per row
-constexpr unsigned kListLeft = 1u << 13, kListRight = 1u << 14;  // in a packed split: which children are listed
-constexpr unsigned kNotListed = 0xffffffffu;
-
-template <typename BIN_T, typename GRAD_T>  // GRAD_T: int2 / int copied along; char: none
-__global__ void __launch_bounds__(256, 3)
-descend_list_kernel(const unsigned char *__restrict__ bins_cm, const size_t cm_rows,
-                    const NodeRec *__restrict__ rec, const int P, unsigned short *__restrict__ node_of,
-                    const unsigned *__restrict__ parent_begin, unsigned *__restrict__ cursor,
-                    unsigned *__restrict__ list, const GRAD_T *__restrict__ grad,
-                    GRAD_T *__restrict__ list_grad, const size_t n, const int n_dense, const bool use_trick) {
-  overlap_release();
-  overlap_wait();
-  __shared__ unsigned table[kFusedParents];          // packed split of every parent, with the list flags
-  __shared__ unsigned pbeg[kFusedParents + 1];       // prefix counts of the parents
-  __shared__ unsigned s_rank[2][2 * kFusedParents];  // per child: the CTA's listed rows of this turn
-  __shared__ unsigned s_base[2 * kFusedParents];     // per child: where the CTA's rows go in its list
-  for (int i = threadIdx.x; i < P; i += blockDim.x) {
-    const NodeRec r = rec[i];
-    unsigned e = r.fid < 0 ? 0xffff0000u
-                           : (unsigned(r.fid) << 16) | unsigned(r.bin) | (r.fid >= n_dense ? kCatFlag : 0u);
-    if (use_trick) e |= (r.lh <= r.th - r.lh) ? kListLeft : kListRight;
-    else e |= kListLeft | kListRight;
-    table[i] = e;
-  }
-  for (int i = threadIdx.x; i <= P; i += blockDim.x) pbeg[i] = parent_begin[i];
-  for (int i = threadIdx.x; i < 4 * kFusedParents; i += blockDim.x) (&s_rank[0][0])[i] = 0;
-  __syncthreads();
-  const BIN_T *__restrict__ cm = reinterpret_cast<const BIN_T *>(bins_cm);
-  const int lane = threadIdx.x & 31;
-  const unsigned lt = (1u << lane) - 1u;
-  int parity = 0;
-  for (size_t base = size_t(blockIdx.x) * kFusedRows; base < n; base += size_t(gridDim.x) * kFusedRows, parity ^= 1) {
-    unsigned *rank_of = s_rank[parity];
-    // per row of the lane: child << 16 | rank among the CTA's rows of that child this turn
-    // (a turn has 8192 rows, a level at most 2048 children), or kNotListed
-    unsigned slot[kFusedSteps * kWideRows];
-#pragma unroll
-    for (int step = 0; step < kFusedSteps; ++step) {
-      // step by step a warp covers 256 consecutive rows, a lane 8 of them
-      const size_t r0 = base + (size_t(step) * 256 + threadIdx.x) * kWideRows;
-      const bool whole = r0 + kWideRows <= n;
-      uint4 nodes = make_uint4(0u, 0u, 0u, 0u);  // eight nodes, two to a word (low half first)
-      if (P > 1 && r0 < n) nodes = *reinterpret_cast<const uint4 *>(node_of + r0);
-      unsigned nw[4] = {nodes.x, nodes.y, nodes.z, nodes.w};
-      unsigned ent[kWideRows];
-      int binv[kWideRows];
-#pragma unroll
-      for (int k = 0; k < kWideRows; ++k) {
-        const bool valid = r0 + k < n;
-        if (!valid) nw[k >> 1] &= ~(0xffffu << (16 * (k & 1)));  // what lies past the last row is no node
-        const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
-        ent[k] = table[node];
-        const unsigned fid = ent[k] >> 16;
-        binv[k] = -1;  // no split, or past the end: left
-        if (fid != 0xffffu && valid) binv[k] = int(cm[size_t(fid) * cm_rows + r0 + k]);
-      }
-      unsigned out[4] = {0u, 0u, 0u, 0u};
-      unsigned key[kWideRows];
-#pragma unroll
-      for (int k = 0; k < kWideRows; ++k) {
-        const unsigned node = (nw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
-        const int sbin = int(ent[k] & 0x7ffu);
-        const bool right = (ent[k] & kCatFlag) ? (binv[k] >= 0 && binv[k] != sbin) : binv[k] > sbin;
-        const unsigned child = 2u * node + (right ? 1u : 0u);
-        out[k >> 1] |= child << (16 * (k & 1));
-        const bool listed = r0 + k < n && (ent[k] & (right ? kListRight : kListLeft));
-        key[k] = listed ? child : kNotListed;
-      }
-      if (whole) {
-        *reinterpret_cast<uint4 *>(node_of + r0) = make_uint4(out[0], out[1], out[2], out[3]);
-      } else {
-        for (int k = 0; r0 + k < n; ++k) node_of[r0 + k] = (unsigned short)((out[k >> 1] >> (16 * (k & 1))) & 0xffffu);
-      }
-#pragma unroll
-      for (int k = 0; k < kWideRows; ++k) {
-        unsigned rank = 0;
-        if (P <= kBallotParents) {  // the few children of the level, one ballot each
-          for (unsigned c = 0; c < unsigned(2 * P); ++c) {
-            const unsigned m = __ballot_sync(0xffffffffu, key[k] == c);
-            if (m == 0) continue;
-            const int leader = __ffs(m) - 1;
-            unsigned first = 0;
-            if (lane == leader) first = atomicAdd(&rank_of[c], unsigned(__popc(m)));
-            first = __shfl_sync(0xffffffffu, first, leader);
-            if (key[k] == c) rank = first + unsigned(__popc(m & lt));
-          }
-        } else if (P <= kMatchParents) {
-          const unsigned peers = __match_any_sync(0xffffffffu, key[k]);
-          if (key[k] != kNotListed) {
-            const int leader = __ffs(peers) - 1;
-            unsigned first = 0;
-            if (lane == leader) first = atomicAdd(&rank_of[key[k]], unsigned(__popc(peers)));
-            first = __shfl_sync(peers, first, leader);
-            rank = first + unsigned(__popc(peers & lt));
-          }
-        } else if (key[k] != kNotListed) {
-          rank = atomicAdd(&rank_of[key[k]], 1u);
-        }
-        slot[step * kWideRows + k] = key[k] == kNotListed ? kNotListed : (key[k] << 16) | rank;
-      }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < 2 * P; i += blockDim.x) {
-      const unsigned c = rank_of[i];
-      if (c) s_base[i] = atomicAdd(&cursor[size_t(i) * kPad], c);
-      // the other set of counters is idle between its turns: cleared here, before the barrier
-      // that separates this turn's writes from the next turn's ranks
-      s_rank[parity ^ 1][i] = 0;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int step = 0; step < kFusedSteps; ++step) {
-      const size_t r0 = base + (size_t(step) * 256 + threadIdx.x) * kWideRows;
-#pragma unroll
-      for (int k = 0; k < kWideRows; ++k) {
-        const unsigned sl = slot[step * kWideRows + k];
-        if (sl == kNotListed) continue;
-        const unsigned child = sl >> 16, parent = child >> 1, at = s_base[child] + (sl & 0xffffu);
-        const unsigned pos = (child & 1u) ? pbeg[parent + 1] - 1u - at : pbeg[parent] + at;
-        list[pos] = unsigned(r0 + k);
-        if (sizeof(GRAD_T) > 1) list_grad[pos] = grad[r0 + k];
-      }
-    }
-  }
-}
-
 }  // namespace
 
 void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
   launch_overlapped(plan_level_kernel, 1, 256, 0, s, a.child_count, a.parent_begin, a.node_begin, a.parent_rec,
-                    a.L, a.item_rows, a.use_trick, a.by_hessian, a.fused, a.clear_cursors, a.pb, a.max_items);
+                    a.L, a.item_rows, a.use_trick, a.by_hessian, a.pb, a.max_items, a.hist_grid_x,
+                    std::max(1, a.items_per_run));
   count_launch();
 }
 
@@ -720,35 +580,6 @@ void launch_gather_lists(const unsigned short *node_of, size_t n, int L, const P
   else
     launch_overlapped(gather_lists_kernel<int>, grid, kListThreads, 0, s, node_of, n, L, pb.list_base, pb.cursor,
                       list, static_cast<const int *>(grad), static_cast<int *>(list_grad));
-  count_launch();
-}
-
-bool descend_lists_applies(const DescendListLaunch &a) {
-  return a.geo.bins_cm != nullptr && a.parents <= kFusedParents && a.n > 0 &&
-         reinterpret_cast<uintptr_t>(a.node_of) % 16 == 0;
-}
-
-void launch_descend_lists(const DescendListLaunch &a, cudaStream_t s) {
-  const Geometry &g = a.geo;
-  const size_t turns = (a.n + kFusedRows - 1) / kFusedRows;
-#define ARB_LAUNCH(T, G)                                                                              \
-  do {                                                                                                \
-    const int resident = resident_ctas_cached(descend_list_kernel<T, G>, 256);                        \
-    const int grid = int(std::min<size_t>(turns, size_t(resident)));                                  \
-    launch_overlapped(descend_list_kernel<T, G>, grid, 256, 0, s, g.bins_cm, g.cm_rows, a.rec,        \
-                      a.parents, a.node_of, a.parent_begin, a.cursor, a.list,                         \
-                      static_cast<const G *>(a.grad), static_cast<G *>(a.list_grad), a.n, g.n_dense,  \
-                      a.use_trick);                                                                   \
-  } while (0)
-#define ARB_LAUNCH_T(T)                                          \
-  do {                                                           \
-    if (!a.list_grad) ARB_LAUNCH(T, char);                       \
-    else if (a.pair) ARB_LAUNCH(T, int2);                        \
-    else ARB_LAUNCH(T, int);                                     \
-  } while (0)
-  if (g.bin_bytes == 1) ARB_LAUNCH_T(unsigned char); else ARB_LAUNCH_T(unsigned short);
-#undef ARB_LAUNCH_T
-#undef ARB_LAUNCH
   count_launch();
 }
 
