@@ -447,6 +447,7 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   j["tree_ms"] = Json::number(t.tree);
   j["h2d_bytes"] = Json::number(t.h2d_bytes);
   j["kernel_launches"] = Json::integer(g_kernel_launches);
+  j["level_exchange"] = Json::string(g->peer_exchange ? "peer memory" : g->allreduce ? "ncclAllReduce" : "none");
   static thread_local std::string text;
   text.clear();
   json_write(j, text);

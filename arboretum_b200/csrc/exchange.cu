@@ -144,11 +144,22 @@ u64 wait_limit_ns() {  // ARBORETUM_PEER_WAIT_MS in the environment; 20 s by def
 
 }  // namespace
 
+PeerExchange *PeerExchange::Acquire(size_t bytes, const ShardInfo &sh, cudaStream_t s) {
+  static PeerExchange *kept = nullptr;  // one per process, like its communicator
+  if (kept && kept->rank_ == sh.rank && kept->world_ == sh.world && kept->bytes_ >= bytes) return kept;
+  // (a smaller one that exists stays mapped: see the header)
+  PeerExchange *x = Create(bytes, sh, s);
+  if (x) kept = x;
+  return x;
+}
+
 PeerExchange *PeerExchange::Create(size_t bytes, const ShardInfo &sh, cudaStream_t s) {
   if (!sh.allgather || sh.world < 2 || sh.world > kMaxPeers) return nullptr;
   const int world = sh.world;
   const Layout lay(bytes, world);
-  std::unique_ptr<PeerExchange> x(new PeerExchange());
+  PeerExchange *x = new PeerExchange();  // kept for the life of the process (or leaked with its
+                                         // mappings when the set-up fails half way: rare, and
+                                         // unmapping could not be agreed with the peers)
   x->rank_ = sh.rank;
   x->world_ = world;
   x->bytes_ = bytes;
@@ -209,14 +220,7 @@ PeerExchange *PeerExchange::Create(size_t bytes, const ShardInfo &sh, cudaStream
   }
   x->d_counter_ = reinterpret_cast<unsigned *>(static_cast<char *>(x->region_) + lay.counter);
   x->d_status_ = reinterpret_cast<int *>(static_cast<char *>(x->region_) + lay.status);
-  return x.release();
-}
-
-PeerExchange::~PeerExchange() {
-  cudaDeviceSynchronize();
-  for (int q = 0; q < kMaxPeers; ++q)
-    if (peer_region_[q]) cudaIpcCloseMemHandle(peer_region_[q]);
-  if (region_) cudaFree(region_);
+  return x;
 }
 
 void PeerExchange::AllReduce(size_t count, cudaStream_t s) {

@@ -32,11 +32,15 @@ struct PeerPointers {  // by rank; entry `rank` is this rank's own memory
 
 class PeerExchange {
  public:
-  // Allocates this rank's region (2 x `bytes` + flags), exchanges its handle with the other
-  // ranks through `sh.allgather` and maps theirs.  Returns nullptr when any rank could not
-  // (every rank then returns nullptr: the decision itself is exchanged).
-  static PeerExchange *Create(size_t bytes, const ShardInfo &sh, cudaStream_t s);
-  ~PeerExchange();
+  // The process's exchange for this rank and world size, with room for `bytes` per buffer.
+  // The first call (and any call that needs more room than there is) allocates this rank's
+  // region (2 x `bytes` + flags), exchanges its handle with the other ranks through
+  // `sh.allgather` and maps theirs; every rank must make the same calls.  Like the process's
+  // communicator the exchange is kept until the process exits and never unmapped: freeing
+  // memory that a peer still has mapped is undefined, and a rank must not wait for its peers
+  // while it tears down.  Returns nullptr when any rank could not set it up (every rank then
+  // returns nullptr: the decision itself is exchanged).
+  static PeerExchange *Acquire(size_t bytes, const ShardInfo &sh, cudaStream_t s);
   long long *send_buffer() const { return ptrs_.send[rank_]; }
   const long long *result_buffer() const { return ptrs_.recv[rank_]; }
   size_t capacity_bytes() const { return bytes_; }
@@ -52,6 +56,8 @@ class PeerExchange {
 
  private:
   PeerExchange() {}
+  ~PeerExchange() {}
+  static PeerExchange *Create(size_t bytes, const ShardInfo &sh, cudaStream_t s);
   int rank_ = 0, world_ = 1;
   size_t bytes_ = 0;
   void *region_ = nullptr;               // cudaMalloc'ed, exported

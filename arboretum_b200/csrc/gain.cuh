@@ -82,36 +82,4 @@ __host__ __device__ inline float split_gain(double lg, double lh, double tg, dou
   return (diff > p.gamma_absolute && diff > p.gamma_relative * q) * diff;
 }
 
-// The same difference l + r - p in single precision, without the gamma thresholds: a cheap
-// stand-in that is only used to decide which candidates deserve the exact arithmetic above.
-// The three terms are non-negative and of the size of the parent's term p, so the result is
-// off by at most a few 1e-7 x (2 p + diff).  Candidates that fail the row-count or hessian
-// limits return -INFINITY.
-template <bool PAIR>
-__host__ __device__ inline float split_gain_approx(float lg, float lh, float tg, float th,
-                                                   unsigned long long lc, unsigned long long tc,
-                                                   const GainParams &p, float *parent_term) {
-  const float rg = tg - lg, rh = th - lh;
-  const unsigned long long rc = tc - lc;
-  bool ok = lc >= p.min_leaf_size && rc >= p.min_leaf_size;
-  if (PAIR) ok = ok && fabsf(lh) >= p.hess && fabsf(rh) >= p.hess;
-  auto weight = [&](float g, float h, unsigned long long c) {
-    const float den = PAIR ? h : float(c);
-    float w = 0.0f;
-    if (c >= p.min_leaf_size && den >= p.hess) {
-      const float a = fmaxf(0.0f, fabsf(g) - p.alpha);
-      w = (g < 0.0f ? -a : a) / (den + p.lambda);
-    }
-    return threshold_weight(w, p.max_leaf_weight);
-  };
-  auto term = [&](float g, float h, unsigned long long c, float w) {
-    const float den = PAIR ? h : float(c);
-    return -2.0f * (g * (-w) + 0.5f * (den + p.lambda) * w * w + p.alpha * fabsf(w));
-  };
-  const float q = term(tg, th, tc, weight(tg, th, tc));
-  *parent_term = q;
-  if (!ok) return -INFINITY;
-  return term(lg, lh, lc, weight(lg, lh, lc)) + term(rg, rh, rc, weight(rg, rh, rc)) - q;
-}
-
 }  // namespace arb

@@ -468,6 +468,7 @@ class Builder {
   // rows (the reference's count histogram, gain.cu:125-134): the reg:linear kernel run on a
   // "gradient" array of ones; same level buffers, same subtraction, same exchange
   PeerExchange *xchg_ = nullptr;  // row shards of one box: the level exchange over peer memory
+                                  // (the process's; not owned)
   PinnedBuf h_xchg_status_;
   bool count_plane_ = false;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
@@ -703,8 +704,9 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     // trick one child per parent below the root), for every histogram set
     const size_t root_bytes = size_t(geo_.NT) * kHistWords * 2 * sizeof(long long);
     const size_t most = cfg.internal.use_hist_subtraction_trick ? std::max(compact_bytes, root_bytes) : level_hist_bytes;
-    xchg_ = PeerExchange::Create((count_plane_ ? 2 : 1) * most, g->shards, s);
+    xchg_ = PeerExchange::Acquire((count_plane_ ? 2 : 1) * most, g->shards, s);
     if (xchg_) h_xchg_status_.alloc(sizeof(int));
+    g->peer_exchange = xchg_ != nullptr;
   }
   if (sharded && cfg.internal.use_hist_subtraction_trick && !xchg_) d_compact_.alloc(compact_bytes);
   if (count_plane_) {
@@ -779,7 +781,6 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
 }
 
 Builder::~Builder() {
-  delete xchg_;
   if (events_made_) {
     for (auto &e : ev_) cudaEventDestroy(e);
     for (auto &e : ev_tree_) cudaEventDestroy(e);

@@ -154,6 +154,7 @@ class Garden {
   ShardInfo shards;  // rank, world and the all-gather of the sharded quantizer
   void *allreduce_ctx = nullptr;
   bool profile = false;
+  bool peer_exchange = false;  // the level exchange of the row shards runs over peer memory
   PhaseTimes times;
   // device copies of the forest for inference
   void SyncForest();

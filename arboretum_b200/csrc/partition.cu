@@ -33,6 +33,7 @@ constexpr int kDescendPasses = 8;   // a warp takes 32 * 8 consecutive rows per 
 constexpr int kSmemNodes = 2048;    // nodes of a level whose tables fit in shared memory
 constexpr int kListRows = 2048;     // rows of one CTA of the list pass
 constexpr int kListThreads = 256;
+constexpr int kPlanThreads = 1024;  // one CTA: its loops over nodes and work items are latency-bound
 // Counters that many CTAs add to (children counts, list cursors) sit one per 128-byte line:
 // atomics on one line are served one after the other by a single L2 slice, so packed
 // counters would serialise every CTA's updates of a whole level.
@@ -494,7 +495,7 @@ gather_lists_kernel(const unsigned short *__restrict__ node_of, const size_t n, 
 }  // namespace
 
 void launch_plan_level(const LevelPlanLaunch &a, cudaStream_t s) {
-  launch_overlapped(plan_level_kernel, 1, 256, 0, s, a.child_count, a.parent_begin, a.node_begin, a.parent_rec,
+  launch_overlapped(plan_level_kernel, 1, kPlanThreads, 0, s, a.child_count, a.parent_begin, a.node_begin, a.parent_rec,
                     a.L, a.item_rows, a.use_trick, a.by_hessian, a.pb, a.max_items, a.hist_grid_x,
                     std::max(1, a.items_per_run));
   count_launch();

@@ -88,9 +88,6 @@ split_kernel(const long long *__restrict__ hist, const long long *__restrict__ c
   __shared__ float best_gain[kSplitThreads];
   __shared__ int best_bin[kSplitThreads];
   __shared__ bool is_last;
-  __shared__ unsigned q_count;            // candidates that survived the single-precision look
-  __shared__ unsigned long long s_key;    // the CTA's best exact candidate, packed
-  __shared__ long long s_tg, s_th, s_tcn; // the node's totals (every feature's bins add up to them)
   const int node = blockIdx.x, tile = blockIdx.y;
   const int lane = threadIdx.x % TW;
   const int chunk = threadIdx.x / TW;
@@ -201,41 +198,17 @@ split_kernel(const long long *__restrict__ hist, const long long *__restrict__ c
     rec[node].tg = tg;
     rec[node].th = th;
   }
-  if (threadIdx.x == 0) {  // lane 0 of a tile is one of its real features
-    s_tg = tg;
-    s_th = th;
-    s_tcn = tcn;
-    q_count = 0;
-    s_key = 0ull;
-  }
+  float bgain = 0.0f;
+  int bbin = -1;
   // the gain search of a (node, tile) is dealt to `parts` CTAs (a power of two): bin k of
   // every thread's 8 goes to CTA k % parts; all of them redo the cheap prefix sums above,
   // so the long double-precision chains run side by side instead of one after another
   const bool active = f < F && feature_active[f];
   // > 0: a categorical feature; a candidate sends the rows of ONE bin left (builder.h:75-105)
   const int ncand = (active && cat_candidates) ? cat_candidates[f] : 0;
-  // The exact gain is some 150 double-precision operations per candidate, and only the largest
-  // matters.  So every candidate is first valued in single precision; the exact arithmetic
-  // then runs for those within a slack of the CTA's largest approximate value that is twenty
-  // times what single precision can be off by (1e-5 x (2 x parent term + difference), see
-  // split_gain_approx).  The winner and the tie order come from exact values only.
-  const double isg = qs->inv_sg, ish = qs->inv_sh;
-  const double dtg = double(tg) * isg, dth = double(th) * ish;
-  float approx[kBinsPerThread];
-  float amax = -INFINITY, parent_term = 0.0f;
-  auto counts_of = [&](long long lh, long long rc_k, unsigned long long &lc, unsigned long long &tc) {
-    if (COUNTS) {  // true row counts (gain.cu:125-134 gates every candidate on them)
-      lc = (unsigned long long)rc_k;
-      tc = (unsigned long long)tcn;
-    } else if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
-      lc = lh > 0;
-      tc = lc + ((th - lh) > 0);
-    } else {  // h_q == 1 for every row: the sum is the row count
-      lc = (unsigned long long)lh;
-      tc = (unsigned long long)th;
-    }
-  };
   if (active && th != 0) {
+    const double isg = qs->inv_sg, ish = qs->inv_sh;
+    const double dtg = double(tg) * isg, dth = double(th) * ish;
     long long rg = og, rh = oh, rc = oc;
 #pragma unroll
     for (int k = 0; k < kBinsPerThread; ++k) {
@@ -243,92 +216,41 @@ split_kernel(const long long *__restrict__ hist, const long long *__restrict__ c
       rg += v[k].x;
       rh += v[k].y;
       if (COUNTS) rc += cv[k];
-      approx[k] = -INFINITY;
       if (bin >= hist_size) continue;  // ids >= hist_size hold missing values: never a threshold
       if ((k & (parts - 1)) != int(blockIdx.z)) continue;  // another CTA's candidate
       if (ncand > 0 && bin >= ncand) continue;  // the shared bin of the rare categories
       const long long lg = ncand > 0 ? v[k].x : rg, lh = ncand > 0 ? v[k].y : rh;
       unsigned long long lc, tc;
-      counts_of(lh, ncand > 0 ? (COUNTS ? cv[k] : 0) : rc, lc, tc);
-      approx[k] = split_gain_approx<PAIR>(float(double(lg) * isg), float(double(lh) * ish), float(dtg), float(dth),
-                                          lc, tc, gp, &parent_term);
-      amax = fmaxf(amax, approx[k]);
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < kBinsPerThread; ++k) approx[k] = -INFINITY;
-  }
-  {  // the CTA's largest approximate value and the parent's term (equal for all features)
-    __shared__ float warp_max[kSplitThreads / 32], warp_term[kSplitThreads / 32];
-    float m = amax, t = parent_term;
-    for (int o = 16; o > 0; o >>= 1) {
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
-    }
-    if ((threadIdx.x & 31) == 0) {
-      warp_max[threadIdx.x >> 5] = m;
-      warp_term[threadIdx.x >> 5] = t;
-    }
-    __syncthreads();
-    m = warp_max[threadIdx.x & 31];
-    t = warp_term[threadIdx.x & 31];
-    for (int o = 16; o > 0; o >>= 1) {
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
-    }
-    amax = m;
-    parent_term = t;
-  }
-  // The survivors are dealt out again, one to a thread: they sit in neighbouring bins, which
-  // belong to the same few threads, and the exact arithmetic is a long dependent chain.
-  long long *q_lg = part_g, *q_lh = part_h;  // the scan is done with them
-  unsigned *q_lc = reinterpret_cast<unsigned *>(best_gain), *q_id = reinterpret_cast<unsigned *>(best_bin);
-  auto exact = [&](long long lg, long long lh, unsigned lcount, int fid, int bin) {
-    unsigned long long lc, tc;
-    if (COUNTS) {
-      lc = lcount;
-      tc = (unsigned long long)s_tcn;
-    } else if (PAIR) {
-      lc = lh > 0;
-      tc = lc + ((s_th - lh) > 0);
-    } else {
-      lc = (unsigned long long)lh;
-      tc = (unsigned long long)s_th;
-    }
-    const float gain = split_gain<PAIR>(double(lg) * isg, double(lh) * ish, double(s_tg) * isg, double(s_th) * ish,
-                                        lc, tc, gp);
-    if (gain > 0.0f) atomicMax(&s_key, pack_key(gain, fid, bin));
-  };
-  if (active && th != 0 && amax > -INFINITY) {
-    const float floor_value = amax - 1e-5f * (2.0f * fabsf(parent_term) + fabsf(amax)) - 1e-30f;
-    long long rg = og, rh = oh, rc = oc;
-#pragma unroll
-    for (int k = 0; k < kBinsPerThread; ++k) {
-      const int bin = bin0 + k;
-      rg += v[k].x;
-      rh += v[k].y;
-      if (COUNTS) rc += cv[k];
-      if (!(approx[k] >= floor_value)) continue;
-      const long long lg = ncand > 0 ? v[k].x : rg, lh = ncand > 0 ? v[k].y : rh;
-      const unsigned lcount = COUNTS ? unsigned(ncand > 0 ? cv[k] : rc) : 0u;
-      const unsigned at = atomicAdd(&q_count, 1u);
-      if (at < unsigned(kSplitThreads)) {
-        q_lg[at] = lg;
-        q_lh[at] = lh;
-        q_lc[at] = lcount;
-        q_id[at] = (unsigned(f) << 12) | unsigned(bin);
-      } else {  // more survivors than threads (many equal gains): valued where they are
-        exact(lg, lh, lcount, f, bin);
+      if (COUNTS) {  // true row counts (gain.cu:125-134 gates every candidate on them)
+        lc = (unsigned long long)(ncand > 0 ? cv[k] : rc);
+        tc = (unsigned long long)tcn;
+      } else if (PAIR) {  // h_q >= 1 for every row, so a zero sum means "no rows"
+        lc = lh > 0;
+        tc = lc + ((th - lh) > 0);
+      } else {  // h_q == 1 for every row: the sum is the row count
+        lc = (unsigned long long)lh;
+        tc = (unsigned long long)th;
+      }
+      const float gain = split_gain<PAIR>(double(lg) * isg, double(lh) * ish, dtg, dth, lc, tc, gp);
+      if (gain > 0.0f && gain >= bgain) {
+        bgain = gain;
+        bbin = bin;
       }
     }
   }
+  best_gain[threadIdx.x] = bgain;
+  best_bin[threadIdx.x] = bbin;
   __syncthreads();
-  if (threadIdx.x < min(q_count, unsigned(kSplitThreads))) {
-    const unsigned id = q_id[threadIdx.x];
-    exact(q_lg[threadIdx.x], q_lh[threadIdx.x], q_lc[threadIdx.x], int(id >> 12), int(id & 0xfffu));
+  if (chunk == 0 && active) {
+    for (int c = 1; c < nchunks; ++c) {
+      const float g = best_gain[c * TW + lane];
+      if (g > 0.0f && g >= bgain) {
+        bgain = g;
+        bbin = best_bin[c * TW + lane];
+      }
+    }
+    if (bgain > 0.0f) atomicMax(&keys[node], pack_key(bgain, f, bbin));
   }
-  __syncthreads();
-  if (threadIdx.x == 0 && s_key != 0ull) atomicMax(&keys[node], s_key);
   // the last tile of the node to arrive turns the packed winner into the record
   __threadfence();
   __syncthreads();
@@ -352,10 +274,8 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   // has an SM to itself, so more CTAs than SMs would only run as a second wave: the gains
   // they share out would wait in line all the same, after re-reading the tile.
   const int sms = device_sm_count();
-  // (the exact arithmetic of the few candidates that survive the single-precision look is
-  // spread over the threads of one CTA, so a tile is no longer dealt to several CTAs)
-  (void)sms;
-  const int parts = 1;
+  int parts = kBinsPerThread;
+  while (parts > 1 && a.L * a.geo.NT * parts > sms) parts >>= 1;
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair && a.count_hist)
     launch_overlapped(split_kernel<true, true>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,

@@ -542,6 +542,7 @@ def main():
                 "scaling": "strong", "vs_baseline": None, "dtype": "int64 fixed-point sums of f32 gradients",
                 "data": "synthetic", "config": workload_config(args, world), "clocks": clocks,
                 "e2e": e2e, "gpu_launches": int(launches), "wall_ms_per_step": 1000.0 * wall_s / args.steps,
+                "level_exchange": t.get("level_exchange"),
                 "roofline": roofline}
         if world == 1 and not args.no_ref_cuda:
             line["ref_cuda"] = reference_cuda_record(args.workload, args.rows)
