@@ -422,6 +422,9 @@ const char *ASetProfile(VoidPointer garden, int on) {
   Garden *g = static_cast<Garden *>(garden);
   g->profile = on != 0;
   g->times = PhaseTimes();
+  double xms[3];
+  long long xn = 0;
+  BuilderView::exchange_clock(g, xms, &xn, true);  // the exchange clocks start over as well
   ARB_CATCH
 }
 
@@ -447,6 +450,14 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   j["tree_ms"] = Json::number(t.tree);
   j["h2d_bytes"] = Json::number(t.h2d_bytes);
   j["kernel_launches"] = Json::integer(g_kernel_launches);
+  double xms[3];
+  long long xn = 0;
+  if (BuilderView::exchange_clock(g, xms, &xn, false)) {
+    j["exchange_wait_peers_ms"] = Json::number(xms[0]);
+    j["exchange_move_ms"] = Json::number(xms[1]);
+    j["exchange_wait_done_ms"] = Json::number(xms[2]);
+    j["exchanges"] = Json::integer(xn);
+  }
   j["level_exchange"] = Json::string(g->peer_exchange ? "peer memory" : g->allreduce ? "ncclAllReduce" : "none");
   static thread_local std::string text;
   text.clear();

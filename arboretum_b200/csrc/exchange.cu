@@ -51,9 +51,10 @@ __device__ bool wait_flag(const u64 *flag, u64 seq, u64 limit_ns) {
 
 __global__ void __launch_bounds__(256)
 peer_allreduce_kernel(const PeerPointers p, const int rank, const int world, const size_t pairs,
-                      const u64 seq, unsigned *counter, int *status, const u64 limit_ns) {
+                      const u64 seq, unsigned *counter, int *status, const u64 limit_ns, u64 *clock) {
   __shared__ int ok;
   __shared__ bool last;
+  const u64 t_begin = global_timer_ns();
   if (threadIdx.x == 0) ok = 1;
   if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(&p.arrive[threadIdx.x][rank], seq);
   __syncthreads();
@@ -62,6 +63,7 @@ peer_allreduce_kernel(const PeerPointers p, const int rank, const int world, con
     atomicCAS(status, 0, 1);
   }
   __syncthreads();
+  const u64 t_arrived = global_timer_ns();
   if (ok) {
     const size_t per = (pairs + size_t(world) - 1) / size_t(world);
     const size_t lo = size_t(rank) * per, hi = min(pairs, lo + per);
@@ -83,16 +85,26 @@ peer_allreduce_kernel(const PeerPointers p, const int rank, const int world, con
         if (q < world) __stcg(reinterpret_cast<longlong2 *>(p.recv[q]) + i, acc);
     }
   }
-  __threadfence_system();  // this thread's stores, before the CTA is counted as finished
-  __syncthreads();
-  if (threadIdx.x == 0) last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  __syncthreads();  // the CTA's stores are issued ...
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // ... and ordered, for every observer, before the CTA counts as finished
+    last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
   __syncthreads();
   if (!last) return;
   __threadfence_system();  // the other CTAs' stores (seen through the counter) before the flags
   if (threadIdx.x == 0) *counter = 0;
+  const u64 t_moved = global_timer_ns();
   if (threadIdx.x < world) {
     st_release_sys(&p.done[threadIdx.x][rank], seq);
     if (!wait_flag(&p.done[rank][threadIdx.x], seq, limit_ns)) atomicCAS(status, 0, 2);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {  // where the time of the exchanges goes (read by the host on request)
+    clock[0] += t_arrived - t_begin;         // until every peer's buffer was ready
+    clock[1] += t_moved - t_arrived;         // this rank's slice summed and stored everywhere
+    clock[2] += global_timer_ns() - t_moved; // until every peer had stored its slice here
+    clock[3] += 1;
   }
 }
 
@@ -121,7 +133,7 @@ __global__ void peer_max_kernel(const PeerPointers p, const int rank, const int 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct Layout {
-  size_t send, recv, arrive, done, small, small_flag, counter, status, total;
+  size_t send, recv, arrive, done, small, small_flag, counter, status, clock, total;
   Layout(size_t bytes, int world) {
     size_t at = 0;
     send = at, at += align256(bytes);
@@ -132,6 +144,7 @@ struct Layout {
     small_flag = at, at += align256(sizeof(u64) * world);
     counter = at, at += 256;
     status = at, at += 256;
+    clock = at, at += 256;
     total = at;
   }
 };
@@ -220,6 +233,7 @@ PeerExchange *PeerExchange::Create(size_t bytes, const ShardInfo &sh, cudaStream
   }
   x->d_counter_ = reinterpret_cast<unsigned *>(static_cast<char *>(x->region_) + lay.counter);
   x->d_status_ = reinterpret_cast<int *>(static_cast<char *>(x->region_) + lay.status);
+  x->d_clock_ = reinterpret_cast<u64 *>(static_cast<char *>(x->region_) + lay.clock);
   return x;
 }
 
@@ -229,7 +243,8 @@ void PeerExchange::AllReduce(size_t count, cudaStream_t s) {
   const size_t slice = (pairs + world_ - 1) / world_;
   const int grid = int(std::max<size_t>(1, std::min<size_t>((slice + 255) / 256, size_t(device_sm_count()) * 4)));
   ++seq_;
-  peer_allreduce_kernel<<<grid, 256, 0, s>>>(ptrs_, rank_, world_, pairs, seq_, d_counter_, d_status_, wait_limit_ns());
+  peer_allreduce_kernel<<<grid, 256, 0, s>>>(ptrs_, rank_, world_, pairs, seq_, d_counter_, d_status_, wait_limit_ns(),
+                                             d_clock_);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
@@ -240,6 +255,14 @@ void PeerExchange::AllMax(unsigned *device_words, int n, cudaStream_t s) {
   peer_max_kernel<<<1, 32, 0, s>>>(ptrs_, rank_, world_, n, device_words, small_seq_, d_status_, wait_limit_ns());
   ARB_CUDA(cudaGetLastError());
   count_launch();
+}
+
+void PeerExchange::Clock(double ms[3], long long *exchanges, bool reset) {
+  u64 v[4] = {0, 0, 0, 0};
+  ARB_CUDA(cudaMemcpy(v, d_clock_, sizeof v, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < 3; ++i) ms[i] = double(v[i]) * 1e-6;
+  *exchanges = (long long)v[3];
+  if (reset) ARB_CUDA(cudaMemset(d_clock_, 0, sizeof v));
 }
 
 int PeerExchange::Status() {

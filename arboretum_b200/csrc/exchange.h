@@ -53,6 +53,9 @@ class PeerExchange {
   // Reads a word of device memory: call it after the stream has been synchronised.
   int Status();
   const int *device_status() const { return d_status_; }
+  // Device time of the AllReduce kernels since the last reset, in milliseconds: waiting for
+  // the peers' buffers, moving this rank's slice, waiting for the peers' slices.
+  void Clock(double ms[3], long long *exchanges, bool reset);
 
  private:
   PeerExchange() {}
@@ -65,6 +68,7 @@ class PeerExchange {
   PeerPointers ptrs_;
   unsigned *d_counter_ = nullptr;        // CTAs of the running exchange that have finished
   int *d_status_ = nullptr;
+  unsigned long long *d_clock_ = nullptr;
   unsigned long long seq_ = 0, small_seq_ = 0;
 };
 

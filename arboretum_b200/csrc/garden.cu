@@ -1298,6 +1298,13 @@ void copy_to_host(void *dst, const void *src_device, size_t bytes) {
 }
 }  // namespace
 
+bool BuilderView::exchange_clock(Garden *g, double ms[3], long long *exchanges, bool reset) {
+  if (!g->builder || !g->builder->xchg_) return false;
+  ARB_CUDA(cudaStreamSynchronize(g->stream));
+  g->builder->xchg_->Clock(ms, exchanges, reset);
+  return true;
+}
+
 void BuilderView::train_yhat(Garden *g, float *out) {
   ARB_CHECK(g->builder, "no tree has been grown yet");
   ARB_CUDA(cudaStreamSynchronize(g->stream));

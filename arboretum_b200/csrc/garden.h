@@ -132,6 +132,8 @@ struct BuilderView {
   static const unsigned *host_node_begin(const Garden *g, int tree_in_round, int *stride);
   static void scales(Garden *g, QuantScale *out);
   static void train_yhat(Garden *g, float *out);
+  // device time of the peer-memory exchanges so far (see PeerExchange::Clock); false: none in use
+  static bool exchange_clock(Garden *g, double ms[3], long long *exchanges, bool reset);
 };
 
 class Garden {

@@ -543,6 +543,11 @@ def main():
                 "data": "synthetic", "config": workload_config(args, world), "clocks": clocks,
                 "e2e": e2e, "gpu_launches": int(launches), "wall_ms_per_step": 1000.0 * wall_s / args.steps,
                 "level_exchange": t.get("level_exchange"),
+                "exchange_ms_per_round": None if "exchanges" not in t else {
+                    "waiting for the peers' buffers": t["exchange_wait_peers_ms"] / prof_rounds,
+                    "summing and storing this rank's slice": t["exchange_move_ms"] / prof_rounds,
+                    "waiting for the peers' slices": t["exchange_wait_done_ms"] / prof_rounds,
+                    "exchanges": t["exchanges"] / prof_rounds},
                 "roofline": roofline}
         if world == 1 and not args.no_ref_cuda:
             line["ref_cuda"] = reference_cuda_record(args.workload, args.rows)
