@@ -33,7 +33,7 @@ def _load_lib():
                  "ASetLabel", "ASetWeights", "ADumpModel", "ALoadModel",
                  # additive entry points of this build
                  "ACreateFromBinnedMatrix", "ASetThresholds", "AQuantize", "AGetTrainY",
-                 "AGetLevelStats", "AGetLevelStatsOf", "AGetGradientStep", "ASetProfile", "AGetTimings", "ABuildHistogram",
+                 "AGetLevelStats", "AGetLevelStatsOf", "AGetGradientStep", "APeerWaitProbe", "ASetProfile", "AGetTimings", "ABuildHistogram",
                  "ABuildHistogramFromParents", "ANcclUniqueId", "AInitNccl", "AThresholdsNoAlloc", "ASharedAtomicPeak",
                  "AReleaseCachedMemory"):
         getattr(lib, name).restype = ctypes.c_char_p
@@ -62,6 +62,7 @@ def _load_lib():
     lib.AGetLevelStatsOf.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 9
     lib.AGetGradientStep.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double),
                                      ctypes.POINTER(ctypes.c_double)]
+    lib.APeerWaitProbe.argtypes = [ctypes.c_double, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double)]
     lib.ASetProfile.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.AGetTimings.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p)]
     lib.ABuildHistogram.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int,
@@ -115,7 +116,7 @@ class DMatrix(object):
             raise ValueError(
                 'y and labels both are not None. Specify labels only for multi label classification')
         if y is not None:
-            assert data.shape[0] == len(y)
+            assert data.shape[0] == (y.shape[0] if hasattr(y, "shape") else len(y))
             self._init_y(y)
         elif labels is not None:
             self.labels_count = int(np.max(labels)) + 1
@@ -140,6 +141,21 @@ class DMatrix(object):
     def _init_from_npy2d(self, mat, missing, category=None):
         if len(mat.shape) != 2:
             raise ValueError('Input numpy.ndarray must be 2 dimensional')
+        cai = getattr(mat, "__cuda_array_interface__", None)
+        if cai is not None:
+            # additive: a C-contiguous float32 matrix that already lives in device memory (torch,
+            # cupy, numba ...) is copied device to device; nothing passes through the host
+            if cai["typestr"] != "<f4" or cai.get("strides") not in (None, (4 * mat.shape[1], 4)):
+                raise ValueError("device matrices must be C-contiguous float32")
+            if category is not None and not np.issubdtype(category.dtype, np.integer):
+                raise ValueError('Categoty''s type must be int like')
+            self.handle = ctypes.c_void_p()
+            cat = None if category is None else np.array(category.reshape(category.size), dtype=np.uint32)
+            _call_and_throw_if_error(_LIB.ACreateFromDenseMatrix(
+                ctypes.c_void_p(cai["data"][0]), _ptr(cat), ctypes.c_int(mat.shape[0]),
+                ctypes.c_int(mat.shape[1]), ctypes.c_int(0 if category is None else category.shape[1]),
+                ctypes.c_float(missing), ctypes.byref(self.handle)))
+            return
         if category is not None and not np.issubdtype(category.dtype, np.integer):
             raise ValueError('Categoty''s type must be int like')
         # no host copy when the caller's matrix is already C-contiguous float32 (the library
@@ -166,6 +182,12 @@ class DMatrix(object):
             ctypes.c_int(hist_size), ctypes.byref(self.handle)))
 
     def _init_y(self, y):
+        cai = getattr(y, "__cuda_array_interface__", None)
+        if cai is not None:  # additive: float32 targets in device memory
+            if cai["typestr"] != "<f4" or int(np.prod(cai["shape"])) != self.rows:
+                raise ValueError("device targets must be %d float32 values" % self.rows)
+            _call_and_throw_if_error(_LIB.ASetY(self.handle, ctypes.c_void_p(cai["data"][0])))
+            return
         data = np.ascontiguousarray(np.asarray(y).reshape(self.rows), dtype=np.float32)
         _call_and_throw_if_error(_LIB.ASetY(self.handle, _ptr(data)))
 
@@ -174,6 +196,23 @@ class DMatrix(object):
         _call_and_throw_if_error(_LIB.ASetLabel(self.handle, _ptr(data)))
 
     # ---- additive helpers -------------------------------------------------------
+    @classmethod
+    def from_device_bins(cls, bins_ptr, rows, columns, hist_size, y_ptr=None):
+        """Rows that are already binned AND already in device memory: ``bins_ptr`` is the
+        address of ``rows x columns`` uint8 bin ids (row-major), ``y_ptr`` of ``rows`` float32
+        targets (e.g. ``tensor.data_ptr()`` of torch CUDA tensors, which must stay alive
+        until this call returns)."""
+        self = cls.__new__(cls)
+        self.labels_count = 1
+        self.rows, self.columns = int(rows), int(columns)
+        self.handle = ctypes.c_void_p()
+        _call_and_throw_if_error(_LIB.ACreateFromBinnedMatrix(
+            ctypes.c_void_p(bins_ptr), ctypes.c_int64(rows), ctypes.c_int(columns),
+            ctypes.c_int(hist_size), ctypes.byref(self.handle)))
+        if y_ptr is not None:
+            _call_and_throw_if_error(_LIB.ASetY(self.handle, ctypes.c_void_p(y_ptr)))
+        return self
+
     def set_thresholds(self, thresholds, sizes):
         """Use thresholds computed elsewhere ([columns][hist_size], bins in use)."""
         thr = np.ascontiguousarray(thresholds, dtype=np.float32)

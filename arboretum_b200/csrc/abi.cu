@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/arboretum_b200.h"
+#include "exchange.h"
 #include "garden.h"
 
 using namespace arb;
@@ -43,6 +44,8 @@ struct NcclApi {
                             cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;  // optional
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;                          // optional
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
   void load() {
     if (handle) return;
@@ -56,6 +59,8 @@ struct NcclApi {
     AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(handle, "ncclAllGather"));
     CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(handle, "ncclCommDestroy"));
     GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(handle, "ncclGetErrorString"));
+    CommGetAsyncError = reinterpret_cast<decltype(CommGetAsyncError)>(dlsym(handle, "ncclCommGetAsyncError"));
+    CommAbort = reinterpret_cast<decltype(CommAbort)>(dlsym(handle, "ncclCommAbort"));
     if (!GetUniqueId || !CommInitRank || !AllReduce || !AllGather || !CommDestroy || !GetErrorString)
       throw std::runtime_error("libnccl.so.2 lacks a required symbol");
   }
@@ -92,6 +97,21 @@ int nccl_allreduce_max(void *ctx, unsigned *buf, size_t count, cudaStream_t s) {
   return r == ncclSuccess ? 0 : 1;
 }
 
+// CommCheckFn of the NCCL path (see garden.h)
+int nccl_check(void *ctx, int give_up, char *msg, size_t msg_len) {
+  NcclCtx *c = static_cast<NcclCtx *>(ctx);
+  ncclResult_t state = ncclSuccess;
+  if (g_nccl.CommGetAsyncError && g_nccl.CommGetAsyncError(c->comm, &state) != ncclSuccess) state = ncclInternalError;
+  if (state == ncclInProgress) state = ncclSuccess;
+  if (state == ncclSuccess && !give_up) return 0;
+  if (state != ncclSuccess && msg_len)
+    std::snprintf(msg, msg_len, "NCCL reports %s", g_nccl.GetErrorString(state));
+  if (g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
+  if (c->comm == g_process_comm) g_process_comm = nullptr;  // never handed out again
+  c->comm = nullptr;
+  return 1;
+}
+
 void host_scales(float max_g, float max_h, int qb, bool pair, QuantScale *q) {
   int eg = 0, eh = 0;
   if (max_g > 0.0f && std::isfinite(max_g)) std::frexp(max_g, &eg);
@@ -105,6 +125,16 @@ void host_scales(float max_g, float max_h, int qb, bool pair, QuantScale *q) {
 
 // Targets follow the matrix: when it sits in HBM they are copied straight from the
 // caller's buffer to the same device (no host copy is kept); false = keep them on the host.
+// true when `p` points into device memory (such a buffer can only be copied, not read, here)
+bool is_device_pointer(const void *p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice;
+}
+
 bool upload_beside_matrix(DataMatrix *d, DevBuf &dst, const void *src, size_t bytes) {
   if (d->device < 0) return false;
   int cur = -1;
@@ -120,7 +150,7 @@ bool upload_beside_matrix(DataMatrix *d, DevBuf &dst, const void *src, size_t by
       dst.bytes = bytes;
     }
   }
-  ok = ok && cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice) == cudaSuccess;
+  ok = ok && cudaMemcpy(dst.p, src, bytes, cudaMemcpyDefault) == cudaSuccess;  // host or device source
   if (!ok) {
     cudaGetLastError();
     dst.release();
@@ -143,6 +173,7 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
   ARB_CHECK(ccol == 0 || categories != nullptr, "categories is NULL");
   std::unique_ptr<DataMatrix> m(new DataMatrix(nrow, ncol, ccol));
   if (ccol > 0) {  // arboretum_wrapper.cu:30-33; kept on the host for the quantiser
+    ARB_CHECK(!is_device_pointer(categories), "category codes are read on the host: pass host memory");
     m->cat.assign(categories, categories + size_t(nrow) * ccol);
   }
   StageTrace trace("ACreateFromDenseMatrix");
@@ -157,13 +188,16 @@ const char *ACreateFromDenseMatrix(const float *data, const unsigned int *catego
     if (dev_alloc(&p, bytes) == cudaSuccess) {
       m->d_x.p = p;
       m->d_x.bytes = bytes;
-      on_device = cudaMemcpy(p, data, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+      // `data` may be host memory or (additive) device memory, e.g. an array another
+      // library left on the GPU: the copy takes either
+      on_device = cudaMemcpy(p, data, bytes, cudaMemcpyDefault) == cudaSuccess &&
                   cudaGetDevice(&m->device) == cudaSuccess;
       if (!on_device) m->d_x.release();
     }
   }
   if (!on_device) {
     cudaGetLastError();  // clear the error state: the host copy below is the fallback storage
+    ARB_CHECK(!is_device_pointer(data), "a matrix in device memory that does not fit beside its training state");
     m->x.assign(data, data + size_t(nrow) * ncol);
   }
   trace.lap("matrix to HBM");
@@ -196,13 +230,15 @@ const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol,
     if (dev_alloc(&p, bytes) == cudaSuccess) {
       m->d_raw.p = p;
       m->d_raw.bytes = bytes;
-      on_device = cudaMemcpy(p, bins, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+      // the rows may already be in device memory (generated or decoded there): any source works
+      on_device = cudaMemcpy(p, bins, bytes, cudaMemcpyDefault) == cudaSuccess &&
                   cudaGetDevice(&m->device) == cudaSuccess;
       if (!on_device) m->d_raw.release();
     }
   }
   if (!on_device) {
     cudaGetLastError();
+    ARB_CHECK(!is_device_pointer(bins), "rows in device memory that do not fit beside their training state");
     m->host_bins.assign(bins, bins + bytes);
   }
   *out = m.release();
@@ -213,7 +249,10 @@ const char *ASetY(VoidPointer data, const float *y) {
   ARB_TRY
   ARB_CHECK(data && y, "NULL argument");
   DataMatrix *d = static_cast<DataMatrix *>(data);
-  if (!upload_beside_matrix(d, d->d_y, y, size_t(d->rows) * sizeof(float))) d->y.assign(y, y + d->rows);
+  if (!upload_beside_matrix(d, d->d_y, y, size_t(d->rows) * sizeof(float))) {
+    ARB_CHECK(!is_device_pointer(y), "targets in device memory need the matrix in device memory");
+    d->y.assign(y, y + d->rows);
+  }
   ARB_CATCH
 }
 
@@ -351,6 +390,7 @@ const char *AFreeGarden(VoidPointer ptr) {
   Garden *g = static_cast<Garden *>(ptr);
   if (g && g->allreduce_ctx) {
     NcclCtx *c = static_cast<NcclCtx *>(g->allreduce_ctx);
+    g->ReleaseBuilder();  // before the communicator it may still be using
     if (c->comm && !c->shared) g_nccl.CommDestroy(c->comm);
     delete c;
     g->allreduce_ctx = nullptr;
@@ -684,6 +724,14 @@ const char *ABuildHistogramFromParents(const void *bins, int bin_bytes, int64_t 
                          quant_bits, out_g, out_h, 0, nullptr, parent_g, parent_h);
 }
 
+const char *APeerWaitProbe(double limit_ms, int *timed_out, double *waited_ms) {
+  ARB_TRY
+  ARB_CHECK(timed_out && waited_ms, "NULL argument");
+  ARB_CHECK(limit_ms > 0 && limit_ms <= 2000, "limit_ms must be in (0, 2000]");
+  peer_wait_probe(limit_ms, timed_out, waited_ms);
+  ARB_CATCH
+}
+
 const char *ANcclUniqueId(char *id128) {
   ARB_TRY
   ARB_CHECK(id128, "NULL argument");
@@ -725,6 +773,7 @@ const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128
   }
   g->allreduce = nccl_allreduce;
   g->allreduce_max = nccl_allreduce_max;
+  g->comm_check = nccl_check;
   g->shards.rank = rank;
   g->shards.world = world;
   g->shards.allgather = nccl_allgather;

@@ -130,6 +130,10 @@ __global__ void peer_max_kernel(const PeerPointers p, const int rank, const int 
   }
 }
 
+__global__ void wait_probe_kernel(const u64 *flag, u64 limit_ns, int *timed_out) {
+  *timed_out = wait_flag(flag, 1, limit_ns) ? 0 : 1;
+}
+
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct Layout {
@@ -263,6 +267,28 @@ void PeerExchange::Clock(double ms[3], long long *exchanges, bool reset) {
   for (int i = 0; i < 3; ++i) ms[i] = double(v[i]) * 1e-6;
   *exchanges = (long long)v[3];
   if (reset) ARB_CUDA(cudaMemset(d_clock_, 0, sizeof v));
+}
+
+void peer_wait_probe(double limit_ms, int *timed_out, double *waited_ms) {
+  DevBuf d;
+  d.alloc(512);
+  ARB_CUDA(cudaMemset(d.p, 0, 512));
+  u64 *flag = d.as<u64>();
+  int *out = reinterpret_cast<int *>(d.as<char>() + 256);
+  cudaEvent_t e0, e1;
+  ARB_CUDA(cudaEventCreate(&e0));
+  ARB_CUDA(cudaEventCreate(&e1));
+  ARB_CUDA(cudaEventRecord(e0, nullptr));
+  wait_probe_kernel<<<1, 1>>>(flag, u64(limit_ms * 1e6), out);
+  ARB_CUDA(cudaEventRecord(e1, nullptr));
+  const cudaError_t e = cudaEventSynchronize(e1);
+  float ms = 0.0f;
+  if (e == cudaSuccess) cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  ARB_CUDA(e);
+  ARB_CUDA(cudaMemcpy(timed_out, out, sizeof(int), cudaMemcpyDeviceToHost));
+  *waited_ms = ms;
 }
 
 int PeerExchange::Status() {

@@ -72,4 +72,9 @@ class PeerExchange {
   unsigned long long seq_ = 0, small_seq_ = 0;
 };
 
+// The bounded wait of the exchange kernels on a word that nothing ever sets: one thread waits
+// `limit_ms`, gives up, and the kernel returns normally.  *timed_out = 1 when the wait ran
+// into its limit (it must), *waited_ms = the kernel's device time.
+void peer_wait_probe(double limit_ms, int *timed_out, double *waited_ms);
+
 }  // namespace arb

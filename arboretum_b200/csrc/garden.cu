@@ -7,6 +7,7 @@
 #include "exchange.h"
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <limits>
@@ -1135,6 +1136,46 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
                            cudaMemcpyDeviceToHost, s));
   if (xchg_) ARB_CUDA(cudaMemcpyAsync(h_xchg_status_.p, xchg_->device_status(), sizeof(int), cudaMemcpyDeviceToHost, s));
+  if (g_->allreduce && !xchg_ && g_->comm_check) {
+    // Row shards over a collective library: a rank that died leaves its peers inside a
+    // collective for good.  The host therefore does not block in the synchronisation: it
+    // polls the stream, asks the communicator for asynchronous errors meanwhile, and gives
+    // up after a time limit (ARBORETUM_EXCHANGE_TIMEOUT_S, 300 s by default); either way the
+    // communicator is aborted and the caller gets an error string.
+    static const double limit_s = [] {
+      const char *e = std::getenv("ARBORETUM_EXCHANGE_TIMEOUT_S");
+      const double v = e ? std::atof(e) : 300.0;
+      return v > 0 ? v : 300.0;
+    }();
+    cudaEvent_t done;
+    ARB_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+    ARB_CUDA(cudaEventRecord(done, s));
+    const auto t0 = std::chrono::steady_clock::now();
+    unsigned polls = 0;
+    char msg[256] = "";
+    for (;;) {
+      const cudaError_t q = cudaEventQuery(done);
+      if (q == cudaSuccess) break;
+      if (q != cudaErrorNotReady) {
+        cudaEventDestroy(done);
+        ARB_CUDA(q);
+      }
+      if ((++polls & 255u) == 0u) {
+        const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        const int give_up = waited > limit_s ? 1 : 0;
+        if (g_->comm_check(g_->allreduce_ctx, give_up, msg, sizeof msg) != 0 || give_up) {
+          cudaEventDestroy(done);
+          cudaStreamSynchronize(s);  // the aborted collectives end
+          cudaGetLastError();
+          throw std::runtime_error(std::string("the exchange between the GPUs failed: ") +
+                                   (msg[0] ? msg : "no answer from a peer within the time limit"));
+        }
+      } else {
+        std::this_thread::yield();
+      }
+    }
+    cudaEventDestroy(done);
+  }
   ARB_CUDA(cudaStreamSynchronize(s));
   if (xchg_ && *h_xchg_status_.as<int>() != 0)
     throw std::runtime_error("a peer GPU did not answer within the time limit (exchange step " +
@@ -1332,6 +1373,11 @@ void Garden::EnsureStream() {
   if (stream) return;
   if (cfg.internal.device >= 0) ARB_CUDA(cudaSetDevice(cfg.internal.device));
   ARB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+}
+
+void Garden::ReleaseBuilder() {
+  delete builder;
+  builder = nullptr;
 }
 
 Garden::~Garden() {

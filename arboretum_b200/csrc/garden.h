@@ -109,6 +109,12 @@ typedef int (*AllreduceFn)(void *ctx, long long *device_buf, size_t count, cudaS
 // scale: every rank must quantise with the same one).
 typedef int (*AllreduceMaxFn)(void *ctx, unsigned *device_buf, size_t count, cudaStream_t stream);
 
+// Health of the communicator behind `allreduce`, asked by the host while it waits for a tree:
+// 0 = fine; otherwise `msg` says what the library reported and the communicator has been
+// aborted (so that the kernels waiting in it end and the stream can be synchronised).
+// `give_up` != 0: abort it in any case (the host's time limit ran out).
+typedef int (*CommCheckFn)(void *ctx, int give_up, char *msg, size_t msg_len);
+
 struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
   // (partition = the descend steps, plan = plan kernel + row lists, update = the final descend)
   double grad = 0, hist = 0, subtract = 0, split = 0, partition = 0, plan = 0, update = 0, allreduce = 0;
@@ -155,12 +161,14 @@ class Garden {
   AllreduceMaxFn allreduce_max = nullptr;
   ShardInfo shards;  // rank, world and the all-gather of the sharded quantizer
   void *allreduce_ctx = nullptr;
+  CommCheckFn comm_check = nullptr;
   bool profile = false;
   bool peer_exchange = false;  // the level exchange of the row shards runs over peer memory
   PhaseTimes times;
   // device copies of the forest for inference
   void SyncForest();
   void EnsureStream();
+  void ReleaseBuilder();
   DevBuf d_fid, d_thr, d_w, d_label, d_category;
   size_t forest_trees_on_device = 0;
   cudaStream_t stream = nullptr;

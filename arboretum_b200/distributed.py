@@ -62,6 +62,35 @@ def share_thresholds(data, hist_size, rank, world, thresholds=None, sizes=None, 
     return thr, size
 
 
+def all_ranks_ok(ok, what="set-up"):
+    """Every rank says whether its own step went well; all return True only if all did.
+    A rank that failed before a collective must not leave the others waiting inside it: call
+    this (``torch.distributed``, any backend) after the step and before the next exchange,
+    and raise on every rank when it returns False."""
+    import torch
+    import torch.distributed as dist
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+    if dist.get_backend() == "nccl":
+        flag = flag.cuda()
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(int(flag.item()) == 1)
+
+
+def guarded(step, what="set-up"):
+    """Runs ``step()`` on this rank, then agrees with the other ranks: if it raised anywhere,
+    it raises here too (``ArboretumError``), and no rank goes on to the next exchange."""
+    from . import core
+    err = None
+    try:
+        result = step()
+    except Exception as e:  # noqa: BLE001  (reported below, on every rank)
+        err, result = e, None
+    if not all_ranks_ok(err is None, what):
+        raise core.ArboretumError("%s failed on %s" % (what, "this rank: %r" % (err,) if err is not None
+                                                       else "another rank"))
+    return result
+
+
 _PROCESS_COMM = None  # (rank, world) of the communicator this process keeps
 
 

@@ -325,6 +325,86 @@ def reference_cuda_record(workload, rows):
             "first_round_with_quantisation_s": rec["first_round_with_quantisation_s"], "how": rec["how"]}
 
 
+def run_c5b(rows_per_gpu, steps, warmup, rank, world, local_rank, base_cfg):
+    """The out-of-core-scale configuration's sharded mode: rows pre-binned to uint8 x 100
+    features, `rows_per_gpu` of them generated ON every GPU (never on the host), a logistic
+    label from 10 active features, max_depth 8; rows sharded over the ranks with the
+    per-level histogram exchange.  Weak scaling: the per-GPU work is fixed, so rounds/s at N
+    GPUs against rounds/s at 1 GPU is the scaling of the row throughput.  Returns the
+    sub-record of the bench line (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+    import arboretum_b200 as arboretum
+    from arboretum_b200 import distributed as adist
+    F = 100
+    dev = torch.device("cuda", local_rank)
+    ok = torch.ones(1, device=dev)
+    model = None
+    try:
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(5000 + rank)
+        bins = torch.randint(0, 255, (rows_per_gpu, F), dtype=torch.uint8, device=dev, generator=gen)
+        prm = np.random.default_rng(5)
+        active = torch.as_tensor(prm.choice(F, 10, replace=False), device=dev)
+        coef = torch.as_tensor(prm.normal(0, 2, 10).astype(np.float32), device=dev)
+        logit = torch.zeros(rows_per_gpu, device=dev)
+        for j in range(10):  # column by column: no rows x 10 float temporary
+            logit += (bins[:, active[j]].float() / 255.0 - 0.5) * coef[j]
+        y = (torch.rand(rows_per_gpu, device=dev, generator=gen) < torch.sigmoid(logit)).float()
+        del logit
+        torch.cuda.synchronize()
+        data = arboretum.DMatrix.from_device_bins(bins.data_ptr(), rows_per_gpu, F, 255, y.data_ptr())
+        del bins, y
+        torch.cuda.empty_cache()
+        cfg = json.loads(json.dumps(base_cfg))
+        cfg["internals"]["device"] = local_rank
+        model = arboretum.Garden(cfg)
+        model.data = data
+        if world > 1:
+            adist.init_nccl(model, rank, world)
+    except Exception as e:  # e.g. not enough memory for this many rows
+        ok.zero_()
+        err = repr(e)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0:  # every rank leaves together, before any exchange
+        return {"unavailable": "set-up failed on a rank" + (": " + err if "err" in dir() else "")} if rank == 0 else None
+    for _ in range(max(1, warmup)):
+        model.grow_tree()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        model.grow_tree()
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1) / 1000.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_s = float(t.item()) / steps
+    model.set_profile(True)
+    model.grow_tree()
+    tm = model.timings()
+    del model, data
+    if rank != 0:
+        return None
+    return {"workload": "pre-binned uint8 %d rows per GPU x 100 features, reg:logistic, max_depth 8, rows sharded "
+                        "over the GPUs (configs[4] mode b), generated on the devices" % rows_per_gpu,
+            "rows_per_gpu": rows_per_gpu, "rows_total": rows_per_gpu * world, "n_gpus": world,
+            "scaling": "weak", "value": 1.0 / step_s, "unit": "rounds/s", "ms_per_step": 1000.0 * step_s,
+            "steps": steps, "warmup": max(1, warmup),
+            "rows_x_features_per_s": rows_per_gpu * world * F / step_s,
+            "hist_rows_x_features_per_s_per_gpu": tm["hist_rows"] * F / (tm["hist_ms"] * 1e-3) if tm["hist_ms"] > 0 else None,
+            "hist_frac_of_hbm_peak": (tm["hist_bytes"] / (tm["hist_ms"] * 1e-3) / 1e9 / measured_peak()[0]) if tm["hist_ms"] > 0 else None,
+            "level_exchange": tm.get("level_exchange"),
+            "phase_ms_per_round": {k: tm[k] for k in ("grad_ms", "partition_ms", "plan_ms", "hist_ms", "allreduce_ms",
+                                                      "subtract_ms", "split_ms", "update_ms")}}
+
+
 def shared_atomics(t, features):
     """The histogram pass against the ceiling of its inner loop: (g, h) pair updates per
     second of the two shared-memory reductions alone, measured by the library on this GPU
@@ -361,6 +441,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the end-to-end jobs (profiling runs: fewer launches before the timed rounds)")
     ap.add_argument("--internals", default="", help='JSON merged into the "internals" configuration')
+    ap.add_argument("--c5b-rows-per-gpu", type=int, default=250_000_000,
+                    help="rows per GPU of the sharded out-of-core-scale sub-record (0: skip it)")
     args = ap.parse_args()
     if args.rows <= 0:
         args.rows = WORKLOADS[args.workload][0]
@@ -535,6 +617,14 @@ def main():
                     "tree_ms": t["tree_ms"] / max(1, t["trees"]),
                     "rows_streamed_per_s": t["h2d_bytes"] / ((features + 31) // 32 * 32) / (t["tree_ms"] * 1e-3)}
 
+    # ---- the 2 B-row configuration's sharded mode, per-GPU share fixed (weak scaling) ------
+    c5b = None
+    if args.c5b_rows_per_gpu > 0 and args.workload == "c2":
+        del model, data, yhat, xp, Xh, X
+        arboretum.release_cached_memory()
+        torch.cuda.empty_cache()
+        c5b = run_c5b(args.c5b_rows_per_gpu, 5, 2, rank, world, local_rank, WORKLOADS["c5"][3])
+
     if rank == 0:
         line = {"metric": "boosting_rounds_per_sec", "value": args.steps / step_s, "unit": "rounds/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -549,6 +639,8 @@ def main():
                     "waiting for the peers' slices": t["exchange_wait_done_ms"] / prof_rounds,
                     "exchanges": t["exchanges"] / prof_rounds},
                 "roofline": roofline}
+        if c5b is not None:
+            line["c5b"] = c5b
         if world == 1 and not args.no_ref_cuda:
             line["ref_cuda"] = reference_cuda_record(args.workload, args.rows)
         if world == 1 and not args.no_cpu_baseline:

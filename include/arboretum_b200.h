@@ -56,7 +56,9 @@ const char *ADeleteArray(float *in);
 /* ------------------------------- additive ---------------------------------- */
 
 /* Rows that are already binned (uint8 ids < hist_size, row-major [nrow][ncol]);
- * the reference ingests fp32 only (arboretum_wrapper.h:6-9). */
+ * the reference ingests fp32 only (arboretum_wrapper.h:6-9).  `bins` may point to host or
+ * to device memory (rows generated or decoded on the GPU); so may ASetY's `y` for a matrix
+ * that lives in device memory. */
 const char *ACreateFromBinnedMatrix(const uint8_t *bins, int64_t nrow, int ncol, int hist_size,
                                     VoidPointer *out);
 /* Thresholds computed elsewhere (e.g. on the whole data set before sharding rows
@@ -116,6 +118,13 @@ const char *ABuildHistogramFromParents(const void *bins, int bin_bytes, int64_t 
  * the same time. */
 const char *ANcclUniqueId(char *id128);
 const char *AInitNccl(VoidPointer garden, int rank, int world, const char *id128);
+
+/* No counterpart in the reference.  The waits of the exchange between row shards over peer
+ * memory are bounded: a peer that never answers makes a kernel give up after a time limit,
+ * record where, and return (the host then reports an error after the tree; the context stays
+ * usable).  This call exercises exactly that wait on a word that nothing sets, on the
+ * current device: *timed_out becomes 1, *waited_ms about limit_ms (at most 2000). */
+const char *APeerWaitProbe(double limit_ms, int *timed_out, double *waited_ms);
 
 /* No counterpart in the reference.  Threshold search of ONE feature for callers that
  * must not allocate device memory (a process whose GPU memory is owned by one

@@ -80,3 +80,38 @@ def test_two_gloo_ranks():
         out = m.dict()
         mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
         assert all(out[r] for r in range(world))
+
+
+def _failing_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import arboretum_b200
+    from arboretum_b200.distributed import guarded
+
+    def step():
+        if rank == 1:
+            raise MemoryError("no room for the level buffers")  # a set-up step that fails on one rank
+        return "ready"
+
+    try:
+        guarded(step, "building the level buffers")
+        out[rank] = "went on"
+    except arboretum_b200.ArboretumError as e:
+        out[rank] = str(e)
+    # a step that works everywhere goes through on every rank
+    out[(rank, "second")] = guarded(lambda: rank * 10, "a step that works")
+    dist.destroy_process_group()
+
+
+def test_a_rank_that_fails_during_set_up_stops_all_ranks():
+    """One rank's set-up raises: every rank gets an error instead of entering the next
+    exchange, where the others would wait for the one that never comes."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_failing_worker, args=(world, port, out), nprocs=world, join=True)
+        assert "another rank" in out[0]
+        assert "this rank" in out[1] and "no room" in out[1]
+        assert out[(0, "second")] == 0 and out[(1, "second")] == 10

@@ -639,3 +639,29 @@ def test_out_of_core_prebinned_input():
     for a, b in zip(got, exp):
         assert [nd.get("fid") for nd in a["nodes"]] == [nd.get("fid") for nd in b["nodes"]]
         assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
+
+
+def test_a_wait_on_a_peer_that_never_answers_gives_up():
+    """The exchange kernels between row shards wait for their peers with a time limit.  Here the
+    same wait runs on a word that nothing sets: it gives up after the limit, the kernel returns
+    normally, the status says so, and the device goes on working."""
+    import ctypes
+    from arboretum_b200 import core
+    timed_out, waited = ctypes.c_int(-1), ctypes.c_double(0)
+    assert core.lib().APeerWaitProbe(50.0, ctypes.byref(timed_out), ctypes.byref(waited)) is None
+    assert timed_out.value == 1
+    assert 45.0 <= waited.value < 1000.0
+    assert core.shared_atomic_peak(50) > 0  # the context is intact
+
+
+def test_matrix_and_targets_from_device_memory():
+    """A float32 matrix and targets that already live on the GPU (anything with
+    __cuda_array_interface__) train to the same model as the same values from host memory."""
+    import torch
+    arboretum = arb()
+    X, y = synth("logistic", 20000, 12, seed=3)
+    cfg = make_config(1, 5)
+    host = arboretum.train(cfg, arboretum.DMatrix(X, y=y), 3).dump()
+    Xd, yd = torch.from_numpy(X).cuda(), torch.from_numpy(y).cuda()
+    dev = arboretum.train(cfg, arboretum.DMatrix(Xd, y=yd), 3).dump()
+    assert dev == host
