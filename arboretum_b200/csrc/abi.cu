@@ -657,6 +657,15 @@ static const char *build_histogram(const void *bins, int bin_bytes, int64_t nrow
   h.n_items = d_nitems.as<int>();
   h.max_items = n_items;
   h.partials = d_partials.as<int>();
+  // rows named by `rowid` are gathered through the TMA unit where that is possible, like in training
+  RowGatherMap row_map;
+  DevBuf d_gather_status;
+  if (rowid && make_row_gather_map(&row_map, geo.bins, geo.pitch, n)) {
+    d_gather_status.alloc(sizeof(int));
+    ARB_CUDA(cudaMemsetAsync(d_gather_status.p, 0, sizeof(int), s));
+    h.row_map = &row_map;
+    h.status = d_gather_status.as<int>();
+  }
   ReduceLaunch rd;
   rd.partials = d_partials.as<int>();
   rd.item_first = d_first.as<int>();
@@ -691,7 +700,11 @@ static const char *build_histogram(const void *bins, int bin_bytes, int64_t nrow
   launch_reduce(rd, s);
   std::vector<long long> host(words);
   ARB_CUDA(cudaMemcpyAsync(host.data(), d_hist.p, d_hist.bytes, cudaMemcpyDeviceToHost, s));
+  int gather_status = 0;
+  if (h.status)
+    ARB_CUDA(cudaMemcpyAsync(&gather_status, h.status, sizeof(int), cudaMemcpyDeviceToHost, s));
   ARB_CUDA(cudaStreamSynchronize(s));
+  ARB_CHECK(gather_status == 0, "a row gather of the histogram kernel did not arrive within its time limit");
   const int HW = hist_size + 1;
   for (int node = 0; node < n_nodes; ++node)
     for (int f = 0; f < ncol; ++f) {

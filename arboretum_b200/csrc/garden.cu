@@ -471,6 +471,12 @@ class Builder {
   PeerExchange *xchg_ = nullptr;  // row shards of one box: the level exchange over peer memory
                                   // (the process's; not owned)
   PinnedBuf h_xchg_status_;
+  // the histogram kernel's row gather through the TMA unit: a tensor map of the resident bin
+  // matrix and the word in which a kernel reports a gather that never arrived
+  RowGatherMap row_map_;
+  bool has_row_map_ = false;
+  DevBuf d_hist_status_;
+  PinnedBuf h_hist_status_;
   bool count_plane_ = false;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
   // records of every tree of the last round (multi:softmax grows labels_count of them)
@@ -559,6 +565,14 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   geo_.NT = (F_ + geo_.TW - 1) / geo_.TW;
   geo_.bins_cm = d->d_bins_cm.as<unsigned char>();
   geo_.cm_rows = n_;
+  if (geo_.bins && geo_.bin_bytes == 1 && geo_.TW == 32 &&
+      make_row_gather_map(&row_map_, geo_.bins, geo_.pitch, n_)) {
+    has_row_map_ = true;
+    d_hist_status_.alloc(sizeof(int));
+    ARB_CUDA(cudaMemsetAsync(d_hist_status_.p, 0, sizeof(int), s));
+    h_hist_status_.alloc(sizeof(int));
+    *h_hist_status_.as<int>() = 0;
+  }
 
   size_t n_global = n_;
   if (g->shards.world > 1 && g->shards.allgather) {
@@ -1042,6 +1056,10 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
         h.partials = d_partials_.as<int>();
         h.list_grad = (l == 0 || k > 0) ? nullptr : list_grad;
+        if (has_row_map_ && geo.bins == geo_.bins) {
+          h.row_map = &row_map_;
+          h.status = d_hist_status_.as<int>();
+        }
         launch_hist(h, s);
         ReduceLaunch rd;
         rd.partials = d_partials_.as<int>();
@@ -1136,6 +1154,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   ARB_CUDA(cudaMemcpyAsync(h_node_begin_.p, d_node_begin_.p, d_node_begin_.bytes,
                            cudaMemcpyDeviceToHost, s));
   if (xchg_) ARB_CUDA(cudaMemcpyAsync(h_xchg_status_.p, xchg_->device_status(), sizeof(int), cudaMemcpyDeviceToHost, s));
+  if (has_row_map_)
+    ARB_CUDA(cudaMemcpyAsync(h_hist_status_.p, d_hist_status_.p, sizeof(int), cudaMemcpyDeviceToHost, s));
   if (g_->allreduce && !xchg_ && g_->comm_check) {
     // Row shards over a collective library: a rank that died leaves its peers inside a
     // collective for good.  The host therefore does not block in the synchronisation: it
@@ -1177,6 +1197,9 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     cudaEventDestroy(done);
   }
   ARB_CUDA(cudaStreamSynchronize(s));
+  if (has_row_map_ && *h_hist_status_.as<int>() != 0)
+    throw std::runtime_error("a row gather of the histogram kernel did not arrive within its time limit: "
+                             "the tree is incomplete");
   if (xchg_ && *h_xchg_status_.as<int>() != 0)
     throw std::runtime_error("a peer GPU did not answer within the time limit (exchange step " +
                              std::to_string(*h_xchg_status_.as<int>()) + "): the tree is incomplete");

@@ -24,9 +24,20 @@
 //    says which rows a node has: ids and gradients are read in list order, the bins
 //    are gathered with the 64-byte L2 fetch qualifier, since a plain copy would pull
 //    the whole 128-byte line (four rows) for the one row the node wants.
+//    With ARBORETUM_TMA_GATHER in the environment (and the matrix resident in HBM) the gather
+//    is done by the TMA unit instead: cp.async.bulk.tensor.2d ... tile::gather4 names four
+//    rows per instruction, eight lanes fetch a warp's batch of 32 rows, the tensor map asks
+//    L2 for 64-byte fetches, and completion is counted on a per-warp mbarrier.  The address
+//    work of the gather then no longer goes through the load/store pipe that the
+//    red.shared instructions need; measured, the pass is 6 % slower this way (both gathers
+//    reach the same rate alone, and the reductions bound the pass), so it is not the default.
 //  * The CTA stores its planes with plain coalesced stores; reduce_kernel then
 //    sums the planes of every built node into the level's int64 histogram and, in
 //    the same pass, derives the sibling as parent - built (the subtraction trick).
+#include <cuda.h>
+
+#include <cstring>
+
 #include "kernels.cuh"
 
 namespace arb {
@@ -64,6 +75,46 @@ __device__ __forceinline__ void red_shared(int *p, int v) {
   asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
+// ---- TMA row gather ---------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, int count) {
+  const unsigned a = unsigned(__cvta_generic_to_shared(bar));
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+  const unsigned a = unsigned(__cvta_generic_to_shared(bar));
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+  const unsigned a = unsigned(__cvta_generic_to_shared(bar));
+  unsigned ok;
+  asm volatile(
+    "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+    : "=r"(ok)
+    : "r"(a), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// four rows y0..y3 of the 2-D tensor (bytes of a row, rows), `x` bytes into each, to 4 x 32
+// consecutive bytes of shared memory; x must be a multiple of 16
+__device__ __forceinline__ void tma_gather4(void *dst, const CUtensorMap *map, int x, int y0, int y1, int y2,
+                                            int y3, unsigned long long *bar) {
+  const unsigned d = unsigned(__cvta_generic_to_shared(dst));
+  const unsigned a = unsigned(__cvta_generic_to_shared(bar));
+  asm volatile(
+    "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+    "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(d),
+    "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(a)
+    : "memory");
+}
+// A wait on the gather's barrier gives up after this long and reports it (the data of a
+// copy that never arrives cannot be had any other way; the host then refuses the tree).
+constexpr unsigned long long kGatherWaitNs = 2000000000ull;
+
 // the CTA's two int32 planes -> partials[(item * NT + tile)][2][kHistWords]
 __device__ __forceinline__ void store_planes(const int *smem, int *dst) {
   const int4 *src4 = reinterpret_cast<const int4 *>(smem);
@@ -72,24 +123,43 @@ __device__ __forceinline__ void store_planes(const int *smem, int *dst) {
 }
 
 // uint8 bins, 32 features per tile, 256 bins.
-template <bool PAIR, bool IDENT>
+// TMA: rows are gathered through `row_map` (never with IDENT); `status` takes a 1 when a wait
+// on a gather ran into its time limit.
+template <bool PAIR, bool IDENT, bool TMA>
 __global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
 hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
                const int *__restrict__ item_slot, int *__restrict__ partials,
-               const void *__restrict__ list_grad) {
-  extern __shared__ __align__(16) int smem[];
-  // the histogram of the CTA's first item is cleared while the kernel before this one drains
-  overlap_release();
-  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
-  overlap_wait();
-  bool cleared = true;
-  int *G = smem;
+               const void *__restrict__ list_grad, const __grid_constant__ CUtensorMap row_map,
+               int *__restrict__ status) {
+  static_assert(!(TMA && IDENT), "consecutive rows are copied, not gathered");
+  extern __shared__ __align__(128) int smem[];
   constexpr int kWarps = kHistThreads / 32;
   unsigned char *stage0 = reinterpret_cast<unsigned char *>(smem + 2 * kHistWords);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char *my = stage0 + warp * kStages * kStageBytes;
+  // one barrier per warp and stage, behind the stages
+  unsigned long long *bars =
+    reinterpret_cast<unsigned long long *>(stage0 + kWarps * kStages * kStageBytes) + warp * kStages;
+  unsigned phases = 0;   // bit s: the parity the next wait on stage s looks for
+  bool gave_up = false;  // a wait ran out: no more gathers are issued or waited for
+  // the histogram of the CTA's first item is cleared while the kernel before this one drains
+  overlap_release();
+  for (int w = threadIdx.x; w < 2 * kHistWords; w += kHistThreads) smem[w] = 0;
+  overlap_wait();
+  if (TMA) {
+    // after the wait, not in the preamble: with the barriers initialised before it, a kernel
+    // launched as a programmatic dependent built wrong histograms for the last nodes of a level
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < kStages; ++st) mbar_init(bars + st, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+  }
+  bool cleared = true;
+  int *G = smem;
   const int tile = blockIdx.y;
   const unsigned char *tile_base = bins + size_t(tile) * 32;
   const int q = lane >> 3, m = lane & 7;
@@ -125,19 +195,33 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
     };
     auto issue = [&](int b, int stage, unsigned rid_lane) {
       unsigned char *sb = my + stage * kStageBytes;
-      // bins: lane handles half (lane & 1) of rows (lane >> 1) and 16 + (lane >> 1)
-      const unsigned r0 = __shfl_sync(0xffffffffu, rid_lane, lane >> 1);
-      const unsigned r1 = __shfl_sync(0xffffffffu, rid_lane, 16 + (lane >> 1));
-      if (IDENT) {  // consecutive rows: whole lines are wanted
-        cp_async16(sb + (lane >> 1) * 32 + (lane & 1) * 16,
-                   tile_base + size_t(r0) * pitch + (lane & 1) * 16);
-        cp_async16(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
-                   tile_base + size_t(r1) * pitch + (lane & 1) * 16);
+      if (TMA) {
+        // lane j < 8 names rows 4j..4j+3 of the batch; the barrier expects the batch's 1024 bytes
+        const int src = (lane & 7) * 4;
+        const int y0 = int(__shfl_sync(0xffffffffu, rid_lane, src));
+        const int y1 = int(__shfl_sync(0xffffffffu, rid_lane, src + 1));
+        const int y2 = int(__shfl_sync(0xffffffffu, rid_lane, src + 2));
+        const int y3 = int(__shfl_sync(0xffffffffu, rid_lane, src + 3));
+        if (!gave_up) {
+          if (lane == 0) mbar_expect_tx(bars + stage, 1024);
+          __syncwarp();
+          if (lane < 8) tma_gather4(sb + lane * 128, &row_map, tile * 32, y0, y1, y2, y3, bars + stage);
+        }
       } else {
-        cp_async16_gather(sb + (lane >> 1) * 32 + (lane & 1) * 16,
-                          tile_base + size_t(r0) * pitch + (lane & 1) * 16);
-        cp_async16_gather(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
-                          tile_base + size_t(r1) * pitch + (lane & 1) * 16);
+        // bins: lane handles half (lane & 1) of rows (lane >> 1) and 16 + (lane >> 1)
+        const unsigned r0 = __shfl_sync(0xffffffffu, rid_lane, lane >> 1);
+        const unsigned r1 = __shfl_sync(0xffffffffu, rid_lane, 16 + (lane >> 1));
+        if (IDENT) {  // consecutive rows: whole lines are wanted
+          cp_async16(sb + (lane >> 1) * 32 + (lane & 1) * 16,
+                     tile_base + size_t(r0) * pitch + (lane & 1) * 16);
+          cp_async16(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
+                     tile_base + size_t(r1) * pitch + (lane & 1) * 16);
+        } else {
+          cp_async16_gather(sb + (lane >> 1) * 32 + (lane & 1) * 16,
+                            tile_base + size_t(r0) * pitch + (lane & 1) * 16);
+          cp_async16_gather(sb + (16 + (lane >> 1)) * 32 + (lane & 1) * 16,
+                            tile_base + size_t(r1) * pitch + (lane & 1) * 16);
+        }
       }
       // rows past the end of the item get a zero gradient record: they add nothing
       const bool valid = unsigned(b * 32 + lane) < len;
@@ -162,6 +246,26 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
     int stage = 0;
     for (int b = warp; b < nb; b += kWarps) {
       cp_async_wait<kStages - 1>();
+      if (TMA && !gave_up) {
+        // lane 0 watches the barrier for the warp; the __syncwarp below hands what it saw
+        // (the gathered rows in shared memory) on to the other lanes
+        bool timed_out = false;
+        if (lane == 0) {
+          const unsigned parity = (phases >> stage) & 1u;
+          if (!mbar_try_wait(bars + stage, parity)) {
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_try_wait(bars + stage, parity)) {
+              if (global_timer_ns() - t0 > kGatherWaitNs) {
+                timed_out = true;
+                break;
+              }
+            }
+          }
+          if (timed_out) atomicExch(status, 1);
+        }
+        gave_up = __shfl_sync(0xffffffffu, int(timed_out), 0) != 0;
+        phases ^= 1u << stage;
+      }
       __syncwarp();
       const unsigned char *sb = my + stage * kStageBytes;
       const int nvalid = int(min(32u, len - unsigned(b) * 32));
@@ -202,6 +306,15 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
     __syncthreads();
     store_planes(smem, partials + (size_t(slot) * NT + tile) * 2 * kHistWords);
     __syncthreads();
+  }
+  if (TMA && gave_up) {
+    // gathers issued before the wait ran out may still be on their way into this CTA's shared
+    // memory: give them one more time limit before the CTA ends
+    const unsigned long long t0 = global_timer_ns();
+#pragma unroll
+    for (int st = 0; st < kStages; ++st)
+      while (!mbar_try_wait(bars + st, (phases >> st) & 1u) && global_timer_ns() - t0 < kGatherWaitNs) {
+      }
   }
 }
 
@@ -363,22 +476,74 @@ int hist_grid_x(int max_items, int NT) {
   return std::max(1, std::min(max_items, per_tile));
 }
 
+static_assert(sizeof(RowGatherMap) == sizeof(CUtensorMap) && alignof(RowGatherMap) >= alignof(CUtensorMap),
+              "RowGatherMap is the driver's tensor map, kept opaque in the headers");
+
+bool make_row_gather_map(RowGatherMap *out, const unsigned char *bins, size_t pitch, size_t rows) {
+  // Opt-in: on a B200 the 10 M x 28 workload's histogram pass takes 0.735 ms per round with
+  // this gather against 0.692 ms with cp.async (the bare gather rates are equal, 72 G rows/s,
+  // and the pass is bound by its shared-memory reductions either way; the barrier round trip
+  // per batch costs more than the freed load/store slots give back).
+  const bool on = std::getenv("ARBORETUM_TMA_GATHER") != nullptr;  // read once per matrix
+  if (!on || rows == 0 || rows >= (size_t(1) << 31) || pitch % 16 != 0 || pitch >= (size_t(1) << 32) ||
+      reinterpret_cast<uintptr_t>(bins) % 16 != 0)
+    return false;
+  // the encoder is a driver function: ask the runtime for it instead of linking the driver
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult found;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
+      found != cudaDriverEntryPointSuccess || !fn) {
+    cudaGetLastError();
+    return false;
+  }
+  // bytes of a padded row x rows; a box is the 32 bytes of one feature tile of one row (gather4
+  // fetches four such boxes); L2 fetches 64 bytes for a miss, not the whole 128-byte line
+  const cuuint64_t dims[2] = {cuuint64_t(pitch), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(pitch)};
+  const cuuint32_t box[2] = {32, 1};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult r = reinterpret_cast<EncodeFn>(fn)(
+    &map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<unsigned char *>(bins), dims, strides, box, elem,
+    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_64B,
+    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::memcpy(out, &map, sizeof map);
+  return true;
+}
+
 void launch_hist(const HistLaunch &a, cudaStream_t s) {
   const Geometry &g = a.geo;
   const dim3 grid(a.grid_x > 0 ? a.grid_x : hist_grid_x(a.max_items, g.NT), g.NT);
   const bool ident = a.rowid == nullptr;
   if (g.bin_bytes == 1 && g.TW == 32) {
-    const size_t smem = 2 * kHistWords * 4 + (kHistThreads / 32) * kStages * kStageBytes;
-#define ARB_LAUNCH(P, I)                                                                      \
-  do {                                                                                        \
-    ARB_SET_SMEM((hist_u8_kernel<P, I>), smem);                                               \
-    launch_overlapped(hist_u8_kernel<P, I>, grid, kHistThreads, smem, s, g.bins, g.pitch,     \
-                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.item_slot, a.partials, a.list_grad); \
+    constexpr int kWarps = kHistThreads / 32;
+    const size_t smem = 2 * kHistWords * 4 + kWarps * kStages * kStageBytes + kWarps * kStages * 8;
+    const bool tma = a.row_map != nullptr && a.status != nullptr && !ident;
+    CUtensorMap map;
+    if (tma)
+      std::memcpy(&map, a.row_map, sizeof map);
+    else
+      std::memset(&map, 0, sizeof map);
+#define ARB_LAUNCH(P, I, T)                                                                      \
+  do {                                                                                           \
+    ARB_SET_SMEM((hist_u8_kernel<P, I, T>), smem);                                               \
+    launch_overlapped(hist_u8_kernel<P, I, T>, grid, kHistThreads, smem, s, g.bins, g.pitch,     \
+                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.item_slot, a.partials,        \
+                      a.list_grad, map, a.status);                                               \
   } while (0)
     if (a.pair) {
-      if (ident) ARB_LAUNCH(true, true); else ARB_LAUNCH(true, false);
+      if (ident) ARB_LAUNCH(true, true, false);
+      else if (tma) ARB_LAUNCH(true, false, true);
+      else ARB_LAUNCH(true, false, false);
     } else {
-      if (ident) ARB_LAUNCH(false, true); else ARB_LAUNCH(false, false);
+      if (ident) ARB_LAUNCH(false, true, false);
+      else if (tma) ARB_LAUNCH(false, false, true);
+      else ARB_LAUNCH(false, false, false);
     }
 #undef ARB_LAUNCH
   } else {

@@ -37,6 +37,16 @@ struct Geometry {
   size_t cm_rows = 0;
 };
 
+// The driver's tensor map of a row-major uint8 bin matrix (bytes of a padded row x rows), with
+// which the uint8 histogram kernel gathers rows through the TMA unit.  Opaque here so that only
+// the histogram's translation unit needs the driver's header.
+struct alignas(64) RowGatherMap {
+  unsigned char opaque[128];
+};
+// false: no map (ARBORETUM_TMA_GATHER is not set in the environment, the driver's encoder is
+// not available, the matrix has 2^31 rows or more): the kernel then gathers with cp.async
+bool make_row_gather_map(RowGatherMap *out, const unsigned char *bins, size_t pitch, size_t rows);
+
 struct HistLaunch {
   Geometry geo;
   const unsigned *rowid;  // nullptr: positions are row ids (root level)
@@ -54,6 +64,9 @@ struct HistLaunch {
   const void *list_grad = nullptr;  // gradient records in list order (position p of `rowid` <->
                                     // record p), or nullptr: gathered from `grad` by row id.
                                     // Read by the uint8 kernel only.
+  const RowGatherMap *row_map = nullptr;  // map of geo.bins (host pointer), or nullptr
+  int *status = nullptr;  // device word, set to 1 when a wait on a TMA gather ran out (needed with
+                          // row_map)
 };
 void launch_hist(const HistLaunch &a, cudaStream_t s);
 int hist_grid_x(int max_items, int NT);

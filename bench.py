@@ -441,6 +441,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the end-to-end jobs (profiling runs: fewer launches before the timed rounds)")
     ap.add_argument("--internals", default="", help='JSON merged into the "internals" configuration')
+    ap.add_argument("--predict-rows", type=int, default=0,
+                    help="also time inference (APredict) of the trained model on this many of the rows")
     ap.add_argument("--c5b-rows-per-gpu", type=int, default=250_000_000,
                     help="rows per GPU of the sharded out-of-core-scale sub-record (0: skip it)")
     args = ap.parse_args()
@@ -617,6 +619,22 @@ def main():
                     "tree_ms": t["tree_ms"] / max(1, t["trees"]),
                     "rows_streamed_per_s": t["h2d_bytes"] / ((features + 31) // 32 * 32) / (t["tree_ms"] * 1e-3)}
 
+    # ---- inference on the device (RegTree::Predict of the reference runs on the host) ---------
+    predict = None
+    if args.predict_rows > 0 and not binned:
+        kw_p = {"data_category": cat[:args.predict_rows]} if cat is not None else {}
+        pd = arboretum.DMatrix(np.ascontiguousarray(Xh[:args.predict_rows]), **kw_p)
+        model.predict(pd)  # uploads the forest
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = model.predict(pd)
+        dt = time.perf_counter() - t0
+        trees = len(json.loads(model.dump())["model"])
+        predict = {"rows": int(pd.rows), "trees": trees, "seconds": dt, "rows_x_trees_per_s": pd.rows * trees / dt,
+                   "what": "APredict on a resident matrix: tree walk over raw fp32 rows, link function, "
+                           "result copied to the host"}
+        del pd, out
+
     # ---- the 2 B-row configuration's sharded mode, per-GPU share fixed (weak scaling) ------
     c5b = None
     if args.c5b_rows_per_gpu > 0 and args.workload == "c2":
@@ -641,6 +659,8 @@ def main():
                 "roofline": roofline}
         if c5b is not None:
             line["c5b"] = c5b
+        if predict is not None:
+            line["predict"] = predict
         if world == 1 and not args.no_ref_cuda:
             line["ref_cuda"] = reference_cuda_record(args.workload, args.rows)
         if world == 1 and not args.no_cpu_baseline:

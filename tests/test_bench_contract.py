@@ -48,3 +48,15 @@ def test_reference_arm_prints_one_json_line(workload):
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert d["e2e"]["value"] == d["value"]
     assert "workload" in d["config"] and "model" not in d["config"]
+
+
+def test_every_package_name_the_bench_uses_exists():
+    """The GPU arm cannot run here, so a misspelt or unexported name would only show on a GPU box."""
+    import re
+
+    import arboretum_b200
+    source = open(bench.__file__).read()
+    names = set(re.findall(r"\barboretum\.([A-Za-z_]\w*)", source))
+    assert names, "bench.py no longer calls the package?"
+    missing = sorted(n for n in names if not hasattr(arboretum_b200, n))
+    assert not missing, missing

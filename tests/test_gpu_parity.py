@@ -132,6 +132,28 @@ def test_histogram_matches_oracle(n, F, hist_size, nodes, pair):
         assert (oh == eh).all()  # counts are exact
 
 
+@pytest.mark.parametrize("n,F,nodes,pair", [(5000, 28, 4, True), (5000, 28, 4, False), (300, 28, 4, True),
+                                             (40, 5, 3, True), (200000, 70, 8, True)])
+def test_histogram_tma_gather_is_identical(n, F, nodes, pair, monkeypatch):
+    """The rows a node names by id are fetched with cp.async or, with ARBORETUM_TMA_GATHER set,
+    by the TMA unit (tile::gather4): the sums are integers, so the two must agree exactly."""
+    rng = np.random.default_rng(n + nodes)
+    bins = rng.integers(0, 256, size=(n, F)).astype(np.uint8)
+    g = rng.normal(size=n).astype(np.float32)
+    h = rng.uniform(0.01, 0.25, size=n).astype(np.float32)
+    rowid = rng.permutation(n).astype(np.uint32)
+    node_begin = np.concatenate([[0], np.sort(rng.integers(0, n, size=nodes - 1)), [n]]).astype(np.uint32)
+    grad = np.stack([g, h], axis=1) if pair else g
+    out = []
+    for tma in (False, True):
+        if tma:
+            monkeypatch.setenv("ARBORETUM_TMA_GATHER", "1")
+        else:
+            monkeypatch.delenv("ARBORETUM_TMA_GATHER", raising=False)
+        out.append(arb().build_histogram(bins, grad, 255, rowid=rowid, node_begin=node_begin))
+    assert (out[0][0] == out[1][0]).all() and (out[0][1] == out[1][1]).all()
+
+
 @pytest.mark.parametrize("case", range(5))
 @pytest.mark.parametrize("dtype", [np.uint8, np.uint16])
 def test_histogram_multi_node_reference_kats(case, dtype):
@@ -584,6 +606,28 @@ def test_overlapped_launches_give_the_same_model():
                              capture_output=True, text=True, timeout=600).stdout
         digests.append([l for l in out.splitlines() if l.startswith("digest")][0])
     assert digests[0] == digests[1] == digests[2]
+
+
+def test_tma_row_gather_gives_the_same_model():
+    """With ARBORETUM_TMA_GATHER=1 the uint8 histogram kernel fetches the rows of a node
+    through the TMA unit below the root (four rows per gather instruction, completion on a
+    per-warp mbarrier) instead of with cp.async.  Both must build the same model, byte for
+    byte, on a large matrix and on a small one (few rows per node, most CTAs idle)."""
+    import subprocess
+    import sys
+    arb()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for job in (_OVERLAP_JOB, _OVERLAP_JOB.replace("n, F = 1500000, 28", "n, F = 20000, 28")):
+        digests = []
+        for tma in (False, True):
+            env = dict(os.environ)
+            env.pop("ARBORETUM_TMA_GATHER", None)
+            if tma:
+                env["ARBORETUM_TMA_GATHER"] = "1"
+            out = subprocess.run([sys.executable, "-c", job], cwd=root, env=env, check=True,
+                                 capture_output=True, text=True, timeout=600).stdout
+            digests.append([l for l in out.splitlines() if l.startswith("digest")][0])
+        assert digests[0] == digests[1]
 
 
 def test_bad_calls_return_errors():
