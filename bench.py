@@ -37,9 +37,15 @@ CONFIG = {"objective": 1, "method": 1,
           "verbose": {"gpu": False, "booster": False, "data": False},
           "tree": {"eta": 0.1, "max_depth": 8, "min_child_weight": 1.0, "min_leaf_size": 1,
                    "lambda": 1.0, "alpha": 0.0, "colsample_bytree": 1.0, "colsample_bylevel": 1.0}}
-# DRAM bytes per algorithmic byte of the histogram kernel, from the ncu capture
-# summarised in profiles/ (None until a capture exists for this kernel version).
-HIST_TRAFFIC_RATIO = 1.82
+# DRAM bytes moved per algorithmic byte by the launches the roofline times (the histogram
+# kernel and the reduction of its planes), over one boosting round of this very workload in
+# the ncu capture named below: 2689 MB moved for 34.6 M scanned rows x 36 B (the histogram
+# launches alone: 1.87).
+HIST_TRAFFIC_RATIO = 2.16
+HIST_TRAFFIC_SOURCE = ("profiles/level_kernels_bench10M.md: ncu SpeedOfLight + MemoryWorkloadAnalysis of the 57 "
+                       "launches of one round of this workload (10 M x 28); dram__bytes.sum.per_second x "
+                       "gpu__time_duration.sum of the 8 hist_u8_kernel + 8 reduce_kernel launches / "
+                       "(rows scanned x 36 B); a ratio, applied to this run's algorithmic bytes per launch")
 
 
 def make_rows(n, seed):
@@ -600,6 +606,7 @@ def main():
                     "frac_of_nominal_8TBs": hist_gbs / 8000.0,
                     "traffic": None if HIST_TRAFFIC_RATIO is None or args.workload != "c2"
                     else per_launch_bytes * HIST_TRAFFIC_RATIO,
+                    "traffic_source": HIST_TRAFFIC_SOURCE if args.workload == "c2" else None,
                     "algorithmic_bytes_per_launch": per_launch_bytes,
                     "avg_launch_ms": t["hist_ms"] / max(1, t["hist_launches"]),
                     "rows_x_features_per_s_per_gpu": t["hist_rows"] * features / (t["hist_ms"] * 1e-3),
