@@ -478,6 +478,13 @@ class Builder {
   DevBuf d_hist_status_;
   PinnedBuf h_hist_status_;
   bool count_plane_ = false;
+  // colsample_bytree < 1: the columns a tree samples are copied side by side once per tree and
+  // the histograms and the split search cover those alone (feature ids in the records stay the
+  // matrix's); used when that saves feature tiles, in core, without row shards
+  bool sampled_cols_ = false;
+  Geometry geo_tree_;          // the copy's geometry (no feature-major copy: the descend step reads the matrix)
+  DevBuf d_bins_tree_, d_fmap_;
+  std::vector<int> fmap_host_;
   DevBuf d_ones_, d_cnt_hist_[2], d_compact_cnt_;
   // records of every tree of the last round (multi:softmax grows labels_count of them)
   std::vector<std::vector<NodeRec>> round_rec_;
@@ -612,7 +619,10 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   // are accumulated as one run (see make_items in partition.cu).
   //   items <= rows / item_rows + nodes <= 2 x (kItemsPerCta x CTAs) + rows / item_cap_ + nodes
   //   runs  <= CTAs + nodes + rows / item_cap_ (+ nodes: the short last item of a node)
-  const int hist_ctas = hist_grid_x(1 << 30, geo_.NT);
+  const int cols_tree = int(tp.colsample_bytree * F_);  // columns a tree samples (SampleFeatures)
+  const int NT_tree = (std::max(1, cols_tree) + geo_.TW - 1) / geo_.TW;
+  // fewer tiles get more CTAs each: size the item arrays for either geometry
+  const int hist_ctas = std::max(hist_grid_x(1 << 30, geo_.NT), hist_grid_x(1 << 30, NT_tree));
   max_hist_items_ = 2 * kItemsPerCta * hist_ctas + int(n_ / item_cap_) + 2 * max_nodes_ + 8;
   max_hist_runs_ = hist_ctas + int(n_ / item_cap_) + 2 * max_nodes_ + 8;
 
@@ -761,6 +771,27 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   trace.lap("pinned read-back buffers");
   if (!d->out_of_core) {
     chunks_[0].resident = d->d_bins.as<unsigned char>();
+    // a tree that samples its columns: histograms over a side-by-side copy of those columns,
+    // when that saves feature tiles and the copy fits (ARBORETUM_NO_COLUMN_COPY turns it off)
+    const int cols_t = int(tp.colsample_bytree * F_);
+    const int NT_t = (std::max(1, cols_t) + geo_.TW - 1) / geo_.TW;
+    size_t free_b = 0;
+    ARB_CUDA(dev_available(&free_b));
+    const size_t pitch_t = DataMatrix::PitchFor(std::max(1, cols_t), geo_.bin_bytes);
+    if (cols_t >= 1 && NT_t < geo_.NT && chunks_.size() == 1 && g->shards.world <= 1 && !g->allreduce &&
+        n_ * pitch_t < free_b / 2 && std::getenv("ARBORETUM_NO_COLUMN_COPY") == nullptr) {
+      sampled_cols_ = true;
+      d_bins_tree_.alloc(n_ * pitch_t);
+      d_fmap_.alloc(size_t(cols_t) * sizeof(int));
+      fmap_host_.resize(cols_t);
+      geo_tree_ = geo_;
+      geo_tree_.bins = d_bins_tree_.as<unsigned char>();
+      geo_tree_.pitch = pitch_t;
+      geo_tree_.F = cols_t;
+      geo_tree_.NT = NT_t;
+      geo_tree_.bins_cm = nullptr;
+      geo_tree_.cm_rows = 0;
+    }
   } else {
     // as many leading chunks as fit stay in HBM; the rest cycle through two buffers
     const size_t chunk_bytes = chunks_[0].rows * d->pitch;
@@ -948,6 +979,18 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
   SampleFeatures();
   ARB_CUDA(cudaMemcpyAsync(d_active_.p, active_host_.data(), active_host_.size(),
                            cudaMemcpyHostToDevice, s));
+  if (sampled_cols_) {
+    // the tree's columns (the head of the shuffled list; the per-level shuffles only permute
+    // it), in feature order so that ties between columns fall like ties between features
+    fmap_host_.assign(active_fids_.begin(), active_fids_.begin() + fmap_host_.size());
+    std::sort(fmap_host_.begin(), fmap_host_.end());
+    // pageable source: the call returns once the ids are staged, so the vector may change again
+    ARB_CUDA(cudaMemcpyAsync(d_fmap_.p, fmap_host_.data(), fmap_host_.size() * sizeof(int),
+                             cudaMemcpyHostToDevice, s));
+    launch_compact_columns(geo_.bins, geo_.pitch, geo_.bin_bytes, n_, d_fmap_.as<int>(), geo_tree_.F,
+                           d_bins_tree_.as<unsigned char>(), geo_tree_.pitch, s,
+                           geo_.cm_rows == n_ ? geo_.bins_cm : nullptr);
+  }
   if (prof) ARB_CUDA(cudaEventRecord(ev_tree_[0], s));
   // a tree that threw half way (an exchange that failed) leaves the cyclic visiting order of
   // the streamed chunks out of step: start over from the first one
@@ -979,7 +1022,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     // the exchange.
     const bool compact = trick_level && g_->allreduce != nullptr;
     // words of one histogram set that the ranks exchange at this level
-    const size_t xwords = size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2;
+    const int NTh = sampled_cols_ ? geo_tree_.NT : geo_.NT;  // feature tiles of the histograms
+    const size_t xwords = size_t(compact ? n_build : L) * NTh * kHistWords * 2;
     long long *hist[2], *reduce_to[2];
     const long long *parent_hist[2];
     for (int k = 0; k < n_sets; ++k) {
@@ -991,7 +1035,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       else
         reduce_to[k] = compact ? (k == 0 ? d_compact_ : d_compact_cnt_).as<long long>() : hist[k];
       if (multi)
-        ARB_CUDA(cudaMemsetAsync(reduce_to[k], 0, size_t(compact ? n_build : L) * geo_.NT * kHistWords * 2 * sizeof(long long), s));
+        ARB_CUDA(cudaMemsetAsync(reduce_to[k], 0, size_t(compact ? n_build : L) * NTh * kHistWords * 2 * sizeof(long long), s));
     }
     for (int c = 0; c < n_chunks; ++c) {
       const Chunk &ch = chunks_[c];
@@ -1021,7 +1065,9 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       // rule of multi-GPU / multi-chunk runs has no such bound)
       const bool half = trick_level && !by_hessian;
       const size_t level_rows = half ? rows / 2 + 1 : rows;
-      const int hist_ctas = hist_grid_x(1 << 30, geo.NT);
+      // the histogram pass reads the tree's side-by-side columns where there are any
+      const Geometry &hgeo = sampled_cols_ ? geo_tree_ : geo;
+      const int hist_ctas = hist_grid_x(1 << 30, hgeo.NT);
       int item_rows = item_cap_;  // the largest power-of-two share of a plane's rows that gives
                                   // every CTA about kItemsPerCta items
       while (item_rows > kMinItemRows && level_rows / size_t(item_rows) < size_t(kItemsPerCta) * hist_ctas) item_rows >>= 1;
@@ -1043,7 +1089,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       if (last) mark();
       for (int k = 0; k < n_sets; ++k) {
         HistLaunch h;
-        h.geo = geo;
+        h.geo = hgeo;
         h.rowid = l == 0 ? nullptr : list;
         // the count set: every row's "gradient" is 1 and the hessian plane of the
         // reg:linear kernel counts the rows
@@ -1056,7 +1102,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         h.max_items = int(std::min<size_t>(max_hist_items_, level_rows / item_rows + n_build + 1));
         h.partials = d_partials_.as<int>();
         h.list_grad = (l == 0 || k > 0) ? nullptr : list_grad;
-        if (has_row_map_ && geo.bins == geo_.bins) {
+        if (has_row_map_ && hgeo.bins == geo_.bins) {
           h.row_map = &row_map_;
           h.status = d_hist_status_.as<int>();
         }
@@ -1066,7 +1112,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         rd.item_first = pb_.slot_first;  // the planes of a node's runs
         rd.build_node = compact ? nullptr : pb_.scratch_node;
         rd.n_build = n_build;
-        rd.NT = geo.NT;
+        rd.NT = hgeo.NT;
         rd.level_hist = reduce_to[k];
         rd.parent_hist = parent_hist[k];
         rd.subtract = trick_level && !g_->allreduce && !multi;
@@ -1091,13 +1137,14 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       if (xchg_ && !compact)  // a whole level (the root, or no subtraction): straight to its buffer
         ARB_CUDA(cudaMemcpyAsync(hist[k], summed, xwords * sizeof(long long), cudaMemcpyDeviceToDevice, s));
       if (compact)
-        launch_expand(summed, parent_hist[k], hist[k], pb_.built_child, L / 2, geo_.NT, s);
+        launch_expand(summed, parent_hist[k], hist[k], pb_.built_child, L / 2, NTh, s);
       else if (trick_level && multi)
-        launch_subtract(hist[k], parent_hist[k], pb_.built_child, L / 2, geo_.NT, s);
+        launch_subtract(hist[k], parent_hist[k], pb_.built_child, L / 2, NTh, s);
     }
     mark();
     SplitLaunch sp;
-    sp.geo = geo_;
+    sp.geo = sampled_cols_ ? geo_tree_ : geo_;
+    sp.feature_map = sampled_cols_ ? d_fmap_.as<int>() : nullptr;
     sp.hist = hist[0];
     sp.count_hist = count_plane_ ? hist[1] : nullptr;
     sp.node_begin = node_begin(0, l);
@@ -1291,8 +1338,9 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
         }
       }
       t.hist_rows += rows;
-      t.hist_features += double(F_);
-      t.hist_bytes += rows * (double(F_) * geo_.bin_bytes + (pair_ ? 8.0 : 4.0));
+      const double hist_cols = sampled_cols_ ? double(geo_tree_.F) : double(F_);
+      t.hist_features += hist_cols;
+      t.hist_bytes += rows * (hist_cols * geo_.bin_bytes + (pair_ ? 8.0 : 4.0));
       t.hist_launches += 1;
     }
     t.update += span(e - 1, e);

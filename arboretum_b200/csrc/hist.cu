@@ -160,7 +160,9 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
   }
   bool cleared = true;
   int *G = smem;
-  const int tile = blockIdx.y;
+  // grid = (tiles, shares): the CTAs that take the same rows in neighbouring tiles are launched
+  // side by side, so a row's line is fetched from DRAM once for the tiles that share it
+  const int tile = blockIdx.x;
   const unsigned char *tile_base = bins + size_t(tile) * 32;
   const int q = lane >> 3, m = lane & 7;
   int foff[4], sh[4];
@@ -176,9 +178,9 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
   // (the plan kernel gave them the same slot: together they stay within what an int32 plane
   // holds): their rows lie back to back in the node's list and go through the pipeline as one
   // piece, and the planes are stored once per run.
-  const int per = (total_items + int(gridDim.x) - 1) / int(gridDim.x);
-  const int it_end = min(total_items, (int(blockIdx.x) + 1) * per);
-  for (int it = int(blockIdx.x) * per; it < it_end;) {
+  const int per = (total_items + int(gridDim.y) - 1) / int(gridDim.y);
+  const int it_end = min(total_items, (int(blockIdx.y) + 1) * per);
+  for (int it = int(blockIdx.y) * per; it < it_end;) {
     WorkItem item = items[it];
     const int slot = item_slot ? item_slot[it] : it;
     for (++it; it < it_end && item_slot && item_slot[it] == slot; ++it) item.len += items[it].len;
@@ -329,15 +331,15 @@ hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, 
   extern __shared__ __align__(16) int smem[];
   int *G = smem;
   int *H = smem + kHistWords;
-  const int tile = blockIdx.y;
+  const int tile = blockIdx.x;  // grid = (tiles, shares), see hist_u8_kernel
   const int rows_per_pass = kHistThreads / TW;
   const int f_in_tile = threadIdx.x % TW;
   const int rsub = threadIdx.x / TW;
   const int f = tile * TW + f_in_tile;
   const int total_items = *n_items;
-  const int per = (total_items + int(gridDim.x) - 1) / int(gridDim.x);  // runs of items: see hist_u8_kernel
-  const int it_end = min(total_items, (int(blockIdx.x) + 1) * per);
-  for (int it = int(blockIdx.x) * per; it < it_end;) {
+  const int per = (total_items + int(gridDim.y) - 1) / int(gridDim.y);  // runs of items: see hist_u8_kernel
+  const int it_end = min(total_items, (int(blockIdx.y) + 1) * per);
+  for (int it = int(blockIdx.y) * per; it < it_end;) {
     WorkItem item = items[it];
     const int slot = item_slot ? item_slot[it] : it;
     for (++it; it < it_end && item_slot && item_slot[it] == slot; ++it) item.len += items[it].len;
@@ -518,7 +520,7 @@ bool make_row_gather_map(RowGatherMap *out, const unsigned char *bins, size_t pi
 
 void launch_hist(const HistLaunch &a, cudaStream_t s) {
   const Geometry &g = a.geo;
-  const dim3 grid(a.grid_x > 0 ? a.grid_x : hist_grid_x(a.max_items, g.NT), g.NT);
+  const dim3 grid(g.NT, a.grid_x > 0 ? a.grid_x : hist_grid_x(a.max_items, g.NT));
   const bool ident = a.rowid == nullptr;
   if (g.bin_bytes == 1 && g.TW == 32) {
     constexpr int kWarps = kHistThreads / 32;

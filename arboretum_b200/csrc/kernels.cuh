@@ -111,6 +111,10 @@ struct SplitLaunch {
   const int *feature_size;     // bins in use per feature
   const int *cat_candidates = nullptr;  // per feature: bins a one-vs-rest split may name
                                         // (categorical features), 0 for dense ones; or nullptr
+  // The histogram may cover a subset of the columns (the columns a tree samples, copied side
+  // by side): feature_map[j] is the feature behind column j of `geo`, ascending; records,
+  // feature_active and cat_candidates speak of features.  nullptr: column j is feature j.
+  const int *feature_map = nullptr;
   unsigned long long *keys;    // max_nodes packed (gain, feature, bin) maxima followed by
                                // max_nodes u32 arrival counters; zeroed by the plan kernel of the
                                // level (PlanBuffers::split_scratch)
@@ -123,6 +127,13 @@ struct SplitLaunch {
   int L;
 };
 void launch_split(const SplitLaunch &a, cudaStream_t s);
+
+// out[r][j] = bins[r][map[j]] for j < n_cols (bin_bytes each), rows of `out_pitch` bytes whose
+// padding is zeroed: the columns a tree samples, side by side.  With the feature-major copy
+// bins_cm[f * n + r] at hand (uint8, n a multiple of 16) only the wanted columns are read.
+void launch_compact_columns(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, const int *map,
+                            int n_cols, unsigned char *out, size_t out_pitch, cudaStream_t s,
+                            const unsigned char *bins_cm = nullptr);
 
 // --- node assignment and row lists ---------------------------------------------
 struct PlanBuffers {

@@ -120,22 +120,31 @@ __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_
   // the slot of its previous one, and among the lanes of a warp that hold the same slot
   // in the same step the lowest lane (the smallest position) speaks for all.
   long long last_slot = -1;
+  // base / seg once per thread; the quotient of the following positions by counting up
+  unsigned long long quot = base / seg, rem = base - quot * seg;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     long long slot = -1;
     float mid = 0.0f;
     if (flag[k]) {
       ++run;  // inclusive border count of position i (io.cu:144-153)
-      const size_t i = base + k;
       mid = float((at(first + k + 1) + at(first + k)) * 0.5);  // io.cu:72-79
-      const long long a = (long long)run + 1, b = (long long)(i / seg) + 1;
+      const long long a = (long long)run + 1, b = (long long)quot + 1;  // quot = i / seg
       slot = (a < b ? a : b) - 2;  // io.cu:257
       // slots past the table are a defect of the reference (out-of-range write); skipped
       if (slot >= hist_size || slot == last_slot) slot = -1;
       if (slot >= 0) last_slot = slot;
     }
-    const unsigned peers = __match_any_sync(0xffffffffu, slot);
-    if (slot >= 0 && (peers & ((1u << lane) - 1)) == 0) atomic_min_float(thr + slot, mid);
+    if (++rem == seg) {
+      rem = 0;
+      ++quot;
+    }
+    // most steps have no candidate in the whole warp (a thread's later borders fall in the
+    // slot of its first): the vote is cheap, the match is not
+    if (__any_sync(0xffffffffu, slot >= 0)) {
+      const unsigned peers = __match_any_sync(0xffffffffu, slot);
+      if (slot >= 0 && (peers & ((1u << lane) - 1)) == 0) atomic_min_float(thr + slot, mid);
+    }
   }
 }
 
@@ -199,6 +208,40 @@ __global__ void transpose_bins_kernel(const unsigned char *__restrict__ bins, si
   }
 }
 
+// The same for uint8 bins whose row count is a multiple of 16: a CTA takes 256 rows of one
+// tile of 32 features, reads whole 32-byte row chunks with 16-byte loads (two lanes per row),
+// turns them in shared memory and writes 256 consecutive bytes per feature with 16-byte stores.
+constexpr int kTurnRows = 256;
+constexpr int kTurnStride = kTurnRows + 16;
+__global__ void __launch_bounds__(256)
+transpose_bins_u8_kernel(const unsigned char *__restrict__ bins, size_t pitch, size_t n, int F,
+                         unsigned char *__restrict__ out) {
+  __shared__ __align__(16) unsigned char tile[32 * kTurnStride];
+  const size_t r0 = size_t(blockIdx.x) * kTurnRows;
+  const int f0 = blockIdx.y * 32;
+  const int half = threadIdx.x & 1;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int row = p * 128 + (threadIdx.x >> 1);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r0 + row < n) v = __ldg(reinterpret_cast<const uint4 *>(bins + (r0 + row) * pitch + f0 + half * 16));
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      tile[(half * 16 + j) * kTurnStride + row] = (unsigned char)(w[j >> 2] >> (8 * (j & 3)));
+  }
+  __syncthreads();
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int e = p * 256 + threadIdx.x;  // 32 features x 16 chunks of 16 rows
+    const int f = e >> 4, c = e & 15;
+    const size_t r = r0 + size_t(c) * 16;
+    if (f0 + f < F && r < n)  // n is a multiple of 16: a chunk is inside or outside as a whole
+      *reinterpret_cast<uint4 *>(out + size_t(f0 + f) * n + r) =
+        *reinterpret_cast<const uint4 *>(tile + f * kTurnStride + c * 16);
+  }
+}
+
 // unpadded uint8 rows [n][F] -> padded rows [n][pitch] (padding bytes zero), one
 // 32-bit word of the padded row per thread
 __global__ void pad_rows_kernel(const unsigned char *__restrict__ raw, int F, size_t n,
@@ -226,6 +269,61 @@ __global__ void place_columns_kernel(const BIN_T *__restrict__ src, size_t n, in
     const size_t r = e / ccol;
     const int c = int(e - r * ccol);
     reinterpret_cast<BIN_T *>(bins + r * pitch)[f0 + c] = src[e];
+  }
+}
+
+// the columns map[0..n_cols) of every row, side by side: one 32-bit word of the output row per
+// thread (4 uint8 or 2 uint16 bins), padding words zero
+template <typename BIN_T>
+__global__ void compact_columns_kernel(const unsigned char *__restrict__ bins, size_t pitch, size_t n,
+                                       const int *__restrict__ map, int n_cols,
+                                       unsigned *__restrict__ out, int out_words) {
+  constexpr int kPer = 4 / int(sizeof(BIN_T));
+  const size_t total = n * size_t(out_words);
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = e / out_words;
+    const int j0 = int(e - r * out_words) * kPer;
+    const BIN_T *src = reinterpret_cast<const BIN_T *>(bins + r * pitch);
+    unsigned w = 0;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k)
+      if (j0 + k < n_cols) w |= unsigned(src[__ldg(map + j0 + k)]) << (8 * int(sizeof(BIN_T)) * k);
+    out[e] = w;
+  }
+}
+
+// The same from the feature-major copy (uint8, row count a multiple of 16): only the wanted
+// columns are read, 256 consecutive rows of a column at a time with 16-byte loads; a CTA turns
+// 32 columns x 256 rows in shared memory and writes 32-byte row chunks of the output.
+__global__ void __launch_bounds__(256)
+compact_columns_cm_u8_kernel(const unsigned char *__restrict__ bins_cm, size_t n,
+                             const int *__restrict__ map, int n_cols, unsigned char *__restrict__ out,
+                             size_t out_pitch) {
+  __shared__ __align__(16) unsigned char tile[32 * kTurnStride];
+  const size_t r0 = size_t(blockIdx.x) * kTurnRows;
+  const int j0 = blockIdx.y * 32;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int e = p * 256 + threadIdx.x;  // 32 columns x 16 chunks of 16 rows
+    const int j = e >> 4, c = e & 15;
+    const size_t r = r0 + size_t(c) * 16;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (j0 + j < n_cols && r < n)
+      v = __ldg(reinterpret_cast<const uint4 *>(bins_cm + size_t(__ldg(map + j0 + j)) * n + r));
+    *reinterpret_cast<uint4 *>(tile + j * kTurnStride + c * 16) = v;
+  }
+  __syncthreads();
+  const int half = threadIdx.x & 1;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int row = p * 128 + (threadIdx.x >> 1);
+    if (r0 + row >= n) continue;
+    unsigned w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      w[j >> 2] |= unsigned(tile[(half * 16 + j) * kTurnStride + row]) << (8 * (j & 3));
+    *reinterpret_cast<uint4 *>(out + (r0 + row) * out_pitch + j0 + half * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -264,6 +362,64 @@ __global__ void binning_kernel(const float *__restrict__ X, size_t n, int F,
   }
 }
 
+
+// uint8 bins with at most 255 thresholds per feature: a CTA keeps the tables of a tile of 32
+// features in shared memory (entry i of feature f at i * 33 + f: the lanes of a warp, which
+// look at 8 different features, fall on different banks while they all probe the same entry
+// in the first steps) and walks rows; a thread bins four neighbouring features of a row with a
+// fixed 8-step search and stores them as one 32-bit word.  Same result as lower_bound_thr:
+// entries from size - 1 on read +INF, so a value that is not NaN stops at size - 1 at the
+// latest, and NaN (which compares false everywhere) gets `size` like there.
+constexpr int kBinTileRows = 32;  // rows a CTA bins per step: 256 threads = 32 rows x 8 words
+__global__ void __launch_bounds__(256)
+binning_tile_kernel(const float *__restrict__ X, size_t n, int F, const float *__restrict__ thr,
+                    const int *__restrict__ fsize, int hist_size, bool missing_bin,
+                    unsigned char *__restrict__ bins, size_t pitch) {
+  __shared__ float tbl[255 * 33];
+  __shared__ int size_s[32];
+  const int f_tile = blockIdx.y * 32;
+  for (int e = threadIdx.x; e < 255 * 32; e += 256) {
+    const int f = f_tile + (e & 31), i = e >> 5;
+    float v = INFINITY;
+    if (f < F && i < hist_size && i < fsize[f] - 1) v = thr[size_t(f) * hist_size + i];
+    tbl[i * 33 + (e & 31)] = v;
+  }
+  if (threadIdx.x < 32) size_s[threadIdx.x] = f_tile + threadIdx.x < F ? fsize[f_tile + threadIdx.x] : 0;
+  __syncthreads();
+  const int w = threadIdx.x & 7, row_in = threadIdx.x >> 3;
+  const int f0 = f_tile + 4 * w;
+  if (f0 >= F) return;
+  const int nf = min(4, F - f0);
+  for (size_t r = size_t(blockIdx.x) * kBinTileRows + row_in; r < n; r += size_t(gridDim.x) * kBinTileRows) {
+    const float *x = X + r * F + f0;
+    unsigned word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < nf) {
+        const float v = x[j];
+        const float *t = tbl + 4 * w + j;
+        unsigned b;
+        if (v != v) {
+          b = missing_bin ? unsigned(hist_size) : unsigned(size_s[4 * w + j]);
+        } else {
+          int pos = 0;
+#pragma unroll
+          for (int step = 128; step >= 1; step >>= 1)
+            if (!(v <= t[(pos + step - 1) * 33])) pos += step;
+          b = unsigned(pos);
+        }
+        word |= (b & 255u) << (8 * j);
+      }
+    }
+    unsigned char *dst = bins + r * pitch + f0;
+    if (nf == 4) {
+      *reinterpret_cast<unsigned *>(dst) = word;
+    } else {
+      for (int j = 0; j < nf; ++j) dst[j] = (unsigned char)(word >> (8 * j));
+    }
+  }
+}
+
 }  // namespace
 
 size_t thresholds_scratch_words(size_t n) { return (n + kScanTile - 1) / kScanTile + 1; }
@@ -285,6 +441,14 @@ void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr,
 
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
                            unsigned char *bins_cm, cudaStream_t s) {
+  if (bin_bytes == 1 && n % 16 == 0 && pitch % 32 == 0 && reinterpret_cast<uintptr_t>(bins) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(bins_cm) % 16 == 0) {
+    const dim3 grid_fast(unsigned((n + kTurnRows - 1) / kTurnRows), unsigned((F + 31) / 32));
+    transpose_bins_u8_kernel<<<grid_fast, 256, 0, s>>>(bins, pitch, n, F, bins_cm);
+    ARB_CUDA(cudaGetLastError());
+    count_launch();
+    return;
+  }
   const dim3 grid(unsigned((n + 31) / 32), unsigned((F + 31) / 32));
   if (bin_bytes == 1)
     transpose_bins_kernel<unsigned char><<<grid, 256, 0, s>>>(bins, pitch, n, F, bins_cm);
@@ -302,6 +466,31 @@ void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *b
   const size_t total = n * size_t(words);
   const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
   pad_rows_kernel<<<grid, 256, 0, s>>>(raw, F, n, reinterpret_cast<unsigned *>(bins), words);
+  ARB_CUDA(cudaGetLastError());
+  count_launch();
+}
+
+void launch_compact_columns(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, const int *map,
+                            int n_cols, unsigned char *out, size_t out_pitch, cudaStream_t s,
+                            const unsigned char *bins_cm) {
+  if (n == 0 || n_cols == 0) return;
+  if (bins_cm && bin_bytes == 1 && n % 16 == 0 && out_pitch % 32 == 0 &&
+      reinterpret_cast<uintptr_t>(bins_cm) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    const dim3 grid_cm(unsigned((n + kTurnRows - 1) / kTurnRows), unsigned(out_pitch / 32));
+    compact_columns_cm_u8_kernel<<<grid_cm, 256, 0, s>>>(bins_cm, n, map, n_cols, out, out_pitch);
+    ARB_CUDA(cudaGetLastError());
+    count_launch();
+    return;
+  }
+  const int words = int(out_pitch / 4);
+  const size_t total = n * size_t(words);
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
+  if (bin_bytes == 1)
+    compact_columns_kernel<unsigned char><<<grid, 256, 0, s>>>(bins, pitch, n, map, n_cols,
+                                                               reinterpret_cast<unsigned *>(out), words);
+  else
+    compact_columns_kernel<unsigned short><<<grid, 256, 0, s>>>(bins, pitch, n, map, n_cols,
+                                                                reinterpret_cast<unsigned *>(out), words);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
@@ -355,6 +544,17 @@ void launch_binning(const float *X, size_t n, int F, const float *thr, const int
                     int hist_size, bool missing_bin, unsigned char *bins, size_t pitch, int bin_bytes,
                     cudaStream_t s) {
   if (n == 0) return;
+  if (bin_bytes == 1 && hist_size <= 255 && pitch % 4 == 0 && reinterpret_cast<uintptr_t>(bins) % 4 == 0) {
+    const int tiles = (F + 31) / 32;
+    const size_t row_blocks = (n + kBinTileRows - 1) / kBinTileRows;
+    // every CTA loads its tile's tables once: enough CTAs to fill the SMs, not more
+    const int grid_x = int(std::min<size_t>(row_blocks, size_t(std::max(1, device_sm_count() * 8 / tiles))));
+    binning_tile_kernel<<<dim3(grid_x, tiles), 256, 0, s>>>(X, n, F, thr, fsize, hist_size, missing_bin, bins,
+                                                           pitch);
+    ARB_CUDA(cudaGetLastError());
+    count_launch();
+    return;
+  }
   const int threads = 256;
   const size_t total = n * size_t(F);
   const int grid = int(std::min<size_t>((total + threads - 1) / threads, size_t(device_sm_count()) * 32));

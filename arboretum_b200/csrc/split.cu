@@ -25,8 +25,9 @@ __device__ __forceinline__ unsigned long long pack_key(float gain, int fid, int 
 
 // Decode the winner of a node and sum its left side (one warp).
 __device__ void finalize_node(const long long *__restrict__ hist, const long long *__restrict__ count_hist,
-                              const int *__restrict__ cat_candidates, unsigned long long key,
-                              NodeRec *__restrict__ rec, int node, int TW, int NT, int lane) {
+                              const int *__restrict__ cat_candidates, const int *__restrict__ fmap,
+                              unsigned long long key, NodeRec *__restrict__ rec, int node, int TW, int NT,
+                              int lane) {
   NodeRec r = rec[node];
   r.lcnt = r.tcnt = 0;
   if (count_hist) {  // rows of the node: all bins of its first feature
@@ -45,9 +46,11 @@ __device__ void finalize_node(const long long *__restrict__ hist, const long lon
     r.lcnt = r.tcnt;
   } else {
     r.gain = __uint_as_float(unsigned(key >> 32));
-    r.fid = int(0xFFFFFu - unsigned((key >> 12) & 0xFFFFFu));
+    // the key names the histogram's column; the record names the feature behind it
+    const int col = int(0xFFFFFu - unsigned((key >> 12) & 0xFFFFFu));
+    r.fid = fmap ? fmap[col] : col;
     r.bin = int(key & 0xFFFu);
-    const int tile = r.fid / TW, fl = r.fid % TW;
+    const int tile = col / TW, fl = col % TW;
     const long long *base = hist + (size_t(node) * NT + tile) * kHistWords * 2;
     // a categorical winner sends one bin left, a dense one every bin up to the winner
     const int first_bin = (cat_candidates && cat_candidates[r.fid] > 0) ? r.bin : 0;
@@ -79,7 +82,7 @@ template <bool PAIR, bool COUNTS>
 __global__ void __launch_bounds__(kSplitThreads)
 split_kernel(const long long *__restrict__ hist, const long long *__restrict__ count_hist,
              const unsigned char *__restrict__ feature_active, const int *__restrict__ cat_candidates,
-             unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
+             const int *__restrict__ fmap, unsigned long long *__restrict__ keys, unsigned *__restrict__ done,
              NodeRec *__restrict__ rec, const QuantScale *__restrict__ qs, const GainParams gp,
              const int TW, const int NT, const int F, const int hist_size, const int parts) {
   overlap_release();
@@ -203,9 +206,12 @@ split_kernel(const long long *__restrict__ hist, const long long *__restrict__ c
   // the gain search of a (node, tile) is dealt to `parts` CTAs (a power of two): bin k of
   // every thread's 8 goes to CTA k % parts; all of them redo the cheap prefix sums above,
   // so the long double-precision chains run side by side instead of one after another
-  const bool active = f < F && feature_active[f];
+  // f is a column of the histogram; the column order is the feature order (the map ascends),
+  // so ties between columns fall like ties between features
+  const int feat = (f < F && fmap) ? fmap[f] : f;
+  const bool active = f < F && feature_active[feat];
   // > 0: a categorical feature; a candidate sends the rows of ONE bin left (builder.h:75-105)
-  const int ncand = (active && cat_candidates) ? cat_candidates[f] : 0;
+  const int ncand = (active && cat_candidates) ? cat_candidates[feat] : 0;
   if (active && th != 0) {
     const double isg = qs->inv_sg, ish = qs->inv_sh;
     const double dtg = double(tg) * isg, dth = double(th) * ish;
@@ -259,7 +265,7 @@ split_kernel(const long long *__restrict__ hist, const long long *__restrict__ c
   if (is_last && threadIdx.x < 32) {
     __threadfence();
     const unsigned long long key = atomicMax(&keys[node], 0ull);
-    finalize_node(hist, COUNTS ? count_hist : nullptr, cat_candidates, key, rec, node, TW, NT, threadIdx.x);
+    finalize_node(hist, COUNTS ? count_hist : nullptr, cat_candidates, fmap, key, rec, node, TW, NT, threadIdx.x);
   }
 }
 
@@ -279,13 +285,13 @@ void launch_split(const SplitLaunch &a, cudaStream_t s) {
   const dim3 grid(a.L, a.geo.NT, parts);
   if (a.pair && a.count_hist)
     launch_overlapped(split_kernel<true, true>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
-                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+                      a.cat_candidates, a.feature_map, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   else if (a.pair)
     launch_overlapped(split_kernel<true, false>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
-                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+                      a.cat_candidates, a.feature_map, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   else
     launch_overlapped(split_kernel<false, false>, grid, kSplitThreads, 0, s, a.hist, a.count_hist, a.feature_active,
-                      a.cat_candidates, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
+                      a.cat_candidates, a.feature_map, a.keys, done, a.rec, a.qs, a.gp, a.geo.TW, a.geo.NT, a.geo.F, a.geo.hist_size, parts);
   count_launch();
 }
 

@@ -397,6 +397,24 @@ def test_colsample_follows_the_reference_rng():
     compare_with_oracle(cfg, X, y, 4)
 
 
+@pytest.mark.parametrize("kind,objective,hist_size", [("linear", 0, 255), ("logistic", 1, 255), ("logistic", 1, 300)])
+def test_sampled_columns_are_histogrammed_from_a_side_by_side_copy(kind, objective, hist_size, monkeypatch):
+    """With colsample_bytree < 1 and more feature tiles than the sampled columns need, a tree's
+    columns are copied side by side and the histograms and the split search cover those alone
+    (70 features, 28 sampled: 3 tiles -> 1 for uint8 bins, 5 -> 2 for uint16).  The trees must
+    follow the oracle, and be the very trees the full-width histograms give."""
+    arboretum = arb()
+    X, y = synth(kind, 9000, 70, seed=12)
+    X[np.random.default_rng(2).random(X.shape) < 0.1] = np.nan
+    cfg = make_config(objective, 5, hist_size=hist_size, colsample_bytree=0.4, colsample_bylevel=0.8)
+    cfg["internals"]["seed"] = 3
+    monkeypatch.delenv("ARBORETUM_NO_COLUMN_COPY", raising=False)
+    model, data, o, ambiguous = compare_with_oracle(cfg, X, y, 4)
+    monkeypatch.setenv("ARBORETUM_NO_COLUMN_COPY", "1")
+    full = arboretum.train(cfg, arboretum.DMatrix(X, y=y), 4)
+    assert full.dump() == model.dump()
+
+
 def test_missing_values_go_right():
     arboretum = arb()
     X, y = synth("linear", 6000, 8, seed=9)
