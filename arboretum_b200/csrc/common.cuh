@@ -42,8 +42,14 @@ cudaError_t dev_alloc(void **p, size_t bytes);
 void dev_free(void *p);
 // free device memory as cudaMemGetInfo reports it, plus what the pool holds unused
 cudaError_t dev_available(size_t *bytes);
-// give the pool's unused memory back to the driver
+// give the pool's unused memory back to the driver (and the kept pinned blocks, below)
 cudaError_t dev_trim();
+// Pinned host memory: cudaMallocHost / cudaFreeHost cost about a millisecond per call, and a
+// process that builds one model after another asks for the same few small buffers every time.
+// Freed blocks of up to 16 MB are kept (64 MB in all) and handed out again; *cap receives the
+// size of the block that was handed out, which pinned_free wants back.
+cudaError_t pinned_alloc(void **p, size_t bytes, size_t *cap);
+void pinned_free(void *p, size_t cap);
 
 struct DevBuf {
   void *p = nullptr;
@@ -82,6 +88,7 @@ struct DevBuf {
 struct PinnedBuf {
   void *p = nullptr;
   size_t bytes = 0;
+  size_t cap = 0;  // size of the block behind p (>= bytes), when owned
   bool owned = true;
   PinnedBuf() {}
   PinnedBuf(const PinnedBuf &) = delete;
@@ -90,7 +97,7 @@ struct PinnedBuf {
   void alloc(size_t n) {
     release();
     if (n == 0) return;
-    ARB_CUDA(cudaMallocHost(&p, n));
+    ARB_CUDA(pinned_alloc(&p, n, &cap));
     bytes = n;
   }
   void view(void *ptr, size_t n) {
@@ -100,9 +107,10 @@ struct PinnedBuf {
     owned = false;
   }
   void release() {
-    if (p && owned) cudaFreeHost(p);
+    if (p && owned) pinned_free(p, cap);
     p = nullptr;
     bytes = 0;
+    cap = 0;
     owned = true;
   }
   template <typename T>

@@ -3,6 +3,8 @@
 // :78-504).  A whole tree is enqueued on one stream without host
 // synchronisation: node sizes, work lists and split records stay in device
 // memory, and the host reads the finished tree back once per tree.
+#include <mutex>
+
 #include "garden.h"
 #include "exchange.h"
 
@@ -52,7 +54,60 @@ void dev_free(void *p) {
   if (!st || cudaFreeAsync(p, st) != cudaSuccess) cudaFree(p);
 }
 
+namespace {
+constexpr size_t kPinnedKeepBlock = size_t(16) << 20, kPinnedKeepTotal = size_t(64) << 20;
+struct PinnedBlock {
+  void *p;
+  size_t cap;
+};
+std::mutex g_pinned_mutex;
+std::vector<PinnedBlock> g_pinned_free;
+size_t g_pinned_kept = 0;
+void pinned_drop_all() {
+  std::lock_guard<std::mutex> lock(g_pinned_mutex);
+  for (const PinnedBlock &b : g_pinned_free) cudaFreeHost(b.p);
+  g_pinned_free.clear();
+  g_pinned_kept = 0;
+}
+}  // namespace
+
+cudaError_t pinned_alloc(void **p, size_t bytes, size_t *cap) {
+  {
+    std::lock_guard<std::mutex> lock(g_pinned_mutex);
+    int best = -1;  // the smallest kept block that is large enough, and not wastefully large
+    for (int i = 0; i < int(g_pinned_free.size()); ++i)
+      if (g_pinned_free[i].cap >= bytes && g_pinned_free[i].cap <= 2 * bytes + 4096 &&
+          (best < 0 || g_pinned_free[i].cap < g_pinned_free[best].cap))
+        best = i;
+    if (best >= 0) {
+      *p = g_pinned_free[best].p;
+      *cap = g_pinned_free[best].cap;
+      g_pinned_kept -= *cap;
+      g_pinned_free.erase(g_pinned_free.begin() + best);
+      return cudaSuccess;
+    }
+  }
+  *cap = bytes;
+  return cudaMallocHost(p, bytes);
+}
+
+void pinned_free(void *p, size_t cap) {
+  if (!p) return;
+  // a copy that still uses the block must be over before it is handed out again
+  cudaDeviceSynchronize();
+  {
+    std::lock_guard<std::mutex> lock(g_pinned_mutex);
+    if (cap <= kPinnedKeepBlock && g_pinned_kept + cap <= kPinnedKeepTotal) {
+      g_pinned_free.push_back(PinnedBlock{p, cap});
+      g_pinned_kept += cap;
+      return;
+    }
+  }
+  cudaFreeHost(p);
+}
+
 cudaError_t dev_trim() {
+  pinned_drop_all();
   int dev = 0;
   cudaMemPool_t pool = nullptr;
   cudaError_t e = cudaGetDevice(&dev);

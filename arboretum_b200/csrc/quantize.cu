@@ -364,58 +364,51 @@ __global__ void binning_kernel(const float *__restrict__ X, size_t n, int F,
 
 
 // uint8 bins with at most 255 thresholds per feature: a CTA keeps the tables of a tile of 32
-// features in shared memory (entry i of feature f at i * 33 + f: the lanes of a warp, which
-// look at 8 different features, fall on different banks while they all probe the same entry
-// in the first steps) and walks rows; a thread bins four neighbouring features of a row with a
-// fixed 8-step search and stores them as one 32-bit word.  Same result as lower_bound_thr:
-// entries from size - 1 on read +INF, so a value that is not NaN stops at size - 1 at the
-// latest, and NaN (which compares false everywhere) gets `size` like there.
-constexpr int kBinTileRows = 32;  // rows a CTA bins per step: 256 threads = 32 rows x 8 words
+// features in shared memory, entry i of the tile's feature l at i * 32 + l.  A warp bins one
+// row of the tile at a time, lane l its feature l, with a fixed 8-step search: lane l only ever
+// touches bank l, so no step has a bank conflict whatever the values are.  Same result as
+// lower_bound_thr: entries from size - 1 on read +INF, so a value that is not NaN stops at
+// size - 1 at the latest, and NaN (which compares false everywhere) gets `size` like there.
+constexpr int kBinRowsPerStep = 4;  // rows a warp has in flight
 __global__ void __launch_bounds__(256)
 binning_tile_kernel(const float *__restrict__ X, size_t n, int F, const float *__restrict__ thr,
                     const int *__restrict__ fsize, int hist_size, bool missing_bin,
                     unsigned char *__restrict__ bins, size_t pitch) {
-  __shared__ float tbl[255 * 33];
-  __shared__ int size_s[32];
+  __shared__ float tbl[255 * 32];
   const int f_tile = blockIdx.y * 32;
   for (int e = threadIdx.x; e < 255 * 32; e += 256) {
     const int f = f_tile + (e & 31), i = e >> 5;
     float v = INFINITY;
     if (f < F && i < hist_size && i < fsize[f] - 1) v = thr[size_t(f) * hist_size + i];
-    tbl[i * 33 + (e & 31)] = v;
+    tbl[e] = v;
   }
-  if (threadIdx.x < 32) size_s[threadIdx.x] = f_tile + threadIdx.x < F ? fsize[f_tile + threadIdx.x] : 0;
   __syncthreads();
-  const int w = threadIdx.x & 7, row_in = threadIdx.x >> 3;
-  const int f0 = f_tile + 4 * w;
-  if (f0 >= F) return;
-  const int nf = min(4, F - f0);
-  for (size_t r = size_t(blockIdx.x) * kBinTileRows + row_in; r < n; r += size_t(gridDim.x) * kBinTileRows) {
-    const float *x = X + r * F + f0;
-    unsigned word = 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int f = f_tile + lane;
+  if (f >= F) return;
+  const unsigned nan_bin = missing_bin ? unsigned(hist_size) : unsigned(fsize[f]);
+  const float *t = tbl + lane;
+  const size_t step_rows = size_t(gridDim.x) * 8;
+  for (size_t r = size_t(blockIdx.x) * 8 + warp; r < n; r += step_rows * kBinRowsPerStep) {
+    float v[kBinRowsPerStep];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (j < nf) {
-        const float v = x[j];
-        const float *t = tbl + 4 * w + j;
-        unsigned b;
-        if (v != v) {
-          b = missing_bin ? unsigned(hist_size) : unsigned(size_s[4 * w + j]);
-        } else {
-          int pos = 0;
-#pragma unroll
-          for (int step = 128; step >= 1; step >>= 1)
-            if (!(v <= t[(pos + step - 1) * 33])) pos += step;
-          b = unsigned(pos);
-        }
-        word |= (b & 255u) << (8 * j);
-      }
+    for (int k = 0; k < kBinRowsPerStep; ++k) {
+      const size_t rk = r + size_t(k) * step_rows;
+      v[k] = rk < n ? X[rk * F + f] : 0.0f;
     }
-    unsigned char *dst = bins + r * pitch + f0;
-    if (nf == 4) {
-      *reinterpret_cast<unsigned *>(dst) = word;
-    } else {
-      for (int j = 0; j < nf; ++j) dst[j] = (unsigned char)(word >> (8 * j));
+#pragma unroll
+    for (int k = 0; k < kBinRowsPerStep; ++k) {
+      const size_t rk = r + size_t(k) * step_rows;
+      if (rk >= n) break;
+      unsigned b = nan_bin;
+      if (v[k] == v[k]) {
+        int pos = 0;
+#pragma unroll
+        for (int step = 128; step >= 1; step >>= 1)
+          if (!(v[k] <= t[(pos + step - 1) * 32])) pos += step;
+        b = unsigned(pos);
+      }
+      bins[rk * pitch + f] = (unsigned char)b;
     }
   }
 }
@@ -544,9 +537,9 @@ void launch_binning(const float *X, size_t n, int F, const float *thr, const int
                     int hist_size, bool missing_bin, unsigned char *bins, size_t pitch, int bin_bytes,
                     cudaStream_t s) {
   if (n == 0) return;
-  if (bin_bytes == 1 && hist_size <= 255 && pitch % 4 == 0 && reinterpret_cast<uintptr_t>(bins) % 4 == 0) {
+  if (bin_bytes == 1 && hist_size <= 255) {
     const int tiles = (F + 31) / 32;
-    const size_t row_blocks = (n + kBinTileRows - 1) / kBinTileRows;
+    const size_t row_blocks = (n + 7) / 8;
     // every CTA loads its tile's tables once: enough CTAs to fill the SMs, not more
     const int grid_x = int(std::min<size_t>(row_blocks, size_t(std::max(1, device_sm_count() * 8 / tiles))));
     binning_tile_kernel<<<dim3(grid_x, tiles), 256, 0, s>>>(X, n, F, thr, fsize, hist_size, missing_bin, bins,
