@@ -388,28 +388,37 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
     cat_candidates.assign(size_t(cols()), 0);
     if (cols_cat > 0) BinCategories(s);
     if (out_of_core) {  // the bins live in pinned host memory and are streamed per level
-      h_bins.alloc(n * pitch);
-      ARB_CUDA(cudaMemcpyAsync(h_bins.p, d_bins.p, n * pitch, cudaMemcpyDeviceToHost, s));
+      host_pitch = HostPitchFor(cols(), bin_bytes);
+      h_bins.alloc(n * host_pitch);
+      if (host_pitch == pitch)
+        ARB_CUDA(cudaMemcpyAsync(h_bins.p, d_bins.p, n * pitch, cudaMemcpyDeviceToHost, s));
+      else
+        ARB_CUDA(cudaMemcpy2DAsync(h_bins.p, host_pitch, d_bins.p, pitch, host_pitch, n,
+                                   cudaMemcpyDeviceToHost, s));
     }
     ARB_CUDA(cudaStreamSynchronize(s));
     if (out_of_core) d_bins.release();
     trace.lap("binning");
   } else if (out_of_core) {
     ARB_CHECK(bin_bytes == 1, "pre-binned input is uint8: hist_size must be < 256");
-    h_bins.alloc(n * pitch);
-    if (d_raw.p) {  // pad on the device, a slab of rows at a time, and bring the slabs back
+    host_pitch = HostPitchFor(F, bin_bytes);
+    h_bins.alloc(n * host_pitch);
+    if (d_raw.p && host_pitch == size_t(F)) {  // the rows as they are
+      ARB_CUDA(cudaMemcpyAsync(h_bins.p, d_raw.p, n * size_t(F), cudaMemcpyDeviceToHost, s));
+      ARB_CUDA(cudaStreamSynchronize(s));
+    } else if (d_raw.p) {  // pad on the device, a slab of rows at a time, and bring the slabs back
       const size_t slab = std::min<size_t>(n, size_t(1) << 24);
       DevBuf d_slab;
-      d_slab.alloc(slab * pitch);
+      d_slab.alloc(slab * host_pitch);
       for (size_t first = 0; first < n; first += slab) {
         const size_t count = std::min(slab, n - first);
-        launch_pad_rows(d_raw.as<unsigned char>() + first * F, F, count, d_slab.as<unsigned char>(), pitch, s);
-        ARB_CUDA(cudaMemcpyAsync(h_bins.as<unsigned char>() + first * pitch, d_slab.p, count * pitch,
+        launch_pad_rows(d_raw.as<unsigned char>() + first * F, F, count, d_slab.as<unsigned char>(), host_pitch, s);
+        ARB_CUDA(cudaMemcpyAsync(h_bins.as<unsigned char>() + first * host_pitch, d_slab.p, count * host_pitch,
                                  cudaMemcpyDeviceToHost, s));
       }
       ARB_CUDA(cudaStreamSynchronize(s));
     } else {
-      pad_rows_host(host_bins.data(), size_t(F), n, h_bins.as<unsigned char>(), pitch);
+      pad_rows_host(host_bins.data(), size_t(F), n, h_bins.as<unsigned char>(), host_pitch);
     }
     if (thr.empty()) {
       thr.resize(size_t(F) * hs);
@@ -571,6 +580,7 @@ class Builder {
   };
   std::vector<Chunk> chunks_;
   DevBuf d_stage_[2], d_resident_;
+  DevBuf d_stage_raw_[2];  // host rows without padding land here and are padded into d_stage_
   cudaStream_t copy_stream_ = nullptr;
   cudaEvent_t stage_ready_[2], stage_free_[2];
   int stage_of_next_ = 0;
@@ -855,15 +865,32 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
       size_t free_b = 0;
       ARB_CUDA(dev_available(&free_b));
       const size_t budget = free_b / 10 * 8;
-      resident = budget > 2 * chunk_bytes ? int((budget - 2 * chunk_bytes) / chunk_bytes) : 0;
+      // two padded staging buffers, and two unpadded ones where the host rows go without padding
+      const size_t staging = 2 * chunk_bytes + (d->host_pitch != d->pitch ? 2 * chunks_[0].rows * d->host_pitch : 0);
+      resident = budget > staging ? int((budget - staging) / chunk_bytes) : 0;
     }
     resident = std::min<int>(resident, int(chunks_.size()));
     size_t resident_rows = 0;
     for (int c = 0; c < resident; ++c) resident_rows += chunks_[c].rows;
+    const bool tight_rows = d->host_pitch != d->pitch;
     if (resident_rows) {
       d_resident_.alloc(resident_rows * d->pitch);
-      ARB_CUDA(cudaMemcpyAsync(d_resident_.p, d->h_bins.p, resident_rows * d->pitch,
-                               cudaMemcpyHostToDevice, s));
+      if (!tight_rows) {
+        ARB_CUDA(cudaMemcpyAsync(d_resident_.p, d->h_bins.p, resident_rows * d->pitch,
+                                 cudaMemcpyHostToDevice, s));
+      } else {  // a slab of unpadded rows at a time, padded into place
+        const size_t slab = std::min<size_t>(resident_rows, size_t(1) << 24);
+        DevBuf d_slab;
+        d_slab.alloc(slab * d->host_pitch);
+        for (size_t first = 0; first < resident_rows; first += slab) {
+          const size_t count = std::min(slab, resident_rows - first);
+          ARB_CUDA(cudaMemcpyAsync(d_slab.p, d->h_bins.as<unsigned char>() + first * d->host_pitch,
+                                   count * d->host_pitch, cudaMemcpyHostToDevice, s));
+          launch_pad_rows(d_slab.as<unsigned char>(), int(d->host_pitch), count,
+                          d_resident_.as<unsigned char>() + first * d->pitch, d->pitch, s);
+        }
+        ARB_CUDA(cudaStreamSynchronize(s));  // the slab goes out of scope
+      }
       for (int c = 0; c < resident; ++c)
         chunks_[c].resident = d_resident_.as<unsigned char>() + chunks_[c].begin * d->pitch;
     }
@@ -871,6 +898,10 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
     if (!streamed_.empty()) {
       d_stage_[0].alloc(chunk_bytes);
       d_stage_[1].alloc(chunk_bytes);
+      if (tight_rows) {
+        d_stage_raw_[0].alloc(chunks_[0].rows * d->host_pitch);
+        d_stage_raw_[1].alloc(chunks_[0].rows * d->host_pitch);
+      }
       ARB_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
       for (int i = 0; i < 2; ++i) {
         ARB_CUDA(cudaEventCreateWithFlags(&stage_ready_[i], cudaEventDisableTiming));
@@ -901,10 +932,18 @@ void Builder::IssueCopy() {
   const Chunk &ch = chunks_[streamed_[issued_ % streamed_.size()]];
   const int buf = int(issued_ & 1);
   ARB_CUDA(cudaStreamWaitEvent(copy_stream_, stage_free_[buf], 0));  // kernels done with it
-  ARB_CUDA(cudaMemcpyAsync(d_stage_[buf].p, data->h_bins.as<unsigned char>() + ch.begin * data->pitch,
-                           ch.rows * data->pitch, cudaMemcpyHostToDevice, copy_stream_));
+  const size_t hp = data->host_pitch;
+  if (hp == data->pitch) {
+    ARB_CUDA(cudaMemcpyAsync(d_stage_[buf].p, data->h_bins.as<unsigned char>() + ch.begin * hp, ch.rows * hp,
+                             cudaMemcpyHostToDevice, copy_stream_));
+  } else {  // unpadded rows cross the link; a kernel on the copy stream pads them
+    ARB_CUDA(cudaMemcpyAsync(d_stage_raw_[buf].p, data->h_bins.as<unsigned char>() + ch.begin * hp,
+                             ch.rows * hp, cudaMemcpyHostToDevice, copy_stream_));
+    launch_pad_rows(d_stage_raw_[buf].as<unsigned char>(), int(hp), ch.rows, d_stage_[buf].as<unsigned char>(),
+                    data->pitch, copy_stream_);
+  }
   ARB_CUDA(cudaEventRecord(stage_ready_[buf], copy_stream_));
-  if (g_->profile) g_->times.h2d_bytes += double(ch.rows * data->pitch);
+  if (g_->profile) g_->times.h2d_bytes += double(ch.rows * hp);
   ++issued_;
 }
 

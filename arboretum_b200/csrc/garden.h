@@ -66,7 +66,16 @@ class DataMatrix {
   size_t pitch = 0;
   DevBuf d_bins;
   DevBuf d_bins_cm;  // feature-major copy for the descend step (in-core only)
-  PinnedBuf h_bins;  // out-of-core: the padded row-major bin matrix in pinned host memory
+  // out-of-core: the row-major bin matrix in pinned host memory, rows of host_pitch bytes.  The
+  // device wants rows padded to 32 bytes; where that padding is an eighth of a row or more
+  // (100 features: 128 against 100 bytes) the host rows go without it, so that it does not
+  // cross the host link once per level, and a kernel pads every chunk on arrival.
+  PinnedBuf h_bins;
+  size_t host_pitch = 0;
+  static size_t HostPitchFor(int F, int bin_bytes) {
+    const size_t padded = PitchFor(F, bin_bytes), tight = (size_t(F) * bin_bytes + 3) / 4 * 4;
+    return padded - tight >= padded / 8 ? tight : padded;
+  }
   bool out_of_core = false;
   std::vector<float> thr;  // [F][hist_size] data_reduced_mapping
   std::vector<int> fsize;  // bins in use per feature
