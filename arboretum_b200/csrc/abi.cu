@@ -477,6 +477,7 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   j["trees"] = Json::integer(t.trees);
   j["grad_ms"] = Json::number(t.grad);
   j["hist_ms"] = Json::number(t.hist);
+  j["hist_kernel_ms"] = Json::number(t.hist_kernel);
   j["plan_ms"] = Json::number(t.plan);
   j["subtract_ms"] = Json::number(t.subtract);
   j["split_ms"] = Json::number(t.split);

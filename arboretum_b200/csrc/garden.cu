@@ -570,6 +570,7 @@ class Builder {
   std::vector<unsigned> h_nb_total_;
   PlanBuffers pb_;
   cudaEvent_t ev_[2 * 8 * kMaxLevels];
+  cudaEvent_t ev_hist_[kMaxLevels];  // behind the first histogram launch of a level (profile mode)
   cudaEvent_t ev_tree_[2];
   // Row chunks (out-of-core): a chunk is a contiguous range of rows whose bins are
   // either resident in HBM or streamed from pinned host memory into one of two
@@ -915,6 +916,7 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
 Builder::~Builder() {
   if (events_made_) {
     for (auto &e : ev_) cudaEventDestroy(e);
+    for (auto &e : ev_hist_) cudaEventDestroy(e);
     for (auto &e : ev_tree_) cudaEventDestroy(e);
   }
   if (copy_stream_) {
@@ -970,6 +972,7 @@ void Builder::Release(int chunk) {
 void Builder::EnsureEvents() {
   if (events_made_) return;
   for (auto &e : ev_) ARB_CUDA(cudaEventCreate(&e));
+  for (auto &e : ev_hist_) ARB_CUDA(cudaEventCreate(&e));
   for (auto &e : ev_tree_) ARB_CUDA(cudaEventCreate(&e));
   events_made_ = true;
 }
@@ -1201,6 +1204,7 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
           h.status = d_hist_status_.as<int>();
         }
         launch_hist(h, s);
+        if (prof && !multi && k == 0) ARB_CUDA(cudaEventRecord(ev_hist_[l], s));
         ReduceLaunch rd;
         rd.partials = d_partials_.as<int>();
         rd.item_first = pb_.slot_first;  // the planes of a node's runs
@@ -1410,6 +1414,11 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
       t.partition += span(e, e + 1);
       t.plan += span(e + 1, e + 2);
       t.hist += span(e + 2, e + 3);
+      {
+        float ms;
+        ARB_CUDA(cudaEventElapsedTime(&ms, ev_[e + 2], ev_hist_[l]));
+        t.hist_kernel += double(ms);
+      }
       t.allreduce += span(e + 3, e + 4);
       t.subtract += span(e + 4, e + 5);
       t.split += span(e + 5, e + 6);

@@ -127,6 +127,8 @@ typedef int (*CommCheckFn)(void *ctx, int give_up, char *msg, size_t msg_len);
 struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
   // (partition = the descend steps, plan = plan kernel + row lists, update = the final descend)
   double grad = 0, hist = 0, subtract = 0, split = 0, partition = 0, plan = 0, update = 0, allreduce = 0;
+  double hist_kernel = 0;  // of `hist`: the histogram kernel's launches alone (the rest is the
+                           // reduction of their planes)
   long long hist_launches = 0;
   double hist_rows = 0;      // rows scanned by histogram launches
   double hist_features = 0;  // features per scanned row (summed per launch)
