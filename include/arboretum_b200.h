@@ -135,8 +135,9 @@ const char *APeerWaitProbe(double limit_ms, int *timed_out, double *waited_ms);
  * scratch is a 128 KB array inside the library image, which every GPU that loads
  * the library holds until the process exits.  n may not exceed 67,108,864 (2^26):
  * larger columns return an error and should go through AQuantize.  The first call on
- * a device looks the array's address up (cudaGetSymbolAddress); make that first
- * call before any stream capture.  All calls on a device share the array, so two
+ * a device looks the array's address up (cudaGetSymbolAddress) and may make the
+ * runtime load the library's kernels, which takes device memory once: make one
+ * warm-up call before a section that must not allocate.  All calls on a device share the array, so two
  * calls that overlap on the GPU (different streams, different threads) race; calls
  * on one stream are safe.  Nothing of an earlier call's scratch contents is read. */
 const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist_size,
@@ -145,7 +146,8 @@ const char *AThresholdsNoAlloc(const float *sorted_device, long long n, int hist
 /* Additive (no counterpart in the reference): the library takes its device memory from the
  * current device's stream-ordered pool and keeps what it frees, so that the next matrix or
  * model does not pay for cudaMalloc again; this call hands the unused part back to the
- * driver (for a process that shares the GPU with other allocators). */
+ * driver (for a process that shares the GPU with other allocators), together with the few
+ * small pinned host blocks it keeps for the same reason. */
 const char *AReleaseCachedMemory(void);
 
 /* Additive (no counterpart in the reference): measures, on the current device, how many
