@@ -489,6 +489,9 @@ const char *AGetTimings(VoidPointer garden, const char **json) {
   j["hist_row_features"] = Json::number(t.hist_features);
   j["hist_bytes"] = Json::number(t.hist_bytes);
   j["tree_ms"] = Json::number(t.tree);
+  j["host_enqueue_ms"] = Json::number(t.enqueue);
+  j["host_wait_ms"] = Json::number(t.host_wait);
+  j["host_trees"] = Json::number(double(t.host_trees));
   j["h2d_bytes"] = Json::number(t.h2d_bytes);
   j["kernel_launches"] = Json::integer(g_kernel_launches);
   double xms[3];

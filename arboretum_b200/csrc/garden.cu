@@ -1064,6 +1064,7 @@ void Builder::SampleFeatures() {
 }
 
 void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
+  const auto host_t0 = std::chrono::steady_clock::now();
   const Configuration &cfg = g_->cfg;
   const TreeParam &tp = cfg.tree;
   cudaStream_t s = g_->stream;
@@ -1341,7 +1342,14 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     }
     cudaEventDestroy(done);
   }
+  const auto host_t1 = std::chrono::steady_clock::now();
   ARB_CUDA(cudaStreamSynchronize(s));
+  {
+    const auto host_t2 = std::chrono::steady_clock::now();
+    g_->times.enqueue += std::chrono::duration<double, std::milli>(host_t1 - host_t0).count();
+    g_->times.host_wait += std::chrono::duration<double, std::milli>(host_t2 - host_t1).count();
+    g_->times.host_trees += 1;
+  }
   if (has_row_map_ && *h_hist_status_.as<int>() != 0)
     throw std::runtime_error("a row gather of the histogram kernel did not arrive within its time limit: "
                              "the tree is incomplete");

@@ -135,6 +135,9 @@ struct PhaseTimes {  // CUDA-event time per kernel class, milliseconds
   double hist_bytes = 0;     // algorithmic bytes of those launches
   long long trees = 0;
   double tree = 0;       // whole GrowTree calls, device time
+  double enqueue = 0;    // host wall time of GrowTree up to the wait for the tree: launching the kernels
+  double host_wait = 0;  // host wall time of that wait (the device is behind the host for this long)
+  long long host_trees = 0;
   double h2d_bytes = 0;  // bins streamed from pinned host memory (out-of-core)
 };
 
