@@ -668,12 +668,17 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
   // node's gain is good to about 2 x 0.4 x step x sqrt(rows) / |sum g|) but fewer rows per
   // int32 sub-histogram (2^(31 - bits)) and so more of them to store and add up.  Unless the
   // configuration names a value, the whole data set's row count decides (so that shards and
-  // row chunks quantise like one GPU): about a thousand sub-histograms for the root level,
-  // between 18 bits (from 4 M rows) and 22 (up to half a million).
+  // row chunks quantise like one GPU) together with the feature tiles every row is
+  // histogrammed in (a sub-histogram is 64 KB per tile: with 32 tiles a thousand rows per
+  // sub-histogram would store and re-read twice the bytes of the bins themselves): about a
+  // thousand sub-histograms for the root level, between 18 bits (from 4 M row-tiles) and 22
+  // (up to half a million).
   qb_ = cfg.internal.quant_bits;
   if (qb_ == 0) {
+    const int cols_hist = std::min(F_, std::max(1, int(tp.colsample_bytree * F_)));
+    const size_t tiles_hist = size_t((cols_hist + geo_.TW - 1) / geo_.TW);
     int lg = 0;
-    while ((size_t(1) << lg) < std::max<size_t>(512, n_global / 1024)) ++lg;
+    while ((size_t(1) << lg) < std::max<size_t>(512, n_global * tiles_hist / 1024)) ++lg;
     qb_ = std::min(22, std::max(18, 31 - lg));
   }
   const int qb = qb_;
@@ -857,6 +862,14 @@ Builder::Builder(Garden *g, DataMatrix *d) : data(d), g_(g), rnd_(g->cfg.interna
       geo_tree_.NT = NT_t;
       geo_tree_.bins_cm = nullptr;
       geo_tree_.cm_rows = 0;
+      // uint8 tiles of 32 features: the copy is kept tile by tile, so that a tile's histogram
+      // reads rows that lie back to back (in a row-major matrix of many tiles every row of a
+      // tile is a 32-byte island)
+      if (geo_.TW == 32 && NT_t > 1 && geo_.cm_rows == n_ &&
+          compact_columns_tile_major_ok(geo_.bin_bytes, n_, geo_.bins_cm)) {
+        geo_tree_.tile_stride = n_ * 32;
+        geo_tree_.pitch = 32;
+      }
     }
   } else {
     // as many leading chunks as fit stay in HBM; the rest cycle through two buffers
@@ -1086,8 +1099,8 @@ void Builder::GrowTree(int label, Tree *tree) {  // garden.cu:167-197
     ARB_CUDA(cudaMemcpyAsync(d_fmap_.p, fmap_host_.data(), fmap_host_.size() * sizeof(int),
                              cudaMemcpyHostToDevice, s));
     launch_compact_columns(geo_.bins, geo_.pitch, geo_.bin_bytes, n_, d_fmap_.as<int>(), geo_tree_.F,
-                           d_bins_tree_.as<unsigned char>(), geo_tree_.pitch, s,
-                           geo_.cm_rows == n_ ? geo_.bins_cm : nullptr);
+                           d_bins_tree_.as<unsigned char>(), DataMatrix::PitchFor(geo_tree_.F, geo_.bin_bytes), s,
+                           geo_.cm_rows == n_ ? geo_.bins_cm : nullptr, geo_tree_.tile_stride != 0);
   }
   if (prof) ARB_CUDA(cudaEventRecord(ev_tree_[0], s));
   // a tree that threw half way (an exchange that failed) leaves the cyclic visiting order of

@@ -127,7 +127,7 @@ __device__ __forceinline__ void store_planes(const int *smem, int *dst) {
 // on a gather ran into its time limit.
 template <bool PAIR, bool IDENT, bool TMA>
 __global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
-hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const int NT,
+hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const size_t tile_stride, const int NT,
                const unsigned *__restrict__ rowid, const void *__restrict__ grad,
                const WorkItem *__restrict__ items, const int *__restrict__ n_items,
                const int *__restrict__ item_slot, int *__restrict__ partials,
@@ -163,7 +163,8 @@ hist_u8_kernel(const unsigned char *__restrict__ bins, const size_t pitch, const
   // grid = (tiles, shares): the CTAs that take the same rows in neighbouring tiles are launched
   // side by side, so a row's line is fetched from DRAM once for the tiles that share it
   const int tile = blockIdx.x;
-  const unsigned char *tile_base = bins + size_t(tile) * 32;
+  // row-major: the tile's 32 bytes inside every row; tile by tile: the tile's own block of rows
+  const unsigned char *tile_base = bins + size_t(tile) * (tile_stride ? tile_stride : size_t(32));
   const int q = lane >> 3, m = lane & 7;
   int foff[4], sh[4];
 #pragma unroll
@@ -473,8 +474,10 @@ void launch_subtract(long long *level_hist, const long long *parent_hist, const 
                      int n_parents, int NT, cudaStream_t s);
 
 int hist_grid_x(int max_items, int NT) {
-  // persistent CTAs: kHistCtasPerSm per SM over all tiles
-  const int per_tile = std::max(8, (kHistCtasPerSm * device_sm_count() + NT - 1) / NT);
+  // persistent CTAs: kHistCtasPerSm per SM over all tiles, and never more than are resident at
+  // once -- a few CTAs left over for a second wave would double the pass (10 shares of 32 tiles
+  // are 320 CTAs for 296 places)
+  const int per_tile = std::max(1, kHistCtasPerSm * device_sm_count() / NT);
   return std::max(1, std::min(max_items, per_tile));
 }
 
@@ -535,7 +538,7 @@ void launch_hist(const HistLaunch &a, cudaStream_t s) {
   do {                                                                                           \
     ARB_SET_SMEM((hist_u8_kernel<P, I, T>), smem);                                               \
     launch_overlapped(hist_u8_kernel<P, I, T>, grid, kHistThreads, smem, s, g.bins, g.pitch,     \
-                      g.NT, a.rowid, a.grad, a.items, a.n_items, a.item_slot, a.partials,        \
+                      g.tile_stride, g.NT, a.rowid, a.grad, a.items, a.n_items, a.item_slot, a.partials,        \
                       a.list_grad, map, a.status);                                               \
   } while (0)
     if (a.pair) {

@@ -35,6 +35,11 @@ struct Geometry {
   // descend step reads one feature of every row, which is sequential in this layout
   const unsigned char *bins_cm = nullptr;
   size_t cm_rows = 0;
+  // 0: row-major, the tiles of a row lie side by side in its `pitch` bytes.  Otherwise the
+  // matrix is kept tile by tile (uint8 bins only): tile t starts `tile_stride` bytes after tile
+  // t - 1 and holds one 32-byte chunk per row (`pitch` = 32), so that the rows a tile's
+  // histogram reads lie back to back however many tiles the matrix has.
+  size_t tile_stride = 0;
 };
 
 // The driver's tensor map of a row-major uint8 bin matrix (bytes of a padded row x rows), with
@@ -131,9 +136,13 @@ void launch_split(const SplitLaunch &a, cudaStream_t s);
 // out[r][j] = bins[r][map[j]] for j < n_cols (bin_bytes each), rows of `out_pitch` bytes whose
 // padding is zeroed: the columns a tree samples, side by side.  With the feature-major copy
 // bins_cm[f * n + r] at hand (uint8, n a multiple of 16) only the wanted columns are read.
+// `tile_major` (needs bins_cm, uint8, n a multiple of 16): the copy is written tile by tile,
+// tile t at out + t * n * 32 with 32 bytes per row (see Geometry::tile_stride).
 void launch_compact_columns(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, const int *map,
                             int n_cols, unsigned char *out, size_t out_pitch, cudaStream_t s,
-                            const unsigned char *bins_cm = nullptr);
+                            const unsigned char *bins_cm = nullptr, bool tile_major = false);
+// whether launch_compact_columns can write the tile-by-tile layout for this matrix
+bool compact_columns_tile_major_ok(int bin_bytes, size_t n, const unsigned char *bins_cm);
 
 // --- node assignment and row lists ---------------------------------------------
 struct PlanBuffers {

@@ -299,7 +299,7 @@ __global__ void compact_columns_kernel(const unsigned char *__restrict__ bins, s
 __global__ void __launch_bounds__(256)
 compact_columns_cm_u8_kernel(const unsigned char *__restrict__ bins_cm, size_t n,
                              const int *__restrict__ map, int n_cols, unsigned char *__restrict__ out,
-                             size_t out_pitch) {
+                             size_t out_pitch, bool tile_major) {
   __shared__ __align__(16) unsigned char tile[32 * kTurnStride];
   const size_t r0 = size_t(blockIdx.x) * kTurnRows;
   const int j0 = blockIdx.y * 32;
@@ -323,7 +323,9 @@ compact_columns_cm_u8_kernel(const unsigned char *__restrict__ bins_cm, size_t n
 #pragma unroll
     for (int j = 0; j < 16; ++j)
       w[j >> 2] |= unsigned(tile[(half * 16 + j) * kTurnStride + row]) << (8 * (j & 3));
-    *reinterpret_cast<uint4 *>(out + (r0 + row) * out_pitch + j0 + half * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    unsigned char *dst = tile_major ? out + (size_t(blockIdx.y) * n + r0 + row) * 32 + half * 16
+                                    : out + (r0 + row) * out_pitch + j0 + half * 16;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -463,18 +465,23 @@ void launch_pad_rows(const unsigned char *raw, int F, size_t n, unsigned char *b
   count_launch();
 }
 
+bool compact_columns_tile_major_ok(int bin_bytes, size_t n, const unsigned char *bins_cm) {
+  return bins_cm && bin_bytes == 1 && n % 16 == 0 && reinterpret_cast<uintptr_t>(bins_cm) % 16 == 0;
+}
+
 void launch_compact_columns(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, const int *map,
                             int n_cols, unsigned char *out, size_t out_pitch, cudaStream_t s,
-                            const unsigned char *bins_cm) {
+                            const unsigned char *bins_cm, bool tile_major) {
   if (n == 0 || n_cols == 0) return;
-  if (bins_cm && bin_bytes == 1 && n % 16 == 0 && out_pitch % 32 == 0 &&
-      reinterpret_cast<uintptr_t>(bins_cm) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+  if (compact_columns_tile_major_ok(bin_bytes, n, bins_cm) && out_pitch % 32 == 0 &&
+      reinterpret_cast<uintptr_t>(out) % 16 == 0) {
     const dim3 grid_cm(unsigned((n + kTurnRows - 1) / kTurnRows), unsigned(out_pitch / 32));
-    compact_columns_cm_u8_kernel<<<grid_cm, 256, 0, s>>>(bins_cm, n, map, n_cols, out, out_pitch);
+    compact_columns_cm_u8_kernel<<<grid_cm, 256, 0, s>>>(bins_cm, n, map, n_cols, out, out_pitch, tile_major);
     ARB_CUDA(cudaGetLastError());
     count_launch();
     return;
   }
+  ARB_CHECK(!tile_major, "the tile-by-tile copy needs the feature-major matrix");
   const int words = int(out_pitch / 4);
   const size_t total = n * size_t(words);
   const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));

@@ -421,7 +421,9 @@ def shared_atomics(t, features):
     (every scanned row updates one pair per feature slot, 32 slots per tile of features)."""
     from arboretum_b200 import core
     peak = core.shared_atomic_peak(2000)
-    slots = (features + 31) // 32 * 32
+    # the columns the histograms cover (the sampled ones when a tree samples its columns)
+    cols = int(round(t["hist_row_features"] / max(1, t["hist_launches"]))) if t.get("hist_row_features") else features
+    slots = (cols + 31) // 32 * 32
     achieved = t["hist_rows"] * slots / ((t.get("hist_kernel_ms") or t["hist_ms"]) * 1e-3)
     return {"achieved": achieved, "peak": peak, "frac": achieved / peak, "unit": "(g, h) updates/s",
             "note": "histogram kernel time of all levels; feature slots padded to 32 per tile"}
