@@ -1498,19 +1498,22 @@ namespace {
 // small pinned buffer (kept for the life of the process) and copy it out, so the faults
 // and the copies run side by side with the DMA.
 void copy_to_host(void *dst, const void *src_device, size_t bytes) {
-  constexpr int kThreads = 4;
+  constexpr int kMaxThreads = 8;
+  static const int kThreads =
+    int(std::max(1u, std::min(unsigned(kMaxThreads), std::thread::hardware_concurrency() / 2)));
   constexpr size_t kPiece = size_t(2) << 20;
   if (bytes < 4 * kPiece) {
     ARB_CUDA(cudaMemcpy(dst, src_device, bytes, cudaMemcpyDeviceToHost));
     return;
   }
-  static void *bounce[kThreads] = {nullptr, nullptr, nullptr, nullptr};
-  for (void *&b : bounce)
-    if (!b) ARB_CUDA(cudaMallocHost(&b, kPiece));
+  static void *bounce[kMaxThreads] = {};
+  for (int t = 0; t < kThreads; ++t)
+    if (!bounce[t]) ARB_CUDA(cudaMallocHost(&bounce[t], kPiece));
   int device = 0;
   ARB_CUDA(cudaGetDevice(&device));
   const size_t pieces = (bytes + kPiece - 1) / kPiece;
-  cudaError_t status[kThreads];
+  cudaError_t status[kMaxThreads];
+  for (cudaError_t &e : status) e = cudaSuccess;
   std::vector<std::thread> pool;
   for (int t = 0; t < kThreads; ++t) {
     status[t] = cudaSuccess;
