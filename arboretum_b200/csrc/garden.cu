@@ -60,8 +60,9 @@ struct PinnedBlock {
   void *p;
   size_t cap;
 };
-std::mutex g_pinned_mutex;
-std::vector<PinnedBlock> g_pinned_free;
+// never destroyed: a buffer may be given back while the process is already on its way out
+std::mutex &g_pinned_mutex = *new std::mutex;
+std::vector<PinnedBlock> &g_pinned_free = *new std::vector<PinnedBlock>;
 size_t g_pinned_kept = 0;
 void pinned_drop_all() {
   std::lock_guard<std::mutex> lock(g_pinned_mutex);
