@@ -12,6 +12,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstring>
+#include <exception>
 #include <limits>
 #include <thread>
 #include <vector>
@@ -256,19 +257,34 @@ void DataMatrix::BinCategories(cudaStream_t s) {
   ARB_CHECK(cat.size() == n * size_t(C), "categories are missing");
   fsize.resize(size_t(cols_dense));
   cat_codes.assign(size_t(C), std::vector<unsigned>());
+  // bin ids column by column ([c][r]): the columns are worked on side by side by a few threads
   std::vector<unsigned char> ids8;
   std::vector<unsigned short> ids16;
   if (bin_bytes == 1) ids8.resize(n * C); else ids16.resize(n * C);
-  std::vector<unsigned> col(n);
-  for (int c = 0; c < C; ++c) {
-    for (size_t r = 0; r < n; ++r) col[r] = cat[r * C + c];
-    std::sort(col.begin(), col.end());
-    std::vector<std::pair<unsigned, size_t>> freq;  // (code, rows)
-    for (size_t i = 0; i < n;) {
-      size_t j = i;
-      while (j < n && col[j] == col[i]) ++j;
-      freq.emplace_back(col[i], j - i);
-      i = j;
+  std::vector<int> col_fsize(C, 0), col_kept(C, 0);
+  auto bin_column = [&](int c) {
+    // (code, rows) of the column, codes ascending: counted in a table while the codes are
+    // small (the usual case), from a sorted copy otherwise
+    std::vector<std::pair<unsigned, size_t>> freq;
+    unsigned max_code = 0;
+    for (size_t r = 0; r < n; ++r) max_code = std::max(max_code, cat[r * C + c]);
+    const bool table = max_code < (1u << 22);
+    std::vector<unsigned> count;
+    if (table) {
+      count.assign(size_t(max_code) + 1, 0u);
+      for (size_t r = 0; r < n; ++r) ++count[cat[r * C + c]];
+      for (size_t code = 0; code < count.size(); ++code)
+        if (count[code]) freq.emplace_back(unsigned(code), size_t(count[code]));
+    } else {
+      std::vector<unsigned> col(n);
+      for (size_t r = 0; r < n; ++r) col[r] = cat[r * C + c];
+      std::sort(col.begin(), col.end());
+      for (size_t i = 0; i < n;) {
+        size_t k = i;
+        while (k < n && col[k] == col[i]) ++k;
+        freq.emplace_back(col[i], k - i);
+        i = k;
+      }
     }
     std::stable_sort(freq.begin(), freq.end(),
                      [](const std::pair<unsigned, size_t> &a, const std::pair<unsigned, size_t> &b) {
@@ -282,20 +298,49 @@ void DataMatrix::BinCategories(cudaStream_t s) {
       by_code.emplace_back(freq[b].first, unsigned(b));
     }
     std::sort(by_code.begin(), by_code.end());
-    fsize.push_back(int(kept + (overflow ? 1 : 0)));
-    cat_candidates[size_t(cols_dense + c)] = int(kept);
+    col_fsize[c] = int(kept + (overflow ? 1 : 0));
+    col_kept[c] = int(kept);
+    if (table) {  // the table now maps a code to its bin
+      std::fill(count.begin(), count.end(), unsigned(kept));
+      for (const auto &cb : by_code) count[cb.first] = cb.second;
+    }
     for (size_t r = 0; r < n; ++r) {
       const unsigned code = cat[r * C + c];
-      auto it = std::lower_bound(by_code.begin(), by_code.end(), std::make_pair(code, 0u));
-      const unsigned b = (it != by_code.end() && it->first == code) ? it->second : unsigned(kept);
-      if (bin_bytes == 1) ids8[r * C + c] = (unsigned char)b; else ids16[r * C + c] = (unsigned short)b;
+      unsigned b;
+      if (table) {
+        b = count[code];
+      } else {
+        auto it = std::lower_bound(by_code.begin(), by_code.end(), std::make_pair(code, 0u));
+        b = (it != by_code.end() && it->first == code) ? it->second : unsigned(kept);
+      }
+      if (bin_bytes == 1) ids8[size_t(c) * n + r] = (unsigned char)b; else ids16[size_t(c) * n + r] = (unsigned short)b;
     }
+  };
+  {
+    const int workers = std::max(1, std::min<int>(C, int(std::min(16u, std::thread::hardware_concurrency()))));
+    std::vector<std::thread> pool;
+    std::vector<std::exception_ptr> failed(workers);
+    for (int t = 0; t < workers; ++t)
+      pool.emplace_back([&, t]() {
+        try {
+          for (int c = t; c < C; c += workers) bin_column(c);
+        } catch (...) {
+          failed[t] = std::current_exception();
+        }
+      });
+    for (auto &th : pool) th.join();
+    for (auto &e : failed)
+      if (e) std::rethrow_exception(e);
+  }
+  for (int c = 0; c < C; ++c) {
+    fsize.push_back(col_fsize[c]);
+    cat_candidates[size_t(cols_dense + c)] = col_kept[c];
   }
   DevBuf d_ids;
   d_ids.alloc(n * C * size_t(bin_bytes));
   const void *src = bin_bytes == 1 ? static_cast<const void *>(ids8.data()) : static_cast<const void *>(ids16.data());
   ARB_CUDA(cudaMemcpyAsync(d_ids.p, src, d_ids.bytes, cudaMemcpyHostToDevice, s));
-  launch_place_columns(d_ids.p, n, C, cols_dense, d_bins.as<unsigned char>(), pitch, bin_bytes, s);
+  launch_place_columns(d_ids.p, n, C, cols_dense, d_bins.as<unsigned char>(), pitch, bin_bytes, s, true);
   ARB_CUDA(cudaStreamSynchronize(s));
 }
 

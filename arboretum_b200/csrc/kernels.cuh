@@ -269,7 +269,7 @@ void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist
 // bin ids of the categorical columns ([n][ccol], BIN_T wide) into columns f0 .. f0 + ccol - 1
 // of the padded row-major bin matrix
 void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned char *bins, size_t pitch,
-                          int bin_bytes, cudaStream_t s);
+                          int bin_bytes, cudaStream_t s, bool by_column = false);
 // row-major padded bins -> feature-major copy
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
                            unsigned char *bins_cm, cudaStream_t s);

@@ -262,12 +262,13 @@ __global__ void pad_rows_kernel(const unsigned char *__restrict__ raw, int F, si
 
 template <typename BIN_T>
 __global__ void place_columns_kernel(const BIN_T *__restrict__ src, size_t n, int ccol, int f0,
-                                     unsigned char *__restrict__ bins, size_t pitch) {
+                                     unsigned char *__restrict__ bins, size_t pitch, bool by_column) {
   const size_t total = n * size_t(ccol);
   for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
        e += size_t(gridDim.x) * blockDim.x) {
-    const size_t r = e / ccol;
-    const int c = int(e - r * ccol);
+    // by_column: src[c * n + r] (consecutive threads take consecutive rows of a column)
+    const size_t r = by_column ? e % n : e / ccol;
+    const int c = by_column ? int(e / n) : int(e - r * ccol);
     reinterpret_cast<BIN_T *>(bins + r * pitch)[f0 + c] = src[e];
   }
 }
@@ -496,16 +497,16 @@ void launch_compact_columns(const unsigned char *bins, size_t pitch, int bin_byt
 }
 
 void launch_place_columns(const void *src, size_t n, int ccol, int f0, unsigned char *bins, size_t pitch,
-                          int bin_bytes, cudaStream_t s) {
+                          int bin_bytes, cudaStream_t s, bool by_column) {
   if (n == 0 || ccol == 0) return;
   const size_t total = n * size_t(ccol);
   const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
   if (bin_bytes == 1)
     place_columns_kernel<unsigned char><<<grid, 256, 0, s>>>(static_cast<const unsigned char *>(src), n, ccol, f0,
-                                                            bins, pitch);
+                                                            bins, pitch, by_column);
   else
     place_columns_kernel<unsigned short><<<grid, 256, 0, s>>>(static_cast<const unsigned short *>(src), n, ccol,
-                                                             f0, bins, pitch);
+                                                             f0, bins, pitch, by_column);
   ARB_CUDA(cudaGetLastError());
   count_launch();
 }
