@@ -372,34 +372,47 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       trace.lap("sharded column sorts + thresholds");
     } else if (!thresholds_given) {
       const int block_cols = std::min(F, 32);  // columns made contiguous at a time
+      // short columns are sorted a block at a time (one sort over (column, value) keys): a
+      // 1 M-row column alone is launch-bound; long ones one by one (half the bytes per key)
+      const bool batched = block_cols > 1 && n <= (size_t(1) << 21);
+      DevBuf d_keys_a, d_keys_b;
       {  // one allocation (and later one free) for the quantizer's temporaries
         struct Want {
           DevBuf *buf;
           size_t bytes;
         };
+        const size_t key_bytes = batched ? n * block_cols * sizeof(unsigned long long) : 0;
         const Want wants[] = {
           {&d_col, n * block_cols * sizeof(float)},
-          {&d_sorted, n * sizeof(float)},
-          {&d_tmp, sort_floats_temp_bytes(n)},
+          {&d_sorted, batched ? 0 : n * sizeof(float)},
+          {&d_tmp, batched ? sort_columns_temp_bytes(n, block_cols) : sort_floats_temp_bytes(n)},
           {&d_scratch, thresholds_scratch_words(n) * sizeof(unsigned)},
           {&d_thr_f, size_t(F) * hs * sizeof(float)},
+          {&d_keys_a, key_bytes},
+          {&d_keys_b, key_bytes},
         };
         size_t total = 0;
         for (const Want &w : wants) total += (w.bytes + 255) / 256 * 256;
         d_quant_arena.alloc(total);
         size_t at = 0;
         for (const Want &w : wants) {
-          w.buf->view(static_cast<char *>(d_quant_arena.p) + at, w.bytes);
+          if (w.bytes) w.buf->view(static_cast<char *>(d_quant_arena.p) + at, w.bytes);
           at += (w.bytes + 255) / 256 * 256;
         }
       }
       for (int f0 = 0; f0 < F; f0 += block_cols) {
         const int nf = std::min(block_cols, F - f0);
         launch_transpose_columns(d_x.as<float>(), n, F, f0, nf, d_col.as<float>(), s);
+        if (batched)
+          sort_columns(d_col.as<float>(), n, nf, d_keys_a.as<unsigned long long>(),
+                       d_keys_b.as<unsigned long long>(), d_tmp, s);
         for (int f = f0; f < f0 + nf; ++f) {
-          sort_floats(d_col.as<float>() + size_t(f - f0) * n, d_sorted.as<float>(), n, d_tmp, s);
-          launch_thresholds(d_sorted.as<float>(), n, hs, d_thr_f.as<float>() + size_t(f) * hs,
-                            d_scratch.as<unsigned>(), s);
+          const float *sorted = d_col.as<float>() + size_t(f - f0) * n;
+          if (!batched) {
+            sort_floats(sorted, d_sorted.as<float>(), n, d_tmp, s);
+            sorted = d_sorted.as<float>();
+          }
+          launch_thresholds(sorted, n, hs, d_thr_f.as<float>() + size_t(f) * hs, d_scratch.as<unsigned>(), s);
         }
       }
       trace.lap("column sorts + thresholds");

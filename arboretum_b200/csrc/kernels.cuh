@@ -284,5 +284,11 @@ void launch_transpose_columns(const float *X, size_t n, int F, int f0, int nf, f
 // sort_floats_temp_bytes(n) bytes
 size_t sort_floats_temp_bytes(size_t n);
 void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_t s);
+// nf columns of n values each, cols[c * n + r], every column sorted in place in the same
+// order sort_floats gives, in one pass of the library's sort over 64-bit (column, value) keys;
+// keys_a and keys_b hold n * nf keys each, tmp grows to sort_columns_temp_bytes(n, nf)
+size_t sort_columns_temp_bytes(size_t n, int nf);
+void sort_columns(float *cols, size_t n, int nf, unsigned long long *keys_a, unsigned long long *keys_b,
+                  DevBuf &tmp, cudaStream_t s);
 
 }  // namespace arb

@@ -148,6 +148,29 @@ __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_
   }
 }
 
+// Several short columns sorted in one go: a key is (column, value in radix order), 64 bits.
+// A 1 M-row column alone is six small launches of the library's sort; thirty-two of them as
+// one array of keys are the same six launches over thirty-two times the data.  The value
+// half is the float's bit pattern turned the way the library's own float sort turns it
+// (negative values inverted, the sign bit of the others set), so the order is the same.
+__device__ __forceinline__ unsigned radix_order(float x) {
+  const unsigned u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float radix_order_back(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__global__ void pack_sort_keys_kernel(const float *__restrict__ cols, size_t n, size_t total,
+                                      unsigned long long *__restrict__ keys) {
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += size_t(gridDim.x) * blockDim.x)
+    keys[e] = ((unsigned long long)(e / n) << 32) | radix_order(cols[e]);
+}
+__global__ void unpack_sort_keys_kernel(const unsigned long long *__restrict__ keys, size_t total,
+                                        float *__restrict__ cols) {
+  for (size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += size_t(gridDim.x) * blockDim.x)
+    cols[e] = radix_order_back(unsigned(keys[e]));
+}
+
 __global__ void fill_inf_kernel(float *thr, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) thr[i] = INFINITY;
@@ -539,6 +562,37 @@ void sort_floats(const float *in, float *out, size_t n, DevBuf &tmp, cudaStream_
   ARB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes, in, out, n, 0, 32, s));
   if (tmp.bytes < bytes) tmp.alloc(bytes);
   ARB_CUDA(cub::DeviceRadixSort::SortKeys(tmp.p, bytes, in, out, n, 0, 32, s));
+}
+
+namespace {
+int column_key_bits(int nf) {
+  int bits = 0;
+  while ((1 << bits) < nf) ++bits;
+  return 32 + bits;
+}
+}  // namespace
+
+size_t sort_columns_temp_bytes(size_t n, int nf) {
+  size_t bytes = 0;
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes, static_cast<const unsigned long long *>(nullptr),
+                                          static_cast<unsigned long long *>(nullptr), n * size_t(nf), 0,
+                                          column_key_bits(nf), nullptr));
+  return bytes;
+}
+
+void sort_columns(float *cols, size_t n, int nf, unsigned long long *keys_a, unsigned long long *keys_b,
+                  DevBuf &tmp, cudaStream_t s) {
+  const size_t total = n * size_t(nf);
+  if (total == 0) return;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(device_sm_count()) * 32));
+  pack_sort_keys_kernel<<<grid, 256, 0, s>>>(cols, n, total, keys_a);
+  size_t bytes = 0;
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes, keys_a, keys_b, total, 0, column_key_bits(nf), s));
+  if (tmp.bytes < bytes) tmp.alloc(bytes);
+  ARB_CUDA(cub::DeviceRadixSort::SortKeys(tmp.p, bytes, keys_a, keys_b, total, 0, column_key_bits(nf), s));
+  unpack_sort_keys_kernel<<<grid, 256, 0, s>>>(keys_b, total, cols);
+  ARB_CUDA(cudaGetLastError());
+  count_launch(2);
 }
 
 void launch_binning(const float *X, size_t n, int F, const float *thr, const int *fsize,
