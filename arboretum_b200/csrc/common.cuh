@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <chrono>
+#include <cstring>
 #include <cstdio>
 #include <cstdlib>
 
@@ -178,14 +179,18 @@ inline void launch_overlapped(void (*kernel)(P...), dim3 grid, dim3 block, size_
 // Host-side stage timer of the set-up paths: with ARBORETUM_TRACE set in the environment,
 // lap("name") synchronises the device and prints the wall time since the previous lap.
 struct StageTrace {
-  bool on;
+  bool on, sync;
   std::chrono::steady_clock::time_point t;
   const char *scope;
+  // ARBORETUM_TRACE=host: the host's own time per stage, without waiting for the device
   explicit StageTrace(const char *scope_name)
-      : on(std::getenv("ARBORETUM_TRACE") != nullptr), t(std::chrono::steady_clock::now()), scope(scope_name) {}
+      : on(std::getenv("ARBORETUM_TRACE") != nullptr),
+        sync(on && std::strcmp(std::getenv("ARBORETUM_TRACE"), "host") != 0),
+        t(std::chrono::steady_clock::now()),
+        scope(scope_name) {}
   void lap(const char *what) {
     if (!on) return;
-    cudaDeviceSynchronize();
+    if (sync) cudaDeviceSynchronize();
     const auto now = std::chrono::steady_clock::now();
     std::fprintf(stderr, "[arboretum] %s: %s %.3f ms\n", scope, what,
                  std::chrono::duration<double, std::milli>(now - t).count());

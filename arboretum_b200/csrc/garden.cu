@@ -374,7 +374,8 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       const int block_cols = std::min(F, 32);  // columns made contiguous at a time
       // short columns are sorted a block at a time (one sort over (column, value) keys): a
       // 1 M-row column alone is launch-bound; long ones one by one (half the bytes per key)
-      const bool batched = block_cols > 1 && n <= (size_t(1) << 21);
+      const bool batched = block_cols > 1 && n <= (size_t(1) << 21) &&
+                           std::getenv("ARBORETUM_NO_BATCHED_SORT") == nullptr;
       DevBuf d_keys_a, d_keys_b;
       {  // one allocation (and later one free) for the quantizer's temporaries
         struct Want {
@@ -386,7 +387,7 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
           {&d_col, n * block_cols * sizeof(float)},
           {&d_sorted, batched ? 0 : n * sizeof(float)},
           {&d_tmp, batched ? sort_columns_temp_bytes(n, block_cols) : sort_floats_temp_bytes(n)},
-          {&d_scratch, thresholds_scratch_words(n) * sizeof(unsigned)},
+          {&d_scratch, thresholds_scratch_words(n) * sizeof(unsigned) * (batched ? block_cols : 1)},
           {&d_thr_f, size_t(F) * hs * sizeof(float)},
           {&d_keys_a, key_bytes},
           {&d_keys_b, key_bytes},
@@ -403,9 +404,13 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       for (int f0 = 0; f0 < F; f0 += block_cols) {
         const int nf = std::min(block_cols, F - f0);
         launch_transpose_columns(d_x.as<float>(), n, F, f0, nf, d_col.as<float>(), s);
-        if (batched)
+        if (batched) {
           sort_columns(d_col.as<float>(), n, nf, d_keys_a.as<unsigned long long>(),
                        d_keys_b.as<unsigned long long>(), d_tmp, s);
+          launch_thresholds_columns(d_col.as<float>(), n, nf, hs, d_thr_f.as<float>() + size_t(f0) * hs,
+                                    d_scratch.as<unsigned>(), s);
+          continue;
+        }
         for (int f = f0; f < f0 + nf; ++f) {
           const float *sorted = d_col.as<float>() + size_t(f - f0) * n;
           if (!batched) {

@@ -261,6 +261,10 @@ void launch_link(int objective, int K, size_t n, const float *internal /*[K][n]*
 // thresholds of one sorted column (device) -> thr[hist_size]
 void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
                        cudaStream_t s);
+// the same for nf columns of n sorted values each (sorted_cols[c * n + i]): thresholds of
+// column c to thr + c * hist_size; scratch of nf x thresholds_scratch_words(n) words
+void launch_thresholds_columns(const float *sorted_cols, size_t n, int nf, int hist_size, float *thr,
+                               unsigned *scratch, cudaStream_t s);
 size_t thresholds_scratch_words(size_t n);
 // bin every (row, feature) of a row-major fp32 matrix
 void launch_binning(const float *X, size_t n, int F, const float *thr /*[F][hist_size]*/,

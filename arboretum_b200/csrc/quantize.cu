@@ -26,8 +26,13 @@ constexpr int kScanTile = kScanThreads * kScanItems;
 
 __device__ __forceinline__ bool is_border(const float *s, size_t i) { return i > 0 && s[i] != s[i - 1]; }
 
+// The three border kernels take several columns of n sorted values at once (grid.y = column):
+// column c lies at s + c * n, its block counts at block_count + c * gridDim.x, its
+// thresholds at thr + c * hist_size.
 __global__ void border_count_kernel(const float *__restrict__ s, size_t n, unsigned *block_count) {
   __shared__ unsigned warp_sums[kScanThreads / 32];
+  s += size_t(blockIdx.y) * n;
+  block_count += size_t(blockIdx.y) * gridDim.x;
   const size_t base = size_t(blockIdx.x) * kScanTile;
   unsigned c = 0;
 #pragma unroll
@@ -49,6 +54,7 @@ __global__ void border_count_kernel(const float *__restrict__ s, size_t n, unsig
 __global__ void border_scan_kernel(unsigned *block_count, int nblocks) {
   __shared__ unsigned warp_sums[32];
   __shared__ unsigned carry_s;
+  block_count += size_t(blockIdx.y) * nblocks;
   if (threadIdx.x == 0) carry_s = 0;
   __syncthreads();
   for (int base = 0; base < nblocks; base += blockDim.x) {
@@ -88,6 +94,9 @@ __global__ void border_apply_kernel(const float *__restrict__ s, size_t n, size_
   // the tile and the value before it, read coalesced; a thread then walks 8 consecutive
   // values, so slot p is kept at p + p / 32: the 32 lanes' strides of 8 fall on 32 banks
   __shared__ float tile[kScanTile + 1 + (kScanTile + 1) / 32 + 1];
+  s += size_t(blockIdx.y) * n;
+  block_off += size_t(blockIdx.y) * gridDim.x;
+  thr += size_t(blockIdx.y) * hist_size;
   const size_t tile_base = size_t(blockIdx.x) * kScanTile;
   for (int p = threadIdx.x; p < kScanTile + 1; p += kScanThreads) {
     const size_t i = tile_base + size_t(p);  // tile[p] = s[i - 1]
@@ -443,19 +452,25 @@ binning_tile_kernel(const float *__restrict__ X, size_t n, int F, const float *_
 
 size_t thresholds_scratch_words(size_t n) { return (n + kScanTile - 1) / kScanTile + 1; }
 
-void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
-                       cudaStream_t s) {
-  fill_inf_kernel<<<ceil_div(hist_size, 256), 256, 0, s>>>(thr, hist_size);  // io.cu:387
+void launch_thresholds_columns(const float *sorted_cols, size_t n, int nf, int hist_size, float *thr,
+                               unsigned *scratch, cudaStream_t s) {
+  if (nf <= 0) return;
+  fill_inf_kernel<<<ceil_div(size_t(hist_size) * nf, 256), 256, 0, s>>>(thr, hist_size * nf);  // io.cu:387
   ARB_CUDA(cudaGetLastError());
   count_launch();
   if (n < 2) return;
   const int nblocks = int((n + kScanTile - 1) / kScanTile);
   const size_t seg = std::max<size_t>(1, n / size_t(hist_size));  // io.cu:376-377
-  border_count_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, scratch);
-  border_scan_kernel<<<1, 1024, 0, s>>>(scratch, nblocks);
-  border_apply_kernel<<<nblocks, kScanThreads, 0, s>>>(sorted, n, seg, hist_size, scratch, thr);
+  border_count_kernel<<<dim3(nblocks, nf), kScanThreads, 0, s>>>(sorted_cols, n, scratch);
+  border_scan_kernel<<<dim3(1, nf), 1024, 0, s>>>(scratch, nblocks);
+  border_apply_kernel<<<dim3(nblocks, nf), kScanThreads, 0, s>>>(sorted_cols, n, seg, hist_size, scratch, thr);
   ARB_CUDA(cudaGetLastError());
   count_launch(3);
+}
+
+void launch_thresholds(const float *sorted, size_t n, int hist_size, float *thr, unsigned *scratch,
+                       cudaStream_t s) {
+  launch_thresholds_columns(sorted, n, 1, hist_size, thr, scratch, s);
 }
 
 void launch_transpose_bins(const unsigned char *bins, size_t pitch, int bin_bytes, size_t n, int F,
