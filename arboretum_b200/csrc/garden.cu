@@ -377,16 +377,17 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
       const bool batched = block_cols > 1 && n <= (size_t(1) << 21) &&
                            std::getenv("ARBORETUM_NO_BATCHED_SORT") == nullptr;
       DevBuf d_keys_a, d_keys_b;
+      const int sort_cols = std::min(block_cols, 8);  // columns per sort: keeps the key buffers small
       {  // one allocation (and later one free) for the quantizer's temporaries
         struct Want {
           DevBuf *buf;
           size_t bytes;
         };
-        const size_t key_bytes = batched ? n * block_cols * sizeof(unsigned long long) : 0;
+        const size_t key_bytes = batched ? n * sort_cols * sizeof(unsigned long long) : 0;
         const Want wants[] = {
           {&d_col, n * block_cols * sizeof(float)},
           {&d_sorted, batched ? 0 : n * sizeof(float)},
-          {&d_tmp, batched ? sort_columns_temp_bytes(n, block_cols) : sort_floats_temp_bytes(n)},
+          {&d_tmp, batched ? sort_columns_temp_bytes(n, sort_cols) : sort_floats_temp_bytes(n)},
           {&d_scratch, thresholds_scratch_words(n) * sizeof(unsigned) * (batched ? block_cols : 1)},
           {&d_thr_f, size_t(F) * hs * sizeof(float)},
           {&d_keys_a, key_bytes},
@@ -405,8 +406,9 @@ void DataMatrix::InitHist(int hs, bool missing_bin, bool verbose, cudaStream_t s
         const int nf = std::min(block_cols, F - f0);
         launch_transpose_columns(d_x.as<float>(), n, F, f0, nf, d_col.as<float>(), s);
         if (batched) {
-          sort_columns(d_col.as<float>(), n, nf, d_keys_a.as<unsigned long long>(),
-                       d_keys_b.as<unsigned long long>(), d_tmp, s);
+          for (int c0 = 0; c0 < nf; c0 += sort_cols)
+            sort_columns(d_col.as<float>() + size_t(c0) * n, n, std::min(sort_cols, nf - c0),
+                         d_keys_a.as<unsigned long long>(), d_keys_b.as<unsigned long long>(), d_tmp, s);
           launch_thresholds_columns(d_col.as<float>(), n, nf, hs, d_thr_f.as<float>() + size_t(f0) * hs,
                                     d_scratch.as<unsigned>(), s);
           continue;
