@@ -329,7 +329,7 @@ hist_generic_kernel(const unsigned char *__restrict__ bins, const size_t pitch, 
                     const void *__restrict__ grad, const WorkItem *__restrict__ items,
                     const int *__restrict__ n_items, const int *__restrict__ item_slot,
                     int *__restrict__ partials) {
-  extern __shared__ __align__(16) int smem[];
+  extern __shared__ __align__(128) int smem[];
   int *G = smem;
   int *H = smem + kHistWords;
   const int tile = blockIdx.x;  // grid = (tiles, shares), see hist_u8_kernel
@@ -584,7 +584,7 @@ namespace {
 // in flight: 2.6 T pairs/s with 32 warps, 2.9 T with 64).
 constexpr int kPeakThreads = 1024;
 __global__ void __launch_bounds__(kPeakThreads, 2) shared_atomic_peak_kernel(int steps, int *sink) {
-  extern __shared__ __align__(16) int smem[];
+  extern __shared__ __align__(128) int smem[];
   for (int w = threadIdx.x; w < 2 * kHistWords; w += kPeakThreads) smem[w] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31;
