@@ -60,3 +60,8 @@ def test_every_package_name_the_bench_uses_exists():
     assert names, "bench.py no longer calls the package?"
     missing = sorted(n for n in names if not hasattr(arboretum_b200, n))
     assert not missing, missing
+
+
+def test_every_workload_states_the_rounds_of_its_whole_job():
+    assert set(bench.JOB_ROUNDS) == set(bench.WORKLOADS)
+    assert bench.JOB_ROUNDS["c2"] == 500 and bench.JOB_ROUNDS["c1"] == 100
