@@ -703,6 +703,33 @@ def test_out_of_core_prebinned_input():
         assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("F", [100, 27, 64])
+def test_out_of_core_prebinned_rows_from_device_memory(F):
+    """Pre-binned rows handed over in device memory and trained out of core: the rows go to
+    pinned host memory (without the padding to 32 bytes where that is an eighth of a row or
+    more: 100 and 27 columns; with it for 64) and come back chunk by chunk.  Same trees as
+    the matrix held in HBM."""
+    import torch
+    arboretum = arb()
+    rng = np.random.default_rng(F)
+    n = 30000
+    bins = rng.integers(0, 255, size=(n, F)).astype(np.uint8)
+    active = rng.choice(F, 8, replace=False)
+    logit = ((bins[:, active] / 255.0 - 0.5) * rng.normal(0, 2, 8)).sum(axis=1)
+    y = (rng.random(n) < 1 / (1 + np.exp(-logit))).astype(np.float32)
+    d_bins = torch.from_numpy(bins).cuda()
+    d_y = torch.from_numpy(y).cuda()
+    base = make_config(1, 5)
+    ref = arboretum.train(base, arboretum.DMatrix(bins, y=y, binned_hist_size=255), 3)
+    cfg = make_config(1, 5)
+    cfg["internals"]["chunk_rows"] = 7000
+    cfg["internals"]["resident_chunks"] = 1
+    data = arboretum.DMatrix.from_device_bins(d_bins.data_ptr(), n, F, 255, d_y.data_ptr())
+    ooc = arboretum.train(cfg, data, 3)
+    assert json.loads(ooc.dump())["model"] == json.loads(ref.dump())["model"]
+    assert np.array_equal(ooc.train_yhat(), ref.train_yhat())
+
+
 def test_a_wait_on_a_peer_that_never_answers_gives_up():
     """The exchange kernels between row shards wait for their peers with a time limit.  Here the
     same wait runs on a word that nothing sets: it gives up after the limit, the kernel returns
