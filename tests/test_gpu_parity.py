@@ -703,6 +703,30 @@ def test_out_of_core_prebinned_input():
         assert np.allclose(a["weights"], b["weights"], rtol=1e-4, atol=1e-6)
 
 
+def test_sampled_columns_with_row_counts():
+    """min_leaf_size > 1 with a (gradient, hessian) objective keeps a second histogram of row
+    counts; with sampled columns both histograms run over the side-by-side copy."""
+    X, y = synth("logistic", 12000, 70, seed=21)
+    cfg = make_config(1, 5, colsample_bytree=0.4, min_leaf_size=40)
+    cfg["internals"]["seed"] = 5
+    compare_with_oracle(cfg, X, y, 3)
+
+
+def test_out_of_core_with_two_byte_bins():
+    """hist_size >= 256 makes the bins uint16; 20 columns are 40 bytes of a 64-byte padded row,
+    so the host rows go without the padding."""
+    arboretum = arb()
+    X, y = synth("linear", 20000, 20, seed=8)
+    base = make_config(0, 5, hist_size=400)
+    ref = arboretum.train(base, arboretum.DMatrix(X, y=y), 3)
+    cfg = make_config(0, 5, hist_size=400)
+    cfg["internals"]["chunk_rows"] = 6000
+    cfg["internals"]["resident_chunks"] = 1
+    ooc = arboretum.train(cfg, arboretum.DMatrix(X, y=y), 3)
+    assert json.loads(ooc.dump())["model"] == json.loads(ref.dump())["model"]
+    assert np.array_equal(ooc.train_yhat(), ref.train_yhat())
+
+
 @pytest.mark.parametrize("F", [100, 27, 64])
 def test_out_of_core_prebinned_rows_from_device_memory(F):
     """Pre-binned rows handed over in device memory and trained out of core: the rows go to
